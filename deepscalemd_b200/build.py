@@ -1,0 +1,54 @@
+"""In-tree build of the CUDA library (sm_100a) with nvcc.
+
+``python -m deepscalemd_b200.build`` compiles ``csrc/*.cu`` into ``libdsmd_b200.so`` beside this file. The built
+library is loaded by :mod:`deepscalemd_b200.capi` through ctypes; there is no other compute path.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SOURCES = ["csrc/dsmd_core.cu", "csrc/dsmd_edges.cu"]
+LIBRARY = os.path.join(HERE, "libdsmd_b200.so")
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "--use_fast_math=false",
+         "-Xcompiler", "-fPIC", "-shared"]
+
+
+def nvcc_path() -> str:
+    path = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(path):
+        raise RuntimeError("nvcc not found: the CUDA toolkit is required to build libdsmd_b200.so")
+    return path
+
+
+def sources() -> list[str]:
+    return [os.path.join(HERE, s) for s in SOURCES if os.path.exists(os.path.join(HERE, s))]
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIBRARY):
+        return True
+    built = os.path.getmtime(LIBRARY)
+    deps = sources() + [os.path.join(HERE, "csrc", f) for f in os.listdir(os.path.join(HERE, "csrc"))]
+    deps.append(os.path.join(HERE, "..", "include", "dsmd_b200.h"))
+    return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not is_stale():
+        return LIBRARY
+    flags = [f for f in FLAGS if f != "--use_fast_math=false"]
+    cmd = [nvcc_path(), *flags, "-ccbin", "/usr/bin/g++", "-o", LIBRARY, *sources()]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+        print(" ".join(cmd))
+    subprocess.run(cmd, check=True, cwd=HERE)
+    return LIBRARY
+
+
+if __name__ == "__main__":
+    build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(LIBRARY)

@@ -1,0 +1,402 @@
+"""ctypes binding of the C ABI in ``include/dsmd_b200.h`` (``libdsmd_b200.so``).
+
+There is no fallback: if the library is missing or fails to load, importing the symbols raises. Device buffers handed
+to the library are torch CUDA tensors (``data_ptr()``); streams are ``torch.cuda.Stream.cuda_stream`` integers.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY = os.path.join(_HERE, "libdsmd_b200.so")
+
+OK = 0
+ERR_INVALID, ERR_CUDA, ERR_BOX_TOO_SMALL, ERR_OUT_OF_DOMAIN, ERR_CAPACITY, ERR_STATE, ERR_TIMEOUT = range(1, 8)
+PHASE_FULL, PHASE_INTERIOR, PHASE_BOUNDARY = 0, 1, 2
+FIELDS = ["x", "y", "z", "vx", "vy", "vz", "fx", "fy", "fz", "mass", "charge", "type", "global_id"]
+FIELD_ID = {name: k for k, name in enumerate(FIELDS)}
+
+# every symbol include/dsmd_b200.h declares
+SYMBOLS = [
+    "dsmd_create", "dsmd_destroy", "dsmd_last_error", "dsmd_set_box", "dsmd_set_pair_params", "dsmd_set_coulomb",
+    "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
+    "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned",
+    "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq",
+    "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_run_nve",
+    "dsmd_forces_host", "dsmd_launch_count", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
+    "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_edges_create", "dsmd_edges_destroy",
+    "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
+    "dsmd_edges_result_compact",
+]
+
+_lib = None
+
+c_void_p, c_int, c_int64, c_double = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_double
+_pd = ctypes.POINTER(ctypes.c_double)
+
+
+class DsmdError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"dsmd status {code}: {message}")
+        self.code = code
+
+
+def load():
+    """Loads libdsmd_b200.so (raises if it has not been built: there is no other compute path)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIBRARY):
+        raise ImportError(f"{LIBRARY} is missing: build it with `python -m deepscalemd_b200.build` (needs nvcc)")
+    lib = ctypes.CDLL(LIBRARY)
+    lib.dsmd_last_error.restype = ctypes.c_char_p
+    lib.dsmd_last_error.argtypes = [c_void_p]
+    lib.dsmd_edges_last_error.restype = ctypes.c_char_p
+    lib.dsmd_edges_last_error.argtypes = [c_void_p]
+    lib.dsmd_launch_count.restype = c_int64
+    lib.dsmd_launch_count.argtypes = [c_void_p]
+    lib.dsmd_destroy.restype = None
+    lib.dsmd_destroy.argtypes = [c_void_p]
+    lib.dsmd_edges_destroy.restype = None
+    lib.dsmd_edges_destroy.argtypes = [c_void_p]
+    _lib = lib
+    return lib
+
+
+def _arr(a, dtype):
+    return None if a is None else np.ascontiguousarray(a, dtype=dtype)
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(c_void_p)
+
+
+def _stream_handle(stream):
+    if stream is None:
+        return c_void_p(0)
+    if hasattr(stream, "cuda_stream"):
+        return c_void_p(stream.cuda_stream)
+    return c_void_p(int(stream))
+
+
+class Context:
+    """One ``dsmd_ctx``: the device-resident particle arrays, neighbour list and kernels of one GPU."""
+
+    def __init__(self, capacity: int, device: int = 0):
+        self.lib = load()
+        self.h = c_void_p()
+        rc = self.lib.dsmd_create(c_int(device), c_int64(capacity), ctypes.byref(self.h))
+        if rc != OK:
+            msg = self.lib.dsmd_last_error(self.h).decode() if self.h else "dsmd_create failed"
+            raise DsmdError(rc, msg)
+        self.capacity = capacity
+        self.device = device
+        self._keep = []
+
+    def _check(self, rc):
+        if rc != OK:
+            raise DsmdError(rc, self.lib.dsmd_last_error(self.h).decode())
+
+    def close(self):
+        if self.h:
+            self.lib.dsmd_destroy(self.h)
+            self.h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- set-up -----------------------------------------------------------------------------------------------------
+    def set_box(self, box, periodic=(1, 1, 1), lo=(0, 0, 0), hi=(0, 0, 0), halo=0.0):
+        b, p, l, h = _arr(box, np.float64), _arr(periodic, np.int32), _arr(lo, np.float64), _arr(hi, np.float64)
+        self._check(self.lib.dsmd_set_box(self.h, _p(b), _p(p), _p(l), _p(h), c_double(halo)))
+
+    def set_pair_params(self, eps, sig, cutoff, skin, switch=-1.0):
+        e = _arr(np.atleast_2d(eps), np.float64)
+        s = _arr(np.atleast_2d(sig), np.float64)
+        self._check(self.lib.dsmd_set_pair_params(self.h, c_int(e.shape[0]), _p(e), _p(s), c_double(cutoff),
+                                                  c_double(skin), c_double(switch)))
+
+    def set_coulomb(self, enabled=True, alpha=0.0):
+        self._check(self.lib.dsmd_set_coulomb(self.h, c_int(int(enabled)), c_double(alpha)))
+
+    def ewald_alpha(self):
+        a = c_double(0.0)
+        self._check(self.lib.dsmd_get_ewald_alpha(self.h, ctypes.byref(a)))
+        return a.value
+
+    def set_exclusions(self, n_global, pairs):
+        if pairs is None or len(pairs) == 0:
+            self._check(self.lib.dsmd_set_exclusions(self.h, c_int64(n_global), c_int64(0), None, None))
+            return
+        pairs = np.asarray(pairs)
+        a, b = _arr(pairs[:, 0], np.int32), _arr(pairs[:, 1], np.int32)
+        self._check(self.lib.dsmd_set_exclusions(self.h, c_int64(n_global), c_int64(len(a)), _p(a), _p(b)))
+
+    # -- particles ----------------------------------------------------------------------------------------------------
+    def upload(self, pos, n_owned=None, vel=None, mass=None, charge=None, types=None, gid=None, stream=None):
+        pos = np.asarray(pos, dtype=np.float64)
+        n = len(pos)
+        n_owned = n if n_owned is None else n_owned
+        cols = [_arr(pos[:, k], np.float64) for k in range(3)]
+        vcols = [None] * 3 if vel is None else [_arr(np.asarray(vel)[:, k], np.float64) for k in range(3)]
+        m, q = _arr(mass, np.float64), _arr(charge, np.float64)
+        t, g = _arr(types, np.int32), _arr(gid, np.int32)
+        self._check(self.lib.dsmd_upload(self.h, c_int64(n_owned), c_int64(n), _p(cols[0]), _p(cols[1]), _p(cols[2]),
+                                         _p(vcols[0]), _p(vcols[1]), _p(vcols[2]), _p(m), _p(q), _p(t), _p(g),
+                                         _stream_handle(stream)))
+        import torch
+        torch.cuda.synchronize()
+
+    def upload_positions_ptr(self, x_ptr, y_ptr, z_ptr, stream=None):
+        self._check(self.lib.dsmd_upload_positions(self.h, c_void_p(x_ptr), c_void_p(y_ptr), c_void_p(z_ptr),
+                                                   _stream_handle(stream)))
+
+    def counts(self):
+        a, b = c_int64(0), c_int64(0)
+        self._check(self.lib.dsmd_counts(self.h, ctypes.byref(a), ctypes.byref(b)))
+        return a.value, b.value
+
+    def set_counts(self, n_owned, n_total):
+        self._check(self.lib.dsmd_set_counts(self.h, c_int64(n_owned), c_int64(n_total)))
+
+    def download(self, field, n=None, stream=None):
+        n_owned, n_total = self.counts()
+        n = n_total if n is None else n
+        fid = FIELD_ID[field]
+        out = np.zeros(n, dtype=np.int32 if fid >= 11 else np.float64)
+        self._check(self.lib.dsmd_download(self.h, c_int(fid), c_int64(n), _p(out), _stream_handle(stream)))
+        return out
+
+    def device_pointer(self, field):
+        p = c_void_p()
+        self._check(self.lib.dsmd_device_pointer(self.h, c_int(FIELD_ID[field]), ctypes.byref(p)))
+        return p.value
+
+    def forces_by_gid(self, n_global=None):
+        """[n_global, 3] forces of the owned atoms scattered by global id (NaN where this context owns no atom)."""
+        n_owned, _ = self.counts()
+        gid = self.download("global_id", n_owned)
+        n_global = int(gid.max()) + 1 if n_global is None else n_global
+        out = np.full((n_global, 3), np.nan)
+        for k, name in enumerate(("fx", "fy", "fz")):
+            out[gid, k] = self.download(name, n_owned)
+        return out
+
+    def field_by_gid(self, names, n_global=None):
+        n_owned, _ = self.counts()
+        gid = self.download("global_id", n_owned)
+        n_global = int(gid.max()) + 1 if n_global is None else n_global
+        out = np.full((n_global, len(names)), np.nan)
+        for k, name in enumerate(names):
+            out[gid, k] = self.download(name, n_owned)
+        return out
+
+    # -- list -----------------------------------------------------------------------------------------------------------
+    def build_neighbor_list(self, stream=None):
+        self._check(self.lib.dsmd_build_neighbor_list(self.h, _stream_handle(stream)))
+
+    def sort_owned(self, stream=None):
+        self._check(self.lib.dsmd_sort_owned(self.h, _stream_handle(stream)))
+
+    def ghost_slots_ptr(self):
+        p = c_void_p()
+        self._check(self.lib.dsmd_ghost_slots(self.h, ctypes.byref(p)))
+        return p.value
+
+    def list_stats(self):
+        e, i = c_int64(0), c_int64(0)
+        s, c, r = c_int(0), c_int(0), c_int(0)
+        self._check(self.lib.dsmd_list_stats(self.h, ctypes.byref(e), ctypes.byref(i), ctypes.byref(s), ctypes.byref(c),
+                                             ctypes.byref(r)))
+        return dict(directed_entries=e.value, interior_entries=i.value, row_stride=s.value, cells=c.value,
+                    rechecked_fp64=r.value)
+
+    def list_pairs(self, stream=None):
+        """Directed list entries as numpy arrays (i slot, j slot, excluded flag)."""
+        import torch
+        n = c_int64(0)
+        self._check(self.lib.dsmd_list_export(self.h, None, None, None, c_int64(0), ctypes.byref(n),
+                                              _stream_handle(stream)))
+        dev = torch.device("cuda", self.device)
+        ti = torch.empty(max(n.value, 1), dtype=torch.int32, device=dev)
+        tj = torch.empty(max(n.value, 1), dtype=torch.int32, device=dev)
+        tf = torch.empty(max(n.value, 1), dtype=torch.uint8, device=dev)
+        self._check(self.lib.dsmd_list_export(self.h, c_void_p(ti.data_ptr()), c_void_p(tj.data_ptr()),
+                                              c_void_p(tf.data_ptr()), c_int64(n.value), ctypes.byref(n),
+                                              _stream_handle(stream)))
+        k = n.value
+        return ti[:k].cpu().numpy(), tj[:k].cpu().numpy(), tf[:k].cpu().numpy()
+
+    # -- per step -------------------------------------------------------------------------------------------------------
+    def pack_positions(self, first=0, count=None, stream=None):
+        _, n_total = self.counts()
+        count = n_total - first if count is None else count
+        self._check(self.lib.dsmd_pack_positions(self.h, c_int64(first), c_int64(count), _stream_handle(stream)))
+
+    def max_displacement_sq(self, stream=None):
+        v = c_double(0.0)
+        self._check(self.lib.dsmd_max_displacement_sq(self.h, ctypes.byref(v), _stream_handle(stream)))
+        return v.value
+
+    def compute_forces(self, phase=PHASE_FULL, want_energy=False, stream=None):
+        self._check(self.lib.dsmd_compute_forces(self.h, c_int(phase), c_int(int(want_energy)), _stream_handle(stream)))
+
+    def read_scalars(self, stream=None):
+        out = (c_double * 5)()
+        self._check(self.lib.dsmd_read_scalars(self.h, out, _stream_handle(stream)))
+        v = np.array(list(out))
+        return dict(pe=v[0], virial=v[1], virial_diag=v[2:5].copy())
+
+    def integrate(self, half, dt, force_to_accel=1.0, stream=None):
+        self._check(self.lib.dsmd_integrate(self.h, c_int(half), c_double(dt), c_double(force_to_accel),
+                                            _stream_handle(stream)))
+
+    def kinetic_energy(self, stream=None):
+        v = c_double(0.0)
+        self._check(self.lib.dsmd_kinetic_energy(self.h, ctypes.byref(v), _stream_handle(stream)))
+        return v.value
+
+    def run_nve(self, n_steps, dt, force_to_accel=1.0, hi_frac=0.5, every=0, lagged=True, stream=None):
+        nr, worst = c_int64(0), c_double(0.0)
+        self._check(self.lib.dsmd_run_nve(self.h, c_int64(n_steps), c_double(dt), c_double(force_to_accel),
+                                          c_double(hi_frac), c_int(every), c_int(int(lagged)), ctypes.byref(nr),
+                                          ctypes.byref(worst), _stream_handle(stream)))
+        return dict(rebuilds=nr.value, worst_disp_sq=worst.value)
+
+    def forces_host(self, x, y, z, fx, fy, fz, rebuild=False, scalars=None, stream=None):
+        """Host-buffer force call; all arguments are numpy arrays or raw host addresses (ints) in context order."""
+        def addr(a):
+            return c_void_p(a) if isinstance(a, int) else _p(a)
+        sc = None if scalars is None else _p(scalars)
+        self._check(self.lib.dsmd_forces_host(self.h, addr(x), addr(y), addr(z), c_int(int(rebuild)), addr(fx), addr(fy),
+                                              addr(fz), sc, _stream_handle(stream)))
+
+    def launch_count(self):
+        return self.lib.dsmd_launch_count(self.h)
+
+    # -- halo -------------------------------------------------------------------------------------------------------------
+    def halo_select(self, lo, hi, index_tensor, stream=None):
+        l, h = _arr(lo, np.float64), _arr(hi, np.float64)
+        n = c_int64(0)
+        self._check(self.lib.dsmd_halo_select(self.h, _p(l), _p(h), c_void_p(index_tensor.data_ptr()),
+                                              c_int64(index_tensor.numel()), ctypes.byref(n), _stream_handle(stream)))
+        return n.value
+
+    def halo_pack(self, index_tensor, count, shift, out_tensor, stream=None):
+        s = _arr(shift, np.float64)
+        self._check(self.lib.dsmd_halo_pack(self.h, c_void_p(index_tensor.data_ptr()), c_int64(count), _p(s),
+                                            c_void_p(out_tensor.data_ptr()), _stream_handle(stream)))
+
+    def halo_unpack(self, in_tensor, first_ghost, count, stream=None):
+        self._check(self.lib.dsmd_halo_unpack(self.h, c_void_p(in_tensor.data_ptr()), c_int64(first_ghost),
+                                              c_int64(count), _stream_handle(stream)))
+
+    def halo_pack_records(self, index_tensor, count, shift, real_out, int_out, stream=None):
+        s = _arr(shift, np.float64)
+        self._check(self.lib.dsmd_halo_pack_records(self.h, c_void_p(index_tensor.data_ptr()), c_int64(count), _p(s),
+                                                    c_void_p(real_out.data_ptr()), c_void_p(int_out.data_ptr()),
+                                                    _stream_handle(stream)))
+
+    def halo_append_records(self, real_in, int_in, count, stream=None):
+        self._check(self.lib.dsmd_halo_append_records(self.h, c_void_p(real_in.data_ptr()), c_void_p(int_in.data_ptr()),
+                                                      c_int64(count), _stream_handle(stream)))
+
+
+class EdgeBuilder:
+    """``dsmd_edges``: the radius-graph builder (the reference's EdgeBuilder, include/EdgeBuilder.cuh)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = load()
+        self.h = c_void_p()
+        rc = self.lib.dsmd_edges_create(c_int(device), ctypes.byref(self.h))
+        if rc != OK:
+            raise DsmdError(rc, "dsmd_edges_create failed")
+        self.device = device
+
+    def _check(self, rc):
+        if rc != OK:
+            raise DsmdError(rc, self.lib.dsmd_edges_last_error(self.h).decode())
+
+    def close(self):
+        if self.h:
+            self.lib.dsmd_edges_destroy(self.h)
+            self.h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def build(self, x, y, z, cutoff, lo=None, hi=None, n_centers=None, owner=None, shift=None, receiver_ok=None,
+              row=1, stream=None):
+        """x, y, z: torch CUDA float64 tensors. Returns (edge_index [2, E] int64, edge_shift [E, 3] float64 or None)
+        as torch tensors that view the builder's buffers (valid until the next build)."""
+        import torch
+        n = x.numel()
+        l, h = _arr(lo, np.float64), _arr(hi, np.float64)
+        nc = n if n_centers is None else n_centers
+        ne = c_int64(0)
+        sx = sy = sz = None
+        if shift is not None:
+            sx, sy, sz = shift
+        self._check(self.lib.dsmd_edges_build(
+            self.h, c_void_p(x.data_ptr()), c_void_p(y.data_ptr()), c_void_p(z.data_ptr()), c_int64(n), c_double(cutoff),
+            _p(l), _p(h), c_int64(nc), c_void_p(owner.data_ptr()) if owner is not None else None,
+            c_void_p(sx.data_ptr()) if sx is not None else None, c_void_p(sy.data_ptr()) if sy is not None else None,
+            c_void_p(sz.data_ptr()) if sz is not None else None,
+            c_void_p(receiver_ok.data_ptr()) if receiver_ok is not None else None, c_int(row), ctypes.byref(ne),
+            _stream_handle(stream)))
+        return self.result(with_shift=owner is not None)
+
+    def result(self, with_shift=False):
+        import torch
+        pi, ps, ne = c_void_p(), c_void_p(), c_int64(0)
+        self._check(self.lib.dsmd_edges_result(self.h, ctypes.byref(pi), ctypes.byref(ps), ctypes.byref(ne)))
+        E = ne.value
+        dev = torch.device("cuda", self.device)
+        if E == 0:
+            return torch.zeros((2, 0), dtype=torch.int64, device=dev), None
+        idx = _tensor_from_ptr(pi.value, (2, E), torch.int64, dev)
+        sh = _tensor_from_ptr(ps.value, (E, 3), torch.float64, dev) if with_shift and ps.value else None
+        return idx, sh
+
+    def build_periodic(self, x, y, z, box, cutoff, stream=None):
+        import torch
+        n = x.numel()
+        b = _arr(box, np.float64)
+        ne = c_int64(0)
+        self._check(self.lib.dsmd_edges_build_periodic(self.h, c_void_p(x.data_ptr()), c_void_p(y.data_ptr()),
+                                                       c_void_p(z.data_ptr()), c_int64(n), _p(b), c_double(cutoff),
+                                                       ctypes.byref(ne), _stream_handle(stream)))
+        ps, pd_, psh, pv = c_void_p(), c_void_p(), c_void_p(), c_void_p()
+        self._check(self.lib.dsmd_edges_result_compact(self.h, ctypes.byref(ps), ctypes.byref(pd_), ctypes.byref(psh),
+                                                       ctypes.byref(pv), ctypes.byref(ne)))
+        E = ne.value
+        dev = torch.device("cuda", self.device)
+        if E == 0:
+            z32 = torch.zeros(0, dtype=torch.int32, device=dev)
+            return z32, z32, torch.zeros((0, 3), dtype=torch.int8, device=dev), torch.zeros((0, 3), device=dev)
+        return (_tensor_from_ptr(ps.value, (E,), torch.int32, dev), _tensor_from_ptr(pd_.value, (E,), torch.int32, dev),
+                _tensor_from_ptr(psh.value, (E, 3), torch.int8, dev),
+                _tensor_from_ptr(pv.value, (E, 3), torch.float32, dev))
+
+
+def _tensor_from_ptr(ptr, shape, dtype, device):
+    """A torch tensor viewing device memory owned by the library (no copy), through __cuda_array_interface__."""
+    import torch
+    typestr = {torch.int64: "<i8", torch.int32: "<i4", torch.float64: "<f8", torch.float32: "<f4", torch.int8: "|i1",
+               torch.uint8: "|u1"}[dtype]
+
+    class _Holder:
+        pass
+
+    holder = _Holder()
+    holder.__cuda_array_interface__ = dict(shape=tuple(shape), typestr=typestr, data=(int(ptr), False), version=2)
+    return torch.as_tensor(holder, device=device)

@@ -1,0 +1,1494 @@
+// The short-range nonbonded path on one B200 (sm_100a): cell binning and sort, Verlet list build with skin,
+// LJ + real-space Ewald pair kernel, displacement check, velocity-Verlet halves, ghost pack/unpack, and the C ABI
+// declared in include/dsmd_b200.h.
+//
+// Data layout in HBM (all arrays indexed by "slot"; owned atoms occupy [0, n_owned), ghosts [n_owned, n_total); both
+// segments are sorted by cell, x fastest, at every list build):
+//   x y z vx vy vz fx fy fz mass charge   double[capacity] each, two sets (the sort gathers from one into the other)
+//   type gid                               int32[capacity], two sets
+//   pq                                     int4[capacity]: fixed-point x, y, z and the type in w (what the kernels read)
+//   qf                                     float[capacity]: charge (read only with Coulomb on)
+//   xref yref zref                         double[capacity]: owned positions at the last build (displacement check)
+//   cell_start                             int32[2 * cells + 1]: first slot of every cell, owned cells then ghost cells
+//   nbr                                    uint32[ceil(n_owned / 32) * stride * 32]: 32-atom slices, entry k of the 32
+//                                          atoms of a slice is one 128-byte line; bit 31 = excluded pair
+//   deg, deg_int                           int32[n_owned]: entries per atom; of which the partner is owned (come first)
+//
+// No tensor cores: the path is a gather over a sparse geometric neighbourhood, not a dense contraction.
+
+#include <cub/cub.cuh>
+#include <thrust/iterator/counting_iterator.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/dsmd_b200.h"
+#include "dsmd_common.cuh"
+#include "ewald_table.hpp"
+
+using dsmd::Grid;
+using dsmd::Status;
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kPairThreads = 128;
+constexpr unsigned kExclBit = 0x80000000u;
+constexpr unsigned kIndexMask = 0x3FFFFFFFu;
+constexpr int kNumReal = 11;   // x y z vx vy vz fx fy fz mass charge
+constexpr double kCoulomb = 332.0636;
+
+inline unsigned blocks_for(int64_t n, int threads) { return static_cast<unsigned>((n + threads - 1) / threads); }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// kernels: binning, sort support, reorder
+// ---------------------------------------------------------------------------------------------------------------------
+
+struct RealArrays {
+    double* p[kNumReal];
+};
+
+__global__ void k_cell_keys(Grid g, int first, int n_owned, int n_total, const double* __restrict__ x,
+                            const double* __restrict__ y, const double* __restrict__ z, unsigned* __restrict__ key,
+                            int* __restrict__ val, Status* st) {
+    const int s = first + blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n_total) return;
+    unsigned bad = 0;
+    const unsigned fx = dsmd::to_fixed(x[s], 0, g, bad);
+    const unsigned fy = dsmd::to_fixed(y[s], 1, g, bad);
+    const unsigned fz = dsmd::to_fixed(z[s], 2, g, bad);
+    if (bad) atomicAdd(&st->out_of_domain, 1u);
+    const unsigned cx = dsmd::cell_of(fx, g.wrap[0], g.nc[0]);
+    const unsigned cy = dsmd::cell_of(fy, g.wrap[1], g.nc[1]);
+    const unsigned cz = dsmd::cell_of(fz, g.wrap[2], g.nc[2]);
+    unsigned c = (cz * g.nc[1] + cy) * g.nc[0] + cx;
+    if (s >= n_owned) c += g.ncells;
+    key[s - first] = c;
+    val[s - first] = s;
+}
+
+// Gathers every particle array into sorted order, writes the fixed-point layout, the displacement reference, the
+// ghost slot map and the cell start table (a thread whose key differs from its predecessor's owns the cells between).
+__global__ void k_reorder(Grid g, int first, int n_owned, int n_total, const unsigned* __restrict__ key,
+                          const int* __restrict__ val, RealArrays src, RealArrays dst, const int* __restrict__ type_src,
+                          const int* __restrict__ gid_src, int* __restrict__ type_dst, int* __restrict__ gid_dst,
+                          int4* __restrict__ pq, float* __restrict__ qf, double* __restrict__ xref,
+                          double* __restrict__ yref, double* __restrict__ zref, int* __restrict__ cell_start,
+                          int* __restrict__ ghost_slot) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int s = first + t;
+    if (s >= n_total) return;
+    const int from = val[t];
+    double r[kNumReal];
+#pragma unroll
+    for (int f = 0; f < kNumReal; ++f) r[f] = src.p[f][from];
+#pragma unroll
+    for (int f = 0; f < kNumReal; ++f) dst.p[f][s] = r[f];
+    const int ty = type_src[from];
+    type_dst[s] = ty;
+    gid_dst[s] = gid_src[from];
+    unsigned bad = 0;
+    int4 p;
+    p.x = static_cast<int>(dsmd::to_fixed(r[0], 0, g, bad));
+    p.y = static_cast<int>(dsmd::to_fixed(r[1], 1, g, bad));
+    p.z = static_cast<int>(dsmd::to_fixed(r[2], 2, g, bad));
+    p.w = ty;
+    pq[s] = p;
+    qf[s] = static_cast<float>(r[10]);
+    if (s < n_owned) {
+        xref[s] = r[0];
+        yref[s] = r[1];
+        zref[s] = r[2];
+    } else {
+        ghost_slot[from - n_owned] = s;
+    }
+    // Cell starts. Keys of the sorted range [first, n_total) are key[0 .. n_total - first). When only the owned atoms
+    // are sorted (first == 0, n_total == n_owned) the ghost half of the table is filled by the later full build.
+    const int k_here = static_cast<int>(key[t]);
+    const int k_prev = t == 0 ? (first == 0 ? -1 : g.ncells - 1) : static_cast<int>(key[t - 1]);
+    for (int c = k_prev + 1; c <= k_here; ++c) cell_start[c] = s;
+    if (s == n_total - 1)
+        for (int c = k_here + 1; c <= 2 * g.ncells; ++c) cell_start[c] = n_total;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// kernel: Verlet list build
+// ---------------------------------------------------------------------------------------------------------------------
+
+struct ExclusionTable {
+    const int* offsets;    // [n_global + 1] by global id, or null
+    const int* partners;   // sorted per atom
+    int n_global;          // ids at or beyond this have no exclusions
+};
+
+__device__ __forceinline__ bool within_list_fp64(const Grid& g, const double* __restrict__ x,
+                                                 const double* __restrict__ y, const double* __restrict__ z, int i,
+                                                 int j) {
+    double dx = x[i] - x[j], dy = y[i] - y[j], dz = z[i] - z[j];
+    if (g.wrap[0]) dx -= g.box[0] * rint(dx / g.box[0]);
+    if (g.wrap[1]) dy -= g.box[1] * rint(dy / g.box[1]);
+    if (g.wrap[2]) dz -= g.box[2] * rint(dz / g.box[2]);
+    // No FMA contraction: the sum must round as the plain fp64 expression dx*dx + dy*dy + dz*dz does.
+    const double r2 = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
+    return r2 < g.r2_list_d;
+}
+
+// One thread per owned atom. The cell rows of the stencil are contiguous runs of slots (cells are sorted x fastest), so
+// a row costs two table reads and a linear scan. The candidate test runs on the fixed-point coordinates in fp32; only
+// results inside the rounding band around the list radius are re-decided in fp64 on the caller's double positions, which
+// makes list membership identical to an fp64 search. Owned partners are scanned first, then ghosts, so the first
+// deg_int entries of a row are the interior part.
+__global__ void __launch_bounds__(kPairThreads)
+k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, const double* __restrict__ x,
+             const double* __restrict__ y, const double* __restrict__ z, const int* __restrict__ gid,
+             ExclusionTable excl, const int* __restrict__ cell_start, unsigned* __restrict__ nbr, int stride,
+             int* __restrict__ deg, int* __restrict__ deg_int, Status* st) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_owned) return;
+    const int4 pi = pq[i];
+    const int cx = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.x), g.wrap[0], g.nc[0]));
+    const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
+    const int cz = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.z), g.wrap[2], g.nc[2]));
+    const int S = g.stencil;
+    const size_t base = (static_cast<size_t>(i >> 5) * stride) * 32 + (i & 31);
+    int ex_begin = 0, ex_end = 0;
+    if (excl.offsets) {
+        const int gi = gid[i];
+        if (gi >= 0 && gi < excl.n_global) {
+            ex_begin = excl.offsets[gi];
+            ex_end = excl.offsets[gi + 1];
+        }
+    }
+    int count = 0, interior = 0;
+    unsigned rechecked = 0;
+    const int n_seg = n_total > n_owned ? 2 : 1;
+    for (int seg = 0; seg < n_seg; ++seg) {
+        for (int dz = -S; dz <= S; ++dz) {
+            int zc = cz + dz;
+            if (g.wrap[2]) { if (zc < 0) zc += g.nc[2]; else if (zc >= g.nc[2]) zc -= g.nc[2]; }
+            else if (zc < 0 || zc >= g.nc[2]) continue;
+            for (int dy = -S; dy <= S; ++dy) {
+                int yc = cy + dy;
+                if (g.wrap[1]) { if (yc < 0) yc += g.nc[1]; else if (yc >= g.nc[1]) yc -= g.nc[1]; }
+                else if (yc < 0 || yc >= g.nc[1]) continue;
+                const int row = seg * g.ncells + (zc * g.nc[1] + yc) * g.nc[0];
+                // x run [cx - S, cx + S]: one range, or two when it crosses the periodic boundary
+                int a0 = cx - S, b0 = cx + S, a1 = 0, b1 = -1;
+                if (g.wrap[0]) {
+                    if (a0 < 0) { a1 = a0 + g.nc[0]; b1 = g.nc[0] - 1; a0 = 0; }
+                    else if (b0 >= g.nc[0]) { a1 = 0; b1 = b0 - g.nc[0]; b0 = g.nc[0] - 1; }
+                } else {
+                    a0 = max(a0, 0);
+                    b0 = min(b0, g.nc[0] - 1);
+                }
+                for (int part = 0; part < 2; ++part) {
+                    const int a = part == 0 ? a0 : a1, b = part == 0 ? b0 : b1;
+                    if (b < a) continue;
+                    const int s_begin = cell_start[row + a], s_end = cell_start[row + b + 1];
+                    for (int s = s_begin; s < s_end; ++s) {
+                        const int4 pj = __ldg(&pq[s]);
+                        const float fx = dsmd::fixed_delta(pj.x, pi.x, g.scale[0]);
+                        const float fy = dsmd::fixed_delta(pj.y, pi.y, g.scale[1]);
+                        const float fz = dsmd::fixed_delta(pj.z, pi.z, g.scale[2]);
+                        const float r2 = fx * fx + fy * fy + fz * fz;
+                        if (r2 >= g.r2_list + g.band || s == i) continue;
+                        if (r2 >= g.r2_list - g.band) {
+                            ++rechecked;
+                            if (!within_list_fp64(g, x, y, z, i, s)) continue;
+                        }
+                        unsigned entry = static_cast<unsigned>(s);
+                        if (ex_end > ex_begin) {
+                            const int gj = gid[s];
+                            for (int e = ex_begin; e < ex_end; ++e)
+                                if (excl.partners[e] == gj) entry |= kExclBit;
+                        }
+                        if (count < stride) nbr[base + static_cast<size_t>(count) * 32] = entry;
+                        ++count;
+                    }
+                }
+            }
+        }
+        if (seg == 0) interior = count;
+    }
+    deg[i] = min(count, stride);
+    deg_int[i] = min(interior, stride);
+    if (count > stride) atomicMax(&st->need_stride, static_cast<unsigned>(count));
+    // statistics: one atomic per warp
+    unsigned long long c64 = count, i64 = interior;
+    unsigned rc = rechecked;
+    for (int o = 16; o > 0; o >>= 1) {
+        c64 += __shfl_down_sync(0xffffffffu, c64, o);
+        i64 += __shfl_down_sync(0xffffffffu, i64, o);
+        rc += __shfl_down_sync(0xffffffffu, rc, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(&st->entries, c64);
+        atomicAdd(&st->interior, i64);
+        if (rc) atomicAdd(&st->rechecked, rc);
+    }
+}
+
+__global__ void k_list_export(int n_owned, const unsigned* __restrict__ nbr, int stride, const int* __restrict__ deg,
+                              const unsigned long long* __restrict__ offsets, int* out_i, int* out_j,
+                              unsigned char* out_flags, long long capacity) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_owned) return;
+    const size_t base = (static_cast<size_t>(i >> 5) * stride) * 32 + (i & 31);
+    unsigned long long o = offsets[i];
+    for (int k = 0; k < deg[i]; ++k, ++o) {
+        if (static_cast<long long>(o) >= capacity) return;
+        const unsigned e = nbr[base + static_cast<size_t>(k) * 32];
+        out_i[o] = i;
+        out_j[o] = static_cast<int>(e & kIndexMask);
+        if (out_flags) out_flags[o] = (e & kExclBit) ? 1 : 0;
+    }
+}
+
+__global__ void k_deg_to_u64(int n, const int* deg, unsigned long long* out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = static_cast<unsigned long long>(deg[i]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// kernels: per-step pack, displacement, integration
+// ---------------------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void block_max_to_status(double v, Status* st) {
+    for (int o = 16; o > 0; o >>= 1) v = fmax(v, __shfl_down_sync(0xffffffffu, v, o));
+    __shared__ double warp_max[32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) warp_max[w] = v;
+    __syncthreads();
+    if (w == 0) {
+        v = lane < (blockDim.x >> 5) ? warp_max[lane] : 0.0;
+        for (int o = 16; o > 0; o >>= 1) v = fmax(v, __shfl_down_sync(0xffffffffu, v, o));
+        if (lane == 0 && v > 0.0) atomicMax(&st->max_disp2, static_cast<unsigned long long>(__double_as_longlong(v)));
+    }
+}
+
+// INTEGRATE: first velocity-Verlet half before the pack (v += dt/2 a, x += dt v).
+template <bool INTEGRATE>
+__global__ void k_pack(Grid g, int first, int count, int n_owned, double* __restrict__ x, double* __restrict__ y,
+                       double* __restrict__ z, double* __restrict__ vx, double* __restrict__ vy,
+                       double* __restrict__ vz, const double* __restrict__ fx, const double* __restrict__ fy,
+                       const double* __restrict__ fz, const double* __restrict__ mass, const int* __restrict__ type,
+                       const double* __restrict__ xref, const double* __restrict__ yref,
+                       const double* __restrict__ zref, int4* __restrict__ pq, double dt, double half_dt_c,
+                       Status* st) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int s = first + t;
+    double d2 = 0.0;
+    if (t < count) {
+        double px = x[s], py = y[s], pz = z[s];
+        if (INTEGRATE) {
+            const double a = half_dt_c / mass[s];
+            const double ux = vx[s] + a * fx[s], uy = vy[s] + a * fy[s], uz = vz[s] + a * fz[s];
+            vx[s] = ux; vy[s] = uy; vz[s] = uz;
+            px += dt * ux; py += dt * uy; pz += dt * uz;
+            x[s] = px; y[s] = py; z[s] = pz;
+        }
+        unsigned bad = 0;
+        int4 p;
+        p.x = static_cast<int>(dsmd::to_fixed(px, 0, g, bad));
+        p.y = static_cast<int>(dsmd::to_fixed(py, 1, g, bad));
+        p.z = static_cast<int>(dsmd::to_fixed(pz, 2, g, bad));
+        p.w = type[s];
+        pq[s] = p;
+        if (bad) atomicAdd(&st->out_of_domain, 1u);
+        if (s < n_owned) {
+            const double ddx = px - xref[s], ddy = py - yref[s], ddz = pz - zref[s];
+            d2 = ddx * ddx + ddy * ddy + ddz * ddz;
+        }
+    }
+    block_max_to_status(d2, st);
+}
+
+__global__ void k_vv2(int n, double half_dt_c, double* __restrict__ vx, double* __restrict__ vy,
+                      double* __restrict__ vz, const double* __restrict__ fx, const double* __restrict__ fy,
+                      const double* __restrict__ fz, const double* __restrict__ mass) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n) return;
+    const double a = half_dt_c / mass[s];
+    vx[s] += a * fx[s];
+    vy[s] += a * fy[s];
+    vz[s] += a * fz[s];
+}
+
+// Deterministic two-level sums: per-block partials, then one block adds them in a fixed order.
+template <int NV>
+__device__ __forceinline__ void block_sum_to_partials(double (&v)[NV], double* partials) {
+    __shared__ double sh[32][NV];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+        for (int o = 16; o > 0; o >>= 1) v[k] += __shfl_down_sync(0xffffffffu, v[k], o);
+    if (lane == 0)
+        for (int k = 0; k < NV; ++k) sh[w][k] = v[k];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int nw = blockDim.x >> 5;
+        for (int k = 0; k < NV; ++k) {
+            double sum = 0.0;
+            for (int q = 0; q < nw; ++q) sum += sh[q][k];
+            partials[static_cast<size_t>(blockIdx.x) * NV + k] = sum;
+        }
+    }
+}
+
+template <int NV>
+__global__ void k_reduce_partials(const double* __restrict__ partials, int n_blocks, double* __restrict__ out,
+                                  int accumulate) {
+    __shared__ double sh[kThreads];
+    for (int k = 0; k < NV; ++k) {
+        double sum = 0.0;
+        for (int b = threadIdx.x; b < n_blocks; b += blockDim.x) sum += partials[static_cast<size_t>(b) * NV + k];
+        sh[threadIdx.x] = sum;
+        __syncthreads();
+        for (int o = blockDim.x / 2; o > 0; o >>= 1) {
+            if (threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) out[k] = accumulate ? out[k] + sh[0] : sh[0];
+        __syncthreads();
+    }
+}
+
+__global__ void k_kinetic(int n, const double* __restrict__ vx, const double* __restrict__ vy,
+                          const double* __restrict__ vz, const double* __restrict__ mass, double* partials) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    double v[1] = {0.0};
+    if (s < n) v[0] = 0.5 * mass[s] * (vx[s] * vx[s] + vy[s] * vy[s] + vz[s] * vz[s]);
+    block_sum_to_partials<1>(v, partials);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// kernel: LJ + real-space Ewald over the list
+// ---------------------------------------------------------------------------------------------------------------------
+
+struct PairParams {
+    float scale[3];
+    float rc2;
+    float rs2, inv_denom;        // CHARMM switch on r^2 (rs2 < 0: off)
+    float kq;                    // Coulomb constant
+    float alpha, two_alpha_sqrtpi;
+    int ntypes;
+    int ewald_intervals;
+    const float2* c6c12;         // [ntypes * ntypes]
+    const float4* ewald;         // [2 * intervals]: force cubic, energy cubic
+};
+
+__device__ __forceinline__ float fast_rcp(float v) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r * (2.0f - v * r);   // one Newton step: full single precision
+}
+
+// One thread per owned atom, 32 atoms of a slice per warp: entry k of the slice is one coalesced 128-byte read, the
+// partner's int4 comes through the read-only path. Every listed pair is evaluated from the side of each of its owned
+// atoms (full list), so forces need no scatter and no atomics, and the summation order is fixed (bitwise reproducible).
+// Energy and virial take half of every directed entry; an owned-ghost pair is then counted half on each rank, as the
+// reference's list kernel does (src/force_calculator_cuda.cu:1784-1789).
+template <bool COULOMB, bool ENERGY, bool MULTI, bool SWITCH>
+__global__ void __launch_bounds__(kPairThreads)
+k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __restrict__ qf,
+       const unsigned* __restrict__ nbr, int stride, const int* __restrict__ deg, const int* __restrict__ deg_int,
+       int phase, double* __restrict__ fx, double* __restrict__ fy, double* __restrict__ fz,
+       double* __restrict__ partials) {
+    extern __shared__ float4 smem[];
+    float2* s_c6c12 = reinterpret_cast<float2*>(smem);
+    float4* s_ewald = smem + (MULTI ? (p.ntypes * p.ntypes + 1) / 2 : 0);
+    if (MULTI)
+        for (int k = threadIdx.x; k < p.ntypes * p.ntypes; k += blockDim.x) s_c6c12[k] = p.c6c12[k];
+    if (COULOMB)
+        for (int k = threadIdx.x; k < 2 * p.ewald_intervals; k += blockDim.x) s_ewald[k] = p.ewald[k];
+    if (MULTI || COULOMB) __syncthreads();
+
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    float ax = 0.f, ay = 0.f, az = 0.f;
+    float e_sum = 0.f, w_sum = 0.f, wx = 0.f, wy = 0.f, wz = 0.f;
+    if (i < n_owned) {
+        const int4 pi = pq[i];
+        const float qi = COULOMB ? p.kq * qf[i] : 0.f;
+        const float2 single = MULTI ? make_float2(0.f, 0.f) : p.c6c12[0];
+        const int trow = MULTI ? pi.w * p.ntypes : 0;
+        const size_t base = (static_cast<size_t>(i >> 5) * stride) * 32 + (i & 31);
+        const int k_begin = phase == DSMD_PHASE_BOUNDARY ? deg_int[i] : 0;
+        const int k_end = phase == DSMD_PHASE_INTERIOR ? deg_int[i] : deg[i];
+        const unsigned* row = nbr + base;
+#pragma unroll 2
+        for (int k = k_begin; k < k_end; ++k) {
+            const unsigned e = row[static_cast<size_t>(k) * 32];
+            const int j = static_cast<int>(e & kIndexMask);
+            const int4 pj = __ldg(&pq[j]);
+            const float dx = dsmd::fixed_delta(pi.x, pj.x, p.scale[0]);
+            const float dy = dsmd::fixed_delta(pi.y, pj.y, p.scale[1]);
+            const float dz = dsmd::fixed_delta(pi.z, pj.z, p.scale[2]);
+            const float r2 = dx * dx + dy * dy + dz * dz;
+            if (r2 < p.rc2 && r2 >= 1e-10f) {
+                const bool excluded = (e & kExclBit) != 0u;
+                float fmag = 0.f, epair = 0.f;
+                const float r2inv = fast_rcp(r2);
+                if (!excluded) {
+                    const float2 c = MULTI ? s_c6c12[trow + pj.w] : single;
+                    const float r6 = r2inv * r2inv * r2inv;
+                    const float rep = c.y * r6 * r6, att = c.x * r6;
+                    float f = r2inv * (12.f * rep - 6.f * att);
+                    float u = rep - att;
+                    if (SWITCH) {
+                        if (r2 > p.rs2) {
+                            const float a = p.rc2 - r2, b = p.rc2 + 2.f * r2 - 3.f * p.rs2;
+                            const float sw = a * a * b * p.inv_denom;
+                            f = sw * f + 12.f * u * a * (r2 - p.rs2) * p.inv_denom;
+                            u *= sw;
+                        }
+                    }
+                    fmag = f;
+                    if (ENERGY) epair = u;
+                }
+                if (COULOMB) {
+                    const float qq = qi * __ldg(&qf[j]);
+                    const unsigned shifted = __float_as_uint(r2) - dsmd::kEwaldBaseBits;
+                    const unsigned idx = shifted >> dsmd::kEwaldIndexShift;
+                    float ff, ef = 0.f;
+                    if (idx < static_cast<unsigned>(p.ewald_intervals)) {
+                        const float t =
+                            __uint_as_float(0x3F800000u | ((shifted << dsmd::kEwaldBits) & 0x007FFFFFu)) - 1.0f;
+                        const float4 cf = s_ewald[2 * idx];
+                        ff = ((cf.w * t + cf.z) * t + cf.y) * t + cf.x;
+                        if (ENERGY) {
+                            const float4 ce = s_ewald[2 * idx + 1];
+                            ef = ((ce.w * t + ce.z) * t + ce.y) * t + ce.x;
+                        }
+                    } else {   // below the table (r^2 < 0.5): analytic
+                        const float r = sqrtf(r2), ar = p.alpha * r;
+                        const float ec = erfcf(ar) / r;
+                        ff = (ec + p.two_alpha_sqrtpi * __expf(-ar * ar)) * r2inv;
+                        ef = ec;
+                    }
+                    if (excluded) {   // the pair's 1/r is not part of the Ewald sum: erfc -> -erf
+                        const float rinv = rsqrtf(r2);
+                        ff -= rinv * r2inv;
+                        ef -= rinv;
+                    }
+                    fmag += qq * ff;
+                    if (ENERGY) epair += qq * ef;
+                }
+                ax += fmag * dx;
+                ay += fmag * dy;
+                az += fmag * dz;
+                if (ENERGY) {
+                    e_sum += epair;
+                    w_sum += fmag * r2;
+                    wx += fmag * dx * dx;
+                    wy += fmag * dy * dy;
+                    wz += fmag * dz * dz;
+                }
+            }
+        }
+        if (phase == DSMD_PHASE_BOUNDARY) {
+            fx[i] += static_cast<double>(ax);
+            fy[i] += static_cast<double>(ay);
+            fz[i] += static_cast<double>(az);
+        } else {
+            fx[i] = static_cast<double>(ax);
+            fy[i] = static_cast<double>(ay);
+            fz[i] = static_cast<double>(az);
+        }
+    }
+    if (ENERGY) {
+        double v[5] = {0.5 * static_cast<double>(e_sum), 0.5 * static_cast<double>(w_sum), 0.5 * static_cast<double>(wx),
+                       0.5 * static_cast<double>(wy), 0.5 * static_cast<double>(wz)};
+        block_sum_to_partials<5>(v, partials);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// kernels: ghosts
+// ---------------------------------------------------------------------------------------------------------------------
+
+__global__ void k_halo_pack(int count, const int* __restrict__ index, const double* __restrict__ x,
+                            const double* __restrict__ y, const double* __restrict__ z, double sx, double sy, double sz,
+                            double* __restrict__ out) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= count) return;
+    const int s = index[k];
+    out[3 * k] = x[s] + sx;
+    out[3 * k + 1] = y[s] + sy;
+    out[3 * k + 2] = z[s] + sz;
+}
+
+__global__ void k_halo_unpack(Grid g, int first_ghost, int count, const double* __restrict__ in,
+                              const int* __restrict__ ghost_slot, double* __restrict__ x, double* __restrict__ y,
+                              double* __restrict__ z, const int* __restrict__ type, int4* __restrict__ pq, Status* st) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= count) return;
+    const int s = ghost_slot[first_ghost + k];
+    const double px = in[3 * k], py = in[3 * k + 1], pz = in[3 * k + 2];
+    x[s] = px; y[s] = py; z[s] = pz;
+    unsigned bad = 0;
+    int4 p;
+    p.x = static_cast<int>(dsmd::to_fixed(px, 0, g, bad));
+    p.y = static_cast<int>(dsmd::to_fixed(py, 1, g, bad));
+    p.z = static_cast<int>(dsmd::to_fixed(pz, 2, g, bad));
+    p.w = type[s];
+    pq[s] = p;
+    if (bad) atomicAdd(&st->out_of_domain, 1u);
+}
+
+__global__ void k_halo_flag(int n_owned, const double* __restrict__ x, const double* __restrict__ y,
+                            const double* __restrict__ z, double lx, double ly, double lz, double hx, double hy,
+                            double hz, unsigned char* __restrict__ flag) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n_owned) return;
+    const double px = x[s], py = y[s], pz = z[s];
+    flag[s] = (px >= lx && px < hx && py >= ly && py < hy && pz >= lz && pz < hz) ? 1 : 0;
+}
+
+__global__ void k_halo_pack_records(int count, const int* __restrict__ index, RealArrays a,
+                                    const int* __restrict__ type, const int* __restrict__ gid, double sx, double sy,
+                                    double sz, double* __restrict__ real_out, int* __restrict__ int_out) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= count) return;
+    const int s = index[k];
+    double* o = real_out + 8 * static_cast<size_t>(k);
+    o[0] = a.p[0][s] + sx; o[1] = a.p[1][s] + sy; o[2] = a.p[2][s] + sz;
+    o[3] = a.p[3][s]; o[4] = a.p[4][s]; o[5] = a.p[5][s];
+    o[6] = a.p[9][s]; o[7] = a.p[10][s];
+    int_out[2 * k] = type[s];
+    int_out[2 * k + 1] = gid[s];
+}
+
+__global__ void k_halo_append_records(int count, int first_slot, const double* __restrict__ real_in,
+                                      const int* __restrict__ int_in, RealArrays a, int* __restrict__ type,
+                                      int* __restrict__ gid) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= count) return;
+    const int s = first_slot + k;
+    const double* r = real_in + 8 * static_cast<size_t>(k);
+    a.p[0][s] = r[0]; a.p[1][s] = r[1]; a.p[2][s] = r[2];
+    a.p[3][s] = r[3]; a.p[4][s] = r[4]; a.p[5][s] = r[5];
+    a.p[6][s] = 0.0; a.p[7][s] = 0.0; a.p[8][s] = 0.0;
+    a.p[9][s] = r[6]; a.p[10][s] = r[7];
+    type[s] = int_in[2 * k];
+    gid[s] = int_in[2 * k + 1];
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------------
+// the context
+// ---------------------------------------------------------------------------------------------------------------------
+
+struct dsmd_ctx {
+    int device = 0;
+    int64_t capacity = 0;
+    int64_t n_owned = 0, n_total = 0;
+    std::string error;
+    int64_t launches = 0;
+
+    // box
+    double box[3] = {0, 0, 0}, lo[3] = {0, 0, 0}, hi[3] = {0, 0, 0}, halo = 0.0;
+    int periodic[3] = {1, 1, 1};
+    bool box_set = false;
+    // parameters
+    int ntypes = 0;
+    double cutoff = 0.0, skin = 0.0, switch_distance = -1.0;
+    bool params_set = false;
+    bool coulomb = false;
+    double alpha = 0.0;
+    int ewald_intervals = 0;
+    Grid grid{};
+    bool grid_valid = false;
+
+    // device storage
+    double* real[2][kNumReal] = {};
+    int* type[2] = {};
+    int* gid[2] = {};
+    int cur = 0;
+    int4* pq = nullptr;
+    float* qf = nullptr;
+    double* ref[3] = {};
+    unsigned* key[2] = {};
+    int* val[2] = {};
+    int* ghost_slot = nullptr;
+    int* cell_start = nullptr;
+    int64_t cell_capacity = 0;
+    unsigned* nbr = nullptr;
+    size_t nbr_capacity = 0;   // entries
+    int stride = 0;
+    int* deg = nullptr;
+    int* deg_int = nullptr;
+    void* cub_temp = nullptr;
+    size_t cub_temp_bytes = 0;
+    float2* c6c12 = nullptr;
+    float4* ewald = nullptr;
+    int* excl_off = nullptr;
+    int* excl_partner = nullptr;
+    int64_t excl_n_global = 0;
+    double* partials = nullptr;
+    int64_t partial_blocks = 0;
+    double* scalars = nullptr;      // 5 force scalars + 1 kinetic
+    Status* status = nullptr;
+    Status* h_status = nullptr;     // pinned
+    double* h_scalars = nullptr;    // pinned
+    unsigned long long* h_disp[2] = {};   // pinned, lagged displacement read-back
+    cudaEvent_t disp_event[2] = {};
+    unsigned char* flag = nullptr;
+    unsigned long long* offsets64 = nullptr;
+    bool list_valid = false;
+    bool owned_sorted_only = false;
+    int64_t stat_entries = 0, stat_interior = 0;
+    int stat_rechecked = 0;
+};
+
+namespace {
+
+#define DSMD_CUDA(ctx, call)                                                                       \
+    do {                                                                                           \
+        cudaError_t err_ = (call);                                                                 \
+        if (err_ != cudaSuccess) {                                                                 \
+            (ctx)->error = std::string(#call) + ": " + cudaGetErrorString(err_);                   \
+            return DSMD_ERR_CUDA;                                                                  \
+        }                                                                                          \
+    } while (0)
+
+#define DSMD_LAUNCHED(ctx)                                                                         \
+    do {                                                                                           \
+        ++(ctx)->launches;                                                                         \
+        cudaError_t err_ = cudaGetLastError();                                                     \
+        if (err_ != cudaSuccess) {                                                                 \
+            (ctx)->error = std::string("kernel launch: ") + cudaGetErrorString(err_);              \
+            return DSMD_ERR_CUDA;                                                                  \
+        }                                                                                          \
+    } while (0)
+
+int fail(dsmd_ctx* ctx, int code, const std::string& what) {
+    ctx->error = what;
+    return code;
+}
+
+RealArrays arrays_of(dsmd_ctx* c, int set) {
+    RealArrays a;
+    for (int f = 0; f < kNumReal; ++f) a.p[f] = c->real[set][f];
+    return a;
+}
+
+// Chooses the fixed-point mapping and the cell grid for the current box, cutoff and skin.
+int make_grid(dsmd_ctx* c) {
+    if (!c->box_set || !c->params_set) return fail(c, DSMD_ERR_STATE, "box and pair parameters must be set first");
+    Grid& g = c->grid;
+    const double R = c->cutoff + c->skin;
+    double max_scale = 0.0;
+    bool split[3];
+    for (int a = 0; a < 3; ++a) {
+        const bool has_sub = c->hi[a] > c->lo[a];
+        split[a] = has_sub && (c->hi[a] - c->lo[a]) < c->box[a] - 1e-6;
+        g.box[a] = c->box[a];
+        if (c->periodic[a] && !split[a]) {
+            g.wrap[a] = 1;
+            g.org[a] = 0.0;
+            g.inv_len[a] = 1.0 / c->box[a];
+            g.scale[a] = static_cast<float>(c->box[a] / 4294967296.0);
+            max_scale = std::max(max_scale, c->box[a] / 4294967296.0);
+        } else {
+            const double lo = (has_sub ? c->lo[a] : 0.0) - c->halo;
+            const double hi = (has_sub ? c->hi[a] : c->box[a]) + c->halo;
+            g.wrap[a] = 0;
+            g.org[a] = lo;
+            g.inv_len[a] = 1.0 / (hi - lo);
+            g.scale[a] = static_cast<float>((hi - lo) / 2147483648.0);
+            max_scale = std::max(max_scale, (hi - lo) / 2147483648.0);
+        }
+    }
+    // Cells at least R / stencil wide (a hair more, so that fixed-point rounding cannot push a partner one cell too far).
+    int stencil = 2;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        bool ok = true;
+        for (int a = 0; a < 3; ++a) {
+            const double len = 1.0 / g.inv_len[a];
+            const double width = R / stencil * (1.0 + 1e-6);
+            int nc = static_cast<int>(std::floor(len / width));
+            nc = std::max(1, std::min(nc, 1024));
+            if (g.wrap[a] && nc < 2 * stencil + 1) ok = false;
+            g.nc[a] = nc;
+        }
+        if (ok) { g.stencil = stencil; break; }
+        if (stencil == 1) {
+            return fail(c, DSMD_ERR_BOX_TOO_SMALL,
+                        "a periodic axis is shorter than three cells of width cutoff + skin");
+        }
+        stencil = 1;
+    }
+    const int64_t ncells = static_cast<int64_t>(g.nc[0]) * g.nc[1] * g.nc[2];
+    if (2 * ncells + 1 > (1ll << 30)) return fail(c, DSMD_ERR_INVALID, "cell grid too large");
+    g.ncells = static_cast<int>(ncells);
+    g.r2_list = static_cast<float>(R * R);
+    g.r2_list_d = R * R;
+    g.band = static_cast<float>(8.0 * R * max_scale + 16.0 * R * R * 5.9604645e-8);
+    c->grid_valid = true;
+    return DSMD_OK;
+}
+
+int ensure_cells(dsmd_ctx* c) {
+    const int64_t need = 2ll * c->grid.ncells + 1;
+    if (need > c->cell_capacity) {
+        if (c->cell_start) cudaFree(c->cell_start);
+        c->cell_start = nullptr;
+        DSMD_CUDA(c, cudaMalloc(&c->cell_start, sizeof(int) * need));
+        c->cell_capacity = need;
+    }
+    return DSMD_OK;
+}
+
+int ensure_list(dsmd_ctx* c, int stride) {
+    const size_t slices = static_cast<size_t>((c->n_owned + 31) / 32);
+    const size_t need = slices * static_cast<size_t>(stride) * 32;
+    if (need > c->nbr_capacity) {
+        if (c->nbr) cudaFree(c->nbr);
+        c->nbr = nullptr;
+        c->nbr_capacity = 0;
+        DSMD_CUDA(c, cudaMalloc(&c->nbr, sizeof(unsigned) * need));
+        c->nbr_capacity = need;
+    }
+    c->stride = stride;
+    return DSMD_OK;
+}
+
+int ensure_partials(dsmd_ctx* c, int64_t blocks) {
+    if (blocks > c->partial_blocks) {
+        if (c->partials) cudaFree(c->partials);
+        c->partials = nullptr;
+        DSMD_CUDA(c, cudaMalloc(&c->partials, sizeof(double) * 5 * blocks));
+        c->partial_blocks = blocks;
+    }
+    return DSMD_OK;
+}
+
+// Sorts slots [first, n_total) by cell and gathers everything into the other buffer set.
+int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s) {
+    const int64_t n = c->n_total - first;
+    const int from = c->cur, to = 1 - c->cur;
+    if (first > 0) {
+        // The owned atoms are already in place: carry them over unchanged.
+        for (int f = 0; f < kNumReal; ++f)
+            DSMD_CUDA(c, cudaMemcpyAsync(c->real[to][f], c->real[from][f], sizeof(double) * first,
+                                         cudaMemcpyDeviceToDevice, s));
+        DSMD_CUDA(c, cudaMemcpyAsync(c->type[to], c->type[from], sizeof(int) * first, cudaMemcpyDeviceToDevice, s));
+        DSMD_CUDA(c, cudaMemcpyAsync(c->gid[to], c->gid[from], sizeof(int) * first, cudaMemcpyDeviceToDevice, s));
+    }
+    if (n > 0) {
+        k_cell_keys<<<blocks_for(n, kThreads), kThreads, 0, s>>>(
+            c->grid, static_cast<int>(first), static_cast<int>(c->n_owned), static_cast<int>(c->n_total),
+            c->real[from][0], c->real[from][1], c->real[from][2], c->key[0], c->val[0], c->status);
+        DSMD_LAUNCHED(c);
+        int bits = 1;
+        while ((1ll << bits) < 2ll * c->grid.ncells) ++bits;
+        size_t need = 0;
+        cub::DeviceRadixSort::SortPairs(nullptr, need, c->key[0], c->key[1], c->val[0], c->val[1], static_cast<int>(n), 0,
+                                        bits, s);
+        if (need > c->cub_temp_bytes) {
+            if (c->cub_temp) cudaFree(c->cub_temp);
+            c->cub_temp = nullptr;
+            DSMD_CUDA(c, cudaMalloc(&c->cub_temp, need));
+            c->cub_temp_bytes = need;
+        }
+        DSMD_CUDA(c, cub::DeviceRadixSort::SortPairs(c->cub_temp, need, c->key[0], c->key[1], c->val[0], c->val[1],
+                                                     static_cast<int>(n), 0, bits, s));
+        k_reorder<<<blocks_for(n, kThreads), kThreads, 0, s>>>(
+            c->grid, static_cast<int>(first), static_cast<int>(c->n_owned), static_cast<int>(c->n_total), c->key[1],
+            c->val[1], arrays_of(c, from), arrays_of(c, to), c->type[from], c->gid[from], c->type[to], c->gid[to], c->pq,
+            c->qf, c->ref[0], c->ref[1], c->ref[2], c->cell_start, c->ghost_slot);
+        DSMD_LAUNCHED(c);
+    }
+    c->cur = to;
+    return DSMD_OK;
+}
+
+int read_status(dsmd_ctx* c, cudaStream_t s) {
+    DSMD_CUDA(c, cudaMemcpyAsync(c->h_status, c->status, sizeof(Status), cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    return DSMD_OK;
+}
+
+template <bool COULOMB, bool ENERGY, bool MULTI>
+void launch_pair(dsmd_ctx* c, const PairParams& p, int phase, bool sw, cudaStream_t s) {
+    const unsigned blocks = blocks_for(c->n_owned, kPairThreads);
+    size_t smem = 0;
+    if (MULTI) smem += sizeof(float4) * ((p.ntypes * p.ntypes + 1) / 2);
+    if (COULOMB) smem += sizeof(float4) * 2 * p.ewald_intervals;
+    double* fx = c->real[c->cur][DSMD_FX];
+    double* fy = c->real[c->cur][DSMD_FY];
+    double* fz = c->real[c->cur][DSMD_FZ];
+    if (sw)
+        k_pair<COULOMB, ENERGY, MULTI, true><<<blocks, kPairThreads, smem, s>>>(
+            p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, fx, fy, fz,
+            c->partials);
+    else
+        k_pair<COULOMB, ENERGY, MULTI, false><<<blocks, kPairThreads, smem, s>>>(
+            p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, fx, fy, fz,
+            c->partials);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------------------------------
+
+extern "C" {
+
+int dsmd_create(int device, int64_t capacity, dsmd_ctx** out) {
+    if (!out || capacity <= 0 || capacity >= (1ll << 30)) return DSMD_ERR_INVALID;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return DSMD_ERR_CUDA;
+    dsmd_ctx* c = new dsmd_ctx();
+    c->device = device;
+    c->capacity = capacity;
+    *out = c;
+    DSMD_CUDA(c, cudaSetDevice(device));
+    for (int set = 0; set < 2; ++set) {
+        for (int f = 0; f < kNumReal; ++f) {
+            DSMD_CUDA(c, cudaMalloc(&c->real[set][f], sizeof(double) * capacity));
+            DSMD_CUDA(c, cudaMemset(c->real[set][f], 0, sizeof(double) * capacity));
+        }
+        DSMD_CUDA(c, cudaMalloc(&c->type[set], sizeof(int) * capacity));
+        DSMD_CUDA(c, cudaMalloc(&c->gid[set], sizeof(int) * capacity));
+        DSMD_CUDA(c, cudaMalloc(&c->key[set], sizeof(unsigned) * capacity));
+        DSMD_CUDA(c, cudaMalloc(&c->val[set], sizeof(int) * capacity));
+    }
+    DSMD_CUDA(c, cudaMalloc(&c->pq, sizeof(int4) * capacity));
+    DSMD_CUDA(c, cudaMalloc(&c->qf, sizeof(float) * capacity));
+    for (int a = 0; a < 3; ++a) DSMD_CUDA(c, cudaMalloc(&c->ref[a], sizeof(double) * capacity));
+    DSMD_CUDA(c, cudaMalloc(&c->ghost_slot, sizeof(int) * capacity));
+    DSMD_CUDA(c, cudaMalloc(&c->deg, sizeof(int) * capacity));
+    DSMD_CUDA(c, cudaMalloc(&c->deg_int, sizeof(int) * capacity));
+    DSMD_CUDA(c, cudaMalloc(&c->flag, capacity));
+    DSMD_CUDA(c, cudaMalloc(&c->offsets64, sizeof(unsigned long long) * capacity));
+    DSMD_CUDA(c, cudaMalloc(&c->scalars, sizeof(double) * 8));
+    DSMD_CUDA(c, cudaMemset(c->scalars, 0, sizeof(double) * 8));
+    DSMD_CUDA(c, cudaMalloc(&c->status, sizeof(Status)));
+    DSMD_CUDA(c, cudaMemset(c->status, 0, sizeof(Status)));
+    DSMD_CUDA(c, cudaMallocHost(&c->h_status, sizeof(Status)));
+    DSMD_CUDA(c, cudaMallocHost(&c->h_scalars, sizeof(double) * 8));
+    for (int k = 0; k < 2; ++k) {
+        DSMD_CUDA(c, cudaMallocHost(&c->h_disp[k], sizeof(unsigned long long)));
+        *c->h_disp[k] = 0ull;
+        DSMD_CUDA(c, cudaEventCreateWithFlags(&c->disp_event[k], cudaEventDisableTiming));
+    }
+    return DSMD_OK;
+}
+
+void dsmd_destroy(dsmd_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    for (int set = 0; set < 2; ++set) {
+        for (int f = 0; f < kNumReal; ++f) cudaFree(c->real[set][f]);
+        cudaFree(c->type[set]); cudaFree(c->gid[set]); cudaFree(c->key[set]); cudaFree(c->val[set]);
+    }
+    cudaFree(c->pq); cudaFree(c->qf);
+    for (int a = 0; a < 3; ++a) cudaFree(c->ref[a]);
+    cudaFree(c->ghost_slot); cudaFree(c->cell_start); cudaFree(c->nbr); cudaFree(c->deg); cudaFree(c->deg_int);
+    cudaFree(c->cub_temp); cudaFree(c->c6c12); cudaFree(c->ewald); cudaFree(c->excl_off); cudaFree(c->excl_partner);
+    cudaFree(c->partials); cudaFree(c->scalars); cudaFree(c->status); cudaFree(c->flag); cudaFree(c->offsets64);
+    cudaFreeHost(c->h_status); cudaFreeHost(c->h_scalars);
+    for (int k = 0; k < 2; ++k) {
+        cudaFreeHost(c->h_disp[k]);
+        if (c->disp_event[k]) cudaEventDestroy(c->disp_event[k]);
+    }
+    delete c;
+}
+
+const char* dsmd_last_error(const dsmd_ctx* c) { return c ? c->error.c_str() : "null context"; }
+
+int64_t dsmd_launch_count(const dsmd_ctx* c) { return c ? c->launches : 0; }
+
+int dsmd_set_box(dsmd_ctx* c, const double box[3], const int periodic[3], const double lo[3], const double hi[3],
+                 double halo) {
+    if (!c || !box || !periodic) return DSMD_ERR_INVALID;
+    for (int a = 0; a < 3; ++a) {
+        if (!(box[a] > 0.0) || !std::isfinite(box[a])) return fail(c, DSMD_ERR_INVALID, "box lengths must be positive");
+        c->box[a] = box[a];
+        c->periodic[a] = periodic[a] != 0;
+        c->lo[a] = lo ? lo[a] : 0.0;
+        c->hi[a] = hi ? hi[a] : 0.0;
+    }
+    c->halo = halo > 0.0 ? halo : 0.0;
+    c->box_set = true;
+    c->grid_valid = false;
+    c->list_valid = false;
+    return DSMD_OK;
+}
+
+int dsmd_set_pair_params(dsmd_ctx* c, int ntypes, const double* eps, const double* sig, double cutoff, double skin,
+                         double switch_distance) {
+    if (!c || ntypes <= 0 || ntypes > 64 || !eps || !sig) return DSMD_ERR_INVALID;
+    if (!(cutoff > 0.0) || skin < 0.0) return fail(c, DSMD_ERR_INVALID, "cutoff must be positive, skin non-negative");
+    if (switch_distance >= cutoff) return fail(c, DSMD_ERR_INVALID, "switch distance must be below the cutoff");
+    DSMD_CUDA(c, cudaSetDevice(c->device));
+    std::vector<float2> table(static_cast<size_t>(ntypes) * ntypes);
+    for (int k = 0; k < ntypes * ntypes; ++k) {
+        const double s2 = sig[k] * sig[k], s6 = s2 * s2 * s2;
+        const double c6 = 4.0 * eps[k] * s6;
+        table[k] = make_float2(static_cast<float>(c6), static_cast<float>(c6 * s6));
+    }
+    if (c->c6c12) cudaFree(c->c6c12);
+    c->c6c12 = nullptr;
+    DSMD_CUDA(c, cudaMalloc(&c->c6c12, sizeof(float2) * table.size()));
+    DSMD_CUDA(c, cudaMemcpy(c->c6c12, table.data(), sizeof(float2) * table.size(), cudaMemcpyHostToDevice));
+    c->ntypes = ntypes;
+    c->cutoff = cutoff;
+    c->skin = skin;
+    c->switch_distance = switch_distance;
+    c->params_set = true;
+    c->grid_valid = false;
+    c->list_valid = false;
+    if (c->coulomb) return dsmd_set_coulomb(c, 1, c->alpha);
+    return DSMD_OK;
+}
+
+int dsmd_set_coulomb(dsmd_ctx* c, int enabled, double alpha) {
+    if (!c) return DSMD_ERR_INVALID;
+    c->coulomb = enabled != 0;
+    if (!c->coulomb) return DSMD_OK;
+    if (!c->params_set) return fail(c, DSMD_ERR_STATE, "set the pair parameters (cutoff) before Coulomb");
+    DSMD_CUDA(c, cudaSetDevice(c->device));
+    c->alpha = alpha > 0.0 ? alpha : dsmd::ewald_alpha_for(c->cutoff);
+    c->ewald_intervals = dsmd::ewald_intervals(c->cutoff * c->cutoff);
+    const std::vector<float> coef = dsmd::ewald_build_table(c->alpha, c->ewald_intervals);
+    if (c->ewald) cudaFree(c->ewald);
+    c->ewald = nullptr;
+    DSMD_CUDA(c, cudaMalloc(&c->ewald, sizeof(float) * coef.size()));
+    DSMD_CUDA(c, cudaMemcpy(c->ewald, coef.data(), sizeof(float) * coef.size(), cudaMemcpyHostToDevice));
+    return DSMD_OK;
+}
+
+int dsmd_get_ewald_alpha(const dsmd_ctx* c, double* alpha) {
+    if (!c || !alpha) return DSMD_ERR_INVALID;
+    *alpha = c->alpha;
+    return DSMD_OK;
+}
+
+int dsmd_set_exclusions(dsmd_ctx* c, int64_t n_global, int64_t n_pairs, const int32_t* a, const int32_t* b) {
+    if (!c || n_global < 0 || n_pairs < 0 || (n_pairs > 0 && (!a || !b))) return DSMD_ERR_INVALID;
+    DSMD_CUDA(c, cudaSetDevice(c->device));
+    if (c->excl_off) cudaFree(c->excl_off);
+    if (c->excl_partner) cudaFree(c->excl_partner);
+    c->excl_off = c->excl_partner = nullptr;
+    c->excl_n_global = 0;
+    c->list_valid = false;
+    if (n_pairs == 0) return DSMD_OK;
+    std::vector<std::pair<int, int>> directed;
+    directed.reserve(2 * n_pairs);
+    for (int64_t k = 0; k < n_pairs; ++k) {
+        if (a[k] < 0 || b[k] < 0 || a[k] >= n_global || b[k] >= n_global || a[k] == b[k])
+            return fail(c, DSMD_ERR_INVALID, "exclusion pair out of range");
+        directed.emplace_back(a[k], b[k]);
+        directed.emplace_back(b[k], a[k]);
+    }
+    std::sort(directed.begin(), directed.end());
+    directed.erase(std::unique(directed.begin(), directed.end()), directed.end());
+    std::vector<int> off(n_global + 1, 0), partner(directed.size());
+    for (const auto& d : directed) ++off[d.first + 1];
+    for (int64_t g = 0; g < n_global; ++g) off[g + 1] += off[g];
+    for (size_t k = 0; k < directed.size(); ++k) partner[k] = directed[k].second;
+    DSMD_CUDA(c, cudaMalloc(&c->excl_off, sizeof(int) * off.size()));
+    DSMD_CUDA(c, cudaMalloc(&c->excl_partner, sizeof(int) * std::max<size_t>(partner.size(), 1)));
+    DSMD_CUDA(c, cudaMemcpy(c->excl_off, off.data(), sizeof(int) * off.size(), cudaMemcpyHostToDevice));
+    DSMD_CUDA(c, cudaMemcpy(c->excl_partner, partner.data(), sizeof(int) * partner.size(), cudaMemcpyHostToDevice));
+    c->excl_n_global = n_global;
+    return DSMD_OK;
+}
+
+int dsmd_upload(dsmd_ctx* c, int64_t n_owned, int64_t n_total, const double* x, const double* y, const double* z,
+                const double* vx, const double* vy, const double* vz, const double* mass, const double* charge,
+                const int32_t* type, const int32_t* gid, void* stream) {
+    if (!c || n_owned < 0 || n_total < n_owned || !x || !y || !z) return DSMD_ERR_INVALID;
+    if (n_total > c->capacity) return fail(c, DSMD_ERR_CAPACITY, "more atoms than the context's capacity");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DSMD_CUDA(c, cudaSetDevice(c->device));
+    const double* src[kNumReal] = {x, y, z, vx, vy, vz, nullptr, nullptr, nullptr, mass, charge};
+    for (int f = 0; f < kNumReal; ++f) {
+        double* dst = c->real[c->cur][f];
+        if (src[f]) {
+            DSMD_CUDA(c, cudaMemcpyAsync(dst, src[f], sizeof(double) * n_total, cudaMemcpyHostToDevice, s));
+        } else if (f == DSMD_MASS) {
+            std::vector<double> ones(n_total, 1.0);
+            DSMD_CUDA(c, cudaMemcpyAsync(dst, ones.data(), sizeof(double) * n_total, cudaMemcpyHostToDevice, s));
+            DSMD_CUDA(c, cudaStreamSynchronize(s));
+        } else {
+            DSMD_CUDA(c, cudaMemsetAsync(dst, 0, sizeof(double) * n_total, s));
+        }
+    }
+    if (type) {
+        DSMD_CUDA(c, cudaMemcpyAsync(c->type[c->cur], type, sizeof(int) * n_total, cudaMemcpyHostToDevice, s));
+    } else {
+        DSMD_CUDA(c, cudaMemsetAsync(c->type[c->cur], 0, sizeof(int) * n_total, s));
+    }
+    if (gid) {
+        DSMD_CUDA(c, cudaMemcpyAsync(c->gid[c->cur], gid, sizeof(int) * n_total, cudaMemcpyHostToDevice, s));
+    } else {
+        std::vector<int> iota(n_total);
+        for (int64_t k = 0; k < n_total; ++k) iota[k] = static_cast<int>(k);
+        DSMD_CUDA(c, cudaMemcpyAsync(c->gid[c->cur], iota.data(), sizeof(int) * n_total, cudaMemcpyHostToDevice, s));
+        DSMD_CUDA(c, cudaStreamSynchronize(s));
+    }
+    c->n_owned = n_owned;
+    c->n_total = n_total;
+    c->list_valid = false;
+    return DSMD_OK;
+}
+
+int dsmd_upload_positions(dsmd_ctx* c, const double* x, const double* y, const double* z, void* stream) {
+    if (!c || !x || !y || !z) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const double* src[3] = {x, y, z};
+    for (int a = 0; a < 3; ++a)
+        DSMD_CUDA(c, cudaMemcpyAsync(c->real[c->cur][a], src[a], sizeof(double) * c->n_total, cudaMemcpyHostToDevice, s));
+    return DSMD_OK;
+}
+
+int dsmd_download(dsmd_ctx* c, int field, int64_t n, void* host_out, void* stream) {
+    if (!c || field < 0 || field >= DSMD_FIELD_COUNT || n < 0 || n > c->capacity || !host_out) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const void* src = field < kNumReal ? static_cast<const void*>(c->real[c->cur][field])
+                                       : (field == DSMD_TYPE ? static_cast<const void*>(c->type[c->cur])
+                                                             : static_cast<const void*>(c->gid[c->cur]));
+    const size_t bytes = (field < kNumReal ? sizeof(double) : sizeof(int)) * static_cast<size_t>(n);
+    DSMD_CUDA(c, cudaMemcpyAsync(host_out, src, bytes, cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    return DSMD_OK;
+}
+
+int dsmd_device_pointer(dsmd_ctx* c, int field, void** out) {
+    if (!c || field < 0 || field >= DSMD_FIELD_COUNT || !out) return DSMD_ERR_INVALID;
+    *out = field < kNumReal ? static_cast<void*>(c->real[c->cur][field])
+                            : (field == DSMD_TYPE ? static_cast<void*>(c->type[c->cur])
+                                                  : static_cast<void*>(c->gid[c->cur]));
+    return DSMD_OK;
+}
+
+int dsmd_counts(const dsmd_ctx* c, int64_t* n_owned, int64_t* n_total) {
+    if (!c) return DSMD_ERR_INVALID;
+    if (n_owned) *n_owned = c->n_owned;
+    if (n_total) *n_total = c->n_total;
+    return DSMD_OK;
+}
+
+int dsmd_set_counts(dsmd_ctx* c, int64_t n_owned, int64_t n_total) {
+    if (!c || n_owned < 0 || n_total < n_owned) return DSMD_ERR_INVALID;
+    if (n_total > c->capacity) return fail(c, DSMD_ERR_CAPACITY, "more atoms than the context's capacity");
+    c->n_owned = n_owned;
+    c->n_total = n_total;
+    c->list_valid = false;
+    return DSMD_OK;
+}
+
+int dsmd_sort_owned(dsmd_ctx* c, void* stream) {
+    if (!c) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DSMD_CUDA(c, cudaSetDevice(c->device));
+    if (!c->grid_valid) { const int rc = make_grid(c); if (rc) return rc; }
+    { const int rc = ensure_cells(c); if (rc) return rc; }
+    DSMD_CUDA(c, cudaMemsetAsync(c->status, 0, sizeof(Status), s));
+    const int64_t keep_total = c->n_total;
+    c->n_total = c->n_owned;   // sort the owned segment alone
+    const int rc = sort_range(c, 0, s);
+    c->n_total = keep_total;
+    if (rc) return rc;
+    c->n_total = c->n_owned;   // ghosts (if any were present) are dropped: the caller appends the new ones
+    c->list_valid = false;
+    c->owned_sorted_only = true;
+    { const int rc2 = read_status(c, s); if (rc2) return rc2; }
+    if (c->h_status->out_of_domain)
+        return fail(c, DSMD_ERR_OUT_OF_DOMAIN, "an atom lies outside the subdomain + halo, or has a NaN position");
+    return DSMD_OK;
+}
+
+int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
+    if (!c) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DSMD_CUDA(c, cudaSetDevice(c->device));
+    if (c->n_owned <= 0) return fail(c, DSMD_ERR_STATE, "no atoms uploaded");
+    if (!c->grid_valid) { const int rc = make_grid(c); if (rc) return rc; }
+    { const int rc = ensure_cells(c); if (rc) return rc; }
+    DSMD_CUDA(c, cudaMemsetAsync(c->status, 0, sizeof(Status), s));
+    // 1. bin + sort + reorder (everything, or only the ghosts when the owned segment was sorted just before)
+    const int64_t first = c->owned_sorted_only ? c->n_owned : 0;
+    c->owned_sorted_only = false;
+    if (first == 0 || c->n_total > first) { const int rc = sort_range(c, first, s); if (rc) return rc; }
+    // 2. list rows
+    if (c->stride == 0) {
+        double volume = 1.0;
+        for (int a = 0; a < 3; ++a) volume *= 1.0 / c->grid.inv_len[a];
+        const double R = c->cutoff + c->skin;
+        const double expect = static_cast<double>(c->n_total) / volume * 4.18879020479 * R * R * R;
+        c->stride = std::max(32, static_cast<int>(expect * 1.3) + 24);
+        c->stride = (c->stride + 3) & ~3;
+    }
+    for (int attempt = 0; attempt < 4; ++attempt) {
+        { const int rc = ensure_list(c, c->stride); if (rc) return rc; }
+        ExclusionTable ex{c->excl_off, c->excl_partner, static_cast<int>(c->excl_n_global)};
+        k_build_list<<<blocks_for(c->n_owned, kPairThreads), kPairThreads, 0, s>>>(
+            c->grid, static_cast<int>(c->n_owned), static_cast<int>(c->n_total), c->pq, c->real[c->cur][0],
+            c->real[c->cur][1], c->real[c->cur][2], c->gid[c->cur], ex, c->cell_start, c->nbr, c->stride, c->deg,
+            c->deg_int, c->status);
+        DSMD_LAUNCHED(c);
+        { const int rc = read_status(c, s); if (rc) return rc; }
+        if (c->h_status->out_of_domain)
+            return fail(c, DSMD_ERR_OUT_OF_DOMAIN, "an atom lies outside the subdomain + halo, or has a NaN position");
+        if (c->h_status->need_stride <= static_cast<unsigned>(c->stride)) break;
+        // a row overflowed: grow and build again
+        c->stride = (static_cast<int>(c->h_status->need_stride * 1.1) + 8 + 3) & ~3;
+        DSMD_CUDA(c, cudaMemsetAsync(c->status, 0, sizeof(Status), s));
+        if (attempt == 3) return fail(c, DSMD_ERR_CAPACITY, "neighbour rows kept overflowing");
+    }
+    c->stat_entries = static_cast<int64_t>(c->h_status->entries);
+    c->stat_interior = static_cast<int64_t>(c->h_status->interior);
+    c->stat_rechecked = static_cast<int>(c->h_status->rechecked);
+    DSMD_CUDA(c, cudaMemsetAsync(c->status, 0, sizeof(Status), s));   // displacement word restarts at zero
+    c->list_valid = true;
+    return DSMD_OK;
+}
+
+int dsmd_ghost_slots(dsmd_ctx* c, const int32_t** out) {
+    if (!c || !out) return DSMD_ERR_INVALID;
+    *out = c->ghost_slot;
+    return DSMD_OK;
+}
+
+int dsmd_list_stats(dsmd_ctx* c, int64_t* directed_entries, int64_t* interior_entries, int32_t* row_stride,
+                    int32_t* cells, int32_t* rechecked) {
+    if (!c) return DSMD_ERR_INVALID;
+    if (!c->list_valid) return fail(c, DSMD_ERR_STATE, "no neighbour list");
+    if (directed_entries) *directed_entries = c->stat_entries;
+    if (interior_entries) *interior_entries = c->stat_interior;
+    if (row_stride) *row_stride = c->stride;
+    if (cells) *cells = c->grid.ncells;
+    if (rechecked) *rechecked = c->stat_rechecked;
+    return DSMD_OK;
+}
+
+int dsmd_list_export(dsmd_ctx* c, int32_t* d_i, int32_t* d_j, uint8_t* d_flags, int64_t capacity, int64_t* n_pairs,
+                     void* stream) {
+    if (!c || !n_pairs) return DSMD_ERR_INVALID;
+    if (!c->list_valid) return fail(c, DSMD_ERR_STATE, "no neighbour list");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int n = static_cast<int>(c->n_owned);
+    *n_pairs = c->stat_entries;
+    if (!d_i || !d_j || capacity < c->stat_entries) return DSMD_OK;   // size query
+    unsigned long long* scratch = nullptr;
+    DSMD_CUDA(c, cudaMalloc(&scratch, sizeof(unsigned long long) * n));
+    k_deg_to_u64<<<blocks_for(n, kThreads), kThreads, 0, s>>>(n, c->deg, scratch);
+    DSMD_LAUNCHED(c);
+    size_t need = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, need, scratch, c->offsets64, n, s);
+    void* temp = nullptr;
+    DSMD_CUDA(c, cudaMalloc(&temp, need));
+    DSMD_CUDA(c, cub::DeviceScan::ExclusiveSum(temp, need, scratch, c->offsets64, n, s));
+    k_list_export<<<blocks_for(n, kThreads), kThreads, 0, s>>>(n, c->nbr, c->stride, c->deg, c->offsets64, d_i, d_j,
+                                                              d_flags, capacity);
+    DSMD_LAUNCHED(c);
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    cudaFree(temp);
+    cudaFree(scratch);
+    return DSMD_OK;
+}
+
+static int pack_impl(dsmd_ctx* c, int64_t first, int64_t count, bool integrate, double dt, double f2a, cudaStream_t s) {
+    if (count <= 0) return DSMD_OK;
+    double** r = c->real[c->cur];
+    if (integrate)
+        k_pack<true><<<blocks_for(count, kThreads), kThreads, 0, s>>>(
+            c->grid, static_cast<int>(first), static_cast<int>(count), static_cast<int>(c->n_owned), r[0], r[1], r[2],
+            r[3], r[4], r[5], r[6], r[7], r[8], r[9], c->type[c->cur], c->ref[0], c->ref[1], c->ref[2], c->pq, dt,
+            0.5 * dt * f2a, c->status);
+    else
+        k_pack<false><<<blocks_for(count, kThreads), kThreads, 0, s>>>(
+            c->grid, static_cast<int>(first), static_cast<int>(count), static_cast<int>(c->n_owned), r[0], r[1], r[2],
+            r[3], r[4], r[5], r[6], r[7], r[8], r[9], c->type[c->cur], c->ref[0], c->ref[1], c->ref[2], c->pq, 0.0, 0.0,
+            c->status);
+    DSMD_LAUNCHED(c);
+    return DSMD_OK;
+}
+
+int dsmd_pack_positions(dsmd_ctx* c, int64_t first, int64_t count, void* stream) {
+    if (!c || first < 0 || count < 0 || first + count > c->n_total) return DSMD_ERR_INVALID;
+    if (!c->grid_valid) return fail(c, DSMD_ERR_STATE, "no neighbour list built yet");
+    return pack_impl(c, first, count, false, 0.0, 0.0, static_cast<cudaStream_t>(stream));
+}
+
+int dsmd_max_displacement_sq(dsmd_ctx* c, double* out, void* stream) {
+    if (!c || !out) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    { const int rc = read_status(c, s); if (rc) return rc; }
+    double v;
+    const unsigned long long bits = c->h_status->max_disp2;
+    std::memcpy(&v, &bits, sizeof(v));
+    *out = v;
+    if (c->h_status->out_of_domain)
+        return fail(c, DSMD_ERR_OUT_OF_DOMAIN, "an atom left the subdomain + halo, or has a NaN position");
+    return DSMD_OK;
+}
+
+int dsmd_compute_forces(dsmd_ctx* c, int phase, int want_energy, void* stream) {
+    if (!c || phase < DSMD_PHASE_FULL || phase > DSMD_PHASE_BOUNDARY) return DSMD_ERR_INVALID;
+    if (!c->list_valid) return fail(c, DSMD_ERR_STATE, "build the neighbour list before computing forces");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    PairParams p{};
+    for (int a = 0; a < 3; ++a) p.scale[a] = c->grid.scale[a];
+    p.rc2 = static_cast<float>(c->cutoff * c->cutoff);
+    const bool sw = c->switch_distance > 0.0;
+    if (sw) {
+        const double rs2 = c->switch_distance * c->switch_distance, d = c->cutoff * c->cutoff - rs2;
+        p.rs2 = static_cast<float>(rs2);
+        p.inv_denom = static_cast<float>(1.0 / (d * d * d));
+    } else {
+        p.rs2 = -1.f;
+    }
+    p.kq = static_cast<float>(kCoulomb);
+    p.alpha = static_cast<float>(c->alpha);
+    p.two_alpha_sqrtpi = static_cast<float>(2.0 * c->alpha / std::sqrt(3.14159265358979323846));
+    p.ntypes = c->ntypes;
+    p.ewald_intervals = c->ewald_intervals;
+    p.c6c12 = c->c6c12;
+    p.ewald = c->ewald;
+    const bool multi = c->ntypes > 1;
+    const int64_t blocks = blocks_for(c->n_owned, kPairThreads);
+    if (want_energy) { const int rc = ensure_partials(c, blocks); if (rc) return rc; }
+    const bool e = want_energy != 0;
+    if (c->coulomb) {
+        if (e) { if (multi) launch_pair<true, true, true>(c, p, phase, sw, s); else launch_pair<true, true, false>(c, p, phase, sw, s); }
+        else   { if (multi) launch_pair<true, false, true>(c, p, phase, sw, s); else launch_pair<true, false, false>(c, p, phase, sw, s); }
+    } else {
+        if (e) { if (multi) launch_pair<false, true, true>(c, p, phase, sw, s); else launch_pair<false, true, false>(c, p, phase, sw, s); }
+        else   { if (multi) launch_pair<false, false, true>(c, p, phase, sw, s); else launch_pair<false, false, false>(c, p, phase, sw, s); }
+    }
+    DSMD_LAUNCHED(c);
+    if (e) {
+        k_reduce_partials<5><<<1, kThreads, 0, s>>>(c->partials, static_cast<int>(blocks), c->scalars,
+                                                   phase == DSMD_PHASE_BOUNDARY ? 1 : 0);
+        DSMD_LAUNCHED(c);
+    }
+    return DSMD_OK;
+}
+
+int dsmd_read_scalars(dsmd_ctx* c, double out[5], void* stream) {
+    if (!c || !out) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DSMD_CUDA(c, cudaMemcpyAsync(c->h_scalars, c->scalars, sizeof(double) * 5, cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    for (int k = 0; k < 5; ++k) out[k] = c->h_scalars[k];
+    return DSMD_OK;
+}
+
+int dsmd_integrate(dsmd_ctx* c, int half, double dt, double f2a, void* stream) {
+    if (!c || (half != 1 && half != 2)) return DSMD_ERR_INVALID;
+    if (!c->grid_valid) return fail(c, DSMD_ERR_STATE, "no neighbour list built yet");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (half == 1) return pack_impl(c, 0, c->n_owned, true, dt, f2a, s);
+    double** r = c->real[c->cur];
+    k_vv2<<<blocks_for(c->n_owned, kThreads), kThreads, 0, s>>>(static_cast<int>(c->n_owned), 0.5 * dt * f2a, r[3], r[4],
+                                                               r[5], r[6], r[7], r[8], r[9]);
+    DSMD_LAUNCHED(c);
+    return DSMD_OK;
+}
+
+int dsmd_kinetic_energy(dsmd_ctx* c, double* out, void* stream) {
+    if (!c || !out) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t blocks = blocks_for(c->n_owned, kThreads);
+    { const int rc = ensure_partials(c, blocks); if (rc) return rc; }
+    double** r = c->real[c->cur];
+    k_kinetic<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(static_cast<int>(c->n_owned), r[3], r[4], r[5], r[9],
+                                                                 c->partials);
+    DSMD_LAUNCHED(c);
+    k_reduce_partials<1><<<1, kThreads, 0, s>>>(c->partials, static_cast<int>(blocks), c->scalars + 5, 0);
+    DSMD_LAUNCHED(c);
+    DSMD_CUDA(c, cudaMemcpyAsync(c->h_scalars + 5, c->scalars + 5, sizeof(double), cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    *out = c->h_scalars[5];
+    return DSMD_OK;
+}
+
+int dsmd_run_nve(dsmd_ctx* c, int64_t n_steps, double dt, double f2a, double hi_frac, int every, int lagged,
+                 int64_t* n_rebuilds, double* worst_disp_sq, void* stream) {
+    if (!c || n_steps < 0) return DSMD_ERR_INVALID;
+    if (c->n_total != c->n_owned) return fail(c, DSMD_ERR_STATE, "dsmd_run_nve handles single-rank systems only");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (!c->list_valid) {
+        const int rc = dsmd_build_neighbor_list(c, s);
+        if (rc) return rc;
+        const int rc2 = dsmd_compute_forces(c, DSMD_PHASE_FULL, 0, s);
+        if (rc2) return rc2;
+    }
+    const double limit2 = (hi_frac * c->skin) * (hi_frac * c->skin);
+    int64_t rebuilds = 0;
+    double worst = 0.0;
+    int since_build = 0;
+    double d_prev = 0.0, d_prev2 = 0.0;   // displacement (not squared) seen one and two steps ago (lagged mode)
+    int pending = -1;                      // read-back slot in flight
+    auto bits_to_double = [](unsigned long long b) { double v; std::memcpy(&v, &b, sizeof(v)); return v; };
+    for (int64_t step = 0; step < n_steps; ++step) {
+        { const int rc = pack_impl(c, 0, c->n_owned, true, dt, f2a, s); if (rc) return rc; }
+        ++since_build;
+        bool rebuild = every > 0 && since_build >= every;
+        if (!lagged) {
+            double d2 = 0.0;
+            const int rc = dsmd_max_displacement_sq(c, &d2, s);
+            if (rc) return rc;
+            if (d2 > limit2) rebuild = true;
+            if (!rebuild) worst = std::max(worst, d2);
+        } else {
+            // Read back what the previous step saw (its copy finished long ago), queue this step's copy, and decide on
+            // the linear extrapolation of the last two values, as the reference does on several ranks
+            // (src/md_simulation.cpp:1232-1245). The previous step's forces were evaluated under d_prev.
+            if (pending >= 0) {
+                DSMD_CUDA(c, cudaEventSynchronize(c->disp_event[pending]));
+                d_prev2 = d_prev;
+                d_prev = std::sqrt(bits_to_double(*c->h_disp[pending]));
+                worst = std::max(worst, d_prev * d_prev);
+            }
+            const int slot = static_cast<int>(step & 1);
+            DSMD_CUDA(c, cudaMemcpyAsync(c->h_disp[slot], &c->status->max_disp2, sizeof(unsigned long long),
+                                         cudaMemcpyDeviceToHost, s));
+            DSMD_CUDA(c, cudaEventRecord(c->disp_event[slot], s));
+            pending = slot;
+            const double predicted = d_prev + 1.5 * std::max(d_prev - d_prev2, 0.0);
+            if (predicted * predicted > limit2) rebuild = true;
+        }
+        if (rebuild) {
+            const int rc = dsmd_build_neighbor_list(c, s);
+            if (rc) return rc;
+            ++rebuilds;
+            since_build = 0;
+            d_prev = d_prev2 = 0.0;
+            pending = -1;   // the copy queued above predates the new reference positions
+        }
+        { const int rc = dsmd_compute_forces(c, DSMD_PHASE_FULL, 0, s); if (rc) return rc; }
+        { const int rc = dsmd_integrate(c, 2, dt, f2a, s); if (rc) return rc; }
+    }
+    if (lagged && pending >= 0) {
+        DSMD_CUDA(c, cudaEventSynchronize(c->disp_event[pending]));
+        const double d = std::sqrt(bits_to_double(*c->h_disp[pending]));
+        worst = std::max(worst, d * d);
+    }
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    if (n_rebuilds) *n_rebuilds = rebuilds;
+    if (worst_disp_sq) *worst_disp_sq = worst;
+    return DSMD_OK;
+}
+
+int dsmd_forces_host(dsmd_ctx* c, const double* x, const double* y, const double* z, int rebuild, double* fx,
+                     double* fy, double* fz, double* out5, void* stream) {
+    if (!c || !x || !y || !z || !fx || !fy || !fz) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    { const int rc = dsmd_upload_positions(c, x, y, z, s); if (rc) return rc; }
+    if (rebuild || !c->list_valid) {
+        const int rc = dsmd_build_neighbor_list(c, s);
+        if (rc) return rc;
+    } else {
+        const int rc = pack_impl(c, 0, c->n_total, false, 0.0, 0.0, s);
+        if (rc) return rc;
+    }
+    { const int rc = dsmd_compute_forces(c, DSMD_PHASE_FULL, out5 ? 1 : 0, s); if (rc) return rc; }
+    double* dst[3] = {fx, fy, fz};
+    for (int a = 0; a < 3; ++a)
+        DSMD_CUDA(c, cudaMemcpyAsync(dst[a], c->real[c->cur][DSMD_FX + a], sizeof(double) * c->n_owned,
+                                     cudaMemcpyDeviceToHost, s));
+    if (out5) return dsmd_read_scalars(c, out5, s);
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    return DSMD_OK;
+}
+
+// ---- ghosts ---------------------------------------------------------------------------------------------------------
+
+int dsmd_halo_pack(dsmd_ctx* c, const int32_t* d_index, int64_t count, const double shift[3], double* d_out,
+                   void* stream) {
+    if (!c || count < 0 || (count > 0 && (!d_index || !d_out))) return DSMD_ERR_INVALID;
+    if (count == 0) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    double** r = c->real[c->cur];
+    k_halo_pack<<<blocks_for(count, kThreads), kThreads, 0, s>>>(static_cast<int>(count), d_index, r[0], r[1], r[2],
+                                                                shift ? shift[0] : 0.0, shift ? shift[1] : 0.0,
+                                                                shift ? shift[2] : 0.0, d_out);
+    DSMD_LAUNCHED(c);
+    return DSMD_OK;
+}
+
+int dsmd_halo_unpack(dsmd_ctx* c, const double* d_in, int64_t first_ghost, int64_t count, void* stream) {
+    if (!c || count < 0 || first_ghost < 0 || first_ghost + count > c->n_total - c->n_owned) return DSMD_ERR_INVALID;
+    if (count == 0) return DSMD_OK;
+    if (!c->list_valid) return fail(c, DSMD_ERR_STATE, "halo unpack needs the ghost slots of a built list");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    double** r = c->real[c->cur];
+    k_halo_unpack<<<blocks_for(count, kThreads), kThreads, 0, s>>>(c->grid, static_cast<int>(first_ghost),
+                                                                  static_cast<int>(count), d_in, c->ghost_slot, r[0],
+                                                                  r[1], r[2], c->type[c->cur], c->pq, c->status);
+    DSMD_LAUNCHED(c);
+    return DSMD_OK;
+}
+
+int dsmd_halo_select(dsmd_ctx* c, const double lo[3], const double hi[3], int32_t* d_index, int64_t capacity,
+                     int64_t* count, void* stream) {
+    if (!c || !lo || !hi || !count) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int n = static_cast<int>(c->n_owned);
+    *count = 0;
+    if (n == 0) return DSMD_OK;
+    double** r = c->real[c->cur];
+    k_halo_flag<<<blocks_for(n, kThreads), kThreads, 0, s>>>(n, r[0], r[1], r[2], lo[0], lo[1], lo[2], hi[0], hi[1],
+                                                            hi[2], c->flag);
+    DSMD_LAUNCHED(c);
+    size_t need = 0;
+    thrust::counting_iterator<int> iota(0);
+    int* d_selected = c->val[0];   // scratch of capacity entries
+    cub::DeviceSelect::Flagged(nullptr, need, iota, c->flag, d_selected, &c->status->select_count, n, s);
+    if (need > c->cub_temp_bytes) {
+        if (c->cub_temp) cudaFree(c->cub_temp);
+        c->cub_temp = nullptr;
+        DSMD_CUDA(c, cudaMalloc(&c->cub_temp, need));
+        c->cub_temp_bytes = need;
+    }
+    DSMD_CUDA(c, cub::DeviceSelect::Flagged(c->cub_temp, need, iota, c->flag, d_selected, &c->status->select_count, n, s));
+    unsigned long long selected = 0;
+    DSMD_CUDA(c, cudaMemcpyAsync(&selected, &c->status->select_count, sizeof(selected), cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    *count = static_cast<int64_t>(selected);
+    if (d_index && static_cast<int64_t>(selected) <= capacity && selected > 0)
+        DSMD_CUDA(c, cudaMemcpyAsync(d_index, d_selected, sizeof(int) * selected, cudaMemcpyDeviceToDevice, s));
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    return DSMD_OK;
+}
+
+int dsmd_halo_pack_records(dsmd_ctx* c, const int32_t* d_index, int64_t count, const double shift[3],
+                           double* d_real_out, int32_t* d_int_out, void* stream) {
+    if (!c || count < 0 || (count > 0 && (!d_index || !d_real_out || !d_int_out))) return DSMD_ERR_INVALID;
+    if (count == 0) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    k_halo_pack_records<<<blocks_for(count, kThreads), kThreads, 0, s>>>(
+        static_cast<int>(count), d_index, arrays_of(c, c->cur), c->type[c->cur], c->gid[c->cur], shift ? shift[0] : 0.0,
+        shift ? shift[1] : 0.0, shift ? shift[2] : 0.0, d_real_out, d_int_out);
+    DSMD_LAUNCHED(c);
+    return DSMD_OK;
+}
+
+int dsmd_halo_append_records(dsmd_ctx* c, const double* d_real_in, const int32_t* d_int_in, int64_t count,
+                             void* stream) {
+    if (!c || count < 0 || (count > 0 && (!d_real_in || !d_int_in))) return DSMD_ERR_INVALID;
+    if (c->n_total + count > c->capacity) return fail(c, DSMD_ERR_CAPACITY, "ghosts exceed the context's capacity");
+    if (count == 0) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    k_halo_append_records<<<blocks_for(count, kThreads), kThreads, 0, s>>>(
+        static_cast<int>(count), static_cast<int>(c->n_total), d_real_in, d_int_in, arrays_of(c, c->cur),
+        c->type[c->cur], c->gid[c->cur]);
+    DSMD_LAUNCHED(c);
+    c->n_total += count;
+    c->list_valid = false;
+    return DSMD_OK;
+}
+
+}  // extern "C"

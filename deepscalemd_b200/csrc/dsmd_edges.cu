@@ -1,0 +1,607 @@
+// Radius-graph edge builder for the machine-learned-potential backends (sm_100a).
+//
+// Semantics of the reference's EdgeBuilder::build (include/EdgeBuilder.cuh:12-59, src/EdgeBuilder.cu:233-334): every
+// ordered pair (i, j), i != j, |r_j - r_i| < cutoff over the atoms given, no minimum image; optional periodic-image
+// description (centres restricted to the real atoms, neighbour replaced by the atom it copies, per-edge shift) and
+// optional receiver pruning. Output int64 [2, E] + double [E, 3].
+//
+// What is done differently: the neighbourhood search runs ONCE (the reference searches twice, to count and to fill),
+// on 32-bit fixed-point coordinates in fp32 with an fp64 re-decision inside the rounding band (so membership is that of
+// an fp64 search), and leaves its hits in 32-atom slices; after one scan of the counts a warp-cooperative pass expands
+// the slices into the interface arrays with fully coalesced stores, which is where the bytes are (40 B per edge).
+// A second entry point emits the compact periodic form (int32 src/dst, int8 lattice shift, fp32 edge vector).
+
+#include <cub/cub.cuh>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <string>
+
+#include "../../include/dsmd_b200.h"
+#include "dsmd_common.cuh"
+
+using dsmd::Grid;
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kSearchThreads = 128;
+
+inline unsigned blocks_for(int64_t n, int threads) { return static_cast<unsigned>((n + threads - 1) / threads); }
+
+struct EdgeStatus {
+    long long edges;
+    unsigned int out_of_bounds;
+    unsigned int need_stride;
+    unsigned int rechecked;
+    unsigned int pad;
+};
+
+__global__ void k_edge_keys(Grid g, int n, const double* __restrict__ x, const double* __restrict__ y,
+                            const double* __restrict__ z, unsigned* __restrict__ key, int* __restrict__ val,
+                            EdgeStatus* st) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    unsigned bad = 0;
+    const unsigned fx = dsmd::to_fixed(x[i], 0, g, bad);
+    const unsigned fy = dsmd::to_fixed(y[i], 1, g, bad);
+    const unsigned fz = dsmd::to_fixed(z[i], 2, g, bad);
+    if (bad) atomicOr(&st->out_of_bounds, 1u);
+    const unsigned cx = dsmd::cell_of(fx, g.wrap[0], g.nc[0]);
+    const unsigned cy = dsmd::cell_of(fy, g.wrap[1], g.nc[1]);
+    const unsigned cz = dsmd::cell_of(fz, g.wrap[2], g.nc[2]);
+    key[i] = (cz * g.nc[1] + cy) * g.nc[0] + cx;
+    val[i] = i;
+}
+
+// Sorted fixed-point atoms (w = the caller's atom index), inverse permutation and cell starts.
+__global__ void k_edge_gather(Grid g, int n, const unsigned* __restrict__ key, const int* __restrict__ val,
+                              const double* __restrict__ x, const double* __restrict__ y, const double* __restrict__ z,
+                              int4* __restrict__ pq, int* __restrict__ slot_of, int* __restrict__ cell_start) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n) return;
+    const int a = val[s];
+    unsigned bad = 0;
+    int4 p;
+    p.x = static_cast<int>(dsmd::to_fixed(x[a], 0, g, bad));
+    p.y = static_cast<int>(dsmd::to_fixed(y[a], 1, g, bad));
+    p.z = static_cast<int>(dsmd::to_fixed(z[a], 2, g, bad));
+    p.w = a;
+    pq[s] = p;
+    slot_of[a] = s;
+    const int k_here = static_cast<int>(key[s]);
+    const int k_prev = s == 0 ? -1 : static_cast<int>(key[s - 1]);
+    for (int c = k_prev + 1; c <= k_here; ++c) cell_start[c] = s;
+    if (s == n - 1)
+        for (int c = k_here + 1; c <= g.ncells; ++c) cell_start[c] = n;
+}
+
+struct SearchArgs {
+    int n, n_centers, stride, row;
+    const int4* pq;
+    const double *x, *y, *z;
+    const int* cell_start;
+    const int* owner;
+    const unsigned char* ok;
+    unsigned* rows;
+    int* counts;        // by sorted slot (interface form) or by atom index (compact form)
+    EdgeStatus* st;
+};
+
+template <bool PERIODIC>
+__device__ __forceinline__ bool within_fp64(const Grid& g, const SearchArgs& a, int ai, int aj) {
+    double dx = a.x[aj] - a.x[ai], dy = a.y[aj] - a.y[ai], dz = a.z[aj] - a.z[ai];
+    if (PERIODIC) {
+        dx -= g.box[0] * rint(dx / g.box[0]);
+        dy -= g.box[1] * rint(dy / g.box[1]);
+        dz -= g.box[2] * rint(dz / g.box[2]);
+    }
+    const double r2 = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
+    return r2 < g.r2_list_d;
+}
+
+// One thread per sorted slot; hits (the neighbour's atom index) go to the slot's column of its 32-atom slice.
+// PERIODIC: all axes wrap, rows are sorted by neighbour index, counts are stored by the centre's atom index.
+template <bool PERIODIC>
+__global__ void __launch_bounds__(kSearchThreads) k_edge_search(Grid g, SearchArgs a) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= a.n) return;
+    const int4 pi = a.pq[p];
+    const int centre = pi.w;
+    int count = 0;
+    const bool is_centre = centre < a.n_centers && !(a.ok && a.row == 0 && !a.ok[centre]);
+    const size_t base = (static_cast<size_t>(p >> 5) * a.stride) * 32 + (p & 31);
+    unsigned rechecked = 0;
+    if (is_centre) {
+        const bool check_nb = a.ok && a.row == 1;
+        const int cx = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.x), g.wrap[0], g.nc[0]));
+        const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
+        const int cz = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.z), g.wrap[2], g.nc[2]));
+        const int S = g.stencil;
+        for (int dz = -S; dz <= S; ++dz) {
+            int zc = cz + dz;
+            if (g.wrap[2]) { if (zc < 0) zc += g.nc[2]; else if (zc >= g.nc[2]) zc -= g.nc[2]; }
+            else if (zc < 0 || zc >= g.nc[2]) continue;
+            for (int dy = -S; dy <= S; ++dy) {
+                int yc = cy + dy;
+                if (g.wrap[1]) { if (yc < 0) yc += g.nc[1]; else if (yc >= g.nc[1]) yc -= g.nc[1]; }
+                else if (yc < 0 || yc >= g.nc[1]) continue;
+                const int row = (zc * g.nc[1] + yc) * g.nc[0];
+                int a0 = cx - S, b0 = cx + S, a1 = 0, b1 = -1;
+                if (g.wrap[0]) {
+                    if (a0 < 0) { a1 = a0 + g.nc[0]; b1 = g.nc[0] - 1; a0 = 0; }
+                    else if (b0 >= g.nc[0]) { a1 = 0; b1 = b0 - g.nc[0]; b0 = g.nc[0] - 1; }
+                } else {
+                    a0 = max(a0, 0);
+                    b0 = min(b0, g.nc[0] - 1);
+                }
+                for (int part = 0; part < 2; ++part) {
+                    const int lo = part == 0 ? a0 : a1, hi = part == 0 ? b0 : b1;
+                    if (hi < lo) continue;
+                    const int s_begin = a.cell_start[row + lo], s_end = a.cell_start[row + hi + 1];
+                    for (int s = s_begin; s < s_end; ++s) {
+                        const int4 pj = __ldg(&a.pq[s]);
+                        const float fx = dsmd::fixed_delta(pj.x, pi.x, g.scale[0]);
+                        const float fy = dsmd::fixed_delta(pj.y, pi.y, g.scale[1]);
+                        const float fz = dsmd::fixed_delta(pj.z, pi.z, g.scale[2]);
+                        const float r2 = fx * fx + fy * fy + fz * fz;
+                        if (r2 >= g.r2_list + g.band || s == p) continue;
+                        if (r2 >= g.r2_list - g.band) {
+                            ++rechecked;
+                            if (!within_fp64<PERIODIC>(g, a, centre, pj.w)) continue;
+                        }
+                        if (check_nb && !a.ok[a.owner ? a.owner[pj.w] : pj.w]) continue;
+                        if (count < a.stride) {
+                            if (PERIODIC) {   // keep the row sorted by neighbour index (insertion)
+                                int k = count;
+                                while (k > 0) {
+                                    const unsigned prev = a.rows[base + static_cast<size_t>(k - 1) * 32];
+                                    if (prev <= static_cast<unsigned>(pj.w)) break;
+                                    a.rows[base + static_cast<size_t>(k) * 32] = prev;
+                                    --k;
+                                }
+                                a.rows[base + static_cast<size_t>(k) * 32] = static_cast<unsigned>(pj.w);
+                            } else {
+                                a.rows[base + static_cast<size_t>(count) * 32] = static_cast<unsigned>(pj.w);
+                            }
+                        }
+                        ++count;
+                    }
+                }
+            }
+        }
+    }
+    a.counts[PERIODIC ? centre : p] = min(count, a.stride);
+    if (count > a.stride) atomicMax(&a.st->need_stride, static_cast<unsigned>(count));
+    if (rechecked) atomicAdd(&a.st->rechecked, rechecked);
+}
+
+__global__ void k_edge_total(int n, const long long* __restrict__ offsets, const int* __restrict__ counts,
+                             EdgeStatus* st) {
+    st->edges = offsets[n - 1] + counts[n - 1];
+}
+
+// Finds, for flat position t inside a warp's run of edges, the lane (centre) it belongs to: the last lane whose
+// exclusive prefix is <= t.
+__device__ __forceinline__ int owner_lane(int t, int my_prefix) {
+    int lo = 0;
+#pragma unroll
+    for (int step = 16; step > 0; step >>= 1) {
+        const int probe = lo + step;
+        const int v = __shfl_sync(0xffffffffu, my_prefix, probe & 31);
+        if (probe < 32 && v <= t) lo = probe;
+    }
+    return lo;
+}
+
+// Interface form. A warp takes 32 consecutive sorted slots and streams their edges out in flat order, so that the
+// three output arrays are written with contiguous, coalesced stores.
+__global__ void k_edge_fill(int n, long long n_edges, int stride, const int4* __restrict__ pq,
+                            const unsigned* __restrict__ rows, const int* __restrict__ counts,
+                            const long long* __restrict__ offsets, const int* __restrict__ owner,
+                            const double* __restrict__ shift_x, const double* __restrict__ shift_y,
+                            const double* __restrict__ shift_z, long long* __restrict__ edges,
+                            double* __restrict__ shift) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int p = warp * 32 + lane;
+    if (warp * 32 >= n) return;
+    const int cnt = p < n ? counts[p] : 0;
+    const int centre = p < n ? pq[p].w : 0;
+    int prefix = cnt;   // inclusive scan over the warp
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, prefix, o);
+        if (lane >= o) prefix += v;
+    }
+    const int total = __shfl_sync(0xffffffffu, prefix, 31);
+    prefix -= cnt;      // exclusive
+    const long long out0 = offsets[warp * 32];
+    const size_t slice = static_cast<size_t>(warp) * stride * 32;
+    for (int t0 = 0; t0 < total; t0 += 32) {
+        const int t = t0 + lane;
+        const int c = owner_lane(min(t, total - 1), prefix);
+        const int c_prefix = __shfl_sync(0xffffffffu, prefix, c);
+        const int c_centre = __shfl_sync(0xffffffffu, centre, c);
+        if (t < total) {
+            const int k = t - c_prefix;
+            const int nb = static_cast<int>(rows[slice + static_cast<size_t>(k) * 32 + c]);
+            const long long o = out0 + t;
+            edges[o] = c_centre;
+            edges[n_edges + o] = owner ? owner[nb] : nb;
+            if (shift) {
+                shift[3 * o] = shift_x[nb];
+                shift[3 * o + 1] = shift_y[nb];
+                shift[3 * o + 2] = shift_z[nb];
+            }
+        }
+    }
+}
+
+// Compact periodic form: a warp takes 32 consecutive atom indices (edges come out sorted by src, then dst).
+__global__ void k_edge_fill_compact(Grid g, int n, int stride, const int* __restrict__ slot_of,
+                                    const unsigned* __restrict__ rows, const int* __restrict__ counts,
+                                    const long long* __restrict__ offsets, const double* __restrict__ x,
+                                    const double* __restrict__ y, const double* __restrict__ z, int* __restrict__ src,
+                                    int* __restrict__ dst, signed char* __restrict__ shift, float* __restrict__ vec) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int i = warp * 32 + lane;
+    if (warp * 32 >= n) return;
+    const int cnt = i < n ? counts[i] : 0;
+    const int slot = i < n ? slot_of[i] : 0;
+    int prefix = cnt;
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, prefix, o);
+        if (lane >= o) prefix += v;
+    }
+    const int total = __shfl_sync(0xffffffffu, prefix, 31);
+    prefix -= cnt;
+    const long long out0 = offsets[warp * 32];
+    for (int t0 = 0; t0 < total; t0 += 32) {
+        const int t = t0 + lane;
+        const int c = owner_lane(min(t, total - 1), prefix);
+        const int c_prefix = __shfl_sync(0xffffffffu, prefix, c);
+        const int c_slot = __shfl_sync(0xffffffffu, slot, c);
+        if (t < total) {
+            const int k = t - c_prefix;
+            const size_t base = (static_cast<size_t>(c_slot >> 5) * stride) * 32 + (c_slot & 31);
+            const int nb = static_cast<int>(rows[base + static_cast<size_t>(k) * 32]);
+            const int centre = warp * 32 + c;
+            const long long o = out0 + t;
+            double d[3] = {x[nb] - x[centre], y[nb] - y[centre], z[nb] - z[centre]};
+#pragma unroll
+            for (int a = 0; a < 3; ++a) {
+                const double image = -rint(d[a] / g.box[a]);   // lattice shift that brings the neighbour closest
+                shift[3 * o + a] = static_cast<signed char>(image);
+                vec[3 * o + a] = static_cast<float>(d[a] + image * g.box[a]);
+            }
+            src[o] = centre;
+            dst[o] = nb;
+        }
+    }
+}
+
+template <class T>
+bool grow(T*& ptr, size_t& capacity, size_t needed) {
+    if (needed <= capacity) return true;
+    const size_t grown = std::max(needed, capacity + capacity / 2);
+    if (ptr) cudaFree(ptr);
+    ptr = nullptr;
+    capacity = 0;
+    if (cudaMalloc(&ptr, grown * sizeof(T)) != cudaSuccess) return false;
+    capacity = grown;
+    return true;
+}
+
+}  // namespace
+
+struct dsmd_edges {
+    int device = 0;
+    std::string error;
+    unsigned* key[2] = {nullptr, nullptr};  size_t cap_key[2] = {0, 0};
+    int* val[2] = {nullptr, nullptr};       size_t cap_val[2] = {0, 0};
+    int4* pq = nullptr;                     size_t cap_pq = 0;
+    int* slot_of = nullptr;                 size_t cap_slot = 0;
+    int* cell_start = nullptr;              size_t cap_cells = 0;
+    unsigned* rows = nullptr;               size_t cap_rows = 0;
+    int* counts = nullptr;                  size_t cap_counts = 0;
+    long long* offsets = nullptr;           size_t cap_offsets = 0;
+    unsigned char* temp = nullptr;          size_t cap_temp = 0;
+    long long* edges = nullptr;             size_t cap_edges = 0;
+    double* shift = nullptr;                size_t cap_shift = 0;
+    int* c_src = nullptr;                   size_t cap_csrc = 0;
+    int* c_dst = nullptr;                   size_t cap_cdst = 0;
+    signed char* c_shift = nullptr;         size_t cap_cshift = 0;
+    float* c_vec = nullptr;                 size_t cap_cvec = 0;
+    double* bounds = nullptr;               // 6 doubles for the device-side bounding box
+    EdgeStatus* d_status = nullptr;
+    EdgeStatus* h_status = nullptr;
+    int stride = 0;
+    int64_t n_edges = 0;
+    bool have_shift = false;
+    int64_t launches = 0;
+};
+
+namespace {
+
+int efail(dsmd_edges* e, int code, const std::string& what) {
+    e->error = what;
+    return code;
+}
+
+#define EDGE_CUDA(e, call)                                                            \
+    do {                                                                              \
+        cudaError_t err_ = (call);                                                    \
+        if (err_ != cudaSuccess) {                                                    \
+            (e)->error = std::string(#call) + ": " + cudaGetErrorString(err_);        \
+            return DSMD_ERR_CUDA;                                                     \
+        }                                                                             \
+    } while (0)
+
+#define EDGE_ALLOC(e, ok)                                                             \
+    do {                                                                              \
+        if (!(ok)) return efail(e, DSMD_ERR_CUDA, "device allocation failed");        \
+    } while (0)
+
+// Grid over [lo, hi] (non-periodic) or [0, box) (periodic): cells at least cutoff / stencil wide, not more than about
+// two cells per atom (a sparse box must not allocate a huge grid: src/EdgeBuilder.cu:50-61).
+int edge_grid(dsmd_edges* e, Grid& g, const double lo[3], const double hi[3], bool periodic, double cutoff, int64_t n) {
+    double max_scale = 0.0;
+    double len[3];
+    for (int a = 0; a < 3; ++a) {
+        g.box[a] = periodic ? hi[a] : 0.0;
+        if (periodic) {
+            len[a] = hi[a];
+            g.wrap[a] = 1;
+            g.org[a] = 0.0;
+            g.scale[a] = static_cast<float>(len[a] / 4294967296.0);
+            max_scale = std::max(max_scale, len[a] / 4294967296.0);
+        } else {
+            // the upper face belongs to the box: stretch the mapped range by a hair so that hi maps below 1
+            len[a] = std::max(hi[a] - lo[a], cutoff) * (1.0 + 1e-9);
+            g.wrap[a] = 0;
+            g.org[a] = lo[a];
+            g.scale[a] = static_cast<float>(len[a] / 2147483648.0);
+            max_scale = std::max(max_scale, len[a] / 2147483648.0);
+        }
+        g.inv_len[a] = 1.0 / len[a];
+    }
+    const long long max_cells = std::max<long long>(64, 2 * static_cast<long long>(n));
+    bool done = false;
+    for (int stencil = 2; stencil >= 1 && !done; --stencil) {
+        double width = cutoff / stencil * (1.0 + 1e-6);
+        for (int tries = 0; tries < 64; ++tries) {
+            long long cells = 1;
+            bool ok = true;
+            for (int a = 0; a < 3; ++a) {
+                int nc = std::max(1, static_cast<int>(std::floor(len[a] / width)));
+                nc = std::min(nc, 1024);
+                if (periodic && nc < 2 * stencil + 1) ok = false;
+                g.nc[a] = nc;
+                cells *= nc;
+            }
+            if (!ok) break;                       // box too small for this stencil: try the wider cells
+            if (cells <= max_cells || stencil == 1) {
+                if (cells > max_cells) { width *= 1.26; continue; }
+                g.stencil = stencil;
+                g.ncells = static_cast<int>(cells);
+                done = true;
+                break;
+            }
+            break;                                // too many half-width cells: fall back to full-width cells
+        }
+    }
+    if (!done) return efail(e, DSMD_ERR_BOX_TOO_SMALL, "periodic box shorter than three cells of width cutoff");
+    g.r2_list = static_cast<float>(cutoff * cutoff);
+    g.r2_list_d = cutoff * cutoff;
+    g.band = static_cast<float>(8.0 * cutoff * max_scale + 16.0 * cutoff * cutoff * 5.9604645e-8);
+    return DSMD_OK;
+}
+
+// bin, sort, gather, search (with row-overflow retry), scan; leaves the edge count in h_status.
+template <bool PERIODIC>
+int edge_search(dsmd_edges* e, const Grid& g, const double* d_x, const double* d_y, const double* d_z, int64_t n,
+                int64_t n_centers, const int* d_owner, const unsigned char* d_ok, int row, double density_hint,
+                cudaStream_t s) {
+    const size_t un = static_cast<size_t>(n);
+    for (int k = 0; k < 2; ++k) {
+        EDGE_ALLOC(e, grow(e->key[k], e->cap_key[k], un));
+        EDGE_ALLOC(e, grow(e->val[k], e->cap_val[k], un));
+    }
+    EDGE_ALLOC(e, grow(e->pq, e->cap_pq, un));
+    EDGE_ALLOC(e, grow(e->slot_of, e->cap_slot, un));
+    EDGE_ALLOC(e, grow(e->cell_start, e->cap_cells, static_cast<size_t>(g.ncells) + 1));
+    EDGE_ALLOC(e, grow(e->counts, e->cap_counts, un));
+    EDGE_ALLOC(e, grow(e->offsets, e->cap_offsets, un));
+    int bits = 1;
+    while ((1ll << bits) < g.ncells) ++bits;
+    size_t sort_bytes = 0, scan_bytes = 0;
+    cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, e->key[0], e->key[1], e->val[0], e->val[1], static_cast<int>(n),
+                                    0, bits, s);
+    cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, e->counts, e->offsets, static_cast<int>(n), s);
+    EDGE_ALLOC(e, grow(e->temp, e->cap_temp, std::max(sort_bytes, scan_bytes)));
+
+    EDGE_CUDA(e, cudaMemsetAsync(e->d_status, 0, sizeof(EdgeStatus), s));
+    k_edge_keys<<<blocks_for(n, kThreads), kThreads, 0, s>>>(g, static_cast<int>(n), d_x, d_y, d_z, e->key[0], e->val[0],
+                                                            e->d_status);
+    EDGE_CUDA(e, cub::DeviceRadixSort::SortPairs(e->temp, sort_bytes, e->key[0], e->key[1], e->val[0], e->val[1],
+                                                 static_cast<int>(n), 0, bits, s));
+    k_edge_gather<<<blocks_for(n, kThreads), kThreads, 0, s>>>(g, static_cast<int>(n), e->key[1], e->val[1], d_x, d_y,
+                                                              d_z, e->pq, e->slot_of, e->cell_start);
+    e->launches += 2;
+    if (e->stride == 0) {
+        const double expect = density_hint * 4.18879020479 * g.r2_list_d * std::sqrt(g.r2_list_d);
+        e->stride = (std::max(16, static_cast<int>(expect * 1.5) + 16) + 3) & ~3;
+    }
+    for (int attempt = 0; attempt < 5; ++attempt) {
+        const size_t slices = (un + 31) / 32;
+        EDGE_ALLOC(e, grow(e->rows, e->cap_rows, slices * static_cast<size_t>(e->stride) * 32));
+        SearchArgs a{static_cast<int>(n), static_cast<int>(n_centers), e->stride, row, e->pq, d_x, d_y, d_z,
+                     e->cell_start, d_owner, d_ok, e->rows, e->counts, e->d_status};
+        k_edge_search<PERIODIC><<<blocks_for(n, kSearchThreads), kSearchThreads, 0, s>>>(g, a);
+        ++e->launches;
+        EDGE_CUDA(e, cub::DeviceScan::ExclusiveSum(e->temp, scan_bytes, e->counts, e->offsets, static_cast<int>(n), s));
+        k_edge_total<<<1, 1, 0, s>>>(static_cast<int>(n), e->offsets, e->counts, e->d_status);
+        ++e->launches;
+        EDGE_CUDA(e, cudaGetLastError());
+        // the one synchronisation of a build that does not overflow: edge count, bounds flag, row overflow
+        EDGE_CUDA(e, cudaMemcpyAsync(e->h_status, e->d_status, sizeof(EdgeStatus), cudaMemcpyDeviceToHost, s));
+        EDGE_CUDA(e, cudaStreamSynchronize(s));
+        if (e->h_status->out_of_bounds)
+            return efail(e, DSMD_ERR_OUT_OF_DOMAIN, "an atom lies outside the given box (or has a NaN position)");
+        if (e->h_status->need_stride <= static_cast<unsigned>(e->stride)) return DSMD_OK;
+        e->stride = (static_cast<int>(e->h_status->need_stride * 1.2) + 8 + 3) & ~3;
+        EDGE_CUDA(e, cudaMemsetAsync(e->d_status, 0, sizeof(EdgeStatus), s));
+    }
+    return efail(e, DSMD_ERR_CAPACITY, "edge rows kept overflowing");
+}
+
+}  // namespace
+
+extern "C" {
+
+int dsmd_edges_create(int device, dsmd_edges** out) {
+    if (!out) return DSMD_ERR_INVALID;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return DSMD_ERR_CUDA;
+    dsmd_edges* e = new dsmd_edges();
+    e->device = device;
+    *out = e;
+    EDGE_CUDA(e, cudaSetDevice(device));
+    EDGE_CUDA(e, cudaMalloc(&e->d_status, sizeof(EdgeStatus)));
+    EDGE_CUDA(e, cudaMallocHost(&e->h_status, sizeof(EdgeStatus)));
+    EDGE_CUDA(e, cudaMalloc(&e->bounds, sizeof(double) * 6));
+    return DSMD_OK;
+}
+
+void dsmd_edges_destroy(dsmd_edges* e) {
+    if (!e) return;
+    cudaSetDevice(e->device);
+    for (int k = 0; k < 2; ++k) { cudaFree(e->key[k]); cudaFree(e->val[k]); }
+    cudaFree(e->pq); cudaFree(e->slot_of); cudaFree(e->cell_start); cudaFree(e->rows); cudaFree(e->counts);
+    cudaFree(e->offsets); cudaFree(e->temp); cudaFree(e->edges); cudaFree(e->shift); cudaFree(e->c_src);
+    cudaFree(e->c_dst); cudaFree(e->c_shift); cudaFree(e->c_vec); cudaFree(e->bounds); cudaFree(e->d_status);
+    cudaFreeHost(e->h_status);
+    delete e;
+}
+
+const char* dsmd_edges_last_error(const dsmd_edges* e) { return e ? e->error.c_str() : "null edge builder"; }
+
+int dsmd_edges_build(dsmd_edges* e, const double* d_x, const double* d_y, const double* d_z, int64_t n, double cutoff,
+                     const double* lo, const double* hi, int64_t n_centers, const int32_t* d_owner,
+                     const double* d_shift_x, const double* d_shift_y, const double* d_shift_z,
+                     const unsigned char* d_receiver_ok, int row, int64_t* n_edges, void* stream) {
+    if (!e || !n_edges) return DSMD_ERR_INVALID;
+    *n_edges = 0;
+    e->n_edges = 0;
+    e->have_shift = false;
+    if (!(cutoff > 0.0)) return efail(e, DSMD_ERR_INVALID, "cutoff must be positive");
+    if (n < 0 || n >= std::numeric_limits<int32_t>::max() / 2) return efail(e, DSMD_ERR_INVALID, "atom count out of range");
+    const bool images = d_owner != nullptr;
+    if (images && (n_centers < 0 || n_centers > n || !d_shift_x || !d_shift_y || !d_shift_z))
+        return efail(e, DSMD_ERR_INVALID, "invalid periodic image description");
+    if (!images) n_centers = n;
+    if (d_receiver_ok && row != 0 && row != 1) return efail(e, DSMD_ERR_INVALID, "invalid prune description");
+    if (n <= 1) return DSMD_OK;
+    if (!d_x || !d_y || !d_z) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EDGE_CUDA(e, cudaSetDevice(e->device));
+
+    double box_lo[3], box_hi[3];
+    if (lo && hi) {
+        for (int a = 0; a < 3; ++a) { box_lo[a] = lo[a]; box_hi[a] = hi[a]; }
+    } else {   // bounding box on the device: one extra synchronisation
+        const double* axes[3] = {d_x, d_y, d_z};
+        size_t need = 0;
+        cub::DeviceReduce::Min(nullptr, need, d_x, e->bounds, static_cast<int>(n), s);
+        EDGE_ALLOC(e, grow(e->temp, e->cap_temp, need));
+        for (int a = 0; a < 3; ++a) {
+            EDGE_CUDA(e, cub::DeviceReduce::Min(e->temp, need, axes[a], e->bounds + a, static_cast<int>(n), s));
+            EDGE_CUDA(e, cub::DeviceReduce::Max(e->temp, need, axes[a], e->bounds + 3 + a, static_cast<int>(n), s));
+        }
+        double h[6];
+        EDGE_CUDA(e, cudaMemcpyAsync(h, e->bounds, sizeof(h), cudaMemcpyDeviceToHost, s));
+        EDGE_CUDA(e, cudaStreamSynchronize(s));
+        for (int a = 0; a < 3; ++a) { box_lo[a] = h[a]; box_hi[a] = h[3 + a]; }
+    }
+    for (int a = 0; a < 3; ++a)
+        if (!(box_lo[a] <= box_hi[a]) || !std::isfinite(box_lo[a]) || !std::isfinite(box_hi[a]))
+            return efail(e, DSMD_ERR_OUT_OF_DOMAIN, "invalid box or a non-finite position");
+
+    Grid g{};
+    { const int rc = edge_grid(e, g, box_lo, box_hi, false, cutoff, n); if (rc) return rc; }
+    double volume = 1.0;
+    for (int a = 0; a < 3; ++a) volume *= 1.0 / g.inv_len[a];
+    { const int rc = edge_search<false>(e, g, d_x, d_y, d_z, n, n_centers, d_owner, d_receiver_ok, row,
+                                        static_cast<double>(n) / volume, s); if (rc) return rc; }
+    const int64_t E = e->h_status->edges;
+    e->n_edges = E;
+    *n_edges = E;
+    if (E == 0) return DSMD_OK;
+    EDGE_ALLOC(e, grow(e->edges, e->cap_edges, 2 * static_cast<size_t>(E)));
+    if (images) EDGE_ALLOC(e, grow(e->shift, e->cap_shift, 3 * static_cast<size_t>(E)));
+    k_edge_fill<<<blocks_for(n, kThreads), kThreads, 0, s>>>(static_cast<int>(n), E, e->stride, e->pq, e->rows, e->counts,
+                                                            e->offsets, d_owner, d_shift_x, d_shift_y, d_shift_z,
+                                                            e->edges, images ? e->shift : nullptr);
+    ++e->launches;
+    EDGE_CUDA(e, cudaGetLastError());
+    e->have_shift = images;
+    return DSMD_OK;
+}
+
+int dsmd_edges_result(const dsmd_edges* e, const int64_t** d_edge_index, const double** d_edge_shift, int64_t* n_edges) {
+    if (!e) return DSMD_ERR_INVALID;
+    if (d_edge_index) *d_edge_index = reinterpret_cast<const int64_t*>(e->edges);
+    if (d_edge_shift) *d_edge_shift = e->have_shift ? e->shift : nullptr;
+    if (n_edges) *n_edges = e->n_edges;
+    return DSMD_OK;
+}
+
+int dsmd_edges_build_periodic(dsmd_edges* e, const double* d_x, const double* d_y, const double* d_z, int64_t n,
+                              const double box[3], double cutoff, int64_t* n_edges, void* stream) {
+    if (!e || !n_edges || !box) return DSMD_ERR_INVALID;
+    *n_edges = 0;
+    e->n_edges = 0;
+    if (!(cutoff > 0.0)) return efail(e, DSMD_ERR_INVALID, "cutoff must be positive");
+    if (n < 0 || n >= std::numeric_limits<int32_t>::max() / 2) return efail(e, DSMD_ERR_INVALID, "atom count out of range");
+    for (int a = 0; a < 3; ++a)
+        if (!(box[a] > 2.0 * cutoff)) return efail(e, DSMD_ERR_BOX_TOO_SMALL, "box must be longer than two cutoffs");
+    if (n <= 1) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EDGE_CUDA(e, cudaSetDevice(e->device));
+    Grid g{};
+    const double zero[3] = {0.0, 0.0, 0.0};
+    { const int rc = edge_grid(e, g, zero, box, true, cutoff, n); if (rc) return rc; }
+    const double volume = box[0] * box[1] * box[2];
+    { const int rc = edge_search<true>(e, g, d_x, d_y, d_z, n, n, nullptr, nullptr, 1, static_cast<double>(n) / volume, s);
+      if (rc) return rc; }
+    const int64_t E = e->h_status->edges;
+    e->n_edges = E;
+    *n_edges = E;
+    if (E == 0) return DSMD_OK;
+    EDGE_ALLOC(e, grow(e->c_src, e->cap_csrc, static_cast<size_t>(E)));
+    EDGE_ALLOC(e, grow(e->c_dst, e->cap_cdst, static_cast<size_t>(E)));
+    EDGE_ALLOC(e, grow(e->c_shift, e->cap_cshift, 3 * static_cast<size_t>(E)));
+    EDGE_ALLOC(e, grow(e->c_vec, e->cap_cvec, 3 * static_cast<size_t>(E)));
+    k_edge_fill_compact<<<blocks_for(n, kThreads), kThreads, 0, s>>>(g, static_cast<int>(n), e->stride, e->slot_of,
+                                                                    e->rows, e->counts, e->offsets, d_x, d_y, d_z,
+                                                                    e->c_src, e->c_dst, e->c_shift, e->c_vec);
+    ++e->launches;
+    EDGE_CUDA(e, cudaGetLastError());
+    return DSMD_OK;
+}
+
+int dsmd_edges_result_compact(const dsmd_edges* e, const int32_t** d_src, const int32_t** d_dst, const int8_t** d_shift,
+                              const float** d_vec, int64_t* n_edges) {
+    if (!e) return DSMD_ERR_INVALID;
+    if (d_src) *d_src = e->c_src;
+    if (d_dst) *d_dst = e->c_dst;
+    if (d_shift) *d_shift = reinterpret_cast<const int8_t*>(e->c_shift);
+    if (d_vec) *d_vec = e->c_vec;
+    if (n_edges) *n_edges = e->n_edges;
+    return DSMD_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,201 @@
+"""Seeded synthetic systems with the shapes, sizes and value distributions of the benchmark configurations.
+
+Everything is generated from a seed with numpy; no external dataset is read. Units: the LJ systems are in reduced units
+(sigma = epsilon = mass = 1); the water and radius-graph systems are in Angstrom / kcal/mol / e.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+
+@dataclass
+class System:
+    """Host-side description of one input: positions and parameters in the caller's atom order."""
+    name: str
+    pos: np.ndarray                      # [N, 3] float64
+    box: np.ndarray                      # [3]
+    types: np.ndarray                    # [N] int32
+    charge: np.ndarray                   # [N] float64
+    mass: np.ndarray                     # [N] float64
+    eps: np.ndarray                      # [nt, nt] pair epsilon
+    sig: np.ndarray                      # [nt, nt] pair sigma
+    cutoff: float
+    skin: float
+    vel: np.ndarray | None = None        # [N, 3]
+    exclusions: np.ndarray | None = None  # [X, 2] global ids
+    coulomb: bool = False
+    dt: float = 0.005
+    force_to_accel: float = 1.0          # 4.184e-4 in the reference's real units, 1 in reduced units
+    meta: dict = field(default_factory=dict)
+
+    @property
+    def n(self) -> int:
+        return len(self.pos)
+
+
+def lorentz_berthelot(eps_t, sig_t):
+    eps_t = np.asarray(eps_t, dtype=np.float64)
+    sig_t = np.asarray(sig_t, dtype=np.float64)
+    return np.sqrt(np.outer(eps_t, eps_t)), 0.5 * (sig_t[:, None] + sig_t[None, :])
+
+
+def maxwell_boltzmann(n, temperature, mass, rng, kb=1.0):
+    """Velocities N(0, sqrt(kT/m)), zero net momentum, rescaled to the exact temperature with 3N - 3 degrees of freedom."""
+    v = rng.standard_normal((n, 3)) * np.sqrt(kb * temperature / mass)[:, None]
+    v -= (v * mass[:, None]).sum(0) / mass.sum()
+    ke2 = (mass[:, None] * v * v).sum()
+    t_now = ke2 / (kb * (3 * n - 3))
+    return v * np.sqrt(temperature / t_now)
+
+
+def fcc_lj(cells: int, *, density=0.8442, temperature=1.44, jitter=0.05, cutoff=2.5, skin=0.3, seed=12345) -> System:
+    """Single-species LJ fluid started from an FCC lattice of cells^3 unit cells (4 atoms each) with a small seeded
+    jitter (a perfect lattice has many exactly degenerate distances). cells=20 -> 32,000 atoms, cells=100 -> 4,000,000."""
+    rng = np.random.default_rng(seed)
+    a = (4.0 / density) ** (1.0 / 3.0)
+    g = np.arange(cells, dtype=np.float64)
+    cell = np.stack(np.meshgrid(g, g, g, indexing="ij"), axis=-1).reshape(-1, 1, 3)
+    basis = np.array([[0.0, 0.0, 0.0], [0.5, 0.5, 0.0], [0.5, 0.0, 0.5], [0.0, 0.5, 0.5]])
+    pos = ((cell + basis[None]) * a).reshape(-1, 3) + 0.25 * a
+    n = len(pos)
+    pos += rng.uniform(-jitter, jitter, pos.shape)
+    box = np.full(3, cells * a)
+    pos %= box
+    mass = np.ones(n)
+    vel = maxwell_boltzmann(n, temperature, mass, rng)
+    return System(name=f"lj_fcc_{n}", pos=pos, box=box, types=np.zeros(n, dtype=np.int32), charge=np.zeros(n),
+                  mass=mass, eps=np.ones((1, 1)), sig=np.ones((1, 1)), cutoff=cutoff, skin=skin, vel=vel,
+                  meta=dict(seed=seed, cells=cells, density=density, temperature=temperature))
+
+
+def kob_andersen(n_target=1_048_576, *, density=1.2, temperature=0.8, cutoff=2.5, skin=0.3, seed=777) -> System:
+    """80:20 binary LJ mixture. Atoms sit on a seeded random subset of a jittered simple-cubic lattice (uniformly random
+    placement at this density overlaps and gives infinite forces), types are shuffled."""
+    rng = np.random.default_rng(seed)
+    m = int(np.ceil(n_target ** (1.0 / 3.0)))
+    while m ** 3 < n_target:
+        m += 1
+    L = (n_target / density) ** (1.0 / 3.0)
+    a = L / m
+    sites = rng.permutation(m ** 3)[:n_target]
+    sites.sort()
+    ix, iy, iz = np.unravel_index(sites, (m, m, m))
+    pos = (np.stack([ix, iy, iz], axis=1) + 0.5) * a
+    pos += rng.uniform(-0.12, 0.12, pos.shape)
+    box = np.full(3, L)
+    pos %= box
+    types = np.zeros(n_target, dtype=np.int32)
+    types[rng.permutation(n_target)[: n_target // 5]] = 1
+    eps = np.array([[1.0, 1.5], [1.5, 0.5]])
+    sig = np.array([[1.0, 0.8], [0.8, 0.88]])
+    mass = np.ones(n_target)
+    vel = maxwell_boltzmann(n_target, temperature, mass, rng)
+    return System(name=f"kob_andersen_{n_target}", pos=pos, box=box, types=types, charge=np.zeros(n_target), mass=mass,
+                  eps=eps, sig=sig, cutoff=cutoff, skin=skin, vel=vel, meta=dict(seed=seed, density=density))
+
+
+def _random_rotations(n, rng):
+    q = rng.standard_normal((n, 4))
+    q /= np.linalg.norm(q, axis=1, keepdims=True)
+    w, x, y, z = q.T
+    return np.stack([
+        np.stack([1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (x * z + y * w)], axis=1),
+        np.stack([2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w)], axis=1),
+        np.stack([2 * (x * z - y * w), 2 * (y * z + x * w), 1 - 2 * (x * x + y * y)], axis=1)], axis=1)
+
+
+def water_box(cells: int = 60, *, cutoff=10.0, skin=2.0, seed=4242) -> System:
+    """Rigid three-site water geometry (O-H 1.0 A, H-O-H 109.47 deg, charges -0.8476 / +0.4238 e) with seeded random
+    orientations on a jittered cubic lattice at 1.0 g/cm^3; LJ on O-O only; O-H and H-H of a molecule are excluded.
+    cells=60 -> 216,000 molecules, 648,000 atoms. Atom order: O, H, H per molecule."""
+    rng = np.random.default_rng(seed)
+    spacing = (18.01528 / 6.02214076e23 / 1.0e-24) ** (1.0 / 3.0)   # cube root of the volume per molecule in A^3
+    nm = cells ** 3
+    g = np.arange(cells, dtype=np.float64)
+    centre = (np.stack(np.meshgrid(g, g, g, indexing="ij"), axis=-1).reshape(-1, 3) + 0.5) * spacing
+    centre += rng.uniform(-0.3, 0.3, centre.shape)
+    half = np.deg2rad(109.47) / 2.0
+    local = np.array([[0.0, 0.0, 0.0], [np.sin(half), 0.0, np.cos(half)], [-np.sin(half), 0.0, np.cos(half)]])
+    rot = _random_rotations(nm, rng)
+    pos = (centre[:, None, :] + np.einsum("mij,aj->mai", rot, local)).reshape(-1, 3)
+    box = np.full(3, cells * spacing)
+    n = 3 * nm
+    types = np.tile(np.array([0, 1, 1], dtype=np.int32), nm)
+    charge = np.tile(np.array([-0.8476, 0.4238, 0.4238]), nm)
+    mass = np.tile(np.array([15.9994, 1.008, 1.008]), nm)
+    eps = np.array([[0.1553, 0.0], [0.0, 0.0]])
+    sig = np.array([[3.166, 1.583], [1.583, 0.0]])
+    o = 3 * np.arange(nm, dtype=np.int32)
+    excl = np.concatenate([np.stack([o, o + 1], 1), np.stack([o, o + 2], 1), np.stack([o + 1, o + 2], 1)])
+    kb = 0.0019872041
+    vel = maxwell_boltzmann(n, 300.0, mass, rng, kb=kb / (48.88821291 ** 2))
+    return System(name=f"water_{n}", pos=pos, box=box, types=types, charge=charge, mass=mass, eps=eps, sig=sig,
+                  cutoff=cutoff, skin=skin, vel=vel, exclusions=excl, coulomb=True, dt=2.0, force_to_accel=4.184e-4,
+                  meta=dict(seed=seed, molecules=nm))
+
+
+def disordered_solid(n_target=1_000_000, *, density=0.05, min_dist=1.8, cutoff=5.0, seed=99) -> System:
+    """Three-species disordered periodic solid for the radius-graph build: uniform random positions with a minimum
+    distance (seeded rejection: points that sit too close to an earlier point are re-drawn until none is left)."""
+    from scipy.spatial import cKDTree
+    rng = np.random.default_rng(seed)
+    L = (n_target / density) ** (1.0 / 3.0)
+    pos = rng.uniform(0.0, L, (n_target, 3))
+    for _ in range(200):
+        tree = cKDTree(pos, boxsize=L)
+        close = tree.query_pairs(min_dist, output_type="ndarray")
+        if len(close) == 0:
+            break
+        bad = np.unique(close[:, 1])          # the later atom of each close pair is re-drawn
+        pos[bad] = rng.uniform(0.0, L, (len(bad), 3))
+    else:
+        raise RuntimeError("minimum-distance rejection did not converge")
+    types = rng.choice(3, size=n_target, p=[0.5, 0.3, 0.2]).astype(np.int32)
+    return System(name=f"solid_{n_target}", pos=pos, box=np.full(3, L), types=types, charge=np.zeros(n_target),
+                  mass=np.ones(n_target), eps=np.ones((3, 3)), sig=np.ones((3, 3)), cutoff=cutoff, skin=0.0,
+                  meta=dict(seed=seed, density=density, min_dist=min_dist))
+
+
+def brick_decompose(pos, box, dims, halo):
+    """Host-side spatial decomposition used by tests and the benchmark set-up: for every brick of a dims grid over the
+    periodic box, the indices of its owned atoms and (source index, image shift) of its ghost atoms - every periodic
+    image of an atom that lies within `halo` of the brick on the split axes (edges and corners included)."""
+    pos = np.asarray(pos, dtype=np.float64)
+    box = np.asarray(box, dtype=np.float64)
+    dims = np.asarray(dims, dtype=np.int64)
+    wrapped = pos - box * np.floor(pos / box)
+    cell = np.minimum((wrapped / box * dims).astype(np.int64), dims - 1)
+    out = []
+    for cx in range(dims[0]):
+        for cy in range(dims[1]):
+            for cz in range(dims[2]):
+                c = np.array([cx, cy, cz])
+                lo = box * c / dims
+                hi = box * (c + 1) / dims
+                owned = np.nonzero((cell == c).all(1))[0]
+                src_all, img_all = [], []
+                ranges = [(-1, 0, 1) if dims[a] > 1 else (0,) for a in range(3)]
+                for sx in ranges[0]:
+                    for sy in ranges[1]:
+                        for sz in ranges[2]:
+                            s = np.array([sx, sy, sz])
+                            q = wrapped + s * box
+                            inside = np.ones(len(pos), dtype=bool)
+                            brick = np.ones(len(pos), dtype=bool)
+                            for a in range(3):
+                                if dims[a] == 1:
+                                    continue
+                                inside &= (q[:, a] >= lo[a] - halo) & (q[:, a] < hi[a] + halo)
+                                brick &= (q[:, a] >= lo[a]) & (q[:, a] < hi[a])
+                            if sx == 0 and sy == 0 and sz == 0:
+                                inside &= ~brick
+                            idx = np.nonzero(inside)[0]
+                            src_all.append(idx)
+                            img_all.append(np.tile(s, (len(idx), 1)))
+                src = np.concatenate(src_all)
+                img = np.concatenate(img_all)
+                key = np.lexsort((img[:, 2], img[:, 1], img[:, 0], src))
+                out.append(dict(coords=c, lo=lo, hi=hi, owned=owned, ghost_src=src[key], ghost_image=img[key]))
+    return out

@@ -1,0 +1,228 @@
+/* dsmd_b200.h - C ABI of the B200 (sm_100a) short-range nonbonded path.
+ *
+ * One opaque context per GPU. Every entry point returns an int status (DSMD_OK = 0) and never exits or throws;
+ * dsmd_last_error() gives the text of the last failure. All device work is queued on the caller's stream
+ * (a cudaStream_t passed as void*); entry points that return a value to the host synchronise that stream once,
+ * and say so. A context is used from one host thread at a time.
+ *
+ * The reference has no C plugin interface: its seams are C++ abstract classes (ForceCalculator, NeighborList,
+ * HaloBackend, CommBackend, EdgeBuilder). Each entry point below names the reference member it stands behind;
+ * include/dsmd/ *.hpp holds C++ adapters with the reference's own class shapes that call only this ABI.
+ */
+#ifndef DSMD_B200_H
+#define DSMD_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct dsmd_ctx dsmd_ctx;
+
+enum {
+    DSMD_OK = 0,
+    DSMD_ERR_INVALID = 1,        /* bad argument */
+    DSMD_ERR_CUDA = 2,           /* a CUDA runtime call failed */
+    DSMD_ERR_BOX_TOO_SMALL = 3,  /* a periodic axis is shorter than the cell grid needs (reference: "returns nulls",
+                                    src/neighbor_list_kernels.cu:596-617) */
+    DSMD_ERR_OUT_OF_DOMAIN = 4,  /* an atom lies outside the subdomain + halo on a non-wrapping axis, or is NaN
+                                    (reference: EdgeBuilder throws, src/EdgeBuilder.cu:319-321) */
+    DSMD_ERR_CAPACITY = 5,       /* more atoms than the context was created for */
+    DSMD_ERR_STATE = 6,          /* call order: e.g. forces before a list exists */
+    DSMD_ERR_TIMEOUT = 7         /* a bounded device-side wait ran out */
+};
+
+/* phases of a force evaluation (reference: ForceCalculatorCUDA::run_force_phase, src/force_calculator_cuda.cu:5260) */
+enum { DSMD_PHASE_FULL = 0, DSMD_PHASE_INTERIOR = 1, DSMD_PHASE_BOUNDARY = 2 };
+
+/* per-atom device arrays (reference: ForceCalculatorCUDA::get_device_*, include/force_calculator_cuda.h:142-183) */
+enum {
+    DSMD_X = 0, DSMD_Y, DSMD_Z, DSMD_VX, DSMD_VY, DSMD_VZ, DSMD_FX, DSMD_FY, DSMD_FZ, DSMD_MASS, DSMD_CHARGE,
+    DSMD_TYPE, DSMD_GLOBAL_ID, DSMD_FIELD_COUNT
+};
+
+/* -- life cycle ---------------------------------------------------------------------------------------------------- */
+
+/* ForceCalculatorCUDA::initialize / finalize (include/force_calculator_cuda.h:38-40). capacity = most atoms
+ * (owned + ghost) the context will ever hold. Allocates the particle arrays; list storage is sized at the first build. */
+int dsmd_create(int device, int64_t capacity, dsmd_ctx** out);
+void dsmd_destroy(dsmd_ctx* ctx);
+const char* dsmd_last_error(const dsmd_ctx* ctx);
+
+/* -- set-up --------------------------------------------------------------------------------------------------------- */
+
+/* SimulationBox (include/md_types.h:29-37): orthorhombic box lengths, periodic flags and this rank's subdomain
+ * [lo, hi]. lo[a] == hi[a] means the whole box length on that axis. An axis whose subdomain is narrower than the box is
+ * "split": its ghosts arrive image-shifted through the halo exchange and the axis does not wrap; halo = how far ghosts
+ * may sit outside [lo, hi] on a split axis. */
+int dsmd_set_box(dsmd_ctx* ctx, const double box[3], const int periodic[3], const double lo[3], const double hi[3],
+                 double halo);
+
+/* ForceFieldParams mixing tables + cutoff_distance / verlet_skin / lj_switch_distance
+ * (include/md_types.h:98-136, src/force_calculator_cuda.cu:4337-4377). eps, sig: full [ntypes x ntypes] matrices.
+ * switch_distance <= 0: plain truncation. */
+int dsmd_set_pair_params(dsmd_ctx* ctx, int ntypes, const double* eps, const double* sig, double cutoff, double skin,
+                         double switch_distance);
+
+/* Real-space Ewald on/off (force_calculation.type "PME"); alpha <= 0 derives it from erfc(alpha rc) = 1e-5 as
+ * src/force_calculator_cuda.cu:6821-6828 does. Builds the float-bit indexed cubic table (include/ewald_real_table.h). */
+int dsmd_set_coulomb(dsmd_ctx* ctx, int enabled, double alpha);
+int dsmd_get_ewald_alpha(const dsmd_ctx* ctx, double* alpha);
+
+/* Exclusion pairs by global id (Topology::get_exclusion_keys -> exclusion CSR upload,
+ * src/force_calculator_cuda.cu:4379-4423). n_global = atoms in the whole system. */
+int dsmd_set_exclusions(dsmd_ctx* ctx, int64_t n_global, int64_t n_pairs, const int32_t* a, const int32_t* b);
+
+/* -- particle storage ----------------------------------------------------------------------------------------------- */
+
+/* ForceCalculatorCUDA::initial_upload_to_device (src/force_calculator_cuda.cu:4281): host arrays, owned atoms first
+ * then ghosts. vx..vz, charge, type, gid may be NULL (zeros / 0 / 0..n-1). Asynchronous on `stream` for pinned memory. */
+int dsmd_upload(dsmd_ctx* ctx, int64_t n_owned, int64_t n_total, const double* x, const double* y, const double* z,
+                const double* vx, const double* vy, const double* vz, const double* mass, const double* charge,
+                const int32_t* type, const int32_t* gid, void* stream);
+
+/* Positions only, in the context's current atom order (the order of DSMD_GLOBAL_ID). */
+int dsmd_upload_positions(dsmd_ctx* ctx, const double* x, const double* y, const double* z, void* stream);
+
+/* ForceCalculatorCUDA::download_from_device: copies one field of the first n atoms to host memory in the context's
+ * current atom order; doubles for every field but DSMD_TYPE / DSMD_GLOBAL_ID (int32). Synchronises `stream`. */
+int dsmd_download(dsmd_ctx* ctx, int field, int64_t n, void* host_out, void* stream);
+
+/* get_device_x() ... get_device_global_id(): the device array itself. The context sorts its atoms by cell at every
+ * list build (owned atoms stay in [0, n_owned), ghosts behind them), so positions in these arrays change then;
+ * DSMD_GLOBAL_ID identifies the atoms. */
+int dsmd_device_pointer(dsmd_ctx* ctx, int field, void** out);
+int dsmd_counts(const dsmd_ctx* ctx, int64_t* n_owned, int64_t* n_total);
+
+/* ParticleInfo::Provider::resize_particle_info (src/force_calculator_cuda.cu:4143-4216): sets the owned / total counts
+ * after the caller wrote atoms into the device arrays itself (halo exchange, migration). */
+int dsmd_set_counts(dsmd_ctx* ctx, int64_t n_owned, int64_t n_total);
+
+/* -- neighbour list -------------------------------------------------------------------------------------------------- */
+
+/* ForceCalculatorCUDA::build_neighbor_list_on_device (src/force_calculator_cuda.cu:4604) = launch_cuda_tile_list_build
+ * (src/neighbor_list_kernels.cu:554) + build_tile_lists_on_device (:4817): bins the atoms into cells, sorts them by
+ * cell (owned and ghost segments separately), reorders every particle array, converts positions to the fixed-point
+ * layout and builds the per-atom Verlet list with skin. Takes the current positions as the displacement reference
+ * (update_reference_positions_on_device). Synchronises `stream` once to read the build status. */
+int dsmd_build_neighbor_list(dsmd_ctx* ctx, void* stream);
+
+/* The same, split for the multi-GPU rebuild step: sort only the owned atoms (before the halo plan is made), so that
+ * their slots stay fixed when the ghosts arrive. */
+int dsmd_sort_owned(dsmd_ctx* ctx, void* stream);
+
+/* After a build: ghost_slot[k] = the slot, in the sorted arrays, of the k-th ghost as it was handed in (device int32
+ * array of n_total - n_owned entries). The halo refresh unpacks through it. */
+int dsmd_ghost_slots(dsmd_ctx* ctx, const int32_t** device_ghost_slot);
+
+/* List statistics of the last build. pairs_listed counts directed entries (each owned-owned pair twice). */
+int dsmd_list_stats(dsmd_ctx* ctx, int64_t* directed_entries, int64_t* interior_entries, int32_t* row_stride,
+                    int32_t* cells, int32_t* rechecked_fp64);
+
+/* Writes the list as directed (i, j) slot pairs into device int32 arrays of `capacity` entries each (test and parity
+ * hook; the reference's counterpart is NeighborList::get_neighbors / get_offsets, include/neighbor_list.h:37-39).
+ * flags[k] bit 0 = excluded pair. Returns the count in *n_pairs. Synchronises. */
+int dsmd_list_export(dsmd_ctx* ctx, int32_t* device_i, int32_t* device_j, uint8_t* device_flags, int64_t capacity,
+                     int64_t* n_pairs, void* stream);
+
+/* -- per-step work ---------------------------------------------------------------------------------------------------- */
+
+/* nlist_pack_slots_kernel (src/force_calculator_cuda.cu:1168) fused with compute_max_displacement_kernel (:6637):
+ * converts the current double positions of atoms [first, first + count) to the fixed-point layout the pair kernel
+ * reads and folds max |r - r_ref|^2 of the owned ones into the displacement word. */
+int dsmd_pack_positions(dsmd_ctx* ctx, int64_t first, int64_t count, void* stream);
+
+/* compute_max_displacement_on_device (:6689): max displacement^2 since the last build as of the last pack.
+ * Synchronises `stream`. */
+int dsmd_max_displacement_sq(dsmd_ctx* ctx, double* out, void* stream);
+
+/* ForceCalculator::compute_forces / begin_forces_interior / finish_forces_boundary (include/force_calculator.h:24,
+ * include/force_calculator_cuda.h:160-170): LJ (+ real-space Ewald) over the list. FULL and INTERIOR overwrite the
+ * force arrays of the owned atoms (the reference clears, then adds); BOUNDARY adds the ghost-partner part.
+ * want_energy != 0 also accumulates potential energy and virial (scalar + diagonal) in fp64. */
+int dsmd_compute_forces(dsmd_ctx* ctx, int phase, int want_energy, void* stream);
+
+/* get_potential_energy / get_virial / get_virial_diag (include/force_calculator.h:41-68): this rank's sums of the last
+ * evaluation with want_energy (an owned-ghost pair counts half on each rank). out = {PE, W, Wxx, Wyy, Wzz}.
+ * Synchronises `stream`. */
+int dsmd_read_scalars(dsmd_ctx* ctx, double out[5], void* stream);
+
+/* Velocity Verlet halves (launch_vv_step1_kernel / launch_vv_step2_kernel, src/integrator_kernels.cu:149-208):
+ * half 1: v += dt/2 f/m c; x += dt v (and packs positions, see dsmd_pack_positions); half 2: v += dt/2 f/m c. */
+int dsmd_integrate(dsmd_ctx* ctx, int half, double dt, double force_to_accel, void* stream);
+
+/* calculate_kinetic_energy (include/force_calculator.h:70): sum 1/2 m v^2 over owned atoms, raw units. Synchronises. */
+int dsmd_kinetic_energy(dsmd_ctx* ctx, double* out, void* stream);
+
+/* The MD loop of MDSimulation::single_step (src/md_simulation.cpp:899-941) restricted to this path: n_steps of
+ * integrate-1 + pack, rebuild decision (max displacement > (hi_frac skin)^2, or every `every` steps when every > 0;
+ * lagged != 0 uses the previous step's read-back, extrapolated, as the reference does on several ranks), list rebuild,
+ * forces, integrate-2. Single-rank systems only (no ghosts). Returns the number of rebuilds and the largest
+ * displacement that was ever in effect when forces were evaluated (to check the skin was never outrun). */
+int dsmd_run_nve(dsmd_ctx* ctx, int64_t n_steps, double dt, double force_to_accel, double hi_frac, int every, int lagged,
+                 int64_t* n_rebuilds, double* worst_disp_sq, void* stream);
+
+/* One force evaluation with host buffers, as a force-provider plugin is called: uploads positions (context order),
+ * packs, evaluates, downloads forces (and scalars when out5 != NULL). Rebuilds the list first when rebuild != 0.
+ * Synchronises. */
+int dsmd_forces_host(dsmd_ctx* ctx, const double* x, const double* y, const double* z, int rebuild, double* fx,
+                     double* fy, double* fz, double* out5, void* stream);
+
+/* Kernel launches issued by this context so far (benchmark bookkeeping). */
+int64_t dsmd_launch_count(const dsmd_ctx* ctx);
+
+/* -- halo (ghost atoms) ----------------------------------------------------------------------------------------------- */
+
+/* The data-plane half of MDSystem::exchange_halo_on_device (src/md_system.cpp:1448-1463); the transport between the
+ * two calls is the caller's (NCCL send/recv).
+ * pack: gathers positions of the owned atoms listed in device_send_index[0..count) into device_out as 3 doubles per
+ * atom, adding shift[3] (the periodic image offset for that neighbour). */
+int dsmd_halo_pack(dsmd_ctx* ctx, const int32_t* device_send_index, int64_t count, const double shift[3],
+                   double* device_out, void* stream);
+/* unpack: writes `count` received positions (3 doubles each) to the ghosts first_ghost .. first_ghost + count of the
+ * hand-in order, i.e. to slots ghost_slot[first_ghost + k], in both the double arrays and the fixed-point layout. */
+int dsmd_halo_unpack(dsmd_ctx* ctx, const double* device_in, int64_t first_ghost, int64_t count, void* stream);
+/* Selects the owned atoms within [lo, hi) (a neighbour's brick grown by the halo, already shifted into this rank's
+ * frame) into device_send_index; *count returns how many. Synchronises. */
+int dsmd_halo_select(dsmd_ctx* ctx, const double lo[3], const double hi[3], int32_t* device_send_index, int64_t capacity,
+                     int64_t* count, void* stream);
+/* Full records for a plan (re)build: packs {x, y, z, vx, vy, vz, mass, charge} (+shift) as 8 doubles and
+ * {type, gid} as 2 int32 per listed atom; append writes such records behind the current atoms as new ghosts. */
+int dsmd_halo_pack_records(dsmd_ctx* ctx, const int32_t* device_send_index, int64_t count, const double shift[3],
+                           double* device_real_out, int32_t* device_int_out, void* stream);
+int dsmd_halo_append_records(dsmd_ctx* ctx, const double* device_real_in, const int32_t* device_int_in, int64_t count,
+                             void* stream);
+
+/* -- radius graph ------------------------------------------------------------------------------------------------------ */
+
+typedef struct dsmd_edges dsmd_edges;
+
+/* EdgeBuilder (include/EdgeBuilder.cuh:12-84). */
+int dsmd_edges_create(int device, dsmd_edges** out);
+void dsmd_edges_destroy(dsmd_edges* eb);
+const char* dsmd_edges_last_error(const dsmd_edges* eb);
+
+/* EdgeBuilder::build (include/EdgeBuilder.cuh:52-55): every ordered pair (i, j), i != j, |r_j - r_i| < cutoff over the n
+ * atoms given (no minimum image). lo / hi: optional host box containing every atom. n_centers < n with owner / shift
+ * arrays = EdgeBuilder::Images; receiver_ok / row = EdgeBuilder::Prune (NULL keeps every edge).
+ * Results stay valid until the next build: edge_index int64 [2 * E] (row 0 = i, row 1 = j), edge_shift double [E * 3]
+ * (written only with images). *n_edges returns E after the single synchronisation of `stream`. */
+int dsmd_edges_build(dsmd_edges* eb, const double* d_x, const double* d_y, const double* d_z, int64_t n, double cutoff,
+                     const double* lo, const double* hi, int64_t n_centers, const int32_t* d_owner,
+                     const double* d_shift_x, const double* d_shift_y, const double* d_shift_z,
+                     const unsigned char* d_receiver_ok, int row, int64_t* n_edges, void* stream);
+int dsmd_edges_result(const dsmd_edges* eb, const int64_t** d_edge_index, const double** d_edge_shift, int64_t* n_edges);
+
+/* Compact periodic radius graph (no image atoms): n atoms in an orthorhombic periodic box; directed edges as
+ * int32 src / dst, int8 lattice shift [E * 3] (dst image = pos[dst] + shift * box) and fp32 edge vectors [E * 3],
+ * sorted by (src, dst, shift). No counterpart in the reference, which feeds images as explicit atoms. */
+int dsmd_edges_build_periodic(dsmd_edges* eb, const double* d_x, const double* d_y, const double* d_z, int64_t n,
+                              const double box[3], double cutoff, int64_t* n_edges, void* stream);
+int dsmd_edges_result_compact(const dsmd_edges* eb, const int32_t** d_src, const int32_t** d_dst,
+                              const int8_t** d_shift, const float** d_vec, int64_t* n_edges);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSMD_B200_H */

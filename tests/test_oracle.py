@@ -1,0 +1,224 @@
+"""CPU tests of the oracle itself: the restatement against brute force, against the committed golden fixtures (outputs of
+the reference's own CPU code) and, where the compiled reference is present, against that code directly."""
+import hashlib
+import os
+
+import numpy as np
+import pytest
+
+from deepscalemd_b200 import synthetic as syn
+from oracle import cpu_oracle as co
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def golden_cases():
+    return {
+        "lj_fcc_864": (lambda: syn.fcc_lj(6, seed=1)),
+        "lj_fcc_4000_switch": (lambda: syn.fcc_lj(10, seed=2)),
+        "kob_andersen_4096": (lambda: syn.kob_andersen(4096, seed=5)),
+        "water_3993": (lambda: syn.water_box(11, seed=3)),
+    }
+
+
+def rms(a):
+    return float(np.sqrt((np.asarray(a) ** 2).sum(-1).mean()))
+
+
+def oracle_eval(s, switch, ewald_mode):
+    x, y, z = (np.ascontiguousarray(s.pos[:, k]) for k in range(3))
+    pairs = co.pairs(x, y, z, s.n, s.box, search=s.cutoff + s.skin)
+    c6, c12 = co.lj_tables(s.eps, s.sig)
+    alpha = co.ewald_alpha(s.cutoff) if s.coulomb else 0.0
+    f, sc = co.forces(x, y, z, s.n, s.box, pairs, c6, c12, s.cutoff, charge=s.charge, types=s.types, switch=switch,
+                      do_coulomb=s.coulomb, alpha=alpha, ewald_mode=ewald_mode, exclusions=s.exclusions)
+    return pairs, f, sc
+
+
+def test_pairs_match_brute_force():
+    s = syn.fcc_lj(5, seed=11)
+    R = s.cutoff + s.skin
+    x, y, z = (np.ascontiguousarray(s.pos[:, k]) for k in range(3))
+    got = co.canonical_pairs(co.pairs(x, y, z, s.n, s.box, search=R))
+    want = co.canonical_pairs(co.brute_pairs(s.pos, s.box, R))
+    assert np.array_equal(got, want)
+
+
+def test_no_pair_sits_on_the_list_boundary():
+    """The seeded inputs have no pair within 1e-9 (relative) of the list radius, so fp64 evaluation order cannot
+    change the pair set."""
+    s = syn.fcc_lj(6, seed=1)
+    R = s.cutoff + s.skin
+    d = s.pos[:, None, :] - s.pos[None, :, :]
+    d -= s.box * np.round(d / s.box)
+    r2 = (d * d).sum(-1)
+    assert not np.any(np.abs(r2 / (R * R) - 1.0) < 1e-9)
+
+
+@pytest.mark.parametrize("name", list(golden_cases()))
+def test_restatement_matches_golden_reference_output(name):
+    """Pins the oracle: pair set identical (checksum of the canonical list), forces/energy/virial equal to the
+    reference CPU code's to fp64 round-off (the restatement uses the reference's own Ewald table arithmetic here)."""
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    s = golden_cases()[name]()
+    pairs, f, sc = oracle_eval(s, float(g["switch"]), ewald_mode=0)
+    assert len(pairs) == int(g["pairs_in_list"])
+    assert sc["pairs_in_cutoff"] == int(g["pairs_in_cutoff"])
+    sha = hashlib.sha256(co.canonical_pairs(pairs).astype(np.int64).tobytes()).hexdigest()
+    assert sha == str(g["pair_sha256"])
+    assert rms(f - g["forces"]) <= 1e-12 * rms(g["forces"])
+    assert abs(sc["pe"] - float(g["pe_real"])) <= 1e-11 * abs(float(g["pe_real"]))
+    assert abs(sc["virial"] - float(g["virial"])) <= 1e-11 * abs(float(g["virial"]))
+    assert np.allclose(sc["virial_diag"], g["virial_diag"], rtol=1e-10)
+
+
+def test_reference_table_distance_from_exact_erfc():
+    """The reference CPU path interpolates erfc linearly in r^2 (spacing 0.04 A^2): its own forces sit about 2e-4
+    (relative RMS) from the exact-erfc result. Documented here because it bounds how closely any accurate
+    implementation can agree with that path on a charged system."""
+    g = np.load(os.path.join(GOLDEN, "water_3993.npz"))
+    s = golden_cases()["water_3993"]()
+    _, f_exact, sc = oracle_eval(s, -1.0, ewald_mode=1)
+    rel = rms(f_exact - g["forces"]) / rms(g["forces"])
+    assert 1e-5 < rel < 1e-3
+    assert abs(sc["pe"] - float(g["pe_real"])) < 1e-4 * abs(float(g["pe_real"]))
+
+
+@pytest.mark.skipif(not co.ref_available(), reason="compiled reference (oracle/_ref) not present")
+def test_restatement_matches_compiled_reference_with_ghosts():
+    """Two-brick split along x emulated in one process: each brick's owned + ghost atoms go through the reference's
+    list builder and force code and through the restatement; both must agree, and the bricks must add up to the
+    undivided system."""
+    s = syn.fcc_lj(8, seed=21)
+    R = s.cutoff + s.skin
+    halo = R
+    whole_pairs, whole_f, whole_sc = oracle_eval(s, -1.0, 1)
+    total_pe = 0.0
+    f_sum = np.zeros_like(whole_f)
+    for brick in syn.brick_decompose(s.pos, s.box, (2, 1, 1), halo):
+        own, src, img = brick["owned"], brick["ghost_src"], brick["ghost_image"]
+        wrapped = s.pos - s.box * np.floor(s.pos / s.box)
+        pos = np.concatenate([wrapped[own], wrapped[src] + img * s.box])
+        gid = np.concatenate([own, src]).astype(np.int32)
+        x, y, z = (np.ascontiguousarray(pos[:, k]) for k in range(3))
+        lo, hi = brick["lo"].copy(), brick["hi"].copy()
+        ref = co.RefCase(x, y, z, len(own), s.box, s.cutoff, s.skin, lo=lo, hi=hi, gid=gid, n_global=s.n)
+        ref.build_list()
+        rp = co.canonical_pairs(ref.list_pairs())
+        split = (1, 0, 0)
+        op = co.pairs(x, y, z, len(own), s.box, split=split, search=R)
+        assert np.array_equal(rp, co.canonical_pairs(op))
+        f_ref, sc_ref = ref.compute()
+        c6, c12 = co.lj_tables(s.eps, s.sig)
+        f, sc = co.forces(x, y, z, len(own), s.box, op, c6, c12, s.cutoff, gid=gid, split=split)
+        assert rms(f - f_ref) <= 1e-12 * rms(f_ref)
+        assert abs(sc["pe"] - sc_ref["pe"]) <= 1e-11 * abs(sc_ref["pe"])
+        total_pe += sc["pe"]
+        f_sum[own] = f
+        ref.close()
+    assert abs(total_pe - whole_sc["pe"]) <= 1e-10 * abs(whole_sc["pe"])
+    assert rms(f_sum - whole_f) <= 1e-12 * rms(whole_f)
+
+
+def test_cubic_ewald_table_accuracy():
+    """The float-bit indexed cubic table reproduces erfc(a r)/r and its force factor to ~1e-6 relative of the value at worst (float evaluation; the values near the cutoff are ~1e-6 themselves)."""
+    from math import erfc, exp, pi, sqrt
+    alpha = co.ewald_alpha(10.0)
+    fc, ec = co.cubic_table(alpha, 100.0)
+    assert fc.shape[0] == 256
+    rng = np.random.default_rng(0)
+    worst_e = worst_f = 0.0
+    for r2 in rng.uniform(0.5, 100.0, 2000):
+        r = sqrt(r2)
+        e_true = erfc(alpha * r) / r
+        f_true = (e_true + 2 * alpha / sqrt(pi) * exp(-alpha * alpha * r2)) / r2
+        e_tab, f_tab = co.cubic_eval(ec, np.float32(r2)), co.cubic_eval(fc, np.float32(r2))
+        r2f = float(np.float32(r2))
+        rf = sqrt(r2f)
+        e_t = erfc(alpha * rf) / rf
+        f_t = (e_t + 2 * alpha / sqrt(pi) * exp(-alpha * alpha * r2f)) / r2f
+        worst_e = max(worst_e, abs(e_tab - e_t) / e_t)
+        worst_f = max(worst_f, abs(f_tab - f_t) / f_t)
+    assert worst_e < 2e-6 and worst_f < 2e-6
+    assert co.cubic_eval(ec, np.float32(0.3)) is None          # below the table
+
+
+def test_edges_match_brute_force_and_images():
+    rng = np.random.default_rng(3)
+    n, L, cutoff = 400, 12.0, 2.5
+    pos = rng.uniform(0, L, (n, 3))
+    x, y, z = (np.ascontiguousarray(pos[:, k]) for k in range(3))
+    idx, _ = co.edges(x, y, z, cutoff)
+    bf = co.brute_edges(pos, cutoff)
+    key = lambda e: e[:, np.lexsort((e[1], e[0]))]
+    assert np.array_equal(key(idx), key(bf))
+    # periodic images as shifts: every atom gets its images within the cutoff of the box; edges centred on real atoms
+    box = np.full(3, L)
+    im = co.images(x, y, z, box, np.zeros(3), -np.full(3, cutoff + 1e-8), box + cutoff + 1e-8, np.ones(3, dtype=np.int32))
+    total = len(im["x"])
+    assert total > n and np.all(im["owner"][:n] == np.arange(n))
+    idx2, sh2 = co.edges(im["x"], im["y"], im["z"], cutoff, n_centers=n, owner=im["owner"], shift=im["shift"])
+    # the same graph by minimum image
+    d = pos[None, :, :] - pos[:, None, :]
+    img = -np.round(d / L)
+    d += img * L
+    m = (d * d).sum(-1) < cutoff * cutoff
+    np.fill_diagonal(m, False)
+    i, j = np.nonzero(m)
+    want = np.stack([i, j, *(img[i, j, k].astype(np.int64) for k in range(3))])
+    got = np.stack([idx2[0], idx2[1], *(np.rint(sh2[:, k] / L).astype(np.int64) for k in range(3))])
+    order = lambda e: e[:, np.lexsort(e[::-1])]
+    assert np.array_equal(order(got), order(want))
+    # vector reconstruction: pos[j] - pos[i] + shift is the found displacement
+    w = pos - L * np.floor(pos / L)
+    vec = w[idx2[1]] - w[idx2[0]] + sh2
+    assert np.all((vec * vec).sum(1) < cutoff * cutoff)
+
+
+def test_edge_pruning_rows():
+    rng = np.random.default_rng(4)
+    pos = rng.uniform(0, 8.0, (200, 3))
+    x, y, z = (np.ascontiguousarray(pos[:, k]) for k in range(3))
+    ok = (rng.uniform(size=200) < 0.5).astype(np.uint8)
+    full, _ = co.edges(x, y, z, 2.0)
+    for row in (0, 1):
+        pruned, _ = co.edges(x, y, z, 2.0, receiver_ok=ok, row=row)
+        keep = ok[full[row]] != 0
+        assert np.array_equal(pruned, full[:, keep])
+
+
+def test_ghost_selection_matches_independent_construction():
+    s = syn.fcc_lj(6, seed=9)
+    x, y, z = (np.ascontiguousarray(s.pos[:, k]) for k in range(3))
+    halo = s.cutoff + s.skin
+    for dims in ((2, 1, 1), (2, 2, 1), (2, 2, 2)):
+        bricks = syn.brick_decompose(s.pos, s.box, dims, halo)
+        owned_total = 0
+        for b in bricks:
+            src, img = co.ghosts(x, y, z, s.box, (1, 1, 1), dims, b["coords"], halo)
+            assert np.array_equal(src, b["ghost_src"]) and np.array_equal(img, b["ghost_image"])
+            owned_total += len(b["owned"])
+        assert owned_total == s.n
+
+
+def test_velocity_verlet_conserves_energy_on_oracle_forces():
+    s = syn.fcc_lj(4, seed=5)
+    pos = [np.ascontiguousarray(s.pos[:, k]) for k in range(3)]
+    vel = [np.ascontiguousarray(s.vel[:, k]) for k in range(3)]
+    c6, c12 = co.lj_tables(s.eps, s.sig)
+
+    def force():
+        p = co.pairs(*pos, s.n, s.box, search=s.cutoff)
+        f, sc = co.forces(*pos, s.n, s.box, p, c6, c12, s.cutoff)
+        return [np.ascontiguousarray(f[:, k]) for k in range(3)], sc["pe"]
+
+    frc, pe = force()
+    e0 = pe + 0.5 * sum((v * v).sum() for v in vel)
+    dt = 0.002
+    for _ in range(50):
+        co.vv_half(True, dt, 1.0, pos, vel, frc, s.mass)
+        frc, pe = force()
+        co.vv_half(False, dt, 1.0, pos, vel, frc, s.mass)
+    e1 = pe + 0.5 * sum((v * v).sum() for v in vel)
+    # plain truncation at the cutoff makes the energy jump when pairs cross it: small but not round-off small
+    assert abs(e1 - e0) / s.n < 5e-3
