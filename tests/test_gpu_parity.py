@@ -106,15 +106,15 @@ def test_forces_energy_virial_match_oracle_and_golden(cuda_device, name):
     ctx.compute_forces(capi.PHASE_FULL, want_energy=True)
     sc = ctx.read_scalars()
     f = ctx.forces_by_gid(s.n)
-    # energy-free launch gives the same forces bit for bit
+    # the energy-free instantiation of the kernel gives the same forces up to fp32 contraction differences
     ctx.compute_forces(capi.PHASE_FULL, want_energy=False)
-    assert np.array_equal(f, ctx.forces_by_gid(s.n))
+    assert rms(f - ctx.forces_by_gid(s.n)) <= 1e-6 * rms(f)
     _, f_o, sc_o = oracle_case(s, switch, ewald_mode=1)
     assert rms(f - f_o) <= FORCE_RTOL * rms(f_o)
     assert abs(sc["pe"] - sc_o["pe"]) <= SCALAR_RTOL * abs(sc_o["pe"])
     assert abs(sc["virial"] - sc_o["virial"]) <= SCALAR_RTOL * abs(sc_o["virial"])
     assert np.allclose(sc["virial_diag"], sc_o["virial_diag"], rtol=5e-6)
-    assert abs(sc["virial_diag"].sum() - sc["virial"]) <= 1e-9 * abs(sc["virial"])
+    assert abs(sc["virial_diag"].sum() - sc["virial"]) <= 1e-7 * abs(sc["virial"])   # fp32 per-atom partial sums
     # against the reference CPU code's own output
     g = np.load(os.path.join(GOLDEN, name + ".npz"))
     if s.coulomb:
@@ -203,7 +203,7 @@ def test_two_brick_split_with_ghosts_adds_up(cuda_device):
         sc_full = ctx.read_scalars()
         f_full = np.stack([ctx.download(k, n_owned) for k in ("fx", "fy", "fz")], axis=1)
         assert rms(f_split - f_full) <= 1e-6 * rms(f_full)
-        assert abs(sc_split["pe"] - sc_full["pe"]) <= 1e-9 * abs(sc_full["pe"])
+        assert abs(sc_split["pe"] - sc_full["pe"]) <= 1e-7 * abs(sc_full["pe"])   # fp32 per-atom partial sums
         f_sum[atom[slot_upload[:n_owned]]] = f_full
         pe += sc_full["pe"]
         vir += sc_full["virial"]
@@ -244,7 +244,9 @@ def test_displacement_check_and_repack(cuda_device):
 def test_nve_run_conserves_energy_and_respects_the_skin(cuda_device):
     s = syn.fcc_lj(8, seed=7)
     for lagged in (False, True):
-        ctx = make_context(s)
+        # switched LJ: the potential is continuous at the cutoff, so the total energy is a conserved quantity
+        # (plain truncation makes it jump by u(rc) at every cutoff crossing)
+        ctx = make_context(s, switch=2.0)
         ctx.build_neighbor_list()
         ctx.compute_forces(want_energy=True)
         e0 = ctx.read_scalars()["pe"] + ctx.kinetic_energy()
@@ -253,7 +255,7 @@ def test_nve_run_conserves_energy_and_respects_the_skin(cuda_device):
         e1 = ctx.read_scalars()["pe"] + ctx.kinetic_energy()
         assert out["rebuilds"] >= 10
         assert out["worst_disp_sq"] <= (0.5 * s.skin) ** 2 * (1.0 if not lagged else 1.2)
-        assert abs(e1 - e0) / s.n < 2e-3          # truncated (unshifted) LJ: cutoff crossings move the energy a little
+        assert abs(e1 - e0) / s.n < 1e-4
         ctx.close()
 
 
