@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the short-range nonbonded MD step (neighbour list + pair forces) on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N --steps K ...   # the reference's own CPU code on the host cores
+
+One JSON line on stdout (rank 0). A "step" is one MD step of the hot path on the LJ NVE system of 4,000,000 atoms
+(FCC start, density 0.8442, T* = 1.44, cutoff 2.5, skin 0.3, dt = 0.005): first velocity-Verlet half + conversion of the
+positions to the kernels' layout + displacement check, neighbour-list rebuild when the displacement exceeds skin / 2,
+pair forces, second velocity-Verlet half. Inputs are synthetic (seeded); the metric is atom-steps/s over all GPUs.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+DT = 0.005
+ARGON_TAU_FS = 2156.0          # sigma sqrt(m / epsilon) of argon in fs: maps dt = 0.005 tau to 10.78 fs for ns/day
+L2_BYTES = 126e6
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [t.strip() for t in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for k, name in enumerate(names):
+                if f[5 + k].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def fcc_for(workload: str):
+    from deepscalemd_b200 import synthetic as syn
+    cells = {"lj_4m": 100, "lj_500k": 50, "lj_256k": 40, "lj_108k": 30, "lj_32k": 20}[workload]
+    return syn.fcc_lj(cells, seed=12345)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's own CPU code (oracle/_ref), or the oracle restatement when that is not present
+# ---------------------------------------------------------------------------------------------------------------------
+
+class CpuMd:
+    """Velocity-Verlet on the host around the reference's SpatialVerletList + ForceCalculatorCPU."""
+
+    def __init__(self, workload):
+        from oracle import cpu_oracle as co
+        self.co = co
+        self.s = fcc_for(workload)
+        s = self.s
+        self.pos = [np.ascontiguousarray(s.pos[:, k]) for k in range(3)]
+        self.vel = [np.ascontiguousarray(s.vel[:, k]) for k in range(3)]
+        self.kind = "reference" if co.ref_available() else "port"
+        self.rebuilds = 0
+        if self.kind == "reference":
+            self.ref = co.RefCase(*self.pos, s.n, s.box, s.cutoff, s.skin, eps=s.eps, sig=s.sig)
+            self.cores = self.ref.threads()
+            self.simd = self.ref.simd_width()
+            self.ref.build_list()
+            self.frc = self._force()
+        else:
+            self.cores = 1
+            self.simd = 1
+            self.c6, self.c12 = co.lj_tables(s.eps, s.sig)
+            self.ref_pos = [p.copy() for p in self.pos]
+            self.pairs = co.pairs(*self.pos, s.n, s.box, search=s.cutoff + s.skin)
+            self.frc = self._force()
+
+    def _force(self):
+        if self.kind == "reference":
+            f, _ = self.ref.compute(tensor=False)
+        else:
+            f, _ = self.co.forces(*self.pos, self.s.n, self.s.box, self.pairs, self.c6, self.c12, self.s.cutoff)
+        return [np.ascontiguousarray(f[:, k]) for k in range(3)]
+
+    def step(self):
+        s = self.s
+        self.co.vv_half(True, DT, 1.0, self.pos, self.vel, self.frc, s.mass)
+        if self.kind == "reference":
+            self.ref.update_positions(*self.pos)
+            if self.ref.needs_rebuild():
+                self.ref.build_list()
+                self.rebuilds += 1
+        else:
+            d2 = sum((p - r) ** 2 for p, r in zip(self.pos, self.ref_pos)).max()
+            if d2 > (0.5 * s.skin) ** 2:
+                self.pairs = self.co.pairs(*self.pos, s.n, s.box, search=s.cutoff + s.skin)
+                self.ref_pos = [p.copy() for p in self.pos]
+                self.rebuilds += 1
+        self.frc = self._force()
+        self.co.vv_half(False, DT, 1.0, self.pos, self.vel, self.frc, s.mass)
+
+
+def pick_cpu_workload(steps_total: int, budget_s: float):
+    """Largest sample whose run fits the time budget (timed on one step of each candidate, smallest first)."""
+    chosen, chosen_md = None, None
+    for workload in ("lj_32k", "lj_108k", "lj_256k"):
+        md = CpuMd(workload)
+        t0 = time.perf_counter()
+        md.step()
+        md.step()
+        per_step = (time.perf_counter() - t0) / 2
+        if chosen is None or per_step * steps_total * 1.3 < budget_s:
+            chosen, chosen_md = workload, md
+        else:
+            break
+    return chosen, chosen_md
+
+
+def run_cpu_baseline(steps: int, warmup: int, budget_s: float):
+    workload, md = pick_cpu_workload(steps + warmup, budget_s)
+    for _ in range(warmup):
+        md.step()
+    r0 = md.rebuilds
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        md.step()
+    elapsed = time.perf_counter() - t0
+    value = md.s.n * steps / elapsed
+    return {
+        "value": value, "unit": "atom-steps/s", "cores": md.cores, "kind": md.kind,
+        "sample": (f"{md.s.n}-atom FCC LJ box with the benchmark's density, cutoff, skin and dt ({workload}); {steps} "
+                   f"MD steps, {md.rebuilds - r0} list rebuilds (displacement > skin/2); "
+                   + ("reference SpatialVerletList + ForceCalculatorCPU fp64 tile kernels, "
+                      f"SIMD width {md.simd} doubles, OpenMP" if md.kind == "reference"
+                      else "oracle restatement, scalar fp64, 1 thread")),
+        "ms_per_step": 1e3 * elapsed / steps, "atoms": md.s.n,
+    }
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = run_cpu_baseline(args.steps, args.warmup, budget_s=170.0)
+    line = {
+        "impl": "reference", "metric": "atom-steps/s", "value": base["value"], "unit": "atom-steps/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "LJ NVE 4,000,000 atoms (FCC 100^3, rho*=0.8442, T*=1.44, rc=2.5, skin=0.3, dt=0.005)",
+                   "measured_on": base["sample"], "ns_per_day": ns_per_day(base["ms_per_step"])},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "atom-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def ns_per_day(ms_per_step: float) -> float:
+    return DT * ARGON_TAU_FS * 1e-6 * 86400.0 / (ms_per_step * 1e-3)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# this library
+# ---------------------------------------------------------------------------------------------------------------------
+
+def time_calls(fn, repeats, stream):
+    """Average device time of fn() in ms, with CUDA events on `stream` and a synchronise on both sides."""
+    import torch
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record(stream)
+    for _ in range(repeats):
+        fn()
+    stop.record(stream)
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / repeats
+
+
+def single_gpu(args):
+    import torch
+    from deepscalemd_b200 import capi
+    hbm_peak, peak_kind = measured_peaks()
+    torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream()
+    s = fcc_for(args.workload)
+    ctx = capi.Context(s.n)
+    ctx.set_box(s.box)
+    ctx.set_pair_params(s.eps, s.sig, s.cutoff, s.skin)
+    ctx.upload(s.pos, vel=s.vel, mass=s.mass, types=s.types)
+    ctx.build_neighbor_list(stream)
+    ctx.compute_forces(capi.PHASE_FULL, True, stream)
+    sc0 = ctx.read_scalars(stream)
+    e0 = sc0["pe"] + ctx.kinetic_energy(stream)
+
+    # -- the timed region: K MD steps, device resident ----------------------------------------------------------------
+    ctx.run_nve(args.warmup, DT, 1.0, 0.5, 0, True, stream)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = ctx.launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record(stream)
+    out = ctx.run_nve(args.steps, DT, 1.0, 0.5, 0, True, stream)
+    stop.record(stream)
+    torch.cuda.synchronize()
+    elapsed_ms = start.elapsed_time(stop)
+    launches = ctx.launch_count() - launches0
+    clocks = sampler.stop()
+    ms_per_step = elapsed_ms / args.steps
+    value = s.n * args.steps / (elapsed_ms * 1e-3)
+
+    ctx.compute_forces(capi.PHASE_FULL, True, stream)
+    sc1 = ctx.read_scalars(stream)
+    e1 = sc1["pe"] + ctx.kinetic_energy(stream)
+
+    # -- per-kernel times for the roofline (inputs are far larger than L2, so no flush is needed) -----------------------
+    ctx.build_neighbor_list(stream)
+    stats = ctx.list_stats()
+    ctx.compute_forces(capi.PHASE_FULL, True, stream)
+    p_cut = ctx.read_scalars(stream)["pairs_in_cutoff"]
+    p_list = stats["directed_entries"] / 2
+    t_pair = time_calls(lambda: ctx.compute_forces(capi.PHASE_FULL, False, stream), 20, stream)
+    t_pack = time_calls(lambda: ctx.pack_positions(0, None, stream), 20, stream)
+    t_build = time_calls(lambda: ctx.build_neighbor_list(stream), 5, stream)
+    flops = ctx.fma_probe(1, stream)
+    iters = 20000
+    t_probe = time_calls(lambda: ctx.fma_probe(iters, stream), 3, stream)
+    fp32_peak_tflops = flops * iters / (t_probe * 1e-3) / 1e12
+    pair_flops = 8.0 * p_list + 19.0 * p_cut
+    pair_bytes = 16.0 * s.n + 4.0 * p_list + 24.0 * s.n
+    build_bytes = 16.0 * s.n + 4.0 * p_list + 8.0 * s.n / 32
+    pack_bytes = (24.0 + 4.0 + 16.0) * s.n
+    kernels = {
+        "pair_forces": {"ms": t_pair, "tflops": pair_flops / (t_pair * 1e-3) / 1e12,
+                        "frac_fp32": pair_flops / (t_pair * 1e-3) / 1e12 / fp32_peak_tflops,
+                        "gbs": pair_bytes / (t_pair * 1e-3) / 1e9, "frac_hbm": pair_bytes / (t_pair * 1e-3) / 1e9 / hbm_peak},
+        "list_build_total": {"ms": t_build, "gbs": build_bytes / (t_build * 1e-3) / 1e9,
+                             "frac_hbm": build_bytes / (t_build * 1e-3) / 1e9 / hbm_peak},
+        "pack_positions": {"ms": t_pack, "gbs": pack_bytes / (t_pack * 1e-3) / 1e9,
+                           "frac_hbm": pack_bytes / (t_pack * 1e-3) / 1e9 / hbm_peak},
+    }
+    pk = kernels["pair_forces"]
+    roofline = {
+        "kernel": "k_pair (LJ, full list, forces only)", "bound": "hbm", "achieved": pk["gbs"], "peak": hbm_peak,
+        "unit": "GB/s", "frac": pk["frac_hbm"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
+        "traffic": None,
+        "algorithmic_bytes_per_launch": pair_bytes, "algorithmic_flops_per_launch": pair_flops,
+        "fp32": {"achieved_tflops": pk["tflops"], "peak_tflops": fp32_peak_tflops,
+                 "peak_source": "measured in this run (independent FMA chains on every SM)", "frac": pk["frac_fp32"]},
+    }
+
+    # -- end to end: the host-buffer force call (upload positions, pack or rebuild, forces, download forces) --------------
+    order = ctx.download("global_id")
+    host = [torch.from_numpy(ctx.download(k)).pin_memory() for k in ("x", "y", "z")]
+    hf = [torch.empty(s.n, dtype=torch.float64).pin_memory() for _ in range(3)]
+    cadence = max(1, round(args.steps / max(out["rebuilds"], 1)))
+    e2e_steps = max(4, min(args.steps, 40))
+    calls = {"k": 0}
+
+    def one_call():
+        ctx.forces_host(host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), hf[0].data_ptr(), hf[1].data_ptr(),
+                        hf[2].data_ptr(), rebuild=(calls["k"] % cadence == 0), scalars=None, stream=stream)
+        calls["k"] += 1
+
+    for _ in range(3):
+        one_call()
+    calls["k"] = 0
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        one_call()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e_value = s.n * e2e_steps / e2e_s
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        cpu = run_cpu_baseline(steps=30, warmup=3, budget_s=25.0)
+        cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    line = {
+        "metric": "atom-steps/s", "value": value, "unit": "atom-steps/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {
+            "workload": "LJ NVE 4,000,000 atoms (FCC 100^3, rho*=0.8442, T*=1.44, rc=2.5, skin=0.3, dt=0.005)"
+            if args.workload == "lj_4m" else args.workload,
+            "atoms": s.n, "ns_per_day": ns_per_day(ms_per_step), "rebuilds": out["rebuilds"],
+            "steps_per_rebuild": args.steps / max(out["rebuilds"], 1),
+            "worst_displacement_over_half_skin": float(np.sqrt(out["worst_disp_sq"]) / (0.5 * s.skin)),
+            "l2": "inputs larger than L2 (list %.2f GB, positions %.0f MB)" % (4.0 * stats["directed_entries"] / 1e9,
+                                                                               16.0 * s.n / 1e6),
+            "list": stats, "pairs_in_cutoff": p_cut,
+            "energy_per_atom_before": e0 / s.n, "energy_per_atom_after": e1 / s.n,
+            "precision": "fp32 pair math on 32-bit fixed-point coordinates, fp64 positions/velocities/forces/energy sums",
+        },
+        "clocks": clocks,
+        "roofline": roofline,
+        "kernels": kernels,
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "atom-steps/s", "h2d_bytes_per_step": 24 * s.n, "d2h_bytes_per_step": 24 * s.n,
+                "steps": e2e_steps, "rebuild_every": cadence,
+                "call": "dsmd_forces_host: pinned host positions in, forces out, list rebuilt at the MD run's cadence"},
+        "gpu_launches": int(launches),
+    }
+    print(json.dumps(line))
+    ctx.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=100)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="lj_4m")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 or world > 1:
+        from deepscalemd_b200 import domain_bench
+        domain_bench.run(args)
+        return
+    single_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

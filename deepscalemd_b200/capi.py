@@ -26,7 +26,7 @@ SYMBOLS = [
     "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned",
     "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq",
     "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_run_nve",
-    "dsmd_forces_host", "dsmd_launch_count", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
+    "dsmd_forces_host", "dsmd_launch_count", "dsmd_fma_probe", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
     "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_edges_create", "dsmd_edges_destroy",
     "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
     "dsmd_edges_result_compact",
@@ -248,10 +248,10 @@ class Context:
         self._check(self.lib.dsmd_compute_forces(self.h, c_int(phase), c_int(int(want_energy)), _stream_handle(stream)))
 
     def read_scalars(self, stream=None):
-        out = (c_double * 5)()
+        out = (c_double * 6)()
         self._check(self.lib.dsmd_read_scalars(self.h, out, _stream_handle(stream)))
         v = np.array(list(out))
-        return dict(pe=v[0], virial=v[1], virial_diag=v[2:5].copy())
+        return dict(pe=v[0], virial=v[1], virial_diag=v[2:5].copy(), pairs_in_cutoff=v[5])
 
     def integrate(self, half, dt, force_to_accel=1.0, stream=None):
         self._check(self.lib.dsmd_integrate(self.h, c_int(half), c_double(dt), c_double(force_to_accel),
@@ -279,6 +279,12 @@ class Context:
 
     def launch_count(self):
         return self.lib.dsmd_launch_count(self.h)
+
+    def fma_probe(self, iters, stream=None):
+        """Queues the fp32 FMA throughput probe; returns the flops it performs."""
+        f = c_double(0.0)
+        self._check(self.lib.dsmd_fma_probe(self.h, c_int(iters), ctypes.byref(f), _stream_handle(stream)))
+        return f.value
 
     # -- halo -------------------------------------------------------------------------------------------------------------
     def halo_select(self, lo, hi, index_tensor, stream=None):

@@ -409,7 +409,7 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
 
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     float ax = 0.f, ay = 0.f, az = 0.f;
-    float e_sum = 0.f, w_sum = 0.f, wx = 0.f, wy = 0.f, wz = 0.f;
+    float e_sum = 0.f, w_sum = 0.f, wx = 0.f, wy = 0.f, wz = 0.f, n_in = 0.f;
     if (i < n_owned) {
         const int4 pi = pq[i];
         const float qi = COULOMB ? p.kq * qf[i] : 0.f;
@@ -486,6 +486,7 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
                     wx += fmag * dx * dx;
                     wy += fmag * dy * dy;
                     wz += fmag * dz * dz;
+                    n_in += 1.f;
                 }
             }
         }
@@ -500,9 +501,9 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
         }
     }
     if (ENERGY) {
-        double v[5] = {0.5 * static_cast<double>(e_sum), 0.5 * static_cast<double>(w_sum), 0.5 * static_cast<double>(wx),
-                       0.5 * static_cast<double>(wy), 0.5 * static_cast<double>(wz)};
-        block_sum_to_partials<5>(v, partials);
+        double v[6] = {0.5 * static_cast<double>(e_sum), 0.5 * static_cast<double>(w_sum), 0.5 * static_cast<double>(wx),
+                       0.5 * static_cast<double>(wy), 0.5 * static_cast<double>(wz), 0.5 * static_cast<double>(n_in)};
+        block_sum_to_partials<6>(v, partials);
     }
 }
 
@@ -577,6 +578,21 @@ __global__ void k_halo_append_records(int count, int first_slot, const double* _
     gid[s] = int_in[2 * k + 1];
 }
 
+// Dependent-FMA-free throughput probe: 8 independent fp32 FMA chains per thread. The benchmark times it to get the
+// fp32 CUDA-core peak of the device it runs on (the denominator of the pair kernel's compute roofline).
+__global__ void __launch_bounds__(256) k_fma_probe(int iters, float seed, float* out) {
+    float a0 = seed + threadIdx.x, a1 = a0 + 1.f, a2 = a0 + 2.f, a3 = a0 + 3.f, a4 = a0 + 4.f, a5 = a0 + 5.f,
+          a6 = a0 + 6.f, a7 = a0 + 7.f;
+    const float m = 0.999f, c = 0.001f;
+#pragma unroll 4
+    for (int k = 0; k < iters; ++k) {
+        a0 = a0 * m + c; a1 = a1 * m + c; a2 = a2 * m + c; a3 = a3 * m + c;
+        a4 = a4 * m + c; a5 = a5 * m + c; a6 = a6 * m + c; a7 = a7 * m + c;
+    }
+    const float sum = a0 + a1 + a2 + a3 + a4 + a5 + a6 + a7;
+    if (sum == 12345.678f) out[0] = sum;   // never true: keeps the chains alive
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -631,7 +647,7 @@ struct dsmd_ctx {
     int64_t excl_n_global = 0;
     double* partials = nullptr;
     int64_t partial_blocks = 0;
-    double* scalars = nullptr;      // 5 force scalars + 1 kinetic
+    double* scalars = nullptr;      // 6 force scalars + 1 kinetic
     Status* status = nullptr;
     Status* h_status = nullptr;     // pinned
     double* h_scalars = nullptr;    // pinned
@@ -762,7 +778,7 @@ int ensure_partials(dsmd_ctx* c, int64_t blocks) {
     if (blocks > c->partial_blocks) {
         if (c->partials) cudaFree(c->partials);
         c->partials = nullptr;
-        DSMD_CUDA(c, cudaMalloc(&c->partials, sizeof(double) * 5 * blocks));
+        DSMD_CUDA(c, cudaMalloc(&c->partials, sizeof(double) * 6 * blocks));
         c->partial_blocks = blocks;
     }
     return DSMD_OK;
@@ -1269,19 +1285,19 @@ int dsmd_compute_forces(dsmd_ctx* c, int phase, int want_energy, void* stream) {
     }
     DSMD_LAUNCHED(c);
     if (e) {
-        k_reduce_partials<5><<<1, kThreads, 0, s>>>(c->partials, static_cast<int>(blocks), c->scalars,
+        k_reduce_partials<6><<<1, kThreads, 0, s>>>(c->partials, static_cast<int>(blocks), c->scalars,
                                                    phase == DSMD_PHASE_BOUNDARY ? 1 : 0);
         DSMD_LAUNCHED(c);
     }
     return DSMD_OK;
 }
 
-int dsmd_read_scalars(dsmd_ctx* c, double out[5], void* stream) {
+int dsmd_read_scalars(dsmd_ctx* c, double out[6], void* stream) {
     if (!c || !out) return DSMD_ERR_INVALID;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    DSMD_CUDA(c, cudaMemcpyAsync(c->h_scalars, c->scalars, sizeof(double) * 5, cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaMemcpyAsync(c->h_scalars, c->scalars, sizeof(double) * 6, cudaMemcpyDeviceToHost, s));
     DSMD_CUDA(c, cudaStreamSynchronize(s));
-    for (int k = 0; k < 5; ++k) out[k] = c->h_scalars[k];
+    for (int k = 0; k < 6; ++k) out[k] = c->h_scalars[k];
     return DSMD_OK;
 }
 
@@ -1306,11 +1322,11 @@ int dsmd_kinetic_energy(dsmd_ctx* c, double* out, void* stream) {
     k_kinetic<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(static_cast<int>(c->n_owned), r[3], r[4], r[5], r[9],
                                                                  c->partials);
     DSMD_LAUNCHED(c);
-    k_reduce_partials<1><<<1, kThreads, 0, s>>>(c->partials, static_cast<int>(blocks), c->scalars + 5, 0);
+    k_reduce_partials<1><<<1, kThreads, 0, s>>>(c->partials, static_cast<int>(blocks), c->scalars + 6, 0);
     DSMD_LAUNCHED(c);
-    DSMD_CUDA(c, cudaMemcpyAsync(c->h_scalars + 5, c->scalars + 5, sizeof(double), cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaMemcpyAsync(c->h_scalars + 6, c->scalars + 6, sizeof(double), cudaMemcpyDeviceToHost, s));
     DSMD_CUDA(c, cudaStreamSynchronize(s));
-    *out = c->h_scalars[5];
+    *out = c->h_scalars[6];
     return DSMD_OK;
 }
 
@@ -1383,7 +1399,7 @@ int dsmd_run_nve(dsmd_ctx* c, int64_t n_steps, double dt, double f2a, double hi_
 }
 
 int dsmd_forces_host(dsmd_ctx* c, const double* x, const double* y, const double* z, int rebuild, double* fx,
-                     double* fy, double* fz, double* out5, void* stream) {
+                     double* fy, double* fz, double* out6, void* stream) {
     if (!c || !x || !y || !z || !fx || !fy || !fz) return DSMD_ERR_INVALID;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     { const int rc = dsmd_upload_positions(c, x, y, z, s); if (rc) return rc; }
@@ -1394,13 +1410,25 @@ int dsmd_forces_host(dsmd_ctx* c, const double* x, const double* y, const double
         const int rc = pack_impl(c, 0, c->n_total, false, 0.0, 0.0, s);
         if (rc) return rc;
     }
-    { const int rc = dsmd_compute_forces(c, DSMD_PHASE_FULL, out5 ? 1 : 0, s); if (rc) return rc; }
+    { const int rc = dsmd_compute_forces(c, DSMD_PHASE_FULL, out6 ? 1 : 0, s); if (rc) return rc; }
     double* dst[3] = {fx, fy, fz};
     for (int a = 0; a < 3; ++a)
         DSMD_CUDA(c, cudaMemcpyAsync(dst[a], c->real[c->cur][DSMD_FX + a], sizeof(double) * c->n_owned,
                                      cudaMemcpyDeviceToHost, s));
-    if (out5) return dsmd_read_scalars(c, out5, s);
+    if (out6) return dsmd_read_scalars(c, out6, s);
     DSMD_CUDA(c, cudaStreamSynchronize(s));
+    return DSMD_OK;
+}
+
+int dsmd_fma_probe(dsmd_ctx* c, int iters, double* flops, void* stream) {
+    if (!c || iters <= 0 || !flops) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int sms = 0;
+    DSMD_CUDA(c, cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device));
+    const int blocks = sms * 8;
+    k_fma_probe<<<blocks, 256, 0, s>>>(iters, 1.0f, reinterpret_cast<float*>(c->flag));
+    DSMD_LAUNCHED(c);
+    *flops = static_cast<double>(blocks) * 256.0 * static_cast<double>(iters) * 8.0 * 2.0;
     return DSMD_OK;
 }
 

@@ -144,9 +144,10 @@ int dsmd_max_displacement_sq(dsmd_ctx* ctx, double* out, void* stream);
 int dsmd_compute_forces(dsmd_ctx* ctx, int phase, int want_energy, void* stream);
 
 /* get_potential_energy / get_virial / get_virial_diag (include/force_calculator.h:41-68): this rank's sums of the last
- * evaluation with want_energy (an owned-ghost pair counts half on each rank). out = {PE, W, Wxx, Wyy, Wzz}.
+ * evaluation with want_energy (an owned-ghost pair counts half on each rank). out = {PE, W, Wxx, Wyy, Wzz, pairs}:
+ * pairs = how many pairs were inside the cutoff (the count of ForceCalculator::get_lj_pair_counts, summed).
  * Synchronises `stream`. */
-int dsmd_read_scalars(dsmd_ctx* ctx, double out[5], void* stream);
+int dsmd_read_scalars(dsmd_ctx* ctx, double out[6], void* stream);
 
 /* Velocity Verlet halves (launch_vv_step1_kernel / launch_vv_step2_kernel, src/integrator_kernels.cu:149-208):
  * half 1: v += dt/2 f/m c; x += dt v (and packs positions, see dsmd_pack_positions); half 2: v += dt/2 f/m c. */
@@ -164,13 +165,17 @@ int dsmd_run_nve(dsmd_ctx* ctx, int64_t n_steps, double dt, double force_to_acce
                  int64_t* n_rebuilds, double* worst_disp_sq, void* stream);
 
 /* One force evaluation with host buffers, as a force-provider plugin is called: uploads positions (context order),
- * packs, evaluates, downloads forces (and scalars when out5 != NULL). Rebuilds the list first when rebuild != 0.
+ * packs, evaluates, downloads forces (and the six scalars of dsmd_read_scalars when out6 != NULL). Rebuilds the list first when rebuild != 0.
  * Synchronises. */
 int dsmd_forces_host(dsmd_ctx* ctx, const double* x, const double* y, const double* z, int rebuild, double* fx,
-                     double* fy, double* fz, double* out5, void* stream);
+                     double* fy, double* fz, double* out6, void* stream);
 
 /* Kernel launches issued by this context so far (benchmark bookkeeping). */
 int64_t dsmd_launch_count(const dsmd_ctx* ctx);
+
+/* Queues a kernel of independent fp32 FMA chains on every SM and returns its flop count; the caller times it to get the
+ * fp32 CUDA-core peak of this device (the compute-roofline denominator of the pair kernel). No reference counterpart. */
+int dsmd_fma_probe(dsmd_ctx* ctx, int iters, double* flops, void* stream);
 
 /* -- halo (ghost atoms) ----------------------------------------------------------------------------------------------- */
 

@@ -349,6 +349,14 @@ class RefCase:
     def build_list(self):
         return self.L.dsmd_ref_build_list(self.h)
 
+    def update_positions(self, x, y, z):
+        x, y, z = _f64(x), _f64(y), _f64(z)
+        self.L.dsmd_ref_update_positions(self.h, _ptr(x, ctypes.c_double), _ptr(y, ctypes.c_double),
+                                         _ptr(z, ctypes.c_double))
+
+    def needs_rebuild(self):
+        return bool(self.L.dsmd_ref_needs_rebuild(self.h))
+
     def pair_counts(self):
         return int(self.L.dsmd_ref_pairs_inside_list(self.h)), int(self.L.dsmd_ref_pairs_inside_cutoff(self.h))
 

@@ -157,6 +157,20 @@ void dsmd_ref_set_particles(void* h, long n_total, long n_local, const double* x
     c->n_local = static_cast<size_t>(n_local);
 }
 
+// New positions for the atoms already set (same order); everything else is kept.
+void dsmd_ref_update_positions(void* h, const double* x, const double* y, const double* z) {
+    ParticleData& p = static_cast<RefCase*>(h)->system.particles;
+    for (size_t i = 0; i < p.num_particles; ++i) { p.x[i] = x[i]; p.y[i] = y[i]; p.z[i] = z[i]; }
+}
+
+// SpatialVerletList::needs_rebuild (src/neighbor_list_cpu.cpp:205-218): largest owned displacement since the last build
+// above (skin / 2)^2.
+int dsmd_ref_needs_rebuild(void* h) {
+    auto* c = static_cast<RefCase*>(h);
+    if (!c->list) return 1;
+    return c->list->needs_rebuild(c->system.particles, c->system.box, c->n_local) ? 1 : 0;
+}
+
 // eps / sig: full symmetric [ntypes x ntypes] matrices (what ForceFieldParams::epsilon_mixed / sigma_mixed hold
 // after mixing or after an explicit [pair_parameters] table). switch_distance <= 0: plain truncation.
 void dsmd_ref_set_force_field(void* h, int ntypes, const double* eps, const double* sig, double switch_distance) {

@@ -115,6 +115,7 @@ def test_forces_energy_virial_match_oracle_and_golden(cuda_device, name):
     assert abs(sc["virial"] - sc_o["virial"]) <= SCALAR_RTOL * abs(sc_o["virial"])
     assert np.allclose(sc["virial_diag"], sc_o["virial_diag"], rtol=5e-6)
     assert abs(sc["virial_diag"].sum() - sc["virial"]) <= 1e-7 * abs(sc["virial"])   # fp32 per-atom partial sums
+    assert sc["pairs_in_cutoff"] == sc_o["pairs_in_cutoff"]
     # against the reference CPU code's own output
     g = np.load(os.path.join(GOLDEN, name + ".npz"))
     if s.coulomb:
@@ -293,7 +294,7 @@ def test_host_buffer_force_call(cuda_device):
     p = s.pos[order]
     x, y, z = (np.ascontiguousarray(p[:, k]) for k in range(3))
     fx, fy, fz = np.zeros(s.n), np.zeros(s.n), np.zeros(s.n)
-    sc = np.zeros(5)
+    sc = np.zeros(6)
     ctx.forces_host(x, y, z, fx, fy, fz, rebuild=False, scalars=sc)
     f = np.empty((s.n, 3))
     f[order] = np.stack([fx, fy, fz], axis=1)
