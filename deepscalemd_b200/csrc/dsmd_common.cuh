@@ -30,6 +30,8 @@ struct Grid {
     float r2_list;      // (cutoff + skin)^2
     float band;         // |r2 - r2_list| below this is decided in fp64
     double r2_list_d;
+    float cellw[3];     // cell width per axis (length units)
+    float r_pad;        // list radius plus a rounding margin: the reach used to prune cell rows
 };
 
 struct Status {
@@ -73,6 +75,55 @@ __device__ __forceinline__ unsigned int to_fixed(double v, int axis, const Grid&
 
 __device__ __forceinline__ float fixed_delta(unsigned int a, unsigned int b, float scale) {
     return static_cast<float>(static_cast<int>(a - b)) * scale;
+}
+
+// The x cells of the cell row (cy + dy, cz + dz) that can hold a partner of the atom `pi` (home cell cx, cy, cz): the
+// row is skipped when its distance from the atom in the y-z plane already exceeds the list radius; otherwise the
+// x window is the chord of the list sphere at that distance, never wider than the stencil. One range [a0, b0], or two
+// when the window crosses the periodic boundary ([a1, b1] is empty otherwise).
+struct RowWindow {
+    int a0, b0, a1, b1;
+};
+
+__device__ __forceinline__ bool row_window(const Grid& g, const int4& pi, int cy, int cz, int dy, int dz,
+                                           RowWindow& w) {
+    const unsigned ux = static_cast<unsigned>(pi.x), uy = static_cast<unsigned>(pi.y), uz = static_cast<unsigned>(pi.z);
+    // position inside the home cell, in units of the cell width (0 .. 1)
+    const float ty = __uint2float_rn(g.wrap[1] ? uy : uy << 1) * (static_cast<float>(g.nc[1]) * 2.3283064e-10f);
+    const float tz = __uint2float_rn(g.wrap[2] ? uz : uz << 1) * (static_cast<float>(g.nc[2]) * 2.3283064e-10f);
+    // relative to the integer home cell (the float product may round across a cell boundary: clamp, never re-floor)
+    const float fy = fminf(fmaxf(ty - static_cast<float>(cy), 0.f), 1.f);
+    const float fz = fminf(fmaxf(tz - static_cast<float>(cz), 0.f), 1.f);
+    float gy = dy > 0 ? (static_cast<float>(dy) - fy) : (dy < 0 ? (fy - static_cast<float>(dy + 1)) : 0.f);
+    float gz = dz > 0 ? (static_cast<float>(dz) - fz) : (dz < 0 ? (fz - static_cast<float>(dz + 1)) : 0.f);
+    gy = fmaxf(gy - 1e-4f, 0.f) * g.cellw[1];   // 1e-4 of a cell: rounding of the in-cell position
+    gz = fmaxf(gz - 1e-4f, 0.f) * g.cellw[2];
+    const float d2 = gy * gy + gz * gz;
+    const float reach2 = g.r_pad * g.r_pad;
+    if (d2 >= reach2) return false;
+    float hw = sqrtf(reach2 - d2);
+    hw = fminf(hw, static_cast<float>(g.stencil) * g.cellw[0] * 0.9999999f);
+    const unsigned hw_fixed = static_cast<unsigned>(hw / g.scale[0]) + 1u;
+    w.a1 = 0;
+    w.b1 = -1;
+    if (g.wrap[0]) {
+        const int c_lo = static_cast<int>(cell_of(ux - hw_fixed, 1, g.nc[0]));
+        const int c_hi = static_cast<int>(cell_of(ux + hw_fixed, 1, g.nc[0]));
+        if (c_lo <= c_hi) {
+            w.a0 = c_lo;
+            w.b0 = c_hi;
+        } else {
+            w.a0 = 0;
+            w.b0 = c_hi;
+            w.a1 = c_lo;
+            w.b1 = g.nc[0] - 1;
+        }
+    } else {
+        const long long lo = static_cast<long long>(ux) - hw_fixed, hi = static_cast<long long>(ux) + hw_fixed;
+        w.a0 = static_cast<int>(cell_of(static_cast<unsigned>(lo < 0 ? 0 : lo), 0, g.nc[0]));
+        w.b0 = static_cast<int>(cell_of(static_cast<unsigned>(hi > 2147483647ll ? 2147483647ll : hi), 0, g.nc[0]));
+    }
+    return true;
 }
 #endif
 

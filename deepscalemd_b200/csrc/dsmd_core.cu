@@ -111,8 +111,13 @@ __global__ void k_reorder(Grid g, int first, int n_owned, int n_total, const uns
     const int k_here = static_cast<int>(key[t]);
     const int k_prev = t == 0 ? (first == 0 ? -1 : g.ncells - 1) : static_cast<int>(key[t - 1]);
     for (int c = k_prev + 1; c <= k_here; ++c) cell_start[c] = s;
-    if (s == n_total - 1)
-        for (int c = k_here + 1; c <= 2 * g.ncells; ++c) cell_start[c] = n_total;
+}
+
+// Cells behind the last occupied one (and, when only owned atoms were sorted, the whole ghost half) start at the end.
+__global__ void k_cell_tail(const unsigned* __restrict__ key, int n_sorted, int n_total, int table_size,
+                            int* __restrict__ cell_start) {
+    const int c = static_cast<int>(key[n_sorted - 1]) + 1 + blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < table_size) cell_start[c] = n_total;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -150,7 +155,6 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_owned) return;
     const int4 pi = pq[i];
-    const int cx = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.x), g.wrap[0], g.nc[0]));
     const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
     const int cz = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.z), g.wrap[2], g.nc[2]));
     const int S = g.stencil;
@@ -176,15 +180,9 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
                 if (g.wrap[1]) { if (yc < 0) yc += g.nc[1]; else if (yc >= g.nc[1]) yc -= g.nc[1]; }
                 else if (yc < 0 || yc >= g.nc[1]) continue;
                 const int row = seg * g.ncells + (zc * g.nc[1] + yc) * g.nc[0];
-                // x run [cx - S, cx + S]: one range, or two when it crosses the periodic boundary
-                int a0 = cx - S, b0 = cx + S, a1 = 0, b1 = -1;
-                if (g.wrap[0]) {
-                    if (a0 < 0) { a1 = a0 + g.nc[0]; b1 = g.nc[0] - 1; a0 = 0; }
-                    else if (b0 >= g.nc[0]) { a1 = 0; b1 = b0 - g.nc[0]; b0 = g.nc[0] - 1; }
-                } else {
-                    a0 = max(a0, 0);
-                    b0 = min(b0, g.nc[0] - 1);
-                }
+                dsmd::RowWindow win;
+                if (!dsmd::row_window(g, pi, cy, cz, dy, dz, win)) continue;
+                const int a0 = win.a0, b0 = win.b0, a1 = win.a1, b1 = win.b1;
                 for (int part = 0; part < 2; ++part) {
                     const int a = part == 0 ? a0 : a1, b = part == 0 ? b0 : b1;
                     if (b < a) continue;
@@ -387,12 +385,90 @@ __device__ __forceinline__ float fast_rcp(float v) {
     return r * (2.0f - v * r);   // one Newton step: full single precision
 }
 
-// One thread per owned atom, 32 atoms of a slice per warp: entry k of the slice is one coalesced 128-byte read, the
-// partner's int4 comes through the read-only path. Every listed pair is evaluated from the side of each of its owned
-// atoms (full list), so forces need no scatter and no atomics, and the summation order is fixed (bitwise reproducible).
-// Energy and virial take half of every directed entry; an owned-ghost pair is then counted half on each rank, as the
-// reference's list kernel does (src/force_calculator_cuda.cu:1784-1789).
+// One pair of the list, evaluated from atom i's side: adds to the force (and energy / virial) accumulators.
 template <bool COULOMB, bool ENERGY, bool MULTI, bool SWITCH>
+struct PairAccumulator {
+    float ax = 0.f, ay = 0.f, az = 0.f;
+    float e_sum = 0.f, w_sum = 0.f, wx = 0.f, wy = 0.f, wz = 0.f, n_in = 0.f;
+
+    __device__ __forceinline__ void add(const PairParams& p, const int4& pi, const int4& pj, float qi, float qj,
+                                        bool excluded, const float2* s_c6c12, const float4* s_ewald, float2 single,
+                                        int trow) {
+        const float dx = dsmd::fixed_delta(pi.x, pj.x, p.scale[0]);
+        const float dy = dsmd::fixed_delta(pi.y, pj.y, p.scale[1]);
+        const float dz = dsmd::fixed_delta(pi.z, pj.z, p.scale[2]);
+        const float r2 = dx * dx + dy * dy + dz * dz;
+        if (r2 < p.rc2 && r2 >= 1e-10f) {
+            float fmag = 0.f, epair = 0.f;
+            const float r2inv = fast_rcp(r2);
+            if (!excluded) {
+                const float2 c = MULTI ? s_c6c12[trow + pj.w] : single;
+                const float r6 = r2inv * r2inv * r2inv;
+                const float rep = c.y * r6 * r6, att = c.x * r6;
+                float f = r2inv * (12.f * rep - 6.f * att);
+                float u = rep - att;
+                if (SWITCH) {
+                    if (r2 > p.rs2) {
+                        const float a = p.rc2 - r2, b = p.rc2 + 2.f * r2 - 3.f * p.rs2;
+                        const float sw = a * a * b * p.inv_denom;
+                        f = sw * f + 12.f * u * a * (r2 - p.rs2) * p.inv_denom;
+                        u *= sw;
+                    }
+                }
+                fmag = f;
+                if (ENERGY) epair = u;
+            }
+            if (COULOMB) {
+                const float qq = qi * qj;
+                const unsigned shifted = __float_as_uint(r2) - dsmd::kEwaldBaseBits;
+                const unsigned idx = shifted >> dsmd::kEwaldIndexShift;
+                float ff, ef = 0.f;
+                if (idx < static_cast<unsigned>(p.ewald_intervals)) {
+                    const float t = __uint_as_float(0x3F800000u | ((shifted << dsmd::kEwaldBits) & 0x007FFFFFu)) - 1.0f;
+                    const float4 cf = s_ewald[2 * idx];
+                    ff = ((cf.w * t + cf.z) * t + cf.y) * t + cf.x;
+                    if (ENERGY) {
+                        const float4 ce = s_ewald[2 * idx + 1];
+                        ef = ((ce.w * t + ce.z) * t + ce.y) * t + ce.x;
+                    }
+                } else {   // below the table (r^2 < 0.5): analytic
+                    const float r = sqrtf(r2), ar = p.alpha * r;
+                    const float ec = erfcf(ar) / r;
+                    ff = (ec + p.two_alpha_sqrtpi * __expf(-ar * ar)) * r2inv;
+                    ef = ec;
+                }
+                if (excluded) {   // the pair's 1/r is not part of the Ewald sum: erfc -> -erf
+                    const float rinv = rsqrtf(r2);
+                    ff -= rinv * r2inv;
+                    ef -= rinv;
+                }
+                fmag += qq * ff;
+                if (ENERGY) epair += qq * ef;
+            }
+            ax += fmag * dx;
+            ay += fmag * dy;
+            az += fmag * dz;
+            if (ENERGY) {
+                e_sum += epair;
+                w_sum += fmag * r2;
+                wx += fmag * dx * dx;
+                wy += fmag * dy * dy;
+                wz += fmag * dz * dz;
+                n_in += 1.f;
+            }
+        }
+    }
+};
+
+// One thread per owned atom, 32 atoms of a slice per warp: entry k of the slice is one coalesced 128-byte read (streamed
+// past L2 with an evict-first hint, so that the positions stay resident there), the partner's int4 comes through the
+// read-only path. The loop runs four entries at a time with the next four entries and the current four positions in
+// flight before any arithmetic starts; rows are padded to the loop's stride with the atom's own index, which the
+// r^2 >= 1e-10 test discards. Every listed pair is evaluated from the side of each of its owned atoms (full list), so
+// forces need no scatter and no atomics, and the summation order is fixed (bitwise reproducible). Energy and virial
+// take half of every directed entry; an owned-ghost pair is then counted half on each rank, as the reference's list
+// kernel does (src/force_calculator_cuda.cu:1784-1789).
+template <bool COULOMB, bool ENERGY, bool MULTI, bool SWITCH, bool EXCL>
 __global__ void __launch_bounds__(kPairThreads)
 k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __restrict__ qf,
        const unsigned* __restrict__ nbr, int stride, const int* __restrict__ deg, const int* __restrict__ deg_int,
@@ -408,101 +484,51 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
     if (MULTI || COULOMB) __syncthreads();
 
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    float ax = 0.f, ay = 0.f, az = 0.f;
-    float e_sum = 0.f, w_sum = 0.f, wx = 0.f, wy = 0.f, wz = 0.f, n_in = 0.f;
+    PairAccumulator<COULOMB, ENERGY, MULTI, SWITCH> acc;
     if (i < n_owned) {
         const int4 pi = pq[i];
         const float qi = COULOMB ? p.kq * qf[i] : 0.f;
         const float2 single = MULTI ? make_float2(0.f, 0.f) : p.c6c12[0];
         const int trow = MULTI ? pi.w * p.ntypes : 0;
-        const size_t base = (static_cast<size_t>(i >> 5) * stride) * 32 + (i & 31);
         const int k_begin = phase == DSMD_PHASE_BOUNDARY ? deg_int[i] : 0;
         const int k_end = phase == DSMD_PHASE_INTERIOR ? deg_int[i] : deg[i];
-        const unsigned* row = nbr + base;
-#pragma unroll 2
-        for (int k = k_begin; k < k_end; ++k) {
-            const unsigned e = row[static_cast<size_t>(k) * 32];
-            const int j = static_cast<int>(e & kIndexMask);
-            const int4 pj = __ldg(&pq[j]);
-            const float dx = dsmd::fixed_delta(pi.x, pj.x, p.scale[0]);
-            const float dy = dsmd::fixed_delta(pi.y, pj.y, p.scale[1]);
-            const float dz = dsmd::fixed_delta(pi.z, pj.z, p.scale[2]);
-            const float r2 = dx * dx + dy * dy + dz * dz;
-            if (r2 < p.rc2 && r2 >= 1e-10f) {
-                const bool excluded = (e & kExclBit) != 0u;
-                float fmag = 0.f, epair = 0.f;
-                const float r2inv = fast_rcp(r2);
-                if (!excluded) {
-                    const float2 c = MULTI ? s_c6c12[trow + pj.w] : single;
-                    const float r6 = r2inv * r2inv * r2inv;
-                    const float rep = c.y * r6 * r6, att = c.x * r6;
-                    float f = r2inv * (12.f * rep - 6.f * att);
-                    float u = rep - att;
-                    if (SWITCH) {
-                        if (r2 > p.rs2) {
-                            const float a = p.rc2 - r2, b = p.rc2 + 2.f * r2 - 3.f * p.rs2;
-                            const float sw = a * a * b * p.inv_denom;
-                            f = sw * f + 12.f * u * a * (r2 - p.rs2) * p.inv_denom;
-                            u *= sw;
-                        }
-                    }
-                    fmag = f;
-                    if (ENERGY) epair = u;
-                }
-                if (COULOMB) {
-                    const float qq = qi * __ldg(&qf[j]);
-                    const unsigned shifted = __float_as_uint(r2) - dsmd::kEwaldBaseBits;
-                    const unsigned idx = shifted >> dsmd::kEwaldIndexShift;
-                    float ff, ef = 0.f;
-                    if (idx < static_cast<unsigned>(p.ewald_intervals)) {
-                        const float t =
-                            __uint_as_float(0x3F800000u | ((shifted << dsmd::kEwaldBits) & 0x007FFFFFu)) - 1.0f;
-                        const float4 cf = s_ewald[2 * idx];
-                        ff = ((cf.w * t + cf.z) * t + cf.y) * t + cf.x;
-                        if (ENERGY) {
-                            const float4 ce = s_ewald[2 * idx + 1];
-                            ef = ((ce.w * t + ce.z) * t + ce.y) * t + ce.x;
-                        }
-                    } else {   // below the table (r^2 < 0.5): analytic
-                        const float r = sqrtf(r2), ar = p.alpha * r;
-                        const float ec = erfcf(ar) / r;
-                        ff = (ec + p.two_alpha_sqrtpi * __expf(-ar * ar)) * r2inv;
-                        ef = ec;
-                    }
-                    if (excluded) {   // the pair's 1/r is not part of the Ewald sum: erfc -> -erf
-                        const float rinv = rsqrtf(r2);
-                        ff -= rinv * r2inv;
-                        ef -= rinv;
-                    }
-                    fmag += qq * ff;
-                    if (ENERGY) epair += qq * ef;
-                }
-                ax += fmag * dx;
-                ay += fmag * dy;
-                az += fmag * dz;
-                if (ENERGY) {
-                    e_sum += epair;
-                    w_sum += fmag * r2;
-                    wx += fmag * dx * dx;
-                    wy += fmag * dy * dy;
-                    wz += fmag * dz * dz;
-                    n_in += 1.f;
-                }
+        const unsigned* row = nbr + (static_cast<size_t>(i >> 5) * stride) * 32 + (i & 31);
+        const unsigned self = static_cast<unsigned>(i);
+        constexpr int U = 4;
+        unsigned e[U], e_next[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) e_next[u] = (k_begin + u < k_end) ? __ldcs(row + static_cast<size_t>(k_begin + u) * 32) : self;
+        for (int k = k_begin; k < k_end; k += U) {
+            int4 pj[U];
+            float qj[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                e[u] = e_next[u];
+                pj[u] = __ldg(&pq[EXCL ? (e[u] & kIndexMask) : e[u]]);
+                if (COULOMB) qj[u] = __ldg(&qf[EXCL ? (e[u] & kIndexMask) : e[u]]);
             }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                e_next[u] = (k + U + u < k_end) ? __ldcs(row + static_cast<size_t>(k + U + u) * 32) : self;
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                acc.add(p, pi, pj[u], qi, COULOMB ? qj[u] : 0.f, EXCL && (e[u] & kExclBit) != 0u, s_c6c12, s_ewald, single,
+                        trow);
         }
         if (phase == DSMD_PHASE_BOUNDARY) {
-            fx[i] += static_cast<double>(ax);
-            fy[i] += static_cast<double>(ay);
-            fz[i] += static_cast<double>(az);
+            fx[i] += static_cast<double>(acc.ax);
+            fy[i] += static_cast<double>(acc.ay);
+            fz[i] += static_cast<double>(acc.az);
         } else {
-            fx[i] = static_cast<double>(ax);
-            fy[i] = static_cast<double>(ay);
-            fz[i] = static_cast<double>(az);
+            fx[i] = static_cast<double>(acc.ax);
+            fy[i] = static_cast<double>(acc.ay);
+            fz[i] = static_cast<double>(acc.az);
         }
     }
     if (ENERGY) {
-        double v[6] = {0.5 * static_cast<double>(e_sum), 0.5 * static_cast<double>(w_sum), 0.5 * static_cast<double>(wx),
-                       0.5 * static_cast<double>(wy), 0.5 * static_cast<double>(wz), 0.5 * static_cast<double>(n_in)};
+        double v[6] = {0.5 * static_cast<double>(acc.e_sum), 0.5 * static_cast<double>(acc.w_sum),
+                       0.5 * static_cast<double>(acc.wx),    0.5 * static_cast<double>(acc.wy),
+                       0.5 * static_cast<double>(acc.wz),    0.5 * static_cast<double>(acc.n_in)};
         block_sum_to_partials<6>(v, partials);
     }
 }
@@ -745,6 +771,12 @@ int make_grid(dsmd_ctx* c) {
     g.r2_list = static_cast<float>(R * R);
     g.r2_list_d = R * R;
     g.band = static_cast<float>(8.0 * R * max_scale + 16.0 * R * R * 5.9604645e-8);
+    double max_len = 0.0;
+    for (int a = 0; a < 3; ++a) {
+        g.cellw[a] = static_cast<float>(1.0 / (g.inv_len[a] * g.nc[a]));
+        max_len = std::max(max_len, 1.0 / g.inv_len[a]);
+    }
+    g.r_pad = static_cast<float>(R * (1.0 + 1e-4) + 8.0 * max_len * 1.2e-7);
     c->grid_valid = true;
     return DSMD_OK;
 }
@@ -819,6 +851,10 @@ int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s) {
             c->val[1], arrays_of(c, from), arrays_of(c, to), c->type[from], c->gid[from], c->type[to], c->gid[to], c->pq,
             c->qf, c->ref[0], c->ref[1], c->ref[2], c->cell_start, c->ghost_slot);
         DSMD_LAUNCHED(c);
+        const int table = 2 * c->grid.ncells + 1;
+        k_cell_tail<<<blocks_for(table, kThreads), kThreads, 0, s>>>(c->key[1], static_cast<int>(n),
+                                                                  static_cast<int>(c->n_total), table, c->cell_start);
+        DSMD_LAUNCHED(c);
     }
     c->cur = to;
     return DSMD_OK;
@@ -839,14 +875,14 @@ void launch_pair(dsmd_ctx* c, const PairParams& p, int phase, bool sw, cudaStrea
     double* fx = c->real[c->cur][DSMD_FX];
     double* fy = c->real[c->cur][DSMD_FY];
     double* fz = c->real[c->cur][DSMD_FZ];
-    if (sw)
-        k_pair<COULOMB, ENERGY, MULTI, true><<<blocks, kPairThreads, smem, s>>>(
-            p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, fx, fy, fz,
-            c->partials);
-    else
-        k_pair<COULOMB, ENERGY, MULTI, false><<<blocks, kPairThreads, smem, s>>>(
-            p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, fx, fy, fz,
-            c->partials);
+    const bool ex = c->excl_off != nullptr;
+#define DSMD_PAIR_LAUNCH(SW, EX)                                                                                      \
+    k_pair<COULOMB, ENERGY, MULTI, SW, EX><<<blocks, kPairThreads, smem, s>>>(                                          \
+        p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, fx, fy, fz,        \
+        c->partials)
+    if (sw) { if (ex) DSMD_PAIR_LAUNCH(true, true); else DSMD_PAIR_LAUNCH(true, false); }
+    else    { if (ex) DSMD_PAIR_LAUNCH(false, true); else DSMD_PAIR_LAUNCH(false, false); }
+#undef DSMD_PAIR_LAUNCH
 }
 
 }  // namespace

@@ -74,8 +74,12 @@ __global__ void k_edge_gather(Grid g, int n, const unsigned* __restrict__ key, c
     const int k_here = static_cast<int>(key[s]);
     const int k_prev = s == 0 ? -1 : static_cast<int>(key[s - 1]);
     for (int c = k_prev + 1; c <= k_here; ++c) cell_start[c] = s;
-    if (s == n - 1)
-        for (int c = k_here + 1; c <= g.ncells; ++c) cell_start[c] = n;
+}
+
+// Cells behind the last occupied one start at the end of the atom array.
+__global__ void k_edge_cell_tail(const unsigned* __restrict__ key, int n, int table_size, int* __restrict__ cell_start) {
+    const int c = static_cast<int>(key[n - 1]) + 1 + blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < table_size) cell_start[c] = n;
 }
 
 struct SearchArgs {
@@ -116,8 +120,7 @@ __global__ void __launch_bounds__(kSearchThreads) k_edge_search(Grid g, SearchAr
     unsigned rechecked = 0;
     if (is_centre) {
         const bool check_nb = a.ok && a.row == 1;
-        const int cx = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.x), g.wrap[0], g.nc[0]));
-        const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
+            const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
         const int cz = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.z), g.wrap[2], g.nc[2]));
         const int S = g.stencil;
         for (int dz = -S; dz <= S; ++dz) {
@@ -129,14 +132,9 @@ __global__ void __launch_bounds__(kSearchThreads) k_edge_search(Grid g, SearchAr
                 if (g.wrap[1]) { if (yc < 0) yc += g.nc[1]; else if (yc >= g.nc[1]) yc -= g.nc[1]; }
                 else if (yc < 0 || yc >= g.nc[1]) continue;
                 const int row = (zc * g.nc[1] + yc) * g.nc[0];
-                int a0 = cx - S, b0 = cx + S, a1 = 0, b1 = -1;
-                if (g.wrap[0]) {
-                    if (a0 < 0) { a1 = a0 + g.nc[0]; b1 = g.nc[0] - 1; a0 = 0; }
-                    else if (b0 >= g.nc[0]) { a1 = 0; b1 = b0 - g.nc[0]; b0 = g.nc[0] - 1; }
-                } else {
-                    a0 = max(a0, 0);
-                    b0 = min(b0, g.nc[0] - 1);
-                }
+                dsmd::RowWindow win;
+                if (!dsmd::row_window(g, pi, cy, cz, dy, dz, win)) continue;
+                const int a0 = win.a0, b0 = win.b0, a1 = win.a1, b1 = win.b1;
                 for (int part = 0; part < 2; ++part) {
                     const int lo = part == 0 ? a0 : a1, hi = part == 0 ? b0 : b1;
                     if (hi < lo) continue;
@@ -397,6 +395,12 @@ int edge_grid(dsmd_edges* e, Grid& g, const double lo[3], const double hi[3], bo
     g.r2_list = static_cast<float>(cutoff * cutoff);
     g.r2_list_d = cutoff * cutoff;
     g.band = static_cast<float>(8.0 * cutoff * max_scale + 16.0 * cutoff * cutoff * 5.9604645e-8);
+    double max_len = 0.0;
+    for (int a = 0; a < 3; ++a) {
+        g.cellw[a] = static_cast<float>(len[a] / g.nc[a]);
+        max_len = std::max(max_len, len[a]);
+    }
+    g.r_pad = static_cast<float>(cutoff * (1.0 + 1e-4) + 8.0 * max_len * 1.2e-7);
     return DSMD_OK;
 }
 
@@ -430,7 +434,9 @@ int edge_search(dsmd_edges* e, const Grid& g, const double* d_x, const double* d
                                                  static_cast<int>(n), 0, bits, s));
     k_edge_gather<<<blocks_for(n, kThreads), kThreads, 0, s>>>(g, static_cast<int>(n), e->key[1], e->val[1], d_x, d_y,
                                                               d_z, e->pq, e->slot_of, e->cell_start);
-    e->launches += 2;
+    k_edge_cell_tail<<<blocks_for(g.ncells + 1, kThreads), kThreads, 0, s>>>(e->key[1], static_cast<int>(n), g.ncells + 1,
+                                                                           e->cell_start);
+    e->launches += 3;
     if (e->stride == 0) {
         const double expect = density_hint * 4.18879020479 * g.r2_list_d * std::sqrt(g.r2_list_d);
         e->stride = (std::max(16, static_cast<int>(expect * 1.5) + 16) + 3) & ~3;

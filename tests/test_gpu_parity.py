@@ -115,7 +115,8 @@ def test_forces_energy_virial_match_oracle_and_golden(cuda_device, name):
     assert abs(sc["virial"] - sc_o["virial"]) <= SCALAR_RTOL * abs(sc_o["virial"])
     assert np.allclose(sc["virial_diag"], sc_o["virial_diag"], rtol=5e-6)
     assert abs(sc["virial_diag"].sum() - sc["virial"]) <= 1e-7 * abs(sc["virial"])   # fp32 per-atom partial sums
-    assert sc["pairs_in_cutoff"] == sc_o["pairs_in_cutoff"]
+    # the force cutoff is tested in fp32: a pair within ~1e-7 (relative) of rc^2 may fall on the other side
+    assert abs(sc["pairs_in_cutoff"] - sc_o["pairs_in_cutoff"]) <= max(2, 5e-6 * sc_o["pairs_in_cutoff"])
     # against the reference CPU code's own output
     g = np.load(os.path.join(GOLDEN, name + ".npz"))
     if s.coulomb:
