@@ -25,7 +25,7 @@ SYMBOLS = [
     "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
     "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned",
     "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq",
-    "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_run_nve",
+    "dsmd_displacement_word", "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_run_nve",
     "dsmd_forces_host", "dsmd_launch_count", "dsmd_fma_probe", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
     "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_edges_create", "dsmd_edges_destroy",
     "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
@@ -294,10 +294,17 @@ class Context:
                                               c_int64(index_tensor.numel()), ctypes.byref(n), _stream_handle(stream)))
         return n.value
 
-    def halo_pack(self, index_tensor, count, shift, out_tensor, stream=None):
-        s = _arr(shift, np.float64)
-        self._check(self.lib.dsmd_halo_pack(self.h, c_void_p(index_tensor.data_ptr()), c_int64(count), _p(s),
+    def halo_pack(self, index_tensor, image_tensor, count, out_tensor, stream=None):
+        img = None if image_tensor is None else c_void_p(image_tensor.data_ptr())
+        self._check(self.lib.dsmd_halo_pack(self.h, c_void_p(index_tensor.data_ptr()), img, c_int64(count),
                                             c_void_p(out_tensor.data_ptr()), _stream_handle(stream)))
+
+    def displacement_word(self):
+        """The device word holding max displacement^2 (bits of a double) as a one-element int64 torch tensor."""
+        import torch
+        p = c_void_p()
+        self._check(self.lib.dsmd_displacement_word(self.h, ctypes.byref(p)))
+        return _tensor_from_ptr(p.value, (1,), torch.int64, torch.device("cuda", self.device))
 
     def halo_unpack(self, in_tensor, first_ghost, count, stream=None):
         self._check(self.lib.dsmd_halo_unpack(self.h, c_void_p(in_tensor.data_ptr()), c_int64(first_ghost),

@@ -157,7 +157,6 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
     const int4 pi = pq[i];
     const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
     const int cz = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.z), g.wrap[2], g.nc[2]));
-    const int S = g.stencil;
     const size_t base = (static_cast<size_t>(i >> 5) * stride) * 32 + (i & 31);
     int ex_begin = 0, ex_end = 0;
     if (excl.offsets) {
@@ -171,44 +170,34 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
     unsigned rechecked = 0;
     const int n_seg = n_total > n_owned ? 2 : 1;
     for (int seg = 0; seg < n_seg; ++seg) {
-        for (int dz = -S; dz <= S; ++dz) {
-            int zc = cz + dz;
-            if (g.wrap[2]) { if (zc < 0) zc += g.nc[2]; else if (zc >= g.nc[2]) zc -= g.nc[2]; }
-            else if (zc < 0 || zc >= g.nc[2]) continue;
-            for (int dy = -S; dy <= S; ++dy) {
-                int yc = cy + dy;
-                if (g.wrap[1]) { if (yc < 0) yc += g.nc[1]; else if (yc >= g.nc[1]) yc -= g.nc[1]; }
-                else if (yc < 0 || yc >= g.nc[1]) continue;
-                const int row = seg * g.ncells + (zc * g.nc[1] + yc) * g.nc[0];
-                dsmd::RowWindow win;
-                if (!dsmd::row_window(g, pi, cy, cz, dy, dz, win)) continue;
-                const int a0 = win.a0, b0 = win.b0, a1 = win.a1, b1 = win.b1;
-                for (int part = 0; part < 2; ++part) {
-                    const int a = part == 0 ? a0 : a1, b = part == 0 ? b0 : b1;
-                    if (b < a) continue;
-                    const int s_begin = cell_start[row + a], s_end = cell_start[row + b + 1];
-                    for (int s = s_begin; s < s_end; ++s) {
-                        const int4 pj = __ldg(&pq[s]);
-                        const float fx = dsmd::fixed_delta(pj.x, pi.x, g.scale[0]);
-                        const float fy = dsmd::fixed_delta(pj.y, pi.y, g.scale[1]);
-                        const float fz = dsmd::fixed_delta(pj.z, pi.z, g.scale[2]);
-                        const float r2 = fx * fx + fy * fy + fz * fz;
-                        if (r2 >= g.r2_list + g.band || s == i) continue;
-                        if (r2 >= g.r2_list - g.band) {
-                            ++rechecked;
-                            if (!within_list_fp64(g, x, y, z, i, s)) continue;
-                        }
-                        unsigned entry = static_cast<unsigned>(s);
-                        if (ex_end > ex_begin) {
-                            const int gj = gid[s];
-                            for (int e = ex_begin; e < ex_end; ++e)
-                                if (excl.partners[e] == gj) entry |= kExclBit;
-                        }
-                        if (count < stride) nbr[base + static_cast<size_t>(count) * 32] = entry;
-                        ++count;
-                    }
-                }
+        dsmd::CandidateRanges cand;
+        dsmd::collect_candidates(g, pi, cy, cz, seg * g.ncells, cell_start, cand);
+        int r = 0, off = cand.off[0], end = cand.total > 0 ? cand.end[0] : 0;
+        for (int t = 0; t < cand.total; ++t) {
+            while (t >= end) {
+                ++r;
+                off = cand.off[r];
+                end = cand.end[r];
             }
+            const int s = t + off;
+            const int4 pj = __ldg(&pq[s]);
+            const float fx = dsmd::fixed_delta(pj.x, pi.x, g.scale[0]);
+            const float fy = dsmd::fixed_delta(pj.y, pi.y, g.scale[1]);
+            const float fz = dsmd::fixed_delta(pj.z, pi.z, g.scale[2]);
+            const float r2 = fx * fx + fy * fy + fz * fz;
+            if (r2 >= g.r2_list + g.band || s == i) continue;
+            if (r2 >= g.r2_list - g.band) {
+                ++rechecked;
+                if (!within_list_fp64(g, x, y, z, i, s)) continue;
+            }
+            unsigned entry = static_cast<unsigned>(s);
+            if (ex_end > ex_begin) {
+                const int gj = gid[s];
+                for (int e = ex_begin; e < ex_end; ++e)
+                    if (excl.partners[e] == gj) entry |= kExclBit;
+            }
+            if (count < stride) nbr[base + static_cast<size_t>(count) * 32] = entry;
+            ++count;
         }
         if (seg == 0) interior = count;
     }
@@ -537,12 +526,18 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
 // kernels: ghosts
 // ---------------------------------------------------------------------------------------------------------------------
 
-__global__ void k_halo_pack(int count, const int* __restrict__ index, const double* __restrict__ x,
-                            const double* __restrict__ y, const double* __restrict__ z, double sx, double sy, double sz,
-                            double* __restrict__ out) {
+__global__ void k_halo_pack(int count, const int* __restrict__ index, const signed char* __restrict__ image,
+                            const double* __restrict__ x, const double* __restrict__ y, const double* __restrict__ z,
+                            double bx, double by, double bz, double* __restrict__ out) {
     const int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= count) return;
     const int s = index[k];
+    double sx = 0.0, sy = 0.0, sz = 0.0;
+    if (image) {
+        sx = image[3 * k] * bx;
+        sy = image[3 * k + 1] * by;
+        sz = image[3 * k + 2] * bz;
+    }
     out[3 * k] = x[s] + sx;
     out[3 * k + 1] = y[s] + sy;
     out[3 * k + 2] = z[s] + sz;
@@ -1470,16 +1465,22 @@ int dsmd_fma_probe(dsmd_ctx* c, int iters, double* flops, void* stream) {
 
 // ---- ghosts ---------------------------------------------------------------------------------------------------------
 
-int dsmd_halo_pack(dsmd_ctx* c, const int32_t* d_index, int64_t count, const double shift[3], double* d_out,
+int dsmd_halo_pack(dsmd_ctx* c, const int32_t* d_index, const int8_t* d_image, int64_t count, double* d_out,
                    void* stream) {
     if (!c || count < 0 || (count > 0 && (!d_index || !d_out))) return DSMD_ERR_INVALID;
     if (count == 0) return DSMD_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     double** r = c->real[c->cur];
-    k_halo_pack<<<blocks_for(count, kThreads), kThreads, 0, s>>>(static_cast<int>(count), d_index, r[0], r[1], r[2],
-                                                                shift ? shift[0] : 0.0, shift ? shift[1] : 0.0,
-                                                                shift ? shift[2] : 0.0, d_out);
+    k_halo_pack<<<blocks_for(count, kThreads), kThreads, 0, s>>>(static_cast<int>(count), d_index,
+                                                                reinterpret_cast<const signed char*>(d_image), r[0], r[1],
+                                                                r[2], c->box[0], c->box[1], c->box[2], d_out);
     DSMD_LAUNCHED(c);
+    return DSMD_OK;
+}
+
+int dsmd_displacement_word(dsmd_ctx* c, void** device_word) {
+    if (!c || !device_word) return DSMD_ERR_INVALID;
+    *device_word = &c->status->max_disp2;
     return DSMD_OK;
 }
 

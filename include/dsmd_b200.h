@@ -137,6 +137,11 @@ int dsmd_pack_positions(dsmd_ctx* ctx, int64_t first, int64_t count, void* strea
  * Synchronises `stream`. */
 int dsmd_max_displacement_sq(dsmd_ctx* ctx, double* out, void* stream);
 
+/* The device word behind it: the bit pattern of that non-negative double, 8 bytes. Bit patterns of non-negative doubles
+ * order like the values, so ranks can take a MAX over it as a 64-bit integer (CommBackend::unify_rebuild_decision,
+ * src/comm_backend.cpp:85) without a host round trip. Reset to zero by every list build. */
+int dsmd_displacement_word(dsmd_ctx* ctx, void** device_word);
+
 /* ForceCalculator::compute_forces / begin_forces_interior / finish_forces_boundary (include/force_calculator.h:24,
  * include/force_calculator_cuda.h:160-170): LJ (+ real-space Ewald) over the list. FULL and INTERIOR overwrite the
  * force arrays of the owned atoms (the reference clears, then adds); BOUNDARY adds the ghost-partner part.
@@ -182,8 +187,9 @@ int dsmd_fma_probe(dsmd_ctx* ctx, int iters, double* flops, void* stream);
 /* The data-plane half of MDSystem::exchange_halo_on_device (src/md_system.cpp:1448-1463); the transport between the
  * two calls is the caller's (NCCL send/recv).
  * pack: gathers positions of the owned atoms listed in device_send_index[0..count) into device_out as 3 doubles per
- * atom, adding shift[3] (the periodic image offset for that neighbour). */
-int dsmd_halo_pack(dsmd_ctx* ctx, const int32_t* device_send_index, int64_t count, const double shift[3],
+ * atom, adding device_image[3 * k + a] box lengths on axis a (the periodic image the receiving neighbour sees; NULL = no
+ * shift). One launch serves every neighbour: the caller lays the send list out neighbour after neighbour. */
+int dsmd_halo_pack(dsmd_ctx* ctx, const int32_t* device_send_index, const int8_t* device_image, int64_t count,
                    double* device_out, void* stream);
 /* unpack: writes `count` received positions (3 doubles each) to the ghosts first_ghost .. first_ghost + count of the
  * hand-in order, i.e. to slots ghost_slot[first_ghost + k], in both the double arrays and the fixed-point layout. */
