@@ -126,52 +126,6 @@ __device__ __forceinline__ bool row_window(const Grid& g, const int4& pi, int cy
     return true;
 }
 
-// The candidate slots of one atom as a short list of contiguous slot ranges (one or two per cell row of the stencil),
-// flattened: candidate number t (0 <= t < total) is slot t + off[r] for the range r with end[r - 1] <= t < end[r].
-// A thread walks t upwards, so finding r is an occasional step forward. Lanes of a warp differ in how their candidates
-// split over the rows, but much less in their totals, which keeps the warp's lanes busy together.
-constexpr int kMaxRanges = 50;   // (2 * 2 + 1)^2 rows, each split at most once by the periodic boundary
-
-struct CandidateRanges {
-    int off[kMaxRanges];
-    int end[kMaxRanges];
-    int count = 0;
-    int total = 0;
-
-    __device__ __forceinline__ void add(int first_slot, int n_slots) {
-        if (n_slots <= 0 || count >= kMaxRanges) return;
-        off[count] = first_slot - total;
-        total += n_slots;
-        end[count] = total;
-        ++count;
-    }
-};
-
-// Collects the ranges of atom `pi` (home cell cy, cz on the row axes) from one cell table (`row_base` selects the owned or
-// the ghost half).
-__device__ __forceinline__ void collect_candidates(const Grid& g, const int4& pi, int cy, int cz, int row_base,
-                                                   const int* __restrict__ cell_start, CandidateRanges& out) {
-    const int S = g.stencil;
-    for (int dz = -S; dz <= S; ++dz) {
-        int zc = cz + dz;
-        if (g.wrap[2]) { if (zc < 0) zc += g.nc[2]; else if (zc >= g.nc[2]) zc -= g.nc[2]; }
-        else if (zc < 0 || zc >= g.nc[2]) continue;
-        for (int dy = -S; dy <= S; ++dy) {
-            int yc = cy + dy;
-            if (g.wrap[1]) { if (yc < 0) yc += g.nc[1]; else if (yc >= g.nc[1]) yc -= g.nc[1]; }
-            else if (yc < 0 || yc >= g.nc[1]) continue;
-            RowWindow w;
-            if (!row_window(g, pi, cy, cz, dy, dz, w)) continue;
-            const int row = row_base + (zc * g.nc[1] + yc) * g.nc[0];
-            const int s0 = cell_start[row + w.a0];
-            out.add(s0, cell_start[row + w.b0 + 1] - s0);
-            if (w.b1 >= w.a1) {
-                const int s1 = cell_start[row + w.a1];
-                out.add(s1, cell_start[row + w.b1 + 1] - s1);
-            }
-        }
-    }
-}
 #endif
 
 }  // namespace dsmd

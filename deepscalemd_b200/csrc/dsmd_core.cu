@@ -157,6 +157,7 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
     const int4 pi = pq[i];
     const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
     const int cz = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.z), g.wrap[2], g.nc[2]));
+    const int S = g.stencil;
     const size_t base = (static_cast<size_t>(i >> 5) * stride) * 32 + (i & 31);
     int ex_begin = 0, ex_end = 0;
     if (excl.offsets) {
@@ -170,34 +171,44 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
     unsigned rechecked = 0;
     const int n_seg = n_total > n_owned ? 2 : 1;
     for (int seg = 0; seg < n_seg; ++seg) {
-        dsmd::CandidateRanges cand;
-        dsmd::collect_candidates(g, pi, cy, cz, seg * g.ncells, cell_start, cand);
-        int r = 0, off = cand.off[0], end = cand.total > 0 ? cand.end[0] : 0;
-        for (int t = 0; t < cand.total; ++t) {
-            while (t >= end) {
-                ++r;
-                off = cand.off[r];
-                end = cand.end[r];
+        for (int dz = -S; dz <= S; ++dz) {
+            int zc = cz + dz;
+            if (g.wrap[2]) { if (zc < 0) zc += g.nc[2]; else if (zc >= g.nc[2]) zc -= g.nc[2]; }
+            else if (zc < 0 || zc >= g.nc[2]) continue;
+            for (int dy = -S; dy <= S; ++dy) {
+                int yc = cy + dy;
+                if (g.wrap[1]) { if (yc < 0) yc += g.nc[1]; else if (yc >= g.nc[1]) yc -= g.nc[1]; }
+                else if (yc < 0 || yc >= g.nc[1]) continue;
+                const int row = seg * g.ncells + (zc * g.nc[1] + yc) * g.nc[0];
+                dsmd::RowWindow win;
+                if (!dsmd::row_window(g, pi, cy, cz, dy, dz, win)) continue;
+                const int a0 = win.a0, b0 = win.b0, a1 = win.a1, b1 = win.b1;
+                for (int part = 0; part < 2; ++part) {
+                    const int a = part == 0 ? a0 : a1, b = part == 0 ? b0 : b1;
+                    if (b < a) continue;
+                    const int s_begin = cell_start[row + a], s_end = cell_start[row + b + 1];
+                    for (int s = s_begin; s < s_end; ++s) {
+                        const int4 pj = __ldg(&pq[s]);
+                        const float fx = dsmd::fixed_delta(pj.x, pi.x, g.scale[0]);
+                        const float fy = dsmd::fixed_delta(pj.y, pi.y, g.scale[1]);
+                        const float fz = dsmd::fixed_delta(pj.z, pi.z, g.scale[2]);
+                        const float r2 = fx * fx + fy * fy + fz * fz;
+                        if (r2 >= g.r2_list + g.band || s == i) continue;
+                        if (r2 >= g.r2_list - g.band) {
+                            ++rechecked;
+                            if (!within_list_fp64(g, x, y, z, i, s)) continue;
+                        }
+                        unsigned entry = static_cast<unsigned>(s);
+                        if (ex_end > ex_begin) {
+                            const int gj = gid[s];
+                            for (int e = ex_begin; e < ex_end; ++e)
+                                if (excl.partners[e] == gj) entry |= kExclBit;
+                        }
+                        if (count < stride) nbr[base + static_cast<size_t>(count) * 32] = entry;
+                        ++count;
+                    }
+                }
             }
-            const int s = t + off;
-            const int4 pj = __ldg(&pq[s]);
-            const float fx = dsmd::fixed_delta(pj.x, pi.x, g.scale[0]);
-            const float fy = dsmd::fixed_delta(pj.y, pi.y, g.scale[1]);
-            const float fz = dsmd::fixed_delta(pj.z, pi.z, g.scale[2]);
-            const float r2 = fx * fx + fy * fy + fz * fz;
-            if (r2 >= g.r2_list + g.band || s == i) continue;
-            if (r2 >= g.r2_list - g.band) {
-                ++rechecked;
-                if (!within_list_fp64(g, x, y, z, i, s)) continue;
-            }
-            unsigned entry = static_cast<unsigned>(s);
-            if (ex_end > ex_begin) {
-                const int gj = gid[s];
-                for (int e = ex_begin; e < ex_end; ++e)
-                    if (excl.partners[e] == gj) entry |= kExclBit;
-            }
-            if (count < stride) nbr[base + static_cast<size_t>(count) * 32] = entry;
-            ++count;
         }
         if (seg == 0) interior = count;
     }

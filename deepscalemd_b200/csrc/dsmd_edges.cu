@@ -122,42 +122,53 @@ __global__ void __launch_bounds__(kSearchThreads) k_edge_search(Grid g, SearchAr
         const bool check_nb = a.ok && a.row == 1;
             const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
         const int cz = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.z), g.wrap[2], g.nc[2]));
-        dsmd::CandidateRanges cand;
-        dsmd::collect_candidates(g, pi, cy, cz, 0, a.cell_start, cand);
-        int r = 0, off = cand.off[0], end = cand.total > 0 ? cand.end[0] : 0;
-        for (int t = 0; t < cand.total; ++t) {
-            while (t >= end) {
-                ++r;
-                off = cand.off[r];
-                end = cand.end[r];
-            }
-            const int s = t + off;
-            const int4 pj = __ldg(&a.pq[s]);
-            const float fx = dsmd::fixed_delta(pj.x, pi.x, g.scale[0]);
-            const float fy = dsmd::fixed_delta(pj.y, pi.y, g.scale[1]);
-            const float fz = dsmd::fixed_delta(pj.z, pi.z, g.scale[2]);
-            const float r2 = fx * fx + fy * fy + fz * fz;
-            if (r2 >= g.r2_list + g.band || s == p) continue;
-            if (r2 >= g.r2_list - g.band) {
-                ++rechecked;
-                if (!within_fp64<PERIODIC>(g, a, centre, pj.w)) continue;
-            }
-            if (check_nb && !a.ok[a.owner ? a.owner[pj.w] : pj.w]) continue;
-            if (count < a.stride) {
-                if (PERIODIC) {   // keep the row sorted by neighbour index (insertion)
-                    int k = count;
-                    while (k > 0) {
-                        const unsigned prev = a.rows[base + static_cast<size_t>(k - 1) * 32];
-                        if (prev <= static_cast<unsigned>(pj.w)) break;
-                        a.rows[base + static_cast<size_t>(k) * 32] = prev;
-                        --k;
+        const int S = g.stencil;
+        for (int dz = -S; dz <= S; ++dz) {
+            int zc = cz + dz;
+            if (g.wrap[2]) { if (zc < 0) zc += g.nc[2]; else if (zc >= g.nc[2]) zc -= g.nc[2]; }
+            else if (zc < 0 || zc >= g.nc[2]) continue;
+            for (int dy = -S; dy <= S; ++dy) {
+                int yc = cy + dy;
+                if (g.wrap[1]) { if (yc < 0) yc += g.nc[1]; else if (yc >= g.nc[1]) yc -= g.nc[1]; }
+                else if (yc < 0 || yc >= g.nc[1]) continue;
+                const int row = (zc * g.nc[1] + yc) * g.nc[0];
+                dsmd::RowWindow win;
+                if (!dsmd::row_window(g, pi, cy, cz, dy, dz, win)) continue;
+                const int a0 = win.a0, b0 = win.b0, a1 = win.a1, b1 = win.b1;
+                for (int part = 0; part < 2; ++part) {
+                    const int lo = part == 0 ? a0 : a1, hi = part == 0 ? b0 : b1;
+                    if (hi < lo) continue;
+                    const int s_begin = a.cell_start[row + lo], s_end = a.cell_start[row + hi + 1];
+                    for (int s = s_begin; s < s_end; ++s) {
+                        const int4 pj = __ldg(&a.pq[s]);
+                        const float fx = dsmd::fixed_delta(pj.x, pi.x, g.scale[0]);
+                        const float fy = dsmd::fixed_delta(pj.y, pi.y, g.scale[1]);
+                        const float fz = dsmd::fixed_delta(pj.z, pi.z, g.scale[2]);
+                        const float r2 = fx * fx + fy * fy + fz * fz;
+                        if (r2 >= g.r2_list + g.band || s == p) continue;
+                        if (r2 >= g.r2_list - g.band) {
+                            ++rechecked;
+                            if (!within_fp64<PERIODIC>(g, a, centre, pj.w)) continue;
+                        }
+                        if (check_nb && !a.ok[a.owner ? a.owner[pj.w] : pj.w]) continue;
+                        if (count < a.stride) {
+                            if (PERIODIC) {   // keep the row sorted by neighbour index (insertion)
+                                int k = count;
+                                while (k > 0) {
+                                    const unsigned prev = a.rows[base + static_cast<size_t>(k - 1) * 32];
+                                    if (prev <= static_cast<unsigned>(pj.w)) break;
+                                    a.rows[base + static_cast<size_t>(k) * 32] = prev;
+                                    --k;
+                                }
+                                a.rows[base + static_cast<size_t>(k) * 32] = static_cast<unsigned>(pj.w);
+                            } else {
+                                a.rows[base + static_cast<size_t>(count) * 32] = static_cast<unsigned>(pj.w);
+                            }
+                        }
+                        ++count;
                     }
-                    a.rows[base + static_cast<size_t>(k) * 32] = static_cast<unsigned>(pj.w);
-                } else {
-                    a.rows[base + static_cast<size_t>(count) * 32] = static_cast<unsigned>(pj.w);
                 }
             }
-            ++count;
         }
     }
     a.counts[PERIODIC ? centre : p] = min(count, a.stride);

@@ -39,7 +39,7 @@ def grid_dims(world_size: int, box) -> tuple[int, int, int]:
             pz = world_size // (px * py)
             w = [box[0] / px, box[1] / py, box[2] / pz]
             cost = sum((2.0 * w[(a + 1) % 3] * w[(a + 2) % 3]) for a, p in enumerate((px, py, pz)) if p > 1)
-            key = (cost, -px, -py)
+            key = (round(cost, 9), -min(w), -px, -py)   # ties: the thicker brick (room for the halo), then x before y
             if best_cost is None or key < best_cost:
                 best, best_cost = (px, py, pz), key
     return best

@@ -1,0 +1,165 @@
+"""Multi-GPU leg of bench.py: strong scaling of the 4,000,000-atom LJ system over the GPUs of one node, one process per
+GPU (torchrun), bricks of a spatial decomposition, ghost exchange over NCCL point-to-point."""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def run(args):
+    import bench   # the driver script: shared constants and helpers
+    from deepscalemd_b200 import capi, domain
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=device)
+    stream = torch.cuda.current_stream()
+    hbm_peak, peak_kind = bench.measured_peaks()
+
+    s = bench.fcc_for(args.workload)
+    dec = domain.Decomposition(s.box, world, rank)
+    owner = dec.owner_of(s.pos)
+    mine = np.nonzero(owner == rank)[0]
+    halo = s.cutoff + s.skin
+    capacity = int(len(mine) * 2.2) + 200_000
+    ctx = capi.Context(capacity, device=local)
+    lo = [dec.lo[a] if dec.split[a] else 0.0 for a in range(3)]
+    hi = [dec.hi[a] if dec.split[a] else 0.0 for a in range(3)]
+    ctx.set_box(s.box, (1, 1, 1), lo, hi, halo + 2.0 * s.skin)
+    ctx.set_pair_params(s.eps, s.sig, s.cutoff, s.skin)
+    wrapped = s.pos - s.box * np.floor(s.pos / s.box)
+    ctx.upload(wrapped[mine], vel=s.vel[mine], mass=s.mass[mine], types=s.types[mine], gid=mine.astype(np.int32))
+    runner = domain.DomainRunner(ctx, dec, halo, device)
+    runner.rebuild()
+    ctx.compute_forces(capi.PHASE_FULL, True, stream)
+    sc0 = runner.global_scalars()
+    ke = torch.tensor([ctx.kinetic_energy(stream)], dtype=torch.float64, device=device)
+    dist.all_reduce(ke)
+    e0 = sc0["pe"] + float(ke.item())
+
+    def md(n):
+        for _ in range(n):
+            runner.step(bench.DT, 1.0, s.skin, 0.5, lagged=True, overlap=True)
+
+    md(args.warmup)
+    sampler = bench.ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0, rebuilds0 = ctx.launch_count(), runner.rebuilds
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    start.record(stream)
+    md(args.steps)
+    stop.record(stream)
+    torch.cuda.synchronize()
+    elapsed = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+    dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    elapsed_ms = float(elapsed.item())
+    launches = ctx.launch_count() - launches0
+    rebuilds = runner.rebuilds - rebuilds0
+    clocks = sampler.stop() if sampler else None
+    n_owned, n_total = ctx.counts()
+
+    ctx.compute_forces(capi.PHASE_FULL, True, stream)
+    sc1 = runner.global_scalars()
+    ke = torch.tensor([ctx.kinetic_energy(stream)], dtype=torch.float64, device=device)
+    dist.all_reduce(ke)
+    e1 = sc1["pe"] + float(ke.item())
+
+    # per-kernel time of the pair kernel on this rank's share (roofline of the dominant kernel)
+    stats = ctx.list_stats()
+    t_pair = bench.time_calls(lambda: ctx.compute_forces(capi.PHASE_FULL, False, stream), 20, stream)
+    p_list_local = stats["directed_entries"] / 2.0
+    pair_bytes = 16.0 * n_total + 4.0 * p_list_local + 24.0 * n_owned
+    flops = ctx.fma_probe(1, stream)
+    t_probe = bench.time_calls(lambda: ctx.fma_probe(20000, stream), 3, stream)
+    fp32_peak = flops * 20000 / (t_probe * 1e-3) / 1e12
+    # pairs inside the cutoff seen from this rank: owned-owned once, owned-ghost half (the other half is the neighbour's)
+    ctx.compute_forces(capi.PHASE_FULL, True, stream)
+    p_cut_local = ctx.read_scalars(stream)["pairs_in_cutoff"]
+    pair_flops = 8.0 * p_list_local + 19.0 * p_cut_local
+
+    # end to end: host positions in, forces out, ghost refresh in between (every rank its own atoms)
+    host = [torch.from_numpy(ctx.download(k)).pin_memory() for k in ("x", "y", "z")]
+    hf = [torch.empty(n_owned, dtype=torch.float64).pin_memory() for _ in range(3)]
+    fptr = [ctx.device_pointer(k) for k in ("fx", "fy", "fz")]
+
+    def e2e_call():
+        ctx.upload_positions_ptr(host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), stream)
+        ctx.pack_positions(0, n_owned, stream)
+        runner.refresh_begin()
+        ctx.compute_forces(capi.PHASE_INTERIOR, False, stream)
+        runner.refresh_end()
+        ctx.compute_forces(capi.PHASE_BOUNDARY, False, stream)
+        for k in range(3):
+            view = capi._tensor_from_ptr(fptr[k], (n_owned,), torch.float64, device)
+            hf[k].copy_(view, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        e2e_call()
+    e2e_steps = max(4, min(args.steps, 40))
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_call()
+    dist.barrier()
+    e2e_t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
+    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+
+    counts = torch.tensor([n_owned, n_total - n_owned, runner.bytes_sent_per_step], dtype=torch.float64, device=device)
+    gathered = [torch.zeros_like(counts) for _ in range(world)]
+    dist.all_gather(gathered, counts)
+
+    if rank == 0:
+        ms_per_step = elapsed_ms / args.steps
+        value = s.n * args.steps / (elapsed_ms * 1e-3)
+        per_rank = [[int(v) for v in g.tolist()] for g in gathered]
+        line = {
+            "metric": "atom-steps/s", "value": value, "unit": "atom-steps/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": "LJ NVE 4,000,000 atoms (FCC 100^3, rho*=0.8442, T*=1.44, rc=2.5, skin=0.3, dt=0.005)"
+                if args.workload == "lj_4m" else args.workload,
+                "atoms": s.n, "decomposition": "x".join(str(d) for d in dec.dims) + " bricks",
+                "halo_width": halo, "ns_per_day": bench.ns_per_day(ms_per_step), "rebuilds": rebuilds,
+                "owned_ghost_sentbytes_per_rank": per_rank,
+                "worst_displacement_over_half_skin": float(np.sqrt(runner.worst_disp_sq) / (0.5 * s.skin)),
+                "l2": "inputs larger than L2 on every rank (list %.2f GB on rank 0)" % (4.0 * stats["directed_entries"] / 1e9),
+                "energy_per_atom_before": e0 / s.n, "energy_per_atom_after": e1 / s.n,
+                "exchange": "positions-only refresh (24 B/ghost) by grouped NCCL send/recv on a side stream, overlapped "
+                            "with the interior force pass; 8-byte MAX all-reduce for the rebuild vote",
+            },
+            "clocks": clocks,
+            "roofline": {
+                "kernel": "k_pair (LJ, full list, forces only), rank 0's brick", "bound": "hbm",
+                "achieved": pair_bytes / (t_pair * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                "frac": pair_bytes / (t_pair * 1e-3) / 1e9 / hbm_peak, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
+                "traffic": None, "algorithmic_bytes_per_launch": pair_bytes, "algorithmic_flops_per_launch": pair_flops,
+                "ms": t_pair,
+                "fp32": {"achieved_tflops": pair_flops / (t_pair * 1e-3) / 1e12, "peak_tflops": fp32_peak,
+                         "frac": pair_flops / (t_pair * 1e-3) / 1e12 / fp32_peak,
+                         "peak_source": "measured in this run (independent FMA chains on every SM)"},
+            },
+            "cpu_baseline": None,
+            "e2e": {"value": s.n * e2e_steps / float(e2e_t.item()), "unit": "atom-steps/s",
+                    "h2d_bytes_per_step": 24 * n_total, "d2h_bytes_per_step": 24 * n_owned, "steps": e2e_steps,
+                    "call": "per rank: pinned host positions in, pack, ghost refresh, interior + boundary forces, forces out"},
+            "gpu_launches": int(launches),
+        }
+        print(json.dumps(line))
+    ctx.close()
+    dist.barrier()
+    dist.destroy_process_group()

@@ -1,0 +1,106 @@
+"""Multi-GPU parity test (needs two CUDA devices; skipped otherwise): two ranks over NCCL run the real contexts through
+migration, ghost plan, positions-only refresh and list rebuilds; forces, energy and the trajectory must match the
+undivided system computed by the CPU oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from deepscalemd_b200 import synthetic as syn
+from oracle import cpu_oracle as co
+
+pytestmark = pytest.mark.gpu
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def worker(rank, world, port, steps, dt, out_path):
+    import torch.distributed as dist
+    from deepscalemd_b200 import capi, domain
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=device)
+    s = syn.fcc_lj(10, seed=44)
+    dec = domain.Decomposition(s.box, world, rank)
+    mine = np.nonzero(dec.owner_of(s.pos) == rank)[0]
+    halo = s.cutoff + s.skin
+    ctx = capi.Context(s.n * 2, device=rank)
+    lo = [dec.lo[a] if dec.split[a] else 0.0 for a in range(3)]
+    hi = [dec.hi[a] if dec.split[a] else 0.0 for a in range(3)]
+    ctx.set_box(s.box, (1, 1, 1), lo, hi, halo + 2 * s.skin)
+    ctx.set_pair_params(s.eps, s.sig, s.cutoff, s.skin)
+    wrapped = s.pos - s.box * np.floor(s.pos / s.box)
+    ctx.upload(wrapped[mine], vel=s.vel[mine], mass=s.mass[mine], types=s.types[mine], gid=mine.astype(np.int32))
+    run = domain.DomainRunner(ctx, dec, halo, device)
+    run.rebuild()
+    ctx.compute_forces(capi.PHASE_FULL, True)
+    first = run.global_scalars()
+    n_owned, n_total = ctx.counts()
+    gid_first = ctx.download("global_id", n_owned)
+    f_first = np.stack([ctx.download(k, n_owned) for k in ("fx", "fy", "fz")], axis=1)
+    for _ in range(steps):
+        run.step(dt, 1.0, s.skin, 0.5, lagged=True, overlap=True)
+    torch.cuda.synchronize()
+    n_owned, _ = ctx.counts()
+    result = dict(gid_first=gid_first, f_first=f_first, first=first, ghosts=n_total - n_owned,
+                  gid=ctx.download("global_id", n_owned),
+                  pos=np.stack([ctx.download(k, n_owned) for k in "xyz"], axis=1), rebuilds=run.rebuilds,
+                  worst=run.worst_disp_sq)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, result)
+    if rank == 0:
+        torch.save(gathered, out_path)
+    ctx.close()
+    dist.destroy_process_group()
+
+
+def test_two_gpus_equal_the_undivided_system(tmp_path):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import torch.multiprocessing as mp
+    steps, dt = 40, 0.005
+    out = str(tmp_path / "out.pt")
+    mp.spawn(worker, args=(2, free_port(), steps, dt, out), nprocs=2, join=True)
+    parts = torch.load(out, weights_only=False)
+    s = syn.fcc_lj(10, seed=44)
+    pos = [np.ascontiguousarray(s.pos[:, k]) for k in range(3)]
+    vel = [np.ascontiguousarray(s.vel[:, k]) for k in range(3)]
+    c6, c12 = co.lj_tables(s.eps, s.sig)
+
+    def force():
+        p = co.pairs(*pos, s.n, s.box, search=s.cutoff)
+        f, sc = co.forces(*pos, s.n, s.box, p, c6, c12, s.cutoff)
+        return [np.ascontiguousarray(f[:, k]) for k in range(3)], sc
+
+    frc, sc0 = force()
+    f0 = np.stack(frc, axis=1)
+    gid = np.concatenate([p["gid_first"] for p in parts])
+    assert np.array_equal(np.sort(gid), np.arange(s.n))
+    f = np.empty_like(f0)
+    for p in parts:
+        f[p["gid_first"]] = p["f_first"]
+    rms = lambda a: np.sqrt((a * a).sum(1).mean())
+    assert rms(f - f0) <= 1e-5 * rms(f0)
+    assert abs(parts[0]["first"]["pe"] - sc0["pe"]) <= 1e-6 * abs(sc0["pe"])
+    assert abs(parts[0]["first"]["virial"] - sc0["virial"]) <= 1e-6 * abs(sc0["virial"])
+    assert all(p["ghosts"] > 0 for p in parts)
+    for _ in range(steps):
+        co.vv_half(True, dt, 1.0, pos, vel, frc, s.mass)
+        frc, _ = force()
+        co.vv_half(False, dt, 1.0, pos, vel, frc, s.mass)
+    gid = np.concatenate([p["gid"] for p in parts])
+    assert np.array_equal(np.sort(gid), np.arange(s.n))
+    got = np.empty((s.n, 3))
+    for p in parts:
+        got[p["gid"]] = p["pos"]
+    d = got - np.stack(pos, axis=1)
+    d -= s.box * np.round(d / s.box)
+    assert np.abs(d).max() < 5e-6
+    assert parts[0]["rebuilds"] >= 4
+    assert parts[0]["worst"] <= (0.5 * s.skin) ** 2 * 1.2
