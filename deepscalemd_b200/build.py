@@ -11,7 +11,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["csrc/dsmd_core.cu", "csrc/dsmd_edges.cu"]
+SOURCES = ["csrc/dsmd_core.cu", "csrc/dsmd_edges.cu", "csrc/dsmd_noalloc.cu"]
 LIBRARY = os.path.join(HERE, "libdsmd_b200.so")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "--use_fast_math=false",
          "-Xcompiler", "-fPIC", "-shared"]

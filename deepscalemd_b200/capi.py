@@ -29,7 +29,7 @@ SYMBOLS = [
     "dsmd_forces_host", "dsmd_launch_count", "dsmd_fma_probe", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
     "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_edges_create", "dsmd_edges_destroy",
     "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
-    "dsmd_edges_result_compact",
+    "dsmd_edges_result_compact", "dsmd_kinetic_energy_noalloc",
 ]
 
 _lib = None
@@ -319,6 +319,21 @@ class Context:
     def halo_append_records(self, real_in, int_in, count, stream=None):
         self._check(self.lib.dsmd_halo_append_records(self.h, c_void_p(real_in.data_ptr()), c_void_p(int_in.data_ptr()),
                                                       c_int64(count), _stream_handle(stream)))
+
+
+NOALLOC_MAX_ATOMS = 16777216
+
+
+def kinetic_energy_noalloc(vx_ptr, vy_ptr, vz_ptr, mass_ptr, n, out_ptr, stream=None):
+    """``dsmd_kinetic_energy_noalloc``: device pointers in, the sum into the device double at out_ptr; the variant of the
+    kinetic-energy sum for callers that must not allocate device memory (its scratch is a fixed array inside the
+    library). Raises DsmdError with the library's message when n exceeds NOALLOC_MAX_ATOMS."""
+    lib = load()
+    msg = ctypes.c_char_p()
+    rc = lib.dsmd_kinetic_energy_noalloc(c_void_p(vx_ptr), c_void_p(vy_ptr), c_void_p(vz_ptr), c_void_p(mass_ptr),
+                                         c_int64(n), c_void_p(out_ptr), _stream_handle(stream), ctypes.byref(msg))
+    if rc != OK:
+        raise DsmdError(rc, (msg.value or b"").decode())
 
 
 class EdgeBuilder:

@@ -233,6 +233,28 @@ int dsmd_edges_build_periodic(dsmd_edges* eb, const double* d_x, const double* d
 int dsmd_edges_result_compact(const dsmd_edges* eb, const int32_t** d_src, const int32_t** d_dst,
                               const int8_t** d_shift, const float** d_vec, int64_t* n_edges);
 
+/* -- without device allocation ------------------------------------------------------------------------------------------ */
+
+/* Largest atom count dsmd_kinetic_energy_noalloc accepts: its scratch array (one double per 256 atoms, 512 KiB) is
+ * compiled into the library for this size. */
+#define DSMD_NOALLOC_MAX_ATOMS 16777216
+
+/* No counterpart in the reference. The kinetic-energy sum of dsmd_kinetic_energy (sum of m v^2 / 2 over n atoms, raw
+ * units), for callers that must not allocate device memory: a plugin called from inside an engine's step loop, where the
+ * engine's pools already own the device memory and a cudaMalloc would either fail or stall every stream of the step by
+ * synchronising the device. The caller passes device arrays and a device double for the result; the per-block partial
+ * sums live in a fixed array inside the library image, which every GPU that loads the library holds (512 KiB) until the
+ * process exits. Neither this call nor anything it calls allocates or frees memory.
+ *   - n > DSMD_NOALLOC_MAX_ATOMS is refused with DSMD_ERR_CAPACITY and a message in *error (error may be NULL).
+ *   - The first call on a device looks up the array's device address (once per device, with that device current); make
+ *     that first call before any stream capture begins.
+ *   - All calls on a device share the one array, which keeps what the last call wrote. Each call overwrites every
+ *     entry it later reads, so nothing needs clearing between calls; but two calls whose kernels overlap on the GPU
+ *     (different streams, no ordering between them) race on it and give wrong sums. Order them on one stream or with events.
+ * Queued on `stream`; the result is in *d_out when the stream reaches that point. Uses the current device. */
+int dsmd_kinetic_energy_noalloc(const double* d_vx, const double* d_vy, const double* d_vz, const double* d_mass,
+                                int64_t n, double* d_out, void* stream, const char** error);
+
 #ifdef __cplusplus
 }
 #endif
