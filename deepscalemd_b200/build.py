@@ -11,7 +11,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["csrc/dsmd_core.cu", "csrc/dsmd_edges.cu", "csrc/dsmd_noalloc.cu"]
+SOURCES = ["csrc/dsmd_core.cu", "csrc/dsmd_edges.cu", "csrc/dsmd_domain.cu", "csrc/dsmd_noalloc.cu"]
 LIBRARY = os.path.join(HERE, "libdsmd_b200.so")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "--use_fast_math=false",
          "-Xcompiler", "-fPIC", "-shared"]
@@ -41,7 +41,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIBRARY
     flags = [f for f in FLAGS if f != "--use_fast_math=false"]
-    cmd = [nvcc_path(), *flags, "-ccbin", "/usr/bin/g++", "-o", LIBRARY, *sources()]
+    cmd = [nvcc_path(), *flags, "-ccbin", "/usr/bin/g++", "-o", LIBRARY, *sources(), "-ldl"]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
         print(" ".join(cmd))

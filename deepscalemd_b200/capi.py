@@ -29,7 +29,9 @@ SYMBOLS = [
     "dsmd_forces_host", "dsmd_launch_count", "dsmd_fma_probe", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
     "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_edges_create", "dsmd_edges_destroy",
     "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
-    "dsmd_edges_result_compact", "dsmd_kinetic_energy_noalloc",
+    "dsmd_edges_result_compact", "dsmd_kinetic_energy_noalloc", "dsmd_nccl_unique_id", "dsmd_domain_create",
+    "dsmd_domain_destroy", "dsmd_domain_last_error", "dsmd_domain_rebuild", "dsmd_domain_refresh", "dsmd_domain_run",
+    "dsmd_domain_stats",
 ]
 
 _lib = None
@@ -319,6 +321,80 @@ class Context:
     def halo_append_records(self, real_in, int_in, count, stream=None):
         self._check(self.lib.dsmd_halo_append_records(self.h, c_void_p(real_in.data_ptr()), c_void_p(int_in.data_ptr()),
                                                       c_int64(count), _stream_handle(stream)))
+
+
+def nccl_library_path():
+    """The NCCL library that ships with torch (newer than a system one), or None to let the loader search."""
+    try:
+        import nvidia.nccl
+        for base in nvidia.nccl.__path__:
+            path = os.path.join(base, "lib", "libnccl.so.2")
+            if os.path.exists(path):
+                return path
+    except ImportError:
+        pass
+    return None
+
+
+def nccl_unique_id() -> bytes:
+    lib = load()
+    buf = ctypes.create_string_buffer(128)
+    path = nccl_library_path()
+    rc = lib.dsmd_nccl_unique_id(path.encode() if path else None, buf)
+    if rc != OK:
+        raise DsmdError(rc, "cannot create an NCCL unique id (is libnccl.so.2 loadable?)")
+    return buf.raw
+
+
+class Domain:
+    """``dsmd_domain``: one rank's brick of a spatial decomposition - migration, ghost plan, refresh and the MD loop,
+    native, over NCCL point-to-point."""
+
+    def __init__(self, ctx: Context, rank, world, dims, box, halo_width, skin, unique_id: bytes | None):
+        self.lib, self.ctx = ctx.lib, ctx
+        self.lib.dsmd_domain_last_error.restype = ctypes.c_char_p
+        self.lib.dsmd_domain_last_error.argtypes = [c_void_p]
+        self.lib.dsmd_domain_destroy.restype = None
+        self.lib.dsmd_domain_destroy.argtypes = [c_void_p]
+        self.h = c_void_p()
+        d, b = _arr(dims, np.int32), _arr(box, np.float64)
+        path = nccl_library_path()
+        rc = self.lib.dsmd_domain_create(ctx.h, c_int(rank), c_int(world), _p(d), _p(b), c_double(halo_width),
+                                         c_double(skin), path.encode() if path else None, unique_id, ctypes.byref(self.h))
+        self._check(rc)
+
+    def _check(self, rc):
+        if rc != OK:
+            raise DsmdError(rc, self.lib.dsmd_domain_last_error(self.h).decode() if self.h else "dsmd_domain_create failed")
+
+    def rebuild(self, stream=None):
+        self._check(self.lib.dsmd_domain_rebuild(self.h, _stream_handle(stream)))
+
+    def refresh(self, stream=None):
+        self._check(self.lib.dsmd_domain_refresh(self.h, _stream_handle(stream)))
+
+    def run(self, n_steps, dt, force_to_accel=1.0, hi_frac=0.5, stream=None):
+        self._check(self.lib.dsmd_domain_run(self.h, c_int64(n_steps), c_double(dt), c_double(force_to_accel),
+                                             c_double(hi_frac), _stream_handle(stream)))
+
+    def stats(self):
+        v = [c_int64(0) for _ in range(4)]
+        w, l = c_double(0.0), c_int64(0)
+        self._check(self.lib.dsmd_domain_stats(self.h, ctypes.byref(v[0]), ctypes.byref(v[1]), ctypes.byref(v[2]),
+                                               ctypes.byref(v[3]), ctypes.byref(w), ctypes.byref(l)))
+        return dict(rebuilds=v[0].value, migrated=v[1].value, ghosts=v[2].value, positions_sent_per_step=v[3].value,
+                    worst_disp_sq=w.value, launches=l.value)
+
+    def close(self):
+        if self.h:
+            self.lib.dsmd_domain_destroy(self.h)
+            self.h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 NOALLOC_MAX_ATOMS = 16777216

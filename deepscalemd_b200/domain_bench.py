@@ -21,7 +21,8 @@ def run(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=device)
+        # control plane only (unique id, timing reductions): the data plane is the library's own NCCL communicator
+        dist.init_process_group("gloo")
     stream = torch.cuda.current_stream()
     hbm_peak, peak_kind = bench.measured_peaks()
 
@@ -38,23 +39,27 @@ def run(args):
     ctx.set_pair_params(s.eps, s.sig, s.cutoff, s.skin)
     wrapped = s.pos - s.box * np.floor(s.pos / s.box)
     ctx.upload(wrapped[mine], vel=s.vel[mine], mass=s.mass[mine], types=s.types[mine], gid=mine.astype(np.int32))
-    runner = domain.DomainRunner(ctx, dec, halo, device)
-    runner.rebuild()
-    ctx.compute_forces(capi.PHASE_FULL, True, stream)
-    sc0 = runner.global_scalars()
-    ke = torch.tensor([ctx.kinetic_energy(stream)], dtype=torch.float64, device=device)
-    dist.all_reduce(ke)
-    e0 = sc0["pe"] + float(ke.item())
+    uid = [capi.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    dom = capi.Domain(ctx, rank, world, dec.dims, s.box, halo, s.skin, uid[0])
+    dom.rebuild(stream)
+
+    def total_energy():
+        ctx.compute_forces(capi.PHASE_FULL, True, stream)
+        v = torch.tensor([ctx.read_scalars(stream)["pe"] + ctx.kinetic_energy(stream)], dtype=torch.float64)
+        dist.all_reduce(v)
+        return float(v.item())
+
+    e0 = total_energy()
 
     def md(n):
-        for _ in range(n):
-            runner.step(bench.DT, 1.0, s.skin, 0.5, lagged=True, overlap=True)
+        dom.run(n, bench.DT, 1.0, 0.5, stream)
 
     md(args.warmup)
     sampler = bench.ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    launches0, rebuilds0 = ctx.launch_count(), runner.rebuilds
+    launches0, rebuilds0 = ctx.launch_count() + dom.stats()["launches"], dom.stats()["rebuilds"]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dist.barrier()
     torch.cuda.synchronize()
@@ -62,20 +67,17 @@ def run(args):
     md(args.steps)
     stop.record(stream)
     torch.cuda.synchronize()
-    elapsed = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+    elapsed = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64)
     dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
     dist.barrier()
     elapsed_ms = float(elapsed.item())
-    launches = ctx.launch_count() - launches0
-    rebuilds = runner.rebuilds - rebuilds0
+    st = dom.stats()
+    launches = ctx.launch_count() + st["launches"] - launches0
+    rebuilds = st["rebuilds"] - rebuilds0
     clocks = sampler.stop() if sampler else None
     n_owned, n_total = ctx.counts()
 
-    ctx.compute_forces(capi.PHASE_FULL, True, stream)
-    sc1 = runner.global_scalars()
-    ke = torch.tensor([ctx.kinetic_energy(stream)], dtype=torch.float64, device=device)
-    dist.all_reduce(ke)
-    e1 = sc1["pe"] + float(ke.item())
+    e1 = total_energy()
 
     # per-kernel time of the pair kernel on this rank's share (roofline of the dominant kernel)
     stats = ctx.list_stats()
@@ -98,10 +100,8 @@ def run(args):
     def e2e_call():
         ctx.upload_positions_ptr(host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), stream)
         ctx.pack_positions(0, n_owned, stream)
-        runner.refresh_begin()
-        ctx.compute_forces(capi.PHASE_INTERIOR, False, stream)
-        runner.refresh_end()
-        ctx.compute_forces(capi.PHASE_BOUNDARY, False, stream)
+        dom.refresh(stream)
+        ctx.compute_forces(capi.PHASE_FULL, False, stream)
         for k in range(3):
             view = capi._tensor_from_ptr(fptr[k], (n_owned,), torch.float64, device)
             hf[k].copy_(view, non_blocking=True)
@@ -115,10 +115,10 @@ def run(args):
     for _ in range(e2e_steps):
         e2e_call()
     dist.barrier()
-    e2e_t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
+    e2e_t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64)
     dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
 
-    counts = torch.tensor([n_owned, n_total - n_owned, runner.bytes_sent_per_step], dtype=torch.float64, device=device)
+    counts = torch.tensor([n_owned, n_total - n_owned, 24 * st["positions_sent_per_step"]], dtype=torch.float64)
     gathered = [torch.zeros_like(counts) for _ in range(world)]
     dist.all_gather(gathered, counts)
 
@@ -136,11 +136,12 @@ def run(args):
                 "atoms": s.n, "decomposition": "x".join(str(d) for d in dec.dims) + " bricks",
                 "halo_width": halo, "ns_per_day": bench.ns_per_day(ms_per_step), "rebuilds": rebuilds,
                 "owned_ghost_sentbytes_per_rank": per_rank,
-                "worst_displacement_over_half_skin": float(np.sqrt(runner.worst_disp_sq) / (0.5 * s.skin)),
+                "worst_displacement_over_half_skin": float(np.sqrt(st["worst_disp_sq"]) / (0.5 * s.skin)),
                 "l2": "inputs larger than L2 on every rank (list %.2f GB on rank 0)" % (4.0 * stats["directed_entries"] / 1e9),
                 "energy_per_atom_before": e0 / s.n, "energy_per_atom_after": e1 / s.n,
-                "exchange": "positions-only refresh (24 B/ghost) by grouped NCCL send/recv on a side stream, overlapped "
-                            "with the interior force pass; 8-byte MAX all-reduce for the rebuild vote",
+                "exchange": "native loop (dsmd_domain_run): positions-only refresh (24 B/ghost) by grouped ncclSend/ncclRecv "
+                            "on a side stream, overlapped with the interior force pass; 8-byte MAX all-reduce for the "
+                            "rebuild vote; gloo only for set-up and timing reductions",
             },
             "clocks": clocks,
             "roofline": {
@@ -156,10 +157,11 @@ def run(args):
             "cpu_baseline": None,
             "e2e": {"value": s.n * e2e_steps / float(e2e_t.item()), "unit": "atom-steps/s",
                     "h2d_bytes_per_step": 24 * n_total, "d2h_bytes_per_step": 24 * n_owned, "steps": e2e_steps,
-                    "call": "per rank: pinned host positions in, pack, ghost refresh, interior + boundary forces, forces out"},
+                    "call": "per rank: pinned host positions in, pack, ghost refresh, forces, forces out"},
             "gpu_launches": int(launches),
         }
         print(json.dumps(line))
+    dom.close()
     ctx.close()
     dist.barrier()
     dist.destroy_process_group()

@@ -205,6 +205,42 @@ int dsmd_halo_pack_records(dsmd_ctx* ctx, const int32_t* device_send_index, int6
 int dsmd_halo_append_records(dsmd_ctx* ctx, const double* device_real_in, const int32_t* device_int_in, int64_t count,
                              void* stream);
 
+/* -- several GPUs: bricks, migration, ghost plan, MD loop --------------------------------------------------------------- */
+
+typedef struct dsmd_domain dsmd_domain;
+
+/* The 128-byte NCCL unique id that rank 0 creates and hands to the other ranks by whatever channel the engine has (the
+ * reference broadcasts it over MPI: src/force_calculator_cuda.cu:7524-7530). nccl_library_path may be NULL (the loader's
+ * search path is used). */
+int dsmd_nccl_unique_id(const char* nccl_library_path, char out[128]);
+
+/* One rank's view of a dims[0] x dims[1] x dims[2] brick grid over the periodic box (rank = (cx * dims[1] + cy) * dims[2] + cz;
+ * the context's box must have been set to this rank's brick, see dsmd_set_box). halo_width = how far ghosts are taken from
+ * neighbouring bricks (cutoff + skin); skin = the Verlet skin of the rebuild vote. With world > 1 an NCCL communicator is
+ * created (collective over the ranks). What the reference gets from dsdecompx::Decomp (src/md_system.cpp:853-993). */
+int dsmd_domain_create(dsmd_ctx* ctx, int rank, int world, const int dims[3], const double box[3], double halo_width,
+                       double skin, const char* nccl_library_path, const char unique_id[128], dsmd_domain** out);
+void dsmd_domain_destroy(dsmd_domain* dom);
+const char* dsmd_domain_last_error(const dsmd_domain* dom);
+
+/* The rebuild step (MDSimulation::handle_neighbor_phase on a rebuild, src/md_simulation.cpp:1316-1401): migrate atoms that
+ * left the brick (MDSystem::migrate_particles_on_device), sort the owned atoms, select and exchange the ghosts' full records
+ * (exchange_halo_on_device(rebuild = true)), build the list. Collective; synchronises `stream` three times. */
+int dsmd_domain_rebuild(dsmd_domain* dom, void* stream);
+
+/* Positions-only ghost refresh (begin + end_halo_exchange_on_device, src/md_system.cpp:1465-1493): pack, grouped
+ * ncclSend / ncclRecv with the neighbour directions, unpack, on the domain's side stream; `stream` then waits for it. */
+int dsmd_domain_refresh(dsmd_domain* dom, void* stream);
+
+/* n_steps MD steps (MDSimulation::single_step, src/md_simulation.cpp:899-941, restricted to this path): first
+ * velocity-Verlet half + pack, rebuild vote (8-byte MAX all-reduce, read one step late and extrapolated), then either a
+ * rebuild + full force pass, or the ghost refresh on the side stream overlapped with the interior force pass followed by
+ * the boundary pass; second half. Collective. */
+int dsmd_domain_run(dsmd_domain* dom, int64_t n_steps, double dt, double force_to_accel, double hi_frac, void* stream);
+
+int dsmd_domain_stats(const dsmd_domain* dom, int64_t* rebuilds, int64_t* migrated_atoms, int64_t* ghosts,
+                      int64_t* positions_sent_per_step, double* worst_disp_sq, int64_t* launches);
+
 /* -- radius graph ------------------------------------------------------------------------------------------------------ */
 
 typedef struct dsmd_edges dsmd_edges;

@@ -60,13 +60,61 @@ def worker(rank, world, port, steps, dt, out_path):
     dist.destroy_process_group()
 
 
-def test_two_gpus_equal_the_undivided_system(tmp_path):
+def worker_native(rank, world, port, steps, dt, out_path):
+    """The same run through the native domain code (dsmd_domain_*: its own NCCL communicator; gloo only carries the
+    unique id and the result gathering)."""
+    import torch.distributed as dist
+    from deepscalemd_b200 import capi, domain
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    s = syn.fcc_lj(10, seed=44)
+    dec = domain.Decomposition(s.box, world, rank)
+    mine = np.nonzero(dec.owner_of(s.pos) == rank)[0]
+    halo = s.cutoff + s.skin
+    ctx = capi.Context(s.n * 2, device=rank)
+    lo = [dec.lo[a] if dec.split[a] else 0.0 for a in range(3)]
+    hi = [dec.hi[a] if dec.split[a] else 0.0 for a in range(3)]
+    ctx.set_box(s.box, (1, 1, 1), lo, hi, halo + 2 * s.skin)
+    ctx.set_pair_params(s.eps, s.sig, s.cutoff, s.skin)
+    wrapped = s.pos - s.box * np.floor(s.pos / s.box)
+    ctx.upload(wrapped[mine], vel=s.vel[mine], mass=s.mass[mine], types=s.types[mine], gid=mine.astype(np.int32))
+    uid = [capi.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    dom = capi.Domain(ctx, rank, world, dec.dims, s.box, halo, s.skin, uid[0])
+    dom.rebuild()
+    ctx.compute_forces(capi.PHASE_FULL, True)
+    sc = ctx.read_scalars()
+    first = torch.tensor([sc["pe"], sc["virial"]], dtype=torch.float64)
+    dist.all_reduce(first)
+    n_owned, n_total = ctx.counts()
+    gid_first = ctx.download("global_id", n_owned)
+    f_first = np.stack([ctx.download(k, n_owned) for k in ("fx", "fy", "fz")], axis=1)
+    dom.run(steps, dt, 1.0, 0.5)
+    torch.cuda.synchronize()
+    n_owned, _ = ctx.counts()
+    st = dom.stats()
+    result = dict(gid_first=gid_first, f_first=f_first, first=dict(pe=float(first[0]), virial=float(first[1])),
+                  ghosts=n_total - n_owned, gid=ctx.download("global_id", n_owned),
+                  pos=np.stack([ctx.download(k, n_owned) for k in "xyz"], axis=1), rebuilds=st["rebuilds"],
+                  worst=st["worst_disp_sq"])
+    gathered = [None] * world
+    dist.all_gather_object(gathered, result)
+    if rank == 0:
+        torch.save(gathered, out_path)
+    dom.close()
+    ctx.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("which", ["torch_distributed", "native"])
+def test_two_gpus_equal_the_undivided_system(tmp_path, which):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
     import torch.multiprocessing as mp
     steps, dt = 40, 0.005
     out = str(tmp_path / "out.pt")
-    mp.spawn(worker, args=(2, free_port(), steps, dt, out), nprocs=2, join=True)
+    mp.spawn(worker if which == "torch_distributed" else worker_native, args=(2, free_port(), steps, dt, out), nprocs=2,
+             join=True)
     parts = torch.load(out, weights_only=False)
     s = syn.fcc_lj(10, seed=44)
     pos = [np.ascontiguousarray(s.pos[:, k]) for k in range(3)]
