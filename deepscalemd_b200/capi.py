@@ -31,7 +31,7 @@ SYMBOLS = [
     "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
     "dsmd_edges_result_compact", "dsmd_kinetic_energy_noalloc", "dsmd_nccl_unique_id", "dsmd_domain_create",
     "dsmd_domain_destroy", "dsmd_domain_last_error", "dsmd_domain_rebuild", "dsmd_domain_refresh", "dsmd_domain_run",
-    "dsmd_domain_stats",
+    "dsmd_domain_stats", "dsmd_domain_profile",
 ]
 
 _lib = None
@@ -376,6 +376,15 @@ class Domain:
     def run(self, n_steps, dt, force_to_accel=1.0, hi_frac=0.5, stream=None):
         self._check(self.lib.dsmd_domain_run(self.h, c_int64(n_steps), c_double(dt), c_double(force_to_accel),
                                              c_double(hi_frac), _stream_handle(stream)))
+
+    def profile(self, enable=True):
+        """Switches per-phase timing on or off; returns the accumulated per-step averages (ms) so far."""
+        ms = (c_double * 6)()
+        n = c_int64(0)
+        self._check(self.lib.dsmd_domain_profile(self.h, c_int(int(enable)), ms, ctypes.byref(n)))
+        names = ["integrate1_pack", "vote", "refresh_issue_interior", "boundary_or_full", "integrate2", "rebuild"]
+        steps = max(n.value, 1)
+        return {k: ms[i] / steps for i, k in enumerate(names)} | {"steps": n.value}
 
     def stats(self):
         v = [c_int64(0) for _ in range(4)]

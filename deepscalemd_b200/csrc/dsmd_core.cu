@@ -516,9 +516,11 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
                         trow);
         }
         if (phase == DSMD_PHASE_BOUNDARY) {
-            fx[i] += static_cast<double>(acc.ax);
-            fy[i] += static_cast<double>(acc.ay);
-            fz[i] += static_cast<double>(acc.az);
+            if (k_end > k_begin) {   // most atoms of a brick have no ghost partner: leave their forces alone
+                fx[i] += static_cast<double>(acc.ax);
+                fy[i] += static_cast<double>(acc.ay);
+                fz[i] += static_cast<double>(acc.az);
+            }
         } else {
             fx[i] = static_cast<double>(acc.ax);
             fy[i] = static_cast<double>(acc.ay);
@@ -802,11 +804,14 @@ int ensure_list(dsmd_ctx* c, int stride) {
     const size_t slices = static_cast<size_t>((c->n_owned + 31) / 32);
     const size_t need = slices * static_cast<size_t>(stride) * 32;
     if (need > c->nbr_capacity) {
+        // with headroom: the owned count of a brick changes by a few atoms at every migration, and a reallocation of this
+        // (large) buffer synchronises the device
+        const size_t grown = need + need / 8 + 4096;
         if (c->nbr) cudaFree(c->nbr);
         c->nbr = nullptr;
         c->nbr_capacity = 0;
-        DSMD_CUDA(c, cudaMalloc(&c->nbr, sizeof(unsigned) * need));
-        c->nbr_capacity = need;
+        DSMD_CUDA(c, cudaMalloc(&c->nbr, sizeof(unsigned) * grown));
+        c->nbr_capacity = grown;
     }
     c->stride = stride;
     return DSMD_OK;

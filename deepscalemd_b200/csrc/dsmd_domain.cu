@@ -253,6 +253,11 @@ struct dsmd_domain {
     // statistics
     int64_t rebuilds = 0, migrated = 0, launches = 0;
     double worst_disp_sq = 0.0;
+    // optional per-phase timing (profiling mode: synchronises every step)
+    bool profile = false;
+    cudaEvent_t ev_phase[8] = {};
+    double phase_ms[8] = {};   // integrate1, vote, refresh issue + interior, boundary wait + boundary, integrate2, rebuild
+    int64_t phase_steps = 0;
 };
 
 namespace {
@@ -638,8 +643,11 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
     void* word = nullptr;
     DOM_CTX(d, dsmd_displacement_word(d->ctx, &word));
     auto bits_to_double = [](unsigned long long b) { double v; std::memcpy(&v, &b, sizeof(v)); return v; };
+    auto mark = [&](int k) { if (d->profile) cudaEventRecord(d->ev_phase[k], s); };
     for (int64_t step = 0; step < n_steps; ++step) {
+        mark(0);
         DOM_CTX(d, dsmd_integrate(d->ctx, 1, dt, force_to_accel, s));   // v += dt/2 a, x += dt v, pack owned, displacement
+        mark(1);
         // The vote: all ranks take the MAX of their displacement words; the host reads the result of the PREVIOUS step (its
         // copy finished long ago) and extrapolates by its last growth (src/md_simulation.cpp:1232-1245).
         if (d->world > 1) DOM_NCCL(d, g_nccl.AllReduce(word, word, 1, ncclUint64, ncclMax, d->comm, s));
@@ -654,19 +662,48 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
         DOM_CUDA(d, cudaEventRecord(d->ev_vote[slot], s));
         d->vote_pending = slot;
         const double predicted = d->d_prev + 1.5 * std::max(d->d_prev - d->d_prev2, 0.0);
+        mark(2);
+        bool rebuilt = false;
         if (predicted * predicted > limit2) {
             { const int rc = rebuild(d, s); if (rc) return rc; }
+            rebuilt = true;
+            mark(3);
             DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_FULL, 0, s));
+            mark(4);
         } else if (d->world == 1) {
+            mark(3);
             DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_FULL, 0, s));
+            mark(4);
         } else {
             { const int rc = refresh(d, s); if (rc) return rc; }
             DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_INTERIOR, 0, s));
+            mark(3);
             DOM_CUDA(d, cudaStreamWaitEvent(s, d->ev_side, 0));
             DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_BOUNDARY, 0, s));
+            mark(4);
         }
         DOM_CTX(d, dsmd_integrate(d->ctx, 2, dt, force_to_accel, s));
+        mark(5);
+        if (d->profile) {
+            DOM_CUDA(d, cudaStreamSynchronize(s));
+            float ms = 0.f;
+            for (int k = 0; k < 5; ++k) {
+                cudaEventElapsedTime(&ms, d->ev_phase[k], d->ev_phase[k + 1]);
+                d->phase_ms[(rebuilt && k == 2) ? 5 : k] += ms;
+            }
+            ++d->phase_steps;
+        }
     }
+    return DSMD_OK;
+}
+
+int dsmd_domain_profile(dsmd_domain* d, int enable, double phase_ms[6], int64_t* steps) {
+    if (!d) return DSMD_ERR_INVALID;
+    if (enable && !d->ev_phase[0])
+        for (int k = 0; k < 8; ++k) DOM_CUDA(d, cudaEventCreate(&d->ev_phase[k]));
+    if (phase_ms) for (int k = 0; k < 6; ++k) phase_ms[k] = d->phase_ms[k];
+    if (steps) *steps = d->phase_steps;
+    d->profile = enable != 0;
     return DSMD_OK;
 }
 

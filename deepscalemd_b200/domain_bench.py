@@ -15,6 +15,9 @@ def run(args):
     import bench   # the driver script: shared constants and helpers
     from deepscalemd_b200 import capi, domain
 
+    os.environ.setdefault("NCCL_DEBUG", "WARN")   # keep NCCL's banner off stdout: rank 0 prints exactly one JSON line
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
@@ -78,6 +81,10 @@ def run(args):
     n_owned, n_total = ctx.counts()
 
     e1 = total_energy()
+    # phase breakdown of a short profiled run (synchronises every step: not part of the timed region)
+    dom.profile(True)
+    md(min(args.steps, 60))
+    phases = dom.profile(False)
 
     # per-kernel time of the pair kernel on this rank's share (roofline of the dominant kernel)
     stats = ctx.list_stats()
@@ -139,6 +146,7 @@ def run(args):
                 "worst_displacement_over_half_skin": float(np.sqrt(st["worst_disp_sq"]) / (0.5 * s.skin)),
                 "l2": "inputs larger than L2 on every rank (list %.2f GB on rank 0)" % (4.0 * stats["directed_entries"] / 1e9),
                 "energy_per_atom_before": e0 / s.n, "energy_per_atom_after": e1 / s.n,
+                "phase_ms_per_step_rank0": phases,
                 "exchange": "native loop (dsmd_domain_run): positions-only refresh (24 B/ghost) by grouped ncclSend/ncclRecv "
                             "on a side stream, overlapped with the interior force pass; 8-byte MAX all-reduce for the "
                             "rebuild vote; gloo only for set-up and timing reductions",
