@@ -379,10 +379,11 @@ class Domain:
 
     def profile(self, enable=True):
         """Switches per-phase timing on or off; returns the accumulated per-step averages (ms) so far."""
-        ms = (c_double * 6)()
+        ms = (c_double * 10)()
         n = c_int64(0)
         self._check(self.lib.dsmd_domain_profile(self.h, c_int(int(enable)), ms, ctypes.byref(n)))
-        names = ["integrate1_pack", "vote", "refresh_issue_interior", "boundary_or_full", "integrate2", "rebuild"]
+        names = ["integrate1_pack", "vote", "refresh_issue_interior", "boundary_or_full", "integrate2", "rebuild",
+                 "rebuild_migrate", "rebuild_sort_owned", "rebuild_ghost_plan", "rebuild_list"]
         steps = max(n.value, 1)
         return {k: ms[i] / steps for i, k in enumerate(names)} | {"steps": n.value}
 

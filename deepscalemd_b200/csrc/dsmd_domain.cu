@@ -20,6 +20,7 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <string>
@@ -90,11 +91,25 @@ struct DirTable {
 };
 
 // key 0 = stays; key 1 + d = leaves along direction d; key n + 1 = lost (moved further than one brick, or not finite).
+// Adds one to bin `bin` (or nothing when bin < 0) through a per-block histogram in shared memory: one global atomic per
+// non-empty bin and block instead of one per atom (all atoms of a brick but a few hit the same "stays" bin).
+__device__ __forceinline__ void block_histogram_add(int* hist, int bin, int* __restrict__ counts) {
+    if (bin >= 0) atomicAdd(&hist[bin], 1);
+    __syncthreads();
+    if (threadIdx.x < kMaxDirs + 2 && hist[threadIdx.x] > 0) atomicAdd(&counts[threadIdx.x], hist[threadIdx.x]);
+}
+
 __global__ void k_classify_leave(DirTable t, int n_owned, const double* __restrict__ x, const double* __restrict__ y,
                                  const double* __restrict__ z, unsigned* __restrict__ key, int* __restrict__ val,
                                  int* __restrict__ counts) {
+    __shared__ int hist[kMaxDirs + 2];
+    if (threadIdx.x < kMaxDirs + 2) hist[threadIdx.x] = 0;
+    __syncthreads();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_owned) return;
+    if (i >= n_owned) {
+        block_histogram_add(hist, -1, counts);
+        return;
+    }
     const double p[3] = {x[i], y[i], z[i]};
     int e[3] = {0, 0, 0};
     bool lost = false;
@@ -114,7 +129,7 @@ __global__ void k_classify_leave(DirTable t, int n_owned, const double* __restri
     }
     key[i] = k;
     val[i] = i;
-    atomicAdd(&counts[k], 1);
+    block_histogram_add(hist, static_cast<int>(k), counts);
 }
 
 // How many neighbour directions need atom i as a ghost, and which (bit d).
@@ -147,20 +162,25 @@ __global__ void k_halo_count(DirTable t, int n_owned, const double* __restrict__
 __global__ void k_halo_expand(DirTable t, int n_owned, const double* __restrict__ x, const double* __restrict__ y,
                               const double* __restrict__ z, const int* __restrict__ off, unsigned* __restrict__ key,
                               int* __restrict__ val, int* __restrict__ counts, int capacity) {
+    __shared__ int hist[kMaxDirs + 2];
+    if (threadIdx.x < kMaxDirs + 2) hist[threadIdx.x] = 0;
+    __syncthreads();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_owned) return;
-    unsigned mask = halo_mask(t, x[i], y[i], z[i]);
-    int o = off[i];
-    while (mask) {
-        const int d = __ffs(mask) - 1;
-        mask &= mask - 1;
-        if (o < capacity) {
-            key[o] = static_cast<unsigned>(d);
-            val[o] = i;
+    if (i < n_owned) {
+        unsigned mask = halo_mask(t, x[i], y[i], z[i]);
+        int o = off[i];
+        while (mask) {
+            const int d = __ffs(mask) - 1;
+            mask &= mask - 1;
+            if (o < capacity) {
+                key[o] = static_cast<unsigned>(d);
+                val[o] = i;
+            }
+            ++o;
+            atomicAdd(&hist[d], 1);
         }
-        ++o;
-        atomicAdd(&counts[d], 1);
     }
+    block_histogram_add(hist, -1, counts);
 }
 
 struct Fields {
@@ -257,6 +277,7 @@ struct dsmd_domain {
     bool profile = false;
     cudaEvent_t ev_phase[8] = {};
     double phase_ms[8] = {};   // integrate1, vote, refresh issue + interior, boundary wait + boundary, integrate2, rebuild
+    double rebuild_ms[4] = {}; // wall time of migrate, sort owned, ghost plan, list build (profiling mode)
     int64_t phase_steps = 0;
 };
 
@@ -492,10 +513,25 @@ int build_halo(dsmd_domain* d, cudaStream_t s) {
 }
 
 int rebuild(dsmd_domain* d, cudaStream_t s) {
+    auto now = [&]() {
+        if (d->profile) cudaStreamSynchronize(s);
+        return std::chrono::steady_clock::now();
+    };
+    auto lap = [&](int k, std::chrono::steady_clock::time_point& t0) {
+        if (!d->profile) return;
+        const auto t1 = now();
+        d->rebuild_ms[k] += std::chrono::duration<double, std::milli>(t1 - t0).count();
+        t0 = t1;
+    };
+    auto t0 = now();
     if (d->world > 1) { const int rc = migrate(d, s); if (rc) return rc; }
+    lap(0, t0);
     DOM_CTX(d, dsmd_sort_owned(d->ctx, s));
+    lap(1, t0);
     { const int rc = build_halo(d, s); if (rc) return rc; }
+    lap(2, t0);
     DOM_CTX(d, dsmd_build_neighbor_list(d->ctx, s));
+    lap(3, t0);
     ++d->rebuilds;
     d->vote_pending = -1;
     d->d_prev = d->d_prev2 = 0.0;
@@ -697,11 +733,14 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
     return DSMD_OK;
 }
 
-int dsmd_domain_profile(dsmd_domain* d, int enable, double phase_ms[6], int64_t* steps) {
+int dsmd_domain_profile(dsmd_domain* d, int enable, double phase_ms[10], int64_t* steps) {
     if (!d) return DSMD_ERR_INVALID;
     if (enable && !d->ev_phase[0])
         for (int k = 0; k < 8; ++k) DOM_CUDA(d, cudaEventCreate(&d->ev_phase[k]));
-    if (phase_ms) for (int k = 0; k < 6; ++k) phase_ms[k] = d->phase_ms[k];
+    if (phase_ms) {
+        for (int k = 0; k < 6; ++k) phase_ms[k] = d->phase_ms[k];
+        for (int k = 0; k < 4; ++k) phase_ms[6 + k] = d->rebuild_ms[k];
+    }
     if (steps) *steps = d->phase_steps;
     d->profile = enable != 0;
     return DSMD_OK;

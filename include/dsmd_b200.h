@@ -240,8 +240,9 @@ int dsmd_domain_run(dsmd_domain* dom, int64_t n_steps, double dt, double force_t
 
 /* Per-phase device times of dsmd_domain_run, accumulated while enabled (profiling mode synchronises every step, so the
  * totals are not a benchmark): phase_ms = {integrate 1 + pack, vote, refresh issue + interior forces (or nothing),
- * boundary forces incl. the wait for the refresh (or the full pass), integrate 2, rebuild}. Returns the sums so far. */
-int dsmd_domain_profile(dsmd_domain* dom, int enable, double phase_ms[6], int64_t* steps);
+ * boundary forces incl. the wait for the refresh (or the full pass), integrate 2, rebuild, and the wall time of the
+ * rebuild's four parts: migration, sort of the owned atoms, ghost plan, list build}. Returns the sums so far. */
+int dsmd_domain_profile(dsmd_domain* dom, int enable, double phase_ms[10], int64_t* steps);
 
 int dsmd_domain_stats(const dsmd_domain* dom, int64_t* rebuilds, int64_t* migrated_atoms, int64_t* ghosts,
                       int64_t* positions_sent_per_step, double* worst_disp_sq, int64_t* launches);

@@ -130,6 +130,44 @@ def test_forces_energy_virial_match_oracle_and_golden(cuda_device, name):
     ctx.close()
 
 
+def test_larger_box_and_bricks_give_the_oracle_pair_set(cuda_device):
+    """A 6,912-atom box (14 cells per axis, cell rows longer than a thread block's run of atoms): the list must hold exactly
+    the oracle's pairs, in the undivided box and in a two-brick split with ghosts (non-wrapping x axis)."""
+    s = syn.fcc_lj(12, seed=17)
+    R = s.cutoff + s.skin
+    ctx = make_context(s)
+    ctx.build_neighbor_list()
+    gi, gj, _ = gpu_pairs_by_gid(ctx)
+    half = gi < gj
+    got = co.canonical_pairs(np.stack([gi[half], gj[half]], axis=1))
+    want = co.canonical_pairs(co.pairs(*(np.ascontiguousarray(s.pos[:, k]) for k in range(3)), s.n, s.box, search=R))
+    assert len(gi) == 2 * len(want) and np.array_equal(got, want)
+    ctx.compute_forces(want_energy=True)
+    _, f_o, sc_o = oracle_case(s)
+    assert rms(ctx.forces_by_gid(s.n) - f_o) <= FORCE_RTOL * rms(f_o)
+    ctx.close()
+    wrapped = s.pos - s.box * np.floor(s.pos / s.box)
+    halo = R + 0.2
+    for brick in syn.brick_decompose(s.pos, s.box, (2, 1, 1), halo):
+        own, src, img = brick["owned"], brick["ghost_src"], brick["ghost_image"]
+        pos = np.concatenate([wrapped[own], wrapped[src] + img * s.box])
+        atom = np.concatenate([own, src])
+        ctx = make_context(s, pos=pos, n_owned=len(own), gid=np.arange(len(pos), dtype=np.int32), lo=brick["lo"],
+                           hi=brick["hi"], halo=halo, types=s.types[atom], charge=s.charge[atom], n_global=len(pos))
+        ctx.build_neighbor_list()
+        n_owned, n_total = ctx.counts()
+        slot_upload = ctx.download("global_id", n_total)
+        i, j, _ = ctx.list_pairs()
+        ui, uj = slot_upload[i], slot_upload[j]
+        once = (uj >= n_owned) | (ui < uj)
+        got = co.canonical_pairs(np.stack([ui[once], uj[once]], axis=1))
+        x, y, z = (np.ascontiguousarray(pos[:, k]) for k in range(3))
+        want = co.canonical_pairs(co.pairs(x, y, z, len(own), s.box, split=(1, 0, 0), search=R))
+        assert np.array_equal(got, want)
+        assert ctx.list_stats()["interior_entries"] == int((j < n_owned).sum())
+        ctx.close()
+
+
 def test_results_are_bitwise_reproducible(cuda_device):
     s = syn.fcc_lj(8, seed=4)
     out = []
