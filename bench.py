@@ -28,6 +28,7 @@ if ROOT not in sys.path:
 DT = 0.005
 ARGON_TAU_FS = 2156.0          # sigma sqrt(m / epsilon) of argon in fs: maps dt = 0.005 tau to 10.78 fs for ns/day
 L2_BYTES = 126e6
+NCU_PAIR_TRAFFIC_BYTES_PER_ATOM = 174.06e6 / 500_000   # measured DRAM bytes per launch / atoms (full list + positions)
 
 
 def measured_peaks():
@@ -140,10 +141,17 @@ class CpuMd:
         if self.kind == "reference":
             self.ref.update_positions(*self.pos)
             if self.ref.needs_rebuild():
+                # the reference wraps atoms into the box on rebuild steps only (at migration); its CPU list builder bins
+                # by clamping, so it needs wrapped positions, and between rebuilds the list's periodic shifts need
+                # positions that run on
+                for k in range(3):
+                    self.pos[k] -= s.box[k] * np.floor(self.pos[k] / s.box[k])
+                self.ref.update_positions(*self.pos)
                 self.ref.build_list()
                 self.rebuilds += 1
         else:
-            d2 = sum((p - r) ** 2 for p, r in zip(self.pos, self.ref_pos)).max()
+            d = [p - r for p, r in zip(self.pos, self.ref_pos)]
+            d2 = sum((dk - s.box[k] * np.round(dk / s.box[k])) ** 2 for k, dk in enumerate(d)).max()
             if d2 > (0.5 * s.skin) ** 2:
                 self.pairs = self.co.pairs(*self.pos, s.n, s.box, search=s.cutoff + s.skin)
                 self.ref_pos = [p.copy() for p in self.pos]
@@ -291,11 +299,45 @@ def single_gpu(args):
         "pack_positions": {"ms": t_pack, "gbs": pack_bytes / (t_pack * 1e-3) / 1e9,
                            "frac_hbm": pack_bytes / (t_pack * 1e-3) / 1e9 / hbm_peak},
     }
+    # radius-graph edge build on the 1,000,000-atom disordered solid (cutoff 5 A): compact periodic form, and the
+    # reference's interface form (int64 [2, E] + double [E, 3]) over explicit image atoms
+    if args.workload == "lj_4m":
+        from deepscalemd_b200 import synthetic as syn
+        solid = syn.disordered_solid_lattice(100)
+        sx, sy, sz = (torch.tensor(np.ascontiguousarray(solid.pos[:, k]), device="cuda") for k in range(3))
+        eb = capi.EdgeBuilder()
+        eb.build_periodic(sx, sy, sz, solid.box, solid.cutoff, stream)
+        t_compact = time_calls(lambda: eb.build_periodic(sx, sy, sz, solid.box, solid.cutoff, stream), 5, stream)
+        n_edges = int(eb.build_periodic(sx, sy, sz, solid.box, solid.cutoff, stream)[0].numel())
+        reach = solid.cutoff + 1e-8
+        img = eb.images(sx, sy, sz, None, solid.box, np.zeros(3), -np.full(3, reach), solid.box + reach, (1, 1, 1), stream)
+        ix, iy, iz = img["x"].clone(), img["y"].clone(), img["z"].clone()
+        owner, shift = img["owner"].clone(), tuple(t.clone() for t in img["shift"])
+        lo_b, hi_b = -np.full(3, reach), solid.box + reach
+
+        def interface_build():
+            return eb.build(ix, iy, iz, solid.cutoff, lo=lo_b, hi=hi_b, n_centers=solid.n, owner=owner, shift=shift,
+                            stream=stream)
+
+        interface_build()
+        t_interface = time_calls(interface_build, 5, stream)
+        e_interface = int(interface_build()[0].shape[1])
+        compact_bytes = 24.0 * solid.n + 23.0 * n_edges
+        interface_bytes = 24.0 * img["n_all"] + 40.0 * e_interface
+        kernels["edge_build_compact_1m"] = {"ms": t_compact, "edges": n_edges, "gbs": compact_bytes / (t_compact * 1e-3) / 1e9,
+                                            "frac_hbm": compact_bytes / (t_compact * 1e-3) / 1e9 / hbm_peak}
+        kernels["edge_build_interface_1m"] = {"ms": t_interface, "edges": e_interface, "atoms_with_images": img["n_all"],
+                                              "gbs": interface_bytes / (t_interface * 1e-3) / 1e9,
+                                              "frac_hbm": interface_bytes / (t_interface * 1e-3) / 1e9 / hbm_peak}
+        eb.close()
+        del sx, sy, sz, ix, iy, iz, owner, shift, img
     pk = kernels["pair_forces"]
     roofline = {
         "kernel": "k_pair (LJ, full list, forces only)", "bound": "hbm", "achieved": pk["gbs"], "peak": hbm_peak,
         "unit": "GB/s", "frac": pk["frac_hbm"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
-        "traffic": None,
+        # dram__bytes_read + dram__bytes_write of one k_pair launch, from the ncu capture of the 500,000-atom case
+        # (profiles/k_pair_k_build_list_lj_500k_ncu_full.md: 174.1 MB) scaled by the atom count
+        "traffic": NCU_PAIR_TRAFFIC_BYTES_PER_ATOM * s.n,
         "algorithmic_bytes_per_launch": pair_bytes, "algorithmic_flops_per_launch": pair_flops,
         "fp32": {"achieved_tflops": pk["tflops"], "peak_tflops": fp32_peak_tflops,
                  "peak_source": "measured in this run (independent FMA chains on every SM)", "frac": pk["frac_fp32"]},

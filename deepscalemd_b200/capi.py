@@ -29,7 +29,8 @@ SYMBOLS = [
     "dsmd_forces_host", "dsmd_launch_count", "dsmd_fma_probe", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
     "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_edges_create", "dsmd_edges_destroy",
     "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
-    "dsmd_edges_result_compact", "dsmd_kinetic_energy_noalloc", "dsmd_nccl_unique_id", "dsmd_domain_create",
+    "dsmd_edges_result_compact", "dsmd_images_build", "dsmd_images_result", "dsmd_mark_receivers",
+    "dsmd_kinetic_energy_noalloc", "dsmd_nccl_unique_id", "dsmd_domain_create",
     "dsmd_domain_destroy", "dsmd_domain_last_error", "dsmd_domain_rebuild", "dsmd_domain_refresh", "dsmd_domain_run",
     "dsmd_domain_stats", "dsmd_domain_profile",
 ]
@@ -480,6 +481,36 @@ class EdgeBuilder:
         idx = _tensor_from_ptr(pi.value, (2, E), torch.int64, dev)
         sh = _tensor_from_ptr(ps.value, (E, 3), torch.float64, dev) if with_shift and ps.value else None
         return idx, sh
+
+    def images(self, x, y, z, types, box, origin, region_lo, region_hi, shells, stream=None):
+        """Wrapped atoms + periodic images (MLIPStep's image atoms): dict of torch views x, y, z, type, owner, shift."""
+        import torch
+        n = x.numel()
+        args = [_arr(v, np.float64) for v in (box, origin, region_lo, region_hi)]
+        sh = _arr(shells, np.int32)
+        n_all = c_int64(0)
+        self._check(self.lib.dsmd_images_build(
+            self.h, c_void_p(x.data_ptr()), c_void_p(y.data_ptr()), c_void_p(z.data_ptr()),
+            c_void_p(types.data_ptr()) if types is not None else None, c_int64(n), *[_p(a) for a in args], _p(sh),
+            ctypes.byref(n_all), _stream_handle(stream)))
+        ptrs = [c_void_p() for _ in range(8)]
+        self._check(self.lib.dsmd_images_result(self.h, *[ctypes.byref(p) for p in ptrs], ctypes.byref(n_all)))
+        N = n_all.value
+        dev = torch.device("cuda", self.device)
+        f64 = lambda p: _tensor_from_ptr(p.value, (N,), torch.float64, dev)
+        i32 = lambda p: _tensor_from_ptr(p.value, (N,), torch.int32, dev)
+        return dict(x=f64(ptrs[0]), y=f64(ptrs[1]), z=f64(ptrs[2]), type=i32(ptrs[3]), owner=i32(ptrs[4]),
+                    shift=(f64(ptrs[5]), f64(ptrs[6]), f64(ptrs[7])), n_all=N)
+
+    def mark_receivers(self, x, y, z, lo, hi, reach, stream=None):
+        import torch
+        n = x.numel()
+        ok = torch.empty(n, dtype=torch.uint8, device=x.device)
+        l, h = _arr(lo, np.float64), _arr(hi, np.float64)
+        self._check(self.lib.dsmd_mark_receivers(self.h, c_void_p(x.data_ptr()), c_void_p(y.data_ptr()),
+                                                 c_void_p(z.data_ptr()), c_int64(n), _p(l), _p(h), c_double(reach),
+                                                 c_void_p(ok.data_ptr()), _stream_handle(stream)))
+        return ok
 
     def build_periodic(self, x, y, z, box, cutoff, stream=None):
         import torch

@@ -685,8 +685,16 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
         DOM_CTX(d, dsmd_integrate(d->ctx, 1, dt, force_to_accel, s));   // v += dt/2 a, x += dt v, pack owned, displacement
         mark(1);
         // The vote: all ranks take the MAX of their displacement words; the host reads the result of the PREVIOUS step (its
-        // copy finished long ago) and extrapolates by its last growth (src/md_simulation.cpp:1232-1245).
-        if (d->world > 1) DOM_NCCL(d, g_nccl.AllReduce(word, word, 1, ncclUint64, ncclMax, d->comm, s));
+        // copy finished long ago) and extrapolates by its last growth (src/md_simulation.cpp:1232-1245). With several
+        // ranks the all-reduce and the read-back run on the side stream, off the critical path of the force kernels; the
+        // refresh that follows on that stream (or the rebuild, which waits for it) keeps the communicator's call order.
+        cudaStream_t vote_stream = s;
+        if (d->world > 1) {
+            DOM_CUDA(d, cudaEventRecord(d->ev_main, s));
+            DOM_CUDA(d, cudaStreamWaitEvent(d->side, d->ev_main, 0));
+            DOM_NCCL(d, g_nccl.AllReduce(word, word, 1, ncclUint64, ncclMax, d->comm, d->side));
+            vote_stream = d->side;
+        }
         if (d->vote_pending >= 0) {
             DOM_CUDA(d, cudaEventSynchronize(d->ev_vote[d->vote_pending]));
             d->d_prev2 = d->d_prev;
@@ -694,13 +702,14 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
             d->worst_disp_sq = std::max(d->worst_disp_sq, d->d_prev * d->d_prev);
         }
         const int slot = static_cast<int>(step & 1);
-        DOM_CUDA(d, cudaMemcpyAsync(d->h_vote[slot], word, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
-        DOM_CUDA(d, cudaEventRecord(d->ev_vote[slot], s));
+        DOM_CUDA(d, cudaMemcpyAsync(d->h_vote[slot], word, sizeof(unsigned long long), cudaMemcpyDeviceToHost, vote_stream));
+        DOM_CUDA(d, cudaEventRecord(d->ev_vote[slot], vote_stream));
         d->vote_pending = slot;
         const double predicted = d->d_prev + 1.5 * std::max(d->d_prev - d->d_prev2, 0.0);
         mark(2);
         bool rebuilt = false;
         if (predicted * predicted > limit2) {
+            if (d->world > 1) DOM_CUDA(d, cudaStreamWaitEvent(s, d->ev_vote[slot], 0));   // the side stream's all-reduce first
             { const int rc = rebuild(d, s); if (rc) return rc; }
             rebuilt = true;
             mark(3);

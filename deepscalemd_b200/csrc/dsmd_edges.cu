@@ -281,6 +281,86 @@ __global__ void k_edge_fill_compact(Grid g, int n, int stride, const int* __rest
     }
 }
 
+// ---- periodic image atoms and receiver marking (what MLIPStep::prepare does around the edge build) ----------------------
+
+struct ImageSpec {
+    double box[3], origin[3], region_lo[3], region_hi[3];
+    int shells[3];
+};
+
+__device__ __forceinline__ double wrap_from(double v, double origin, double box, int shells) {
+    return shells > 0 ? v - box * floor((v - origin) / box) : v;
+}
+
+// Visits the periodic images of (px, py, pz) that lie inside the region, in the fixed order sx, sy, sz ascending.
+template <class Emit>
+__device__ __forceinline__ void visit_images(const ImageSpec& s, double px, double py, double pz, Emit emit) {
+    for (int sx = -s.shells[0]; sx <= s.shells[0]; ++sx) {
+        const double qx = __dadd_rn(px, __dmul_rn(static_cast<double>(sx), s.box[0]));
+        if (s.shells[0] > 0 && (qx < s.region_lo[0] || qx > s.region_hi[0])) continue;
+        for (int sy = -s.shells[1]; sy <= s.shells[1]; ++sy) {
+            const double qy = __dadd_rn(py, __dmul_rn(static_cast<double>(sy), s.box[1]));
+            if (s.shells[1] > 0 && (qy < s.region_lo[1] || qy > s.region_hi[1])) continue;
+            for (int sz = -s.shells[2]; sz <= s.shells[2]; ++sz) {
+                if (sx == 0 && sy == 0 && sz == 0) continue;
+                const double qz = __dadd_rn(pz, __dmul_rn(static_cast<double>(sz), s.box[2]));
+                if (s.shells[2] > 0 && (qz < s.region_lo[2] || qz > s.region_hi[2])) continue;
+                emit(qx, qy, qz);
+            }
+        }
+    }
+}
+
+__global__ void k_image_count(ImageSpec spec, int n, const double* __restrict__ x, const double* __restrict__ y,
+                              const double* __restrict__ z, long long* __restrict__ counts) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const double px = wrap_from(x[i], spec.origin[0], spec.box[0], spec.shells[0]);
+    const double py = wrap_from(y[i], spec.origin[1], spec.box[1], spec.shells[1]);
+    const double pz = wrap_from(z[i], spec.origin[2], spec.box[2], spec.shells[2]);
+    long long c = 0;
+    visit_images(spec, px, py, pz, [&](double, double, double) { ++c; });
+    counts[i] = c;
+}
+
+// The wrapped atoms in [0, n), their images behind them: those of atom i in slots n + offsets[i] ...
+__global__ void k_image_extend(ImageSpec spec, int n, const double* __restrict__ x, const double* __restrict__ y,
+                               const double* __restrict__ z, const int* __restrict__ type,
+                               const long long* __restrict__ offsets, double* __restrict__ ex, double* __restrict__ ey,
+                               double* __restrict__ ez, int* __restrict__ etype, int* __restrict__ eowner,
+                               double* __restrict__ esx, double* __restrict__ esy, double* __restrict__ esz) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const double px = wrap_from(x[i], spec.origin[0], spec.box[0], spec.shells[0]);
+    const double py = wrap_from(y[i], spec.origin[1], spec.box[1], spec.shells[1]);
+    const double pz = wrap_from(z[i], spec.origin[2], spec.box[2], spec.shells[2]);
+    const int t = type ? type[i] : 0;
+    ex[i] = px; ey[i] = py; ez[i] = pz;
+    etype[i] = t;
+    eowner[i] = i;
+    esx[i] = 0.0; esy[i] = 0.0; esz[i] = 0.0;
+    long long slot = n + offsets[i];
+    visit_images(spec, px, py, pz, [&](double qx, double qy, double qz) {
+        ex[slot] = qx; ey[slot] = qy; ez[slot] = qz;
+        etype[slot] = t;
+        eowner[slot] = i;
+        esx[slot] = qx - px; esy[slot] = qy - py; esz[slot] = qz - pz;
+        ++slot;
+    });
+}
+
+__global__ void k_mark_receivers(int n, const double* __restrict__ x, const double* __restrict__ y,
+                                 const double* __restrict__ z, double lx, double ly, double lz, double hx, double hy,
+                                 double hz, double reach2, unsigned char* __restrict__ ok) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const double dx = fmax(fmax(lx - x[i], x[i] - hx), 0.0);
+    const double dy = fmax(fmax(ly - y[i], y[i] - hy), 0.0);
+    const double dz = fmax(fmax(lz - z[i], z[i] - hz), 0.0);
+    const double d2 = __dadd_rn(__dadd_rn(__dmul_rn(dx, dx), __dmul_rn(dy, dy)), __dmul_rn(dz, dz));
+    ok[i] = d2 <= reach2 ? 1 : 0;   // a NaN position gives 0
+}
+
 template <class T>
 bool grow(T*& ptr, size_t& capacity, size_t needed) {
     if (needed <= capacity) return true;
@@ -313,6 +393,13 @@ struct dsmd_edges {
     int* c_dst = nullptr;                   size_t cap_cdst = 0;
     signed char* c_shift = nullptr;         size_t cap_cshift = 0;
     float* c_vec = nullptr;                 size_t cap_cvec = 0;
+    // image atoms
+    long long* img_counts = nullptr;        size_t cap_img_counts = 0;
+    long long* img_offsets = nullptr;       size_t cap_img_offsets = 0;
+    double* ext[6] = {};                    size_t cap_ext[6] = {};     // x y z shift_x shift_y shift_z
+    int* ext_type = nullptr;                size_t cap_ext_type = 0;
+    int* ext_owner = nullptr;               size_t cap_ext_owner = 0;
+    int64_t n_ext = 0;
     double* bounds = nullptr;               // 6 doubles for the device-side bounding box
     EdgeStatus* d_status = nullptr;
     EdgeStatus* h_status = nullptr;
@@ -489,6 +576,8 @@ void dsmd_edges_destroy(dsmd_edges* e) {
     cudaFree(e->pq); cudaFree(e->slot_of); cudaFree(e->cell_start); cudaFree(e->rows); cudaFree(e->counts);
     cudaFree(e->offsets); cudaFree(e->temp); cudaFree(e->edges); cudaFree(e->shift); cudaFree(e->c_src);
     cudaFree(e->c_dst); cudaFree(e->c_shift); cudaFree(e->c_vec); cudaFree(e->bounds); cudaFree(e->d_status);
+    cudaFree(e->img_counts); cudaFree(e->img_offsets); cudaFree(e->ext_type); cudaFree(e->ext_owner);
+    for (int k = 0; k < 6; ++k) cudaFree(e->ext[k]);
     cudaFreeHost(e->h_status);
     delete e;
 }
@@ -594,6 +683,81 @@ int dsmd_edges_build_periodic(dsmd_edges* e, const double* d_x, const double* d_
     k_edge_fill_compact<<<blocks_for(n, kThreads), kThreads, 0, s>>>(g, static_cast<int>(n), e->stride, e->slot_of,
                                                                     e->rows, e->counts, e->offsets, d_x, d_y, d_z,
                                                                     e->c_src, e->c_dst, e->c_shift, e->c_vec);
+    ++e->launches;
+    EDGE_CUDA(e, cudaGetLastError());
+    return DSMD_OK;
+}
+
+int dsmd_images_build(dsmd_edges* e, const double* d_x, const double* d_y, const double* d_z, const int32_t* d_type,
+                      int64_t n, const double box[3], const double origin[3], const double region_lo[3],
+                      const double region_hi[3], const int shells[3], int64_t* n_all, void* stream) {
+    if (!e || !n_all || !box || !origin || !region_lo || !region_hi || !shells) return DSMD_ERR_INVALID;
+    *n_all = 0;
+    e->n_ext = 0;
+    if (n < 0 || n >= std::numeric_limits<int32_t>::max() / 2) return efail(e, DSMD_ERR_INVALID, "atom count out of range");
+    if (n == 0) return DSMD_OK;
+    if (!d_x || !d_y || !d_z) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EDGE_CUDA(e, cudaSetDevice(e->device));
+    ImageSpec spec;
+    for (int a = 0; a < 3; ++a) {
+        if (shells[a] < 0 || shells[a] > 8) return efail(e, DSMD_ERR_INVALID, "image shells must be in 0 .. 8");
+        if (shells[a] > 0 && !(box[a] > 0.0)) return efail(e, DSMD_ERR_INVALID, "box length must be positive on an image axis");
+        spec.box[a] = box[a]; spec.origin[a] = origin[a];
+        spec.region_lo[a] = region_lo[a]; spec.region_hi[a] = region_hi[a];
+        spec.shells[a] = shells[a];
+    }
+    const size_t un = static_cast<size_t>(n);
+    EDGE_ALLOC(e, grow(e->img_counts, e->cap_img_counts, un));
+    EDGE_ALLOC(e, grow(e->img_offsets, e->cap_img_offsets, un));
+    size_t scan_bytes = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, e->img_counts, e->img_offsets, static_cast<int>(n), s);
+    EDGE_ALLOC(e, grow(e->temp, e->cap_temp, scan_bytes));
+    k_image_count<<<blocks_for(n, kThreads), kThreads, 0, s>>>(spec, static_cast<int>(n), d_x, d_y, d_z, e->img_counts);
+    EDGE_CUDA(e, cub::DeviceScan::ExclusiveSum(e->temp, scan_bytes, e->img_counts, e->img_offsets, static_cast<int>(n), s));
+    // the image count comes to the host: the one synchronisation (MLIPStep::prepare does the same, src/MLIPStep.cu:254-255)
+    long long last[2] = {0, 0};
+    EDGE_CUDA(e, cudaMemcpyAsync(&last[0], e->img_offsets + (n - 1), sizeof(long long), cudaMemcpyDeviceToHost, s));
+    EDGE_CUDA(e, cudaMemcpyAsync(&last[1], e->img_counts + (n - 1), sizeof(long long), cudaMemcpyDeviceToHost, s));
+    EDGE_CUDA(e, cudaStreamSynchronize(s));
+    const int64_t total = n + last[0] + last[1];
+    if (total >= std::numeric_limits<int32_t>::max() / 2) return efail(e, DSMD_ERR_CAPACITY, "too many image atoms");
+    for (int k = 0; k < 6; ++k) EDGE_ALLOC(e, grow(e->ext[k], e->cap_ext[k], static_cast<size_t>(total)));
+    EDGE_ALLOC(e, grow(e->ext_type, e->cap_ext_type, static_cast<size_t>(total)));
+    EDGE_ALLOC(e, grow(e->ext_owner, e->cap_ext_owner, static_cast<size_t>(total)));
+    k_image_extend<<<blocks_for(n, kThreads), kThreads, 0, s>>>(spec, static_cast<int>(n), d_x, d_y, d_z, d_type,
+                                                               e->img_offsets, e->ext[0], e->ext[1], e->ext[2],
+                                                               e->ext_type, e->ext_owner, e->ext[3], e->ext[4], e->ext[5]);
+    e->launches += 2;
+    EDGE_CUDA(e, cudaGetLastError());
+    e->n_ext = total;
+    *n_all = total;
+    return DSMD_OK;
+}
+
+int dsmd_images_result(const dsmd_edges* e, const double** d_x, const double** d_y, const double** d_z,
+                       const int32_t** d_type, const int32_t** d_owner, const double** d_shift_x, const double** d_shift_y,
+                       const double** d_shift_z, int64_t* n_all) {
+    if (!e) return DSMD_ERR_INVALID;
+    if (d_x) *d_x = e->ext[0];
+    if (d_y) *d_y = e->ext[1];
+    if (d_z) *d_z = e->ext[2];
+    if (d_type) *d_type = e->ext_type;
+    if (d_owner) *d_owner = e->ext_owner;
+    if (d_shift_x) *d_shift_x = e->ext[3];
+    if (d_shift_y) *d_shift_y = e->ext[4];
+    if (d_shift_z) *d_shift_z = e->ext[5];
+    if (n_all) *n_all = e->n_ext;
+    return DSMD_OK;
+}
+
+int dsmd_mark_receivers(dsmd_edges* e, const double* d_x, const double* d_y, const double* d_z, int64_t n,
+                        const double lo[3], const double hi[3], double reach, unsigned char* d_ok, void* stream) {
+    if (!e || !lo || !hi || n < 0 || (n > 0 && (!d_x || !d_y || !d_z || !d_ok))) return DSMD_ERR_INVALID;
+    if (n == 0) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    k_mark_receivers<<<blocks_for(n, kThreads), kThreads, 0, s>>>(static_cast<int>(n), d_x, d_y, d_z, lo[0], lo[1], lo[2],
+                                                                 hi[0], hi[1], hi[2], reach * reach, d_ok);
     ++e->launches;
     EDGE_CUDA(e, cudaGetLastError());
     return DSMD_OK;

@@ -158,6 +158,23 @@ def disordered_solid(n_target=1_000_000, *, density=0.05, min_dist=1.8, cutoff=5
                   meta=dict(seed=seed, density=density, min_dist=min_dist))
 
 
+def disordered_solid_lattice(n_side=100, *, density=0.05, jitter=0.45, cutoff=5.0, seed=99) -> System:
+    """The same shape as disordered_solid() in seconds instead of minutes for a million atoms: a simple-cubic lattice at
+    the target density with a seeded uniform jitter per coordinate, which keeps every pair further apart than
+    spacing - 2 * jitter (2.714 - 0.9 = 1.81 A at density 0.05). Used where only sizes and neighbour counts matter (the
+    benchmark's edge-build timing)."""
+    rng = np.random.default_rng(seed)
+    n = n_side ** 3
+    a = (1.0 / density) ** (1.0 / 3.0)
+    g = np.arange(n_side, dtype=np.float64)
+    pos = (np.stack(np.meshgrid(g, g, g, indexing="ij"), axis=-1).reshape(-1, 3) + 0.5) * a
+    pos += rng.uniform(-jitter, jitter, pos.shape)
+    types = rng.choice(3, size=n, p=[0.5, 0.3, 0.2]).astype(np.int32)
+    return System(name=f"solid_lattice_{n}", pos=pos, box=np.full(3, n_side * a), types=types, charge=np.zeros(n),
+                  mass=np.ones(n), eps=np.ones((3, 3)), sig=np.ones((3, 3)), cutoff=cutoff, skin=0.0,
+                  meta=dict(seed=seed, density=density, jitter=jitter))
+
+
 def brick_decompose(pos, box, dims, halo):
     """Host-side spatial decomposition used by tests and the benchmark set-up: for every brick of a dims grid over the
     periodic box, the indices of its owned atoms and (source index, image shift) of its ghost atoms - every periodic

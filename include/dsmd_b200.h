@@ -267,6 +267,24 @@ int dsmd_edges_build(dsmd_edges* eb, const double* d_x, const double* d_y, const
                      const unsigned char* d_receiver_ok, int row, int64_t* n_edges, void* stream);
 int dsmd_edges_result(const dsmd_edges* eb, const int64_t** d_edge_index, const double** d_edge_shift, int64_t* n_edges);
 
+/* Periodic image atoms for the axes a model sees as periodic but the MD does not decompose (MLIPStep::prepare,
+ * src/MLIPStep.cu:31-103, 214-260): positions are wrapped from `origin` on the axes with shells > 0, and every image
+ * (sx, sy, sz) != 0, |s_a| <= shells[a], that lies inside [region_lo, region_hi] on every image axis is appended behind
+ * the n wrapped atoms (images of atom i are consecutive, in the order sx, sy, sz ascending). Results (valid until the next
+ * call): positions, types, the atom each entry copies and its offset from it - the arrays EdgeBuilder::Images wants.
+ * *n_all returns n + images after the single synchronisation of `stream`. */
+int dsmd_images_build(dsmd_edges* eb, const double* d_x, const double* d_y, const double* d_z, const int32_t* d_type,
+                      int64_t n, const double box[3], const double origin[3], const double region_lo[3],
+                      const double region_hi[3], const int shells[3], int64_t* n_all, void* stream);
+int dsmd_images_result(const dsmd_edges* eb, const double** d_x, const double** d_y, const double** d_z,
+                       const int32_t** d_type, const int32_t** d_owner, const double** d_shift_x, const double** d_shift_y,
+                       const double** d_shift_z, int64_t* n_all);
+
+/* Receiver mask (mark_receivers_kernel, src/MLIPStep.cu:150-161): d_ok[i] = 1 when atom i lies within `reach` (Euclidean
+ * distance) of the box [lo, hi]; a NaN position gives 0. The mask EdgeBuilder::Prune wants. */
+int dsmd_mark_receivers(dsmd_edges* eb, const double* d_x, const double* d_y, const double* d_z, int64_t n,
+                        const double lo[3], const double hi[3], double reach, unsigned char* d_ok, void* stream);
+
 /* Compact periodic radius graph (no image atoms): n atoms in an orthorhombic periodic box; directed edges as
  * int32 src / dst, int8 lattice shift [E * 3] (dst image = pos[dst] + shift * box) and fp32 edge vectors [E * 3],
  * sorted by (src, dst, shift). No counterpart in the reference, which feeds images as explicit atoms. */

@@ -103,3 +103,42 @@ def test_compact_periodic_graph(cuda_device):
     assert np.abs(vec - d).max() < 1e-5
     assert abs(len(src) / s.n - 4.18879 * 125 * 0.05) < 1.0      # 26.2 neighbours per atom
     eb.close()
+
+
+def test_image_atoms_receivers_and_the_whole_mlip_preparation(cuda_device):
+    """The device versions of MLIPStep's image atoms and receiver mask equal the oracle's bit for bit, and feeding them
+    to the edge builder (images as shifts + receiver pruning) gives the oracle's edge list: the whole preparation of one
+    model call for a periodic box on one rank, unwrapped input positions included."""
+    import torch
+    rng = np.random.default_rng(21)
+    n, L, cutoff = 4000, 32.0, 5.0
+    box = np.full(3, L)
+    pos = rng.uniform(0, L, (n, 3)) + rng.integers(-2, 3, (n, 3)) * L      # not wrapped
+    types = rng.integers(0, 3, n).astype(np.int32)
+    reach = cutoff + 1e-8
+    lo, hi = -np.full(3, reach), box + reach
+    want = co.images(pos[:, 0], pos[:, 1], pos[:, 2], box, np.zeros(3), lo, hi, np.ones(3, dtype=np.int32))
+    eb = capi.EdgeBuilder()
+    x, y, z = (to_dev(pos[:, k]) for k in range(3))
+    got = eb.images(x, y, z, to_dev(types), box, np.zeros(3), lo, hi, (1, 1, 1))
+    assert got["n_all"] == len(want["x"]) > n
+    for k in "xyz":
+        assert np.array_equal(got[k].cpu().numpy(), want[k])
+    assert np.array_equal(got["owner"].cpu().numpy(), want["owner"])
+    assert np.array_equal(got["type"].cpu().numpy(), types[want["owner"]])
+    assert np.array_equal(torch.stack(got["shift"], dim=1).cpu().numpy(), want["shift"])
+    # receivers: the atoms within 2 A of an inner box
+    inner_lo, inner_hi = np.full(3, 8.0), np.full(3, 20.0)
+    ok_want = co.mark_receivers(want["x"][:n], want["y"][:n], want["z"][:n], inner_lo, inner_hi, 2.0)
+    ok = eb.mark_receivers(got["x"][:n].clone(), got["y"][:n].clone(), got["z"][:n].clone(), inner_lo, inner_hi, 2.0)
+    assert np.array_equal(ok.cpu().numpy(), ok_want) and 0 < ok_want.sum() < n
+    # edges over wrapped atoms + images, centred on real atoms, pruned to edges received by marked atoms
+    gx, gy, gz = got["x"].clone(), got["y"].clone(), got["z"].clone()
+    owner, shift = got["owner"].clone(), tuple(t.clone() for t in got["shift"])
+    idx, sh = eb.build(gx, gy, gz, cutoff, n_centers=n, owner=owner, shift=shift, receiver_ok=ok, row=1)
+    want_idx, want_sh = co.edges(want["x"], want["y"], want["z"], cutoff, n_centers=n, owner=want["owner"],
+                                 shift=want["shift"], receiver_ok=ok_want, row=1)
+    a = np.concatenate([idx.cpu().numpy().astype(np.float64), sh.cpu().numpy().T])
+    b = np.concatenate([want_idx.astype(np.float64), want_sh.T])
+    assert a.shape == b.shape and np.array_equal(canon(a), canon(b))
+    eb.close()

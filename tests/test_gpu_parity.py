@@ -299,6 +299,35 @@ def test_nve_run_conserves_energy_and_respects_the_skin(cuda_device):
         ctx.close()
 
 
+def test_nve_drift_is_no_worse_than_the_reference_over_10k_steps(cuda_device):
+    """The 32,000-atom LJ system, 2,000 equilibration + 10,000 measured velocity-Verlet steps with displacement-triggered
+    rebuilds: the total energy per atom must wander no further than it does in the reference's own CPU code (fixture
+    tests/golden/nve_lj_32000.npz, made by tests/golden/make_nve_golden.py). Plain truncation at the cutoff, as in the
+    reference, so the energy is not exactly conserved by either; the trajectories diverge (chaos), the statistics agree."""
+    g = np.load(os.path.join(GOLDEN, "nve_lj_32000.npz"))
+    dt, every = float(g["dt"]), int(g["every"])
+    s = syn.fcc_lj(20, seed=12345)
+    ctx = make_context(s)
+    ctx.build_neighbor_list()
+    ctx.compute_forces()
+    out = ctx.run_nve(int(g["equilibration"]), dt, 1.0, 0.5, 0, True)
+    trace, rebuilds, worst = [], 0, out["worst_disp_sq"]
+    for k in range(int(g["steps"]) // every + 1):
+        ctx.compute_forces(want_energy=True)
+        trace.append((ctx.read_scalars()["pe"] + ctx.kinetic_energy()) / s.n)
+        if k < int(g["steps"]) // every:
+            out = ctx.run_nve(every, dt, 1.0, 0.5, 0, True)
+            rebuilds += out["rebuilds"]
+            worst = max(worst, out["worst_disp_sq"])
+    trace, ref = np.array(trace), g["energy_per_atom"]
+    wander, wander_ref = np.abs(trace - trace[0]).max(), np.abs(ref - ref[0]).max()
+    assert wander <= max(1.5 * wander_ref, 2e-4), (wander, wander_ref)
+    assert abs(trace[0] - ref[0]) < 5e-3            # same thermodynamic state after equilibration
+    assert abs(rebuilds - int(g["rebuilds"])) <= 0.15 * int(g["rebuilds"])
+    assert worst <= (0.5 * s.skin) ** 2 * 1.2
+    ctx.close()
+
+
 def test_nve_trajectory_tracks_the_oracle(cuda_device):
     """Twenty velocity-Verlet steps on the GPU and on the oracle's fp64 forces stay together to fp32-force accuracy."""
     s = syn.fcc_lj(5, seed=8)
