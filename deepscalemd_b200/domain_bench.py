@@ -20,6 +20,19 @@ def run(args):
         os.environ["NCCL_DEBUG"] = "WARN"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    # Watchdog: a communication hang must end this process (and free its GPU) instead of running into the caller's
+    # limit; the limit is generous for the work below (set-up 15 s, MD a few seconds, timing sections a few seconds).
+    import threading
+
+    def give_up():
+        if rank == 0:
+            print(json.dumps({"metric": "atom-steps/s", "value": None, "n_gpus": world,
+                              "error": "multi-GPU benchmark did not finish within its time limit"}), flush=True)
+        os._exit(3)
+
+    watchdog = threading.Timer(float(os.environ.get("DSMD_BENCH_LIMIT_S", "240")), give_up)
+    watchdog.daemon = True
+    watchdog.start()
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
@@ -169,6 +182,7 @@ def run(args):
             "gpu_launches": int(launches),
         }
         print(json.dumps(line))
+    watchdog.cancel()
     dom.close()
     ctx.close()
     dist.barrier()

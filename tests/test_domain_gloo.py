@@ -20,6 +20,17 @@ def free_port():
         return s.getsockname()[1]
 
 
+_PORT = {}
+
+
+def free_port_once():
+    """One port per test invocation, shared by both ranks."""
+    key = os.environ.get("PYTEST_CURRENT_TEST", "")
+    if key not in _PORT:
+        _PORT[key] = free_port()
+    return _PORT[key]
+
+
 def reference_md(s, steps, dt):
     pos = [np.ascontiguousarray(s.pos[:, k]) for k in range(3)]
     vel = [np.ascontiguousarray(s.vel[:, k]) for k in range(3)]
@@ -77,7 +88,16 @@ def worker(rank, world, port, dims, steps, dt, out_path):
 def test_two_ranks_equal_the_undivided_system(tmp_path, dims):
     steps, dt = 25, 0.005
     out = str(tmp_path / "out.pt")
-    mp.spawn(worker, args=(2, free_port(), dims, steps, dt, out), nprocs=2, join=True)
+    procs = [mp.get_context("spawn").Process(target=worker, args=(rank, 2, free_port_once(), dims, steps, dt, out))
+             for rank in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.terminate()
+    assert not hung and all(p.exitcode == 0 for p in procs)
     parts = torch.load(out, weights_only=False)
     s = syn.fcc_lj(8, seed=33)
     f0, sc0, pos_end, sc_end = reference_md(s, steps, dt)

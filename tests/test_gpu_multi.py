@@ -20,6 +20,29 @@ def free_port():
         return s.getsockname()[1]
 
 
+def run_ranks(worker_fn, args, world, limit_s=240):
+    """Runs worker_fn(rank, *args) in `world` child processes; a rank that has not finished within the limit is terminated
+    (by its own pid) and the test fails, so that a communication hang cannot hold the GPUs."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=worker_fn, args=(rank, *args)) for rank in range(world)]
+    for p in procs:
+        p.start()
+    import time
+    deadline = time.time() + limit_s
+    for p in procs:
+        p.join(max(0.0, deadline - time.time()))
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.terminate()
+    for p in hung:
+        p.join(10)
+        if p.is_alive():
+            p.kill()
+    assert not hung, f"{len(hung)} rank(s) did not finish within {limit_s} s"
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
+
 def worker(rank, world, port, steps, dt, out_path):
     import torch.distributed as dist
     from deepscalemd_b200 import capi, domain
@@ -110,11 +133,9 @@ def worker_native(rank, world, port, steps, dt, out_path):
 def test_two_gpus_equal_the_undivided_system(tmp_path, which):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
-    import torch.multiprocessing as mp
     steps, dt = 40, 0.005
     out = str(tmp_path / "out.pt")
-    mp.spawn(worker if which == "torch_distributed" else worker_native, args=(2, free_port(), steps, dt, out), nprocs=2,
-             join=True)
+    run_ranks(worker if which == "torch_distributed" else worker_native, (2, free_port(), steps, dt, out), 2)
     parts = torch.load(out, weights_only=False)
     s = syn.fcc_lj(10, seed=44)
     pos = [np.ascontiguousarray(s.pos[:, k]) for k in range(3)]
