@@ -222,6 +222,11 @@ class Context:
 
     def list_pairs(self, stream=None):
         """Directed list entries as numpy arrays (i slot, j slot, excluded flag)."""
+        ti, tj, tf = self.list_pairs_device(stream)
+        return ti.cpu().numpy(), tj.cpu().numpy(), tf.cpu().numpy()
+
+    def list_pairs_device(self, stream=None):
+        """Directed list entries as device tensors (i slot int32, j slot int32, excluded flag uint8)."""
         import torch
         n = c_int64(0)
         self._check(self.lib.dsmd_list_export(self.h, None, None, None, c_int64(0), ctypes.byref(n),
@@ -234,7 +239,7 @@ class Context:
                                               c_void_p(tf.data_ptr()), c_int64(n.value), ctypes.byref(n),
                                               _stream_handle(stream)))
         k = n.value
-        return ti[:k].cpu().numpy(), tj[:k].cpu().numpy(), tf[:k].cpu().numpy()
+        return ti[:k], tj[:k], tf[:k]
 
     # -- per step -------------------------------------------------------------------------------------------------------
     def pack_positions(self, first=0, count=None, stream=None):

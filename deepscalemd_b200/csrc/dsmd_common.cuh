@@ -30,8 +30,9 @@ struct Grid {
     float r2_list;      // (cutoff + skin)^2
     float band;         // |r2 - r2_list| below this is decided in fp64
     double r2_list_d;
-    float cellw[3];     // cell width per axis (length units)
+    float cellw[3];     // cell width per axis (length units); the x cells are finer than the y and z cells
     float r_pad;        // list radius plus a rounding margin: the reach used to prune cell rows
+    float x_reach;      // widest half window along x (stencil * width of an unrefined cell, a hair less)
 };
 
 struct Status {
@@ -79,8 +80,10 @@ __device__ __forceinline__ float fixed_delta(unsigned int a, unsigned int b, flo
 
 // The x cells of the cell row (cy + dy, cz + dz) that can hold a partner of the atom `pi` (home cell cx, cy, cz): the
 // row is skipped when its distance from the atom in the y-z plane already exceeds the list radius; otherwise the
-// x window is the chord of the list sphere at that distance, never wider than the stencil. One range [a0, b0], or two
-// when the window crosses the periodic boundary ([a1, b1] is empty otherwise).
+// x window is the chord of the list sphere at that distance, never wider than the stencil, rounded outwards to whole
+// x cells (which is why the grid is finer along x: a row is a contiguous run of slots whatever the x cell width, and
+// narrow x cells waste less of it). One range [a0, b0], or two when the window crosses the periodic boundary
+// ([a1, b1] is empty otherwise).
 struct RowWindow {
     int a0, b0, a1, b1;
 };
@@ -102,7 +105,7 @@ __device__ __forceinline__ bool row_window(const Grid& g, const int4& pi, int cy
     const float reach2 = g.r_pad * g.r_pad;
     if (d2 >= reach2) return false;
     float hw = sqrtf(reach2 - d2);
-    hw = fminf(hw, static_cast<float>(g.stencil) * g.cellw[0] * 0.9999999f);
+    hw = fminf(hw, g.x_reach);
     const unsigned hw_fixed = static_cast<unsigned>(hw / g.scale[0]) + 1u;
     w.a1 = 0;
     w.b1 = -1;

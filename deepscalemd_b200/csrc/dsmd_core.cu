@@ -37,6 +37,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kPairThreads = 128;
+constexpr int kXRefine = 4;    // x cells per cell width of the y and z axes (tighter row windows in the list build)
 constexpr unsigned kExclBit = 0x80000000u;
 constexpr unsigned kIndexMask = 0x3FFFFFFFu;
 constexpr int kNumReal = 11;   // x y z vx vy vz fx fy fz mass charge
@@ -379,10 +380,13 @@ struct PairParams {
     const float4* ewald;         // [2 * intervals]: force cubic, energy cubic
 };
 
+// 1 / v: the hardware approximation (1 ulp) for the force-only kernels, one Newton step more (full single precision)
+// where energy and virial sums are taken.
+template <bool REFINE>
 __device__ __forceinline__ float fast_rcp(float v) {
     float r;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
-    return r * (2.0f - v * r);   // one Newton step: full single precision
+    return REFINE ? r * (2.0f - v * r) : r;
 }
 
 // One pair of the list, evaluated from atom i's side: adds to the force (and energy / virial) accumulators.
@@ -400,13 +404,13 @@ struct PairAccumulator {
         const float r2 = dx * dx + dy * dy + dz * dz;
         if (r2 < p.rc2 && r2 >= 1e-10f) {
             float fmag = 0.f, epair = 0.f;
-            const float r2inv = fast_rcp(r2);
+            const float r2inv = fast_rcp<ENERGY>(r2);
             if (!excluded) {
                 const float2 c = MULTI ? s_c6c12[trow + pj.w] : single;
                 const float r6 = r2inv * r2inv * r2inv;
-                const float rep = c.y * r6 * r6, att = c.x * r6;
-                float f = r2inv * (12.f * rep - 6.f * att);
-                float u = rep - att;
+                const float t = c.y * r6;
+                float f = (r2inv * r6) * (12.f * t - 6.f * c.x);
+                float u = (ENERGY || SWITCH) ? r6 * (t - c.x) : 0.f;
                 if (SWITCH) {
                     if (r2 > p.rs2) {
                         const float a = p.rc2 - r2, b = p.rc2 + 2.f * r2 - 3.f * p.rs2;
@@ -772,6 +776,16 @@ int make_grid(dsmd_ctx* c) {
                         "a periodic axis is shorter than three cells of width cutoff + skin");
         }
         stencil = 1;
+    }
+    // Rows of cells along x are contiguous runs of slots, searched through a window that is rounded outwards to whole
+    // cells: finer x cells (kXRefine per unrefined cell) make the windows tighter at no cost per row.
+    g.x_reach = static_cast<float>(g.stencil * (1.0 / (g.inv_len[0] * g.nc[0])) * 0.9999999);
+    {
+        int refine = kXRefine;
+        while (refine > 1 && (static_cast<int64_t>(g.nc[0]) * refine > 4096 ||
+                              2 * static_cast<int64_t>(g.nc[0]) * refine * g.nc[1] * g.nc[2] + 1 > (1ll << 26)))
+            refine >>= 1;
+        g.nc[0] *= refine;
     }
     const int64_t ncells = static_cast<int64_t>(g.nc[0]) * g.nc[1] * g.nc[2];
     if (2 * ncells + 1 > (1ll << 30)) return fail(c, DSMD_ERR_INVALID, "cell grid too large");

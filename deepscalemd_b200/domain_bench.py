@@ -16,6 +16,8 @@ def run(args):
     from deepscalemd_b200 import capi, domain
 
     os.environ.setdefault("NCCL_DEBUG", "WARN")   # keep NCCL's banner off stdout: rank 0 prints exactly one JSON line
+    # point-to-point messages and an 8-byte all-reduce gain nothing from NVLink multicast objects: do not set them up
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
         os.environ["NCCL_DEBUG"] = "WARN"
     rank = int(os.environ.get("RANK", "0"))

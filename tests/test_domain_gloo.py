@@ -84,12 +84,15 @@ def worker(rank, world, port, dims, steps, dt, out_path):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("dims", [(2, 1, 1), (1, 2, 1)])
-def test_two_ranks_equal_the_undivided_system(tmp_path, dims):
+@pytest.mark.parametrize("dims", [(2, 1, 1), (1, 2, 1), (2, 2, 2)])
+def test_ranks_equal_the_undivided_system(tmp_path, dims):
+    """Two ranks (one split axis) and eight ranks (2 x 2 x 2: every axis split, 26 directions towards 7 peers, several
+    messages per peer)."""
     steps, dt = 25, 0.005
+    world = dims[0] * dims[1] * dims[2]
     out = str(tmp_path / "out.pt")
-    procs = [mp.get_context("spawn").Process(target=worker, args=(rank, 2, free_port_once(), dims, steps, dt, out))
-             for rank in range(2)]
+    procs = [mp.get_context("spawn").Process(target=worker, args=(rank, world, free_port_once(), dims, steps, dt, out))
+             for rank in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -121,7 +124,7 @@ def test_two_ranks_equal_the_undivided_system(tmp_path, dims):
     d -= s.box * np.round(d / s.box)
     assert np.abs(d).max() < 1e-9
     assert abs(parts[0]["last"]["pe"] - sc_end["pe"]) < 1e-9 * abs(sc_end["pe"])
-    assert parts[0]["rebuilds"] >= 3 and parts[0]["rebuilds"] == parts[1]["rebuilds"]
+    assert parts[0]["rebuilds"] >= 3 and all(p["rebuilds"] == parts[0]["rebuilds"] for p in parts)
 
 
 def test_brick_grids_and_directions():

@@ -44,6 +44,7 @@ def run_ranks(worker_fn, args, world, limit_s=240):
 
 
 def worker(rank, world, port, steps, dt, out_path):
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import torch.distributed as dist
     from deepscalemd_b200 import capi, domain
     torch.cuda.set_device(rank)
@@ -86,6 +87,7 @@ def worker(rank, world, port, steps, dt, out_path):
 def worker_native(rank, world, port, steps, dt, out_path):
     """The same run through the native domain code (dsmd_domain_*: its own NCCL communicator; gloo only carries the
     unique id and the result gathering)."""
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import torch.distributed as dist
     from deepscalemd_b200 import capi, domain
     torch.cuda.set_device(rank)

@@ -40,6 +40,31 @@ def make_context(s, switch=-1.0, capacity=None, n_owned=None, pos=None, gid=None
     return ctx
 
 
+def full_size_pair_checksum(ctx, name):
+    """Compares the device list of a full-size system with the committed count and checksum of its pair set (from the CPU
+    oracle and the reference's own list builder; tests/golden/make_full_size_checksums.py): every pair listed from both
+    sides, and each side's set equal to the reference's."""
+    import json
+    import sys
+    import torch
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, here)
+    from pair_checksum import checksum_torch
+    with open(os.path.join(here, "full_size_pair_checksums.json")) as f:
+        want = json.load(f)[name]
+    want = (want["pairs"], int(want["sum1"]), int(want["sum2"]))
+    _, n_total = ctx.counts()
+    gid = torch.from_numpy(ctx.download("global_id", n_total).astype(np.int64)).to(f"cuda:{ctx.device}")
+    ti, tj, tf = ctx.list_pairs_device()
+    gi, gj = gid[ti.long()], gid[tj.long()]
+    del ti, tj
+    up = gi < gj
+    assert checksum_torch(gi[up], gj[up]) == want
+    down = ~up
+    assert checksum_torch(gj[down], gi[down]) == want
+    return int(tf.sum().item())
+
+
 def gpu_pairs_by_gid(ctx):
     """Directed list entries mapped to global ids."""
     _, n_total = ctx.counts()
@@ -200,10 +225,12 @@ def test_unwrapped_positions_and_skin_do_not_change_forces(cuda_device):
     assert rms(f1 - f0) <= 2e-6 * rms(f0)
 
 
-def test_two_brick_split_with_ghosts_adds_up(cuda_device):
-    """A 2 x 1 x 1 decomposition emulated on one device: each brick's context holds owned + ghost atoms (ghosts
-    image-shifted on the split axis, the other axes wrap). Pair sets per brick equal the oracle's; forces equal the
-    undivided system's; energies and virials of the bricks add up (an owned-ghost pair counts half on each side)."""
+@pytest.mark.parametrize("dims", [(2, 1, 1), (2, 2, 1), (2, 2, 2)])
+def test_brick_split_with_ghosts_adds_up(cuda_device, dims):
+    """A brick decomposition emulated on one device (one, two or all three axes split): each brick's context holds
+    owned + ghost atoms (ghosts image-shifted on the split axes, the other axes wrap). Pair sets per brick equal the
+    oracle's; forces equal the undivided system's; energies and virials of the bricks add up (an owned-ghost pair counts
+    half on each side)."""
     s = syn.fcc_lj(8, seed=21)
     R = s.cutoff + s.skin
     halo = R + 0.2
@@ -211,7 +238,8 @@ def test_two_brick_split_with_ghosts_adds_up(cuda_device):
     wrapped = s.pos - s.box * np.floor(s.pos / s.box)
     pe = vir = 0.0
     f_sum = np.full_like(f_whole, np.nan)
-    for brick in syn.brick_decompose(s.pos, s.box, (2, 1, 1), halo):
+    split = tuple(int(d > 1) for d in dims)
+    for brick in syn.brick_decompose(s.pos, s.box, dims, halo):
         own, src, img = brick["owned"], brick["ghost_src"], brick["ghost_image"]
         pos = np.concatenate([wrapped[own], wrapped[src] + img * s.box])
         atom = np.concatenate([own, src])                    # the atom each uploaded entry is (an image of)
@@ -233,7 +261,7 @@ def test_two_brick_split_with_ghosts_adds_up(cuda_device):
         got = co.canonical_pairs(np.stack([ui[once], uj[once]], axis=1))
         assert 2 * len(got) - int((uj >= n_owned).sum()) == len(ui)
         x, y, z = (np.ascontiguousarray(pos[:, k]) for k in range(3))
-        want = co.canonical_pairs(co.pairs(x, y, z, len(own), s.box, split=(1, 0, 0), search=R))
+        want = co.canonical_pairs(co.pairs(x, y, z, len(own), s.box, split=split, search=R))
         assert np.array_equal(got, want)
         ctx.compute_forces(capi.PHASE_INTERIOR, want_energy=True)
         ctx.compute_forces(capi.PHASE_BOUNDARY, want_energy=True)
@@ -428,6 +456,7 @@ def test_full_size_properties_lj_4m(cuda_device):
     assert stats["directed_entries"] % 2 == 0
     per_atom = stats["directed_entries"] / s.n
     assert 76.0 < per_atom < 79.5          # 4/3 pi 2.8^3 * 0.8442 = 77.6
+    full_size_pair_checksum(ctx, "lj_4m")
     ctx.compute_forces(want_energy=True)
     sc = ctx.read_scalars()
     f = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
@@ -450,6 +479,8 @@ def test_full_size_properties_water_648k(cuda_device):
     assert stats["directed_entries"] % 2 == 0
     per_atom = stats["directed_entries"] / s.n
     assert 700.0 < per_atom < 750.0            # 4/3 pi 12^3 * 0.1003 atoms / A^3 = 726
+    flagged = full_size_pair_checksum(ctx, "water_648k")
+    assert flagged == 2 * 3 * (s.n // 3)       # O-H1, O-H2, H1-H2 of every molecule, from both sides
     ctx.compute_forces(want_energy=True)
     sc = ctx.read_scalars()
     f = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
@@ -470,7 +501,8 @@ def test_full_size_properties_kob_andersen_1m(cuda_device):
     ctx.build_neighbor_list()
     stats = ctx.list_stats()
     per_atom = stats["directed_entries"] / s.n
-    assert 105.0 < per_atom < 116.0            # 4/3 pi 2.8^3 * 1.2 = 110.3
+    assert 100.0 < per_atom < 116.0            # 4/3 pi 2.8^3 * 1.2 = 110.3 for an ideal gas; the relaxed mixture has 104.1
+    full_size_pair_checksum(ctx, "kob_andersen_1m")
     ctx.compute_forces(want_energy=True)
     sc = ctx.read_scalars()
     f = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)

@@ -222,3 +222,22 @@ def test_velocity_verlet_conserves_energy_on_oracle_forces():
     e1 = pe + 0.5 * sum((v * v).sum() for v in vel)
     # plain truncation at the cutoff makes the energy jump when pairs cross it: small but not round-off small
     assert abs(e1 - e0) / s.n < 5e-3
+
+
+def test_pair_checksum_is_the_same_in_numpy_and_torch():
+    """The full-size list checks compare a checksum computed in numpy (generator) with one computed in torch (device)."""
+    import sys
+    import torch
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, here)
+    from pair_checksum import checksum_numpy, checksum_torch
+    rng = np.random.default_rng(3)
+    a = rng.integers(0, 4_000_000, 100_000)
+    b = a + rng.integers(1, 4_000_000, 100_000)
+    want = checksum_numpy(a, b)
+    assert checksum_torch(torch.from_numpy(a), torch.from_numpy(b), chunk=30_000) == want
+    perm = rng.permutation(len(a))
+    assert checksum_numpy(a[perm], b[perm]) == want
+    b2 = b.copy()
+    b2[7] += 1
+    assert checksum_numpy(a, b2) != want
