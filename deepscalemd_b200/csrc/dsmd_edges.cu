@@ -479,6 +479,17 @@ int edge_grid(dsmd_edges* e, Grid& g, const double lo[3], const double hi[3], bo
         }
     }
     if (!done) return efail(e, DSMD_ERR_BOX_TOO_SMALL, "periodic box shorter than three cells of width cutoff");
+    // finer cells along x: a cell row is a contiguous run of slots whatever the x cell width, and the search window
+    // (rounded outwards to whole cells) is tighter
+    g.x_reach = static_cast<float>(g.stencil * (len[0] / g.nc[0]) * 0.9999999);
+    for (int refine = 4; refine > 1; refine >>= 1) {
+        if (static_cast<long long>(g.nc[0]) * refine <= 4096 &&
+            static_cast<long long>(g.ncells) * refine <= 4 * max_cells) {
+            g.nc[0] *= refine;
+            g.ncells *= refine;
+            break;
+        }
+    }
     g.r2_list = static_cast<float>(cutoff * cutoff);
     g.r2_list_d = cutoff * cutoff;
     g.band = static_cast<float>(8.0 * cutoff * max_scale + 16.0 * cutoff * cutoff * 5.9604645e-8);

@@ -1,7 +1,9 @@
-"""Generates tests/golden/full_size_pair_checksums.json: for BASELINE's full-size systems (LJ 4,000,000 atoms, the
-1,048,576-atom binary mixture, the 648,000-atom water box) the number of pairs inside the list radius and an
-order-independent checksum of the pair set, computed by the CPU oracle and, where it fits the reference's valid regime,
-by the REFERENCE's own SpatialVerletList (oracle/_ref, compiled in place); the two must agree before anything is written.
+"""Generates tests/golden/full_size_pair_checksums.json and tests/golden/full_size_<case>.npz: for the full-size systems
+(LJ 4,000,000 atoms, the 1,048,576-atom binary mixture, the 648,000-atom water box) the number of pairs inside the list
+radius and an order-independent checksum of the pair set, computed by the CPU oracle and by the REFERENCE's own
+SpatialVerletList (oracle/_ref, compiled in place) - the two must agree before anything is written - and the potential
+energy, virial and the forces on every SAMPLE-th atom from the oracle (exact erfc) and from the reference's
+ForceCalculatorCPU.
 Run from the repository root, where the reference tree is present:
 
     make -C oracle && python tests/golden/make_full_size_checksums.py
@@ -33,6 +35,9 @@ def cases():
     }
 
 
+SAMPLES = 4096
+
+
 def undirected(p):
     a = np.minimum(p[:, 0], p[:, 1])
     b = np.maximum(p[:, 0], p[:, 1])
@@ -47,21 +52,34 @@ def main():
         t0 = time.time()
         p = co.pairs(x, y, z, s.n, s.box, search=s.cutoff + s.skin)
         got = checksum_numpy(*undirected(p))
+        c6, c12 = co.lj_tables(s.eps, s.sig)
+        alpha = co.ewald_alpha(s.cutoff) if s.coulomb else 0.0
+        f, sc = co.forces(x, y, z, s.n, s.box, p, c6, c12, s.cutoff, charge=s.charge, types=s.types, do_coulomb=s.coulomb,
+                          alpha=alpha, ewald_mode=1, exclusions=s.exclusions)
+        sample = np.arange(0, s.n, max(1, s.n // SAMPLES), dtype=np.int64)
+        fixture = dict(sample=sample, f_oracle=f[sample], f_rms_oracle=np.sqrt((f * f).sum(1).mean()),
+                       pe_oracle=sc["pe"], virial_oracle=sc["virial"])
+        del f
         t1 = time.time()
         del p
         entry = dict(atoms=int(s.n), pairs=got[0], sum1=str(got[1]), sum2=str(got[2]), source="oracle")
         if co.ref_available():
-            ref = co.RefCase(x, y, z, s.n, s.box, s.cutoff, s.skin, charge=s.charge, types=s.types,
-                             gid=np.arange(s.n, dtype=np.int32), eps=s.eps, sig=s.sig)
+            ref = co.RefCase(x, y, z, s.n, s.box, s.cutoff, s.skin, charge=s.charge, types=s.types, eps=s.eps,
+                             sig=s.sig, exclusions=s.exclusions)
             ref.build_list()
             rp = ref.list_pairs()
             ref_sum = checksum_numpy(*undirected(rp))
             del rp
+            fr, rsc = ref.compute(do_coulomb=bool(s.coulomb))
+            fixture.update(f_reference=fr[sample], f_rms_reference=np.sqrt((fr * fr).sum(1).mean()),
+                           pe_reference=rsc["pe_real"], virial_reference=rsc["virial"])
+            del fr
             ref.close()
             assert ref_sum == got, (name, ref_sum, got)
             entry["source"] = "oracle and reference SpatialVerletList (equal)"
         print(name, entry, "oracle %.1f s, reference %.1f s" % (t1 - t0, time.time() - t1), flush=True)
         out[name] = entry
+        np.savez(os.path.join(HERE, "full_size_%s.npz" % name), **fixture)
     with open(os.path.join(HERE, "full_size_pair_checksums.json"), "w") as f:
         json.dump(out, f, indent=1, sort_keys=True)
         f.write("\n")

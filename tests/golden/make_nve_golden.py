@@ -1,7 +1,7 @@
 """Energy-drift fixture: the REFERENCE's own CPU code (oracle/_ref) integrates the 32,000-atom LJ system (FCC 20^3,
 density 0.8442, T* = 1.44, cutoff 2.5 plain truncation, skin 0.3, dt 0.005) with velocity Verlet for 2,000 equilibration
 steps and then 10,000 measured steps, rebuilding its list when SpatialVerletList::needs_rebuild says so. Stored: total
-energy per atom every 1,000 measured steps. Run from the repository root where the reference tree is present:
+energy per atom every 100 measured steps. Run from the repository root where the reference tree is present:
 
     make -C oracle && python tests/golden/make_nve_golden.py          (about two minutes on 8 cores)
 """
@@ -17,7 +17,7 @@ from deepscalemd_b200 import synthetic as syn  # noqa: E402
 from oracle import cpu_oracle as co  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DT, EQUIL, STEPS, EVERY = 0.005, 2000, 10000, 1000
+DT, EQUIL, STEPS, EVERY = 0.005, 2000, 10000, 100
 
 
 def main():

@@ -65,6 +65,26 @@ def full_size_pair_checksum(ctx, name):
     return int(tf.sum().item())
 
 
+def full_size_force_parity(ctx, s, name, sc):
+    """Potential energy, virial and the forces on a fixed sample of atoms of a full-size system against the CPU oracle and
+    the reference's own ForceCalculatorCPU (fixture tests/golden/full_size_<name>.npz, made by
+    tests/golden/make_full_size_checksums.py), at the same tolerances as the small cases."""
+    g = np.load(os.path.join(GOLDEN, "full_size_%s.npz" % name))
+    sample = g["sample"]
+    f = ctx.forces_by_gid(s.n)[sample]
+    scale = float(g["f_rms_oracle"])
+    assert rms(f - g["f_oracle"]) <= FORCE_RTOL * scale
+    assert abs(sc["pe"] - float(g["pe_oracle"])) <= SCALAR_RTOL * abs(float(g["pe_oracle"]))
+    assert abs(sc["virial"] - float(g["virial_oracle"])) <= SCALAR_RTOL * abs(float(g["virial_oracle"]))
+    if s.coulomb:   # the reference's CPU path interpolates erfc linearly in r^2 (2.6e-4 from exact erfc on this system)
+        assert rms(f - g["f_reference"]) <= 5e-4 * float(g["f_rms_reference"])
+        assert abs(sc["pe"] - float(g["pe_reference"])) <= 1e-4 * abs(float(g["pe_reference"]))
+    else:
+        assert rms(f - g["f_reference"]) <= FORCE_RTOL * float(g["f_rms_reference"])
+        assert abs(sc["pe"] - float(g["pe_reference"])) <= SCALAR_RTOL * abs(float(g["pe_reference"]))
+        assert abs(sc["virial"] - float(g["virial_reference"])) <= SCALAR_RTOL * abs(float(g["virial_reference"]))
+
+
 def gpu_pairs_by_gid(ctx):
     """Directed list entries mapped to global ids."""
     _, n_total = ctx.counts()
@@ -329,9 +349,12 @@ def test_nve_run_conserves_energy_and_respects_the_skin(cuda_device):
 
 def test_nve_drift_is_no_worse_than_the_reference_over_10k_steps(cuda_device):
     """The 32,000-atom LJ system, 2,000 equilibration + 10,000 measured velocity-Verlet steps with displacement-triggered
-    rebuilds: the total energy per atom must wander no further than it does in the reference's own CPU code (fixture
-    tests/golden/nve_lj_32000.npz, made by tests/golden/make_nve_golden.py). Plain truncation at the cutoff, as in the
-    reference, so the energy is not exactly conserved by either; the trajectories diverge (chaos), the statistics agree."""
+    rebuilds, against the same run of the reference's own CPU code (fixture tests/golden/nve_lj_32000.npz, made by
+    tests/golden/make_nve_golden.py; total energy per atom every 100 steps). With plain truncation at the cutoff, as in
+    the reference, the sampled total energy is a constant plus white noise (pairs crossing the cutoff: standard deviation
+    1.2e-4 per atom in the reference, no correlation between samples) plus whatever the integration drifts. The
+    trajectories diverge (chaos), so the comparison is statistical: the fitted linear trend over the 10,000 steps is no
+    larger than the reference's plus three standard errors of such a fit, and the noise about the trend is the same."""
     g = np.load(os.path.join(GOLDEN, "nve_lj_32000.npz"))
     dt, every = float(g["dt"]), int(g["every"])
     s = syn.fcc_lj(20, seed=12345)
@@ -348,9 +371,18 @@ def test_nve_drift_is_no_worse_than_the_reference_over_10k_steps(cuda_device):
             rebuilds += out["rebuilds"]
             worst = max(worst, out["worst_disp_sq"])
     trace, ref = np.array(trace), g["energy_per_atom"]
-    wander, wander_ref = np.abs(trace - trace[0]).max(), np.abs(ref - ref[0]).max()
-    assert wander <= max(1.5 * wander_ref, 2e-4), (wander, wander_ref)
-    assert abs(trace[0] - ref[0]) < 5e-3            # same thermodynamic state after equilibration
+    assert len(trace) == len(ref)
+
+    def trend_and_noise(e):
+        t = np.arange(len(e))
+        slope, intercept = np.polyfit(t, e, 1)
+        return slope * (len(e) - 1), (e - (slope * t + intercept)).std()
+
+    (drift, noise), (drift_ref, noise_ref) = trend_and_noise(trace), trend_and_noise(ref)
+    standard_error = noise_ref * np.sqrt(12.0 / len(ref))
+    assert abs(drift) <= abs(drift_ref) + 3.0 * standard_error, (drift, drift_ref, standard_error)
+    assert noise <= 1.3 * noise_ref, (noise, noise_ref)
+    assert abs(trace.mean() - ref.mean()) < 5e-3    # same thermodynamic state after equilibration
     assert abs(rebuilds - int(g["rebuilds"])) <= 0.15 * int(g["rebuilds"])
     assert worst <= (0.5 * s.skin) ** 2 * 1.2
     ctx.close()
@@ -446,9 +478,10 @@ def test_row_overflow_is_retried(cuda_device):
 
 
 def test_full_size_properties_lj_4m(cuda_device):
-    """At the benchmark's full size (4,000,000 atoms) the oracle is too slow to run per test, so check what does not
-    depend on size: every pair listed from both sides, forces summing to zero (Newton's third law through the full list),
-    the expected neighbour counts, and the energy per atom of the 32,000-atom system built the same way."""
+    """At the benchmark's full size (4,000,000 atoms) the oracle is too slow to run per test, so the test compares with
+    what it and the reference's own CPU code computed once for this seeded system (committed fixtures): the pair set by
+    count and checksum, from both sides of the full list; the potential energy, the virial and the forces on 4,099
+    sampled atoms; besides what does not depend on size (forces summing to zero, the expected neighbour counts)."""
     s = syn.fcc_lj(100, seed=12345)
     ctx = make_context(s)
     ctx.build_neighbor_list()
@@ -462,16 +495,14 @@ def test_full_size_properties_lj_4m(cuda_device):
     f = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
     assert np.all(np.isfinite(f))
     assert np.abs(f.sum(0)).max() <= 1e-6 * np.abs(f).sum(0).max()
-    small = syn.fcc_lj(20, seed=12345)
-    _, _, sc_small = oracle_case(small)
-    assert abs(sc["pe"] / s.n - sc_small["pe"] / small.n) < 2e-3 * abs(sc_small["pe"] / small.n)
+    full_size_force_parity(ctx, s, "lj_4m", sc)
     ctx.close()
 
 
 def test_full_size_properties_water_648k(cuda_device):
     """The 648,000-atom rigid-water geometry box (LJ on O-O, real-space Ewald, intramolecular exclusions) at full size:
-    list symmetric, forces finite and summing to zero, every exclusion that is inside the list flagged from both sides,
-    and energy per molecule equal to that of the 3,993-atom box of the same construction checked against the oracle."""
+    list symmetric and equal to the reference's by count and checksum, forces finite and summing to zero, every exclusion
+    flagged from both sides, energy, virial and sampled forces equal to the oracle's and the reference's."""
     s = syn.water_box(60, seed=3)
     ctx = make_context(s)
     ctx.build_neighbor_list()
@@ -486,16 +517,13 @@ def test_full_size_properties_water_648k(cuda_device):
     f = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
     assert np.all(np.isfinite(f))
     assert np.abs(f.sum(0)).max() <= 2e-6 * np.abs(f).sum(0).max()
-    small = syn.water_box(11, seed=3)
-    _, _, sc_small = oracle_case(small)
-    # different random orientations, same statistics: the per-molecule energy agrees to a few per cent
-    e_big, e_small = sc["pe"] / (s.n / 3), sc_small["pe"] / (small.n / 3)
-    assert abs(e_big - e_small) < 0.05 * abs(e_small)
+    full_size_force_parity(ctx, s, "water_648k", sc)
     ctx.close()
 
 
 def test_full_size_properties_kob_andersen_1m(cuda_device):
-    """The 1,048,576-atom binary mixture (two types, explicit pair table) at full size."""
+    """The 1,048,576-atom binary mixture (two types, explicit pair table) at full size: pair set, energy, virial and
+    sampled forces against the committed results of the oracle and the reference."""
     s = syn.kob_andersen(1_048_576, seed=5)
     ctx = make_context(s)
     ctx.build_neighbor_list()
@@ -508,7 +536,5 @@ def test_full_size_properties_kob_andersen_1m(cuda_device):
     f = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
     assert np.all(np.isfinite(f))
     assert np.abs(f.sum(0)).max() <= 2e-6 * np.abs(f).sum(0).max()
-    small = syn.kob_andersen(4096, seed=5)
-    _, _, sc_small = oracle_case(small)
-    assert abs(sc["pe"] / s.n - sc_small["pe"] / small.n) < 0.1 * abs(sc_small["pe"] / small.n)
+    full_size_force_parity(ctx, s, "kob_andersen_1m", sc)
     ctx.close()
