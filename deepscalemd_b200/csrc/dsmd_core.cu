@@ -155,14 +155,14 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
              ExclusionTable excl, const int* __restrict__ cell_start, unsigned* __restrict__ nbr, int stride,
              int* __restrict__ deg, int* __restrict__ deg_int, Status* st) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_owned) return;
-    const int4 pi = pq[i];
+    const bool active = i < n_owned;   // lanes past the end stay for the warp sums at the bottom
+    const int4 pi = active ? pq[i] : make_int4(0, 0, 0, 0);
     const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
     const int cz = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.z), g.wrap[2], g.nc[2]));
     const int S = g.stencil;
     const size_t base = (static_cast<size_t>(i >> 5) * stride) * 32 + (i & 31);
     int ex_begin = 0, ex_end = 0;
-    if (excl.offsets) {
+    if (active && excl.offsets) {
         const int gi = gid[i];
         if (gi >= 0 && gi < excl.n_global) {
             ex_begin = excl.offsets[gi];
@@ -171,7 +171,7 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
     }
     int count = 0, interior = 0;
     unsigned rechecked = 0;
-    const int n_seg = n_total > n_owned ? 2 : 1;
+    const int n_seg = !active ? 0 : (n_total > n_owned ? 2 : 1);
     for (int seg = 0; seg < n_seg; ++seg) {
         for (int dz = -S; dz <= S; ++dz) {
             int zc = cz + dz;
@@ -214,9 +214,11 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
         }
         if (seg == 0) interior = count;
     }
-    deg[i] = min(count, stride);
-    deg_int[i] = min(interior, stride);
-    if (count > stride) atomicMax(&st->need_stride, static_cast<unsigned>(count));
+    if (active) {
+        deg[i] = min(count, stride);
+        deg_int[i] = min(interior, stride);
+        if (count > stride) atomicMax(&st->need_stride, static_cast<unsigned>(count));
+    }
     // statistics: one atomic per warp
     unsigned long long c64 = count, i64 = interior;
     unsigned rc = rechecked;

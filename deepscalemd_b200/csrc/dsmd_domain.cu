@@ -92,7 +92,9 @@ struct DirTable {
 
 // key 0 = stays; key 1 + d = leaves along direction d; key n + 1 = lost (moved further than one brick, or not finite).
 // Adds one to bin `bin` (or nothing when bin < 0) through a per-block histogram in shared memory: one global atomic per
-// non-empty bin and block instead of one per atom (all atoms of a brick but a few hit the same "stays" bin).
+// non-empty bin and block instead of one per atom (all atoms of a brick but a few hit the same "stays" bin). Holds a
+// block-wide barrier: call it exactly once, from code that every thread of the block executes (never from one side of a
+// branch, nor after an early return of some threads: a warp whose lanes reach two different barrier instructions hangs).
 __device__ __forceinline__ void block_histogram_add(int* hist, int bin, int* __restrict__ counts) {
     if (bin >= 0) atomicAdd(&hist[bin], 1);
     __syncthreads();
@@ -106,30 +108,30 @@ __global__ void k_classify_leave(DirTable t, int n_owned, const double* __restri
     if (threadIdx.x < kMaxDirs + 2) hist[threadIdx.x] = 0;
     __syncthreads();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_owned) {
-        block_histogram_add(hist, -1, counts);
-        return;
+    int bin = -1;   // threads past the end take part in the block's barrier below, with nothing to add
+    if (i < n_owned) {
+        const double p[3] = {x[i], y[i], z[i]};
+        int e[3] = {0, 0, 0};
+        bool lost = false;
+        for (int a = 0; a < 3; ++a) {
+            if (!t.split[a]) continue;
+            const double w = t.hi[a] - t.lo[a];
+            if (!(p[a] >= t.lo[a] - w && p[a] < t.hi[a] + w)) lost = true;
+            e[a] = p[a] < t.lo[a] ? -1 : (p[a] >= t.hi[a] ? 1 : 0);
+        }
+        unsigned k = 0;
+        if (lost) {
+            k = static_cast<unsigned>(t.n + 1);
+        } else if (e[0] || e[1] || e[2]) {
+            k = static_cast<unsigned>(t.n + 1);
+            for (int d = 0; d < t.n; ++d)
+                if (t.e[d][0] == e[0] && t.e[d][1] == e[1] && t.e[d][2] == e[2]) k = static_cast<unsigned>(d + 1);
+        }
+        key[i] = k;
+        val[i] = i;
+        bin = static_cast<int>(k);
     }
-    const double p[3] = {x[i], y[i], z[i]};
-    int e[3] = {0, 0, 0};
-    bool lost = false;
-    for (int a = 0; a < 3; ++a) {
-        if (!t.split[a]) continue;
-        const double w = t.hi[a] - t.lo[a];
-        if (!(p[a] >= t.lo[a] - w && p[a] < t.hi[a] + w)) lost = true;
-        e[a] = p[a] < t.lo[a] ? -1 : (p[a] >= t.hi[a] ? 1 : 0);
-    }
-    unsigned k = 0;
-    if (lost) {
-        k = static_cast<unsigned>(t.n + 1);
-    } else if (e[0] || e[1] || e[2]) {
-        k = static_cast<unsigned>(t.n + 1);
-        for (int d = 0; d < t.n; ++d)
-            if (t.e[d][0] == e[0] && t.e[d][1] == e[1] && t.e[d][2] == e[2]) k = static_cast<unsigned>(d + 1);
-    }
-    key[i] = k;
-    val[i] = i;
-    block_histogram_add(hist, static_cast<int>(k), counts);
+    block_histogram_add(hist, bin, counts);   // the one barrier of this kernel: every thread of the block reaches it
 }
 
 // How many neighbour directions need atom i as a ghost, and which (bit d).
@@ -685,16 +687,11 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
         DOM_CTX(d, dsmd_integrate(d->ctx, 1, dt, force_to_accel, s));   // v += dt/2 a, x += dt v, pack owned, displacement
         mark(1);
         // The vote: all ranks take the MAX of their displacement words; the host reads the result of the PREVIOUS step (its
-        // copy finished long ago) and extrapolates by its last growth (src/md_simulation.cpp:1232-1245). With several
-        // ranks the all-reduce and the read-back run on the side stream, off the critical path of the force kernels; the
-        // refresh that follows on that stream (or the rebuild, which waits for it) keeps the communicator's call order.
+        // copy finished long ago) and extrapolates by its last growth (src/md_simulation.cpp:1232-1245). The all-reduce
+        // is issued on the main stream, before the refresh goes to the side stream: every call on the communicator is
+        // then ordered by the streams themselves (main -> ev_main -> side -> ev_side -> main).
+        if (d->world > 1) DOM_NCCL(d, g_nccl.AllReduce(word, word, 1, ncclUint64, ncclMax, d->comm, s));
         cudaStream_t vote_stream = s;
-        if (d->world > 1) {
-            DOM_CUDA(d, cudaEventRecord(d->ev_main, s));
-            DOM_CUDA(d, cudaStreamWaitEvent(d->side, d->ev_main, 0));
-            DOM_NCCL(d, g_nccl.AllReduce(word, word, 1, ncclUint64, ncclMax, d->comm, d->side));
-            vote_stream = d->side;
-        }
         if (d->vote_pending >= 0) {
             DOM_CUDA(d, cudaEventSynchronize(d->ev_vote[d->vote_pending]));
             d->d_prev2 = d->d_prev;
@@ -709,7 +706,6 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
         mark(2);
         bool rebuilt = false;
         if (predicted * predicted > limit2) {
-            if (d->world > 1) DOM_CUDA(d, cudaStreamWaitEvent(s, d->ev_vote[slot], 0));   // the side stream's all-reduce first
             { const int rc = rebuild(d, s); if (rc) return rc; }
             rebuilt = true;
             mark(3);
