@@ -13,6 +13,10 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["csrc/dsmd_core.cu", "csrc/dsmd_edges.cu", "csrc/dsmd_domain.cu", "csrc/dsmd_noalloc.cu"]
 LIBRARY = os.path.join(HERE, "libdsmd_b200.so")
+# host-side input layer (run description, coordinate / topology / restart files): plain C++, no CUDA
+HOST_SOURCES = ["csrc/host/run_config.cpp", "csrc/host/system_input.cpp", "csrc/host/restart_file.cpp",
+                "csrc/host/dynamics.cpp", "csrc/host/dsmd_input_capi.cpp"]
+HOST_LIBRARY = os.path.join(HERE, "libdsmd_input.so")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "--use_fast_math=false",
          "-Xcompiler", "-fPIC", "-shared"]
 
@@ -37,7 +41,20 @@ def is_stale() -> bool:
     return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
 
 
+def build_host(force: bool = False) -> str:
+    srcs = [os.path.join(HERE, s) for s in HOST_SOURCES]
+    deps = srcs + [os.path.join(HERE, "csrc", "host", f) for f in os.listdir(os.path.join(HERE, "csrc", "host"))]
+    deps.append(os.path.join(HERE, "..", "include", "dsmd_input.h"))
+    if not force and os.path.exists(HOST_LIBRARY) and all(os.path.getmtime(d) <= os.path.getmtime(HOST_LIBRARY) for d in deps):
+        return HOST_LIBRARY
+    cmd = ["/usr/bin/g++", "-std=c++17", "-O2", "-Wall", "-fPIC", "-shared", "-I", os.path.join(HERE, "..", "include"),
+           "-o", HOST_LIBRARY, *srcs]
+    subprocess.run(cmd, check=True, cwd=HERE)
+    return HOST_LIBRARY
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
+    build_host(force)
     if not force and not is_stale():
         return LIBRARY
     flags = [f for f in FLAGS if f != "--use_fast_math=false"]

@@ -1,0 +1,375 @@
+#include "system_input.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <fstream>
+#include <limits>
+#include <map>
+#include <sstream>
+#include <stdexcept>
+
+#include "text_util.hpp"
+
+namespace dsmd::host {
+
+namespace {
+
+// A data line of the bracketed formats: the text behind the first ';' or '#' is a comment.
+std::vector<std::string> data_tokens(std::string line) {
+    const size_t cut = line.find_first_of(";#");
+    if (cut != std::string::npos) line.erase(cut);
+    return words(line);
+}
+
+// "[ name ]" -> lower-case name; false when the line is not a section header.
+bool section_header(const std::string& cleaned, std::string& name) {
+    if (cleaned.size() < 2 || cleaned.front() != '[' || cleaned.back() != ']') return false;
+    name = lowered(trimmed(cleaned.substr(1, cleaned.size() - 2), " \t"));
+    return true;
+}
+
+std::pair<int, int> ordered(int a, int b) { return {std::min(a, b), std::max(a, b)}; }
+
+int to_int(const std::string& s) { return std::stoi(s); }
+double to_real(const std::string& s) { return std::stod(s); }
+
+void require_atom_count(const SystemInput& s, size_t topology_atoms, const std::string& path) {
+    if (static_cast<size_t>(s.n) != topology_atoms)
+        throw std::runtime_error("topology " + path + " describes " + std::to_string(topology_atoms) +
+                                 " atoms, the coordinate file has " + std::to_string(s.n));
+}
+
+}  // namespace
+
+void read_xyz(const std::string& raw_path, const double box[3], SystemInput& out) {
+    const std::string path = clean_file_name(raw_path);
+    std::ifstream file(path);
+    if (!file.is_open()) throw std::runtime_error("Cannot open coordinate file: " + path);
+    std::string line;
+    std::getline(file, line);
+    long long declared = 0;
+    try {
+        declared = std::stoll(line);
+    } catch (const std::exception&) {
+        throw std::runtime_error("coordinate file " + path + ": the first line must be the atom count");
+    }
+    if (declared <= 0 || declared >= (1ll << 30)) throw std::runtime_error("coordinate file " + path + ": bad atom count");
+    std::getline(file, line);   // comment line
+    const size_t n = static_cast<size_t>(declared);
+    out = SystemInput();
+    out.n = declared;
+    out.x.resize(n); out.y.resize(n); out.z.resize(n);
+    out.vx.assign(n, 0.0); out.vy.assign(n, 0.0); out.vz.assign(n, 0.0);
+    out.mass.assign(n, 1.0); out.charge.assign(n, 0.0);
+    out.type.assign(n, 0);
+    out.element.assign(n, std::string());
+    size_t read = 0;
+    while (read < n && std::getline(file, line)) {
+        std::istringstream in(line);
+        std::string element;
+        double px, py, pz;
+        if (in >> element >> px >> py >> pz) {
+            out.element[read] = element;
+            out.x[read] = px; out.y[read] = py; out.z[read] = pz;
+            ++read;
+        }
+    }
+    if (read != n)
+        throw std::runtime_error("XYZ atom-count mismatch: header declares " + std::to_string(n) + " but " +
+                                 std::to_string(read) + " coordinate records were read");
+    // recentre: mean position -> box centre (plain sums in file order, as the reference adds them)
+    double mean[3] = {0.0, 0.0, 0.0};
+    for (size_t i = 0; i < n; ++i) { mean[0] += out.x[i]; mean[1] += out.y[i]; mean[2] += out.z[i]; }
+    for (double& m : mean) m /= static_cast<double>(n);
+    for (int a = 0; a < 3; ++a) out.shift[a] = box[a] / 2.0 - mean[a];
+    for (size_t i = 0; i < n; ++i) { out.x[i] += out.shift[0]; out.y[i] += out.shift[1]; out.z[i] += out.shift[2]; }
+    out.ntypes = 1;
+    out.type_name = {""};
+    out.epsilon = {0.0};
+    out.sigma = {0.0};
+}
+
+void apply_legacy_topology(const std::string& raw_path, SystemInput& s) {
+    const std::string path = clean_file_name(raw_path);
+    std::ifstream file(path);
+    if (!file.is_open()) throw std::runtime_error("Failed to load topology file: " + path);
+    struct TypeRow { double mass, charge, sigma, epsilon; };
+    std::map<std::string, TypeRow> rows;
+    std::vector<std::string> atom_type_name;   // by 0-based atom id; "" = never named
+    std::string line, section;
+    while (std::getline(file, line)) {
+        if (!line.empty() && line.back() == '\r') line.pop_back();
+        if (line.empty() || line[0] == '#' || line[0] == ';') continue;   // comment marks count in column 1 only
+        const std::string cleaned = trimmed(line, " \t");
+        if (cleaned.empty()) continue;
+        if (section_header(cleaned, section)) continue;
+        const auto t = words(cleaned);
+        if (t.empty()) continue;
+        if (section == "atomtypes") {
+            if (t.size() >= 5) rows[t[0]] = TypeRow{to_real(t[1]), to_real(t[2]), to_real(t[3]), to_real(t[4])};
+        } else if (section == "atoms") {
+            if (t.size() >= 2) {
+                const int id = to_int(t[0]) - 1;
+                if (id < 0) throw std::runtime_error("topology " + path + ": atom ids start at 1");
+                if (static_cast<size_t>(id) >= atom_type_name.size()) atom_type_name.resize(static_cast<size_t>(id) + 1);
+                atom_type_name[static_cast<size_t>(id)] = t[1];
+            }
+        } else if (section == "bonds") {
+            if (t.size() >= 3) ++s.n_bonds;
+        } else if (section == "angles") {
+            if (t.size() >= 4) ++s.n_angles;
+        } else if (section == "dihedrals") {
+            if (t.size() >= 5) ++s.n_dihedrals;
+        }
+    }
+    require_atom_count(s, atom_type_name.size(), path);
+    // type ids: order of first appearance among the atoms
+    std::map<std::string, int> id_of;
+    s.type_name.clear();
+    std::vector<TypeRow> by_id;
+    for (size_t i = 0; i < atom_type_name.size(); ++i) {
+        const std::string& name = atom_type_name[i];
+        auto found = id_of.find(name);
+        if (found == id_of.end()) {
+            const auto row = rows.find(name);
+            if (row == rows.end()) throw std::runtime_error("Atom type not found: " + name);
+            found = id_of.emplace(name, static_cast<int>(id_of.size())).first;
+            s.type_name.push_back(name);
+            by_id.push_back(row->second);
+        }
+        s.type[i] = found->second;
+        s.mass[i] = by_id[static_cast<size_t>(found->second)].mass;
+        s.charge[i] = by_id[static_cast<size_t>(found->second)].charge;
+    }
+    s.ntypes = static_cast<int>(by_id.size());
+    s.epsilon.assign(static_cast<size_t>(s.ntypes) * s.ntypes, 0.0);
+    s.sigma.assign(s.epsilon.size(), 0.0);
+    for (int a = 0; a < s.ntypes; ++a)
+        for (int b = 0; b < s.ntypes; ++b) {   // Lorentz-Berthelot (include/md_types.h:122-136)
+            s.epsilon[static_cast<size_t>(a) * s.ntypes + b] = std::sqrt(by_id[a].epsilon * by_id[b].epsilon);
+            s.sigma[static_cast<size_t>(a) * s.ntypes + b] = 0.5 * (by_id[a].sigma + by_id[b].sigma);
+        }
+    s.explicit_pairs = false;
+    s.mie_n = 12;
+    s.mie_m = 6;
+    s.exclusions.clear();
+    s.constraints.clear();
+}
+
+void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_parameters, SystemInput& s) {
+    const std::string topology_path = clean_file_name(raw_topology), parameter_path = clean_file_name(raw_parameters);
+    const double nan = std::numeric_limits<double>::quiet_NaN();
+
+    // ---- parameter file ------------------------------------------------------------------------------------------------
+    std::ifstream parameters(parameter_path);
+    if (!parameters) throw std::runtime_error("cannot open parameter file: " + parameter_path);
+    std::map<int, std::string> type_names;
+    struct PairRow { int i, j; double sigma, epsilon; };
+    std::vector<PairRow> pair_rows;
+    std::map<std::string, bool> bond_ids, angle_ids, torsion_ids, improper_ids;
+    bool mie_seen = false;
+    std::string line, section;
+    size_t line_number = 0;
+    while (std::getline(parameters, line)) {
+        ++line_number;
+        const std::string cleaned = trimmed(line);
+        if (cleaned.empty() || cleaned[0] == ';' || cleaned[0] == '#') continue;
+        if (section_header(cleaned, section)) continue;
+        const auto t = data_tokens(line);
+        if (t.empty()) continue;
+        auto fail = [&](const std::string& what) {
+            throw std::runtime_error(parameter_path + ":" + std::to_string(line_number) + ": " + what);
+        };
+        if (section == "meta") {
+            if (t.size() < 2) fail("metadata requires key and value");
+            if (t[0] == "schema_version" && t[1] != "1") fail("unsupported schema_version '" + t[1] + "'");
+            if (t[0] == "length_unit" && t[1] != "angstrom") fail("length_unit must be angstrom");
+            if (t[0] == "energy_unit" && t[1] != "kcal_per_mol") fail("energy_unit must be kcal_per_mol");
+            if (t[0] == "charge_unit" && t[1] != "elementary_charge") fail("charge_unit must be elementary_charge");
+        } else if (section == "nonbonded") {
+            if (t[0] == "component") {
+                bool mie = false;
+                int n = -1, m = -1;
+                for (const auto& w : t) {
+                    if (w == "mie") mie = true;
+                    if (w.rfind("n=", 0) == 0) n = to_int(w.substr(2));
+                    if (w.rfind("m=", 0) == 0) m = to_int(w.substr(2));
+                }
+                if (mie) {
+                    if (mie_seen) fail("only one Mie nonbonded component is supported");
+                    if (!((n == 12 && m == 6) || (n == 9 && m == 6))) fail("supported Mie exponents are (12,6) and SPICA (9,6)");
+                    s.mie_n = n;
+                    s.mie_m = m;
+                    mie_seen = true;
+                }
+            }
+        } else if (section == "atom_types") {
+            if (t.size() < 2) fail("atom type requires: type_id name");
+            const int id = to_int(t[0]);
+            if (id < 0 || !type_names.emplace(id, t[1]).second) fail("invalid or duplicate atom type ID");
+        } else if (section == "pair_parameters") {
+            if (t.size() < 5) fail("pair parameter requires: component type_i type_j sigma epsilon");
+            pair_rows.push_back({to_int(t[1]), to_int(t[2]), to_real(t[3]), to_real(t[4])});
+        } else if (section == "bond_parameters") {
+            if (t.size() < 4 || t[1] != "harmonic") fail("only 'param_id harmonic k r0' bond parameters are supported");
+            if (!bond_ids.emplace(t[0], true).second) fail("duplicate bond parameter ID '" + t[0] + "'");
+        } else if (section == "angle_parameters") {
+            if (t.size() < 4 || t[1] != "harmonic") fail("only 'param_id harmonic k theta0_deg' angle parameters are supported");
+            if (!angle_ids.emplace(t[0], true).second) fail("duplicate angle parameter ID '" + t[0] + "'");
+        } else if (section == "torsion_parameters") {
+            if (t.size() < 5 || t[1] != "periodic") fail("only 'param_id periodic k phase_deg multiplicity' torsions are supported");
+            if (!torsion_ids.emplace(t[0], true).second) fail("duplicate torsion parameter ID '" + t[0] + "'");
+        } else if (section == "improper_parameters") {
+            if (t.size() < 4 || (t[1] != "periodic" && t[1] != "harmonic"))
+                fail("improper requires either 'param_id periodic k phase_deg multiplicity' or 'param_id harmonic k phi0_deg'");
+            if (!improper_ids.emplace(t[0], true).second) fail("duplicate improper parameter ID '" + t[0] + "'");
+        } else if (section == "special_pair_parameters") {
+            if (t.size() < 3) fail("special pair parameter requires: param_id sigma epsilon");
+        } else {
+            fail("unknown parameter section [" + section + "]");
+        }
+    }
+    if (!mie_seen) throw std::runtime_error("parameter file has no supported Mie nonbonded component");
+    if (type_names.empty()) throw std::runtime_error("parameter file has no [atom_types]");
+    const int nt = type_names.rbegin()->first + 1;
+    if (static_cast<int>(type_names.size()) != nt) throw std::runtime_error("atom type IDs must be contiguous and start at zero");
+    std::vector<double> sig(static_cast<size_t>(nt) * nt, nan), eps(sig.size(), nan);
+    for (const PairRow& r : pair_rows) {
+        if (r.i < 0 || r.j < 0 || r.i >= nt || r.j >= nt) throw std::runtime_error("pair parameter references an invalid atom type ID");
+        if (!std::isfinite(r.sigma) || !std::isfinite(r.epsilon) || r.sigma < 0.0 || r.epsilon < 0.0)
+            throw std::runtime_error("pair sigma and epsilon must be finite and non-negative");
+        const size_t ab = static_cast<size_t>(r.i) * nt + r.j, ba = static_cast<size_t>(r.j) * nt + r.i;
+        if (std::isfinite(sig[ab]) || std::isfinite(eps[ab]))
+            throw std::runtime_error("duplicate pair parameter for type IDs " + std::to_string(r.i) + "," + std::to_string(r.j));
+        sig[ab] = sig[ba] = r.sigma;
+        eps[ab] = eps[ba] = r.epsilon;
+    }
+    for (int a = 0; a < nt; ++a)
+        for (int b = 0; b < nt; ++b)
+            if (!std::isfinite(sig[static_cast<size_t>(a) * nt + b]) || !std::isfinite(eps[static_cast<size_t>(a) * nt + b]))
+                throw std::runtime_error("pair parameter matrix is incomplete for type IDs " + std::to_string(a) + "," +
+                                         std::to_string(b));
+
+    // ---- topology file -------------------------------------------------------------------------------------------------
+    std::ifstream topology(topology_path);
+    if (!topology) throw std::runtime_error("cannot open topology file: " + topology_path);
+    section.clear();
+    line_number = 0;
+    long long expected_atoms = -1;
+    std::vector<int> type;
+    std::vector<double> mass, charge;
+    std::vector<std::pair<int, int>> listed, bond_ends, angle_ends, dihedral_ends, improper_atoms, special;
+    std::vector<Constraint> constraints;
+    struct Quad { int a, b, c, d; };
+    std::vector<Quad> angles3, dihedrals4, impropers4;
+    while (std::getline(topology, line)) {
+        ++line_number;
+        const std::string cleaned = trimmed(line);
+        if (cleaned.empty() || cleaned[0] == ';' || cleaned[0] == '#') continue;
+        if (section_header(cleaned, section)) continue;
+        const auto t = data_tokens(line);
+        if (t.empty()) continue;
+        auto fail = [&](const std::string& what) {
+            throw std::runtime_error(topology_path + ":" + std::to_string(line_number) + ": " + what);
+        };
+        if (section == "meta") {
+            if (t.size() < 2) fail("metadata requires key and value");
+            if (t[0] == "schema_version" && t[1] != "1") fail("unsupported schema_version '" + t[1] + "'");
+            if (t[0] == "atom_count") {
+                expected_atoms = std::stoll(t[1]);
+                if (expected_atoms <= 0) fail("atom_count must be positive");
+            }
+        } else if (section == "atoms") {
+            if (t.size() < 5) fail("atom requires: atom_id element type_id mass charge [molecule_id residue_id]");
+            if (to_int(t[0]) != static_cast<int>(type.size())) fail("atom IDs must be contiguous and start at zero");
+            const int type_id = to_int(t[2]);
+            if (type_names.find(type_id) == type_names.end()) fail("atom references an invalid type ID");
+            const double m = to_real(t[3]), q = to_real(t[4]);
+            if (!std::isfinite(m) || m <= 0.0 || !std::isfinite(q))
+                fail("atom mass must be finite and positive, and charge must be finite");
+            type.push_back(type_id);
+            mass.push_back(m);
+            charge.push_back(q);
+        } else if (section == "bonds") {
+            if (t.size() < 3) fail("bond requires: atom_i atom_j bond_param_id");
+            if (!bond_ids.count(t[2])) fail("bond references an invalid parameter ID");
+            bond_ends.push_back({to_int(t[0]), to_int(t[1])});
+        } else if (section == "angles") {
+            if (t.size() < 4) fail("angle requires: atom_i atom_j atom_k angle_param_id");
+            if (!angle_ids.count(t[3])) fail("angle references an invalid parameter ID");
+            angles3.push_back({to_int(t[0]), to_int(t[1]), to_int(t[2]), 0});
+        } else if (section == "dihedrals") {
+            if (t.size() < 5) fail("dihedral requires: atom_i atom_j atom_k atom_l torsion_param_id");
+            if (!torsion_ids.count(t[4])) fail("dihedral references an invalid parameter ID");
+            dihedrals4.push_back({to_int(t[0]), to_int(t[1]), to_int(t[2]), to_int(t[3])});
+        } else if (section == "exclusions") {
+            if (t.size() < 2) fail("exclusion requires: atom_i atom_j");
+            listed.push_back({to_int(t[0]), to_int(t[1])});
+        } else if (section == "impropers") {
+            if (t.size() < 5) fail("improper requires: atom_i atom_j atom_k atom_l torsion_param_id");
+            if (!improper_ids.count(t[4])) fail("improper references an invalid parameter ID");
+            impropers4.push_back({to_int(t[0]), to_int(t[1]), to_int(t[2]), to_int(t[3])});
+        } else if (section == "special_pairs") {
+            if (t.size() < 5) fail("special_pair requires: atom_i atom_j pair_param_id lj_scale coulomb_scale");
+            special.push_back({to_int(t[0]), to_int(t[1])});
+        } else if (section == "constraints") {
+            if (t.size() < 3) fail("constraint requires: atom_i atom_j target_distance");
+            constraints.push_back({to_int(t[0]), to_int(t[1]), to_real(t[2])});
+        } else if (section == "virtual_sites") {
+            fail("[" + section + "] is represented by the format but not supported by the current runtime");
+        } else {
+            fail("unknown topology section [" + section + "]");
+        }
+    }
+    if (type.empty()) throw std::runtime_error("topology file has no [atoms]");
+    if (expected_atoms < 0) throw std::runtime_error("topology [meta] has no atom_count");
+    if (expected_atoms != static_cast<long long>(type.size()))
+        throw std::runtime_error("topology atom_count is " + std::to_string(expected_atoms) + " but [atoms] contains " +
+                                 std::to_string(type.size()) + " entries");
+    const int n_atoms = static_cast<int>(type.size());
+    auto check = [&](int id, const char* kind) {
+        if (id < 0 || id >= n_atoms) throw std::runtime_error(std::string(kind) + " references invalid atom ID " + std::to_string(id));
+    };
+    for (const auto& b : bond_ends) { check(b.first, "bond"); check(b.second, "bond"); }
+    for (const auto& a : angles3) { check(a.a, "angle"); check(a.b, "angle"); check(a.c, "angle"); }
+    for (const auto& d : dihedrals4) { check(d.a, "dihedral"); check(d.b, "dihedral"); check(d.c, "dihedral"); check(d.d, "dihedral"); }
+    for (const auto& d : impropers4) { check(d.a, "improper"); check(d.b, "improper"); check(d.c, "improper"); check(d.d, "improper"); }
+    for (const auto& p : special) { check(p.first, "special_pair"); check(p.second, "special_pair"); }
+    for (const auto& c : constraints) {
+        check(c.i, "constraint"); check(c.j, "constraint");
+        if (!std::isfinite(c.distance) || c.distance <= 0.0) throw std::runtime_error("constraint target_distance must be finite and positive");
+    }
+    for (const auto& e : listed) { check(e.first, "exclusion"); check(e.second, "exclusion"); }
+
+    std::vector<std::pair<int, int>> exclusions;
+    for (const auto& e : listed) exclusions.push_back(ordered(e.first, e.second));
+    for (const auto& b : bond_ends) exclusions.push_back(ordered(b.first, b.second));
+    for (const auto& a : angles3) exclusions.push_back(ordered(a.a, a.c));
+    for (const auto& d : dihedrals4) exclusions.push_back(ordered(d.a, d.d));
+    std::sort(exclusions.begin(), exclusions.end());
+    exclusions.erase(std::unique(exclusions.begin(), exclusions.end()), exclusions.end());
+    for (const auto& p : special)
+        if (!std::binary_search(exclusions.begin(), exclusions.end(), ordered(p.first, p.second)))
+            throw std::runtime_error("special_pair " + std::to_string(p.first) + "-" + std::to_string(p.second) +
+                                     " must also appear in [exclusions]");
+
+    require_atom_count(s, type.size(), topology_path);
+    s.type = type;
+    s.mass = mass;
+    s.charge = charge;
+    s.ntypes = nt;
+    s.type_name.clear();
+    for (const auto& kv : type_names) s.type_name.push_back(kv.second);
+    s.epsilon = eps;
+    s.sigma = sig;
+    s.explicit_pairs = true;
+    s.exclusions = exclusions;
+    s.constraints = constraints;
+    s.n_bonds = static_cast<int64_t>(bond_ends.size());
+    s.n_angles = static_cast<int64_t>(angles3.size());
+    s.n_dihedrals = static_cast<int64_t>(dihedrals4.size());
+    s.n_impropers = static_cast<int64_t>(impropers4.size());
+    s.n_special_pairs = static_cast<int64_t>(special.size());
+}
+
+}  // namespace dsmd::host

@@ -1,0 +1,174 @@
+"""ctypes binding of the host-side input layer (``include/dsmd_input.h``, ``libdsmd_input.so``): the reference's run
+description, coordinate, topology / parameter and restart files read by the C++ readers of ``csrc/host``."""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+from ctypes import POINTER, byref, c_char_p, c_double, c_int, c_int32, c_int64, c_uint64, c_void_p
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY = os.path.join(_HERE, "libdsmd_input.so")
+
+SYMBOLS = [
+    "dsmd_input_last_error", "dsmd_input_config_read", "dsmd_input_config_destroy", "dsmd_input_config_json",
+    "dsmd_input_system_load", "dsmd_input_system_load_files", "dsmd_input_system_destroy", "dsmd_input_system_counts",
+    "dsmd_input_system_real", "dsmd_input_system_types", "dsmd_input_system_pair_table", "dsmd_input_system_exclusions",
+    "dsmd_input_system_constraints", "dsmd_input_system_velocities", "dsmd_input_restart_read", "dsmd_input_restart_write",
+    "dsmd_input_nose_hoover_scale",
+]
+
+_lib = None
+
+
+class InputError(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIBRARY):
+            raise InputError(f"{LIBRARY} has not been built (python -m deepscalemd_b200.build)")
+        L = ctypes.CDLL(LIBRARY)
+        L.dsmd_input_last_error.restype = c_char_p
+        for name in SYMBOLS[1:]:
+            getattr(L, name).restype = c_int
+        L.dsmd_input_config_destroy.restype = None
+        L.dsmd_input_system_destroy.restype = None
+        _lib = L
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise InputError(lib().dsmd_input_last_error().decode())
+
+
+class Config:
+    """A run description read by the C++ reader; ``values`` is the resolved configuration."""
+
+    def __init__(self, path):
+        self.h = c_void_p()
+        _check(lib().dsmd_input_config_read(str(path).encode(), byref(self.h)))
+        text = c_char_p()
+        _check(lib().dsmd_input_config_json(self.h, byref(text)))
+        self.values = json.loads(text.value.decode())
+
+    def close(self):
+        if self.h:
+            lib().dsmd_input_config_destroy(self.h)
+            self.h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class System:
+    """Coordinates + topology (+ parameters) read by the C++ readers."""
+
+    def __init__(self, config=None, *, coordinate_file=None, topology_file=None, parameter_file=None, box=None):
+        self.h = c_void_p()
+        if config is not None:
+            _check(lib().dsmd_input_system_load(config.h, byref(self.h)))
+        else:
+            b = (c_double * 3)(*box)
+            _check(lib().dsmd_input_system_load_files(str(coordinate_file).encode(),
+                                                      str(topology_file).encode() if topology_file else None,
+                                                      str(parameter_file).encode() if parameter_file else None, b,
+                                                      byref(self.h)))
+
+    def counts(self):
+        atoms, excl, cons = c_int64(), c_int64(), c_int64()
+        types, explicit = c_int32(), c_int32()
+        _check(lib().dsmd_input_system_counts(self.h, byref(atoms), byref(types), byref(excl), byref(cons), byref(explicit)))
+        return dict(atoms=atoms.value, types=types.value, exclusions=excl.value, constraints=cons.value,
+                    explicit_pairs=bool(explicit.value))
+
+    def real(self, field):
+        index = ["x", "y", "z", "vx", "vy", "vz", "mass", "charge"].index(field)
+        p = POINTER(c_double)()
+        _check(lib().dsmd_input_system_real(self.h, c_int(index), byref(p)))
+        return np.ctypeslib.as_array(p, shape=(self.counts()["atoms"],)).copy()
+
+    def positions(self):
+        return np.stack([self.real(k) for k in "xyz"], axis=1)
+
+    def velocities(self):
+        return np.stack([self.real(k) for k in ("vx", "vy", "vz")], axis=1)
+
+    def types(self):
+        p = POINTER(c_int32)()
+        _check(lib().dsmd_input_system_types(self.h, byref(p)))
+        return np.ctypeslib.as_array(p, shape=(self.counts()["atoms"],)).copy()
+
+    def pair_table(self):
+        e, s = POINTER(c_double)(), POINTER(c_double)()
+        n, m = c_int32(), c_int32()
+        _check(lib().dsmd_input_system_pair_table(self.h, byref(e), byref(s), byref(n), byref(m)))
+        nt = self.counts()["types"]
+        return (np.ctypeslib.as_array(e, shape=(nt, nt)).copy(), np.ctypeslib.as_array(s, shape=(nt, nt)).copy(), n.value,
+                m.value)
+
+    def exclusions(self):
+        n = self.counts()["exclusions"]
+        if n == 0:
+            return np.zeros((0, 2), dtype=np.int32)
+        p = POINTER(c_int32)()
+        _check(lib().dsmd_input_system_exclusions(self.h, byref(p)))
+        return np.ctypeslib.as_array(p, shape=(n, 2)).copy()
+
+    def constraints(self):
+        n = self.counts()["constraints"]
+        if n == 0:
+            return np.zeros(0, dtype=np.int32), np.zeros(0, dtype=np.int32), np.zeros(0)
+        i, j, d = POINTER(c_int32)(), POINTER(c_int32)(), POINTER(c_double)()
+        _check(lib().dsmd_input_system_constraints(self.h, byref(i), byref(j), byref(d)))
+        return (np.ctypeslib.as_array(i, shape=(n,)).copy(), np.ctypeslib.as_array(j, shape=(n,)).copy(),
+                np.ctypeslib.as_array(d, shape=(n,)).copy())
+
+    def init_velocities(self, temperature, seed):
+        _check(lib().dsmd_input_system_velocities(self.h, c_double(temperature), c_uint64(seed)))
+
+    def read_restart(self, path):
+        step, dt, xi = c_int64(), c_double(), c_double()
+        box = (c_double * 3)()
+        name = ctypes.create_string_buffer(64)
+        _check(lib().dsmd_input_restart_read(str(path).encode(), self.h, byref(step), box, byref(dt), name, byref(xi)))
+        return dict(step=step.value, timestep=dt.value, box=np.array(list(box)), thermostat=name.value.decode(), xi=xi.value)
+
+    def close(self):
+        if self.h:
+            lib().dsmd_input_system_destroy(self.h)
+            self.h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def write_restart(path, step, timestep, box, periodic, thermostat, thermostat_state, pos, vel):
+    pos = np.ascontiguousarray(pos, dtype=np.float64)
+    vel = np.ascontiguousarray(vel, dtype=np.float64)
+    cols = [np.ascontiguousarray(a) for a in (pos[:, 0], pos[:, 1], pos[:, 2], vel[:, 0], vel[:, 1], vel[:, 2])]
+    state = np.ascontiguousarray(thermostat_state, dtype=np.float64)
+    ptr = lambda a: a.ctypes.data_as(POINTER(c_double))
+    _check(lib().dsmd_input_restart_write(str(path).encode(), c_int64(step), c_double(timestep), (c_double * 3)(*box),
+                                          (c_int32 * 3)(*[int(bool(p)) for p in periodic]), thermostat.encode(),
+                                          ptr(state) if len(state) else None, c_int32(len(state)), c_int64(len(pos)),
+                                          *[ptr(c) for c in cols]))
+
+
+def nose_hoover_scale(kinetic_kcal, atoms, target_temperature, tau, dt, xi, dof_fraction=1.0):
+    """Returns (scale, new xi)."""
+    x, s = c_double(xi), c_double()
+    _check(lib().dsmd_input_nose_hoover_scale(c_double(kinetic_kcal), c_int64(atoms), c_double(target_temperature),
+                                              c_double(tau), c_double(dt), c_double(dof_fraction), byref(x), byref(s)))
+    return s.value, x.value

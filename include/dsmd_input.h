@@ -1,0 +1,84 @@
+/* C ABI of the host-side input layer (libdsmd_input.so): the reference's run description, coordinate, topology /
+ * parameter and restart files, read into plain arrays that feed the device path of dsmd_b200.h. No CUDA here.
+ *
+ * What each entry point replaces in the reference (sjseo00/DeepScaleMD):
+ *   dsmd_input_config_*   MDSimulation::parse_simulation_config          src/md_simulation.cpp:2753-3100
+ *                         read_dsmd_input_manifest                        src/md_simulation.cpp:280-303
+ *   dsmd_input_system_*   MDSystem::load_standard_xyz                     src/md_system.cpp:562-671
+ *                         Topology::load_topology / load_canonical        src/topology.cpp:335-881
+ *                         MDSystem::setup_force_field_params              src/md_system.cpp:716-790
+ *                         MDSystem::initialize_velocities                 src/md_system.cpp:205-275
+ *   dsmd_input_restart_*  MDSimulation::read_restart_file / write_restart_file   src/md_restart.cpp:110-300
+ *   dsmd_input_nose_hoover_scale   nose_hoover_scale                      src/thermostat.cpp:78-95
+ *
+ * Every function returns 0 on success and a non-zero code otherwise; the message of the last failure of the calling
+ * thread is available from dsmd_input_last_error(). Pointers handed out stay valid until the object is destroyed.
+ */
+#ifndef DSMD_INPUT_H
+#define DSMD_INPUT_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSMD_INPUT_OK 0
+#define DSMD_INPUT_ERR_INVALID 1   /* null pointer, bad argument */
+#define DSMD_INPUT_ERR_FORMAT 2    /* file missing, unreadable or not in the expected format (see the message) */
+
+typedef struct dsmd_input_config dsmd_input_config;
+typedef struct dsmd_input_system dsmd_input_system;
+
+const char* dsmd_input_last_error(void);
+
+/* Run description (YAML subset). */
+int dsmd_input_config_read(const char* path, dsmd_input_config** out);
+void dsmd_input_config_destroy(dsmd_input_config* config);
+/* The resolved configuration as one JSON object (typed keys, "unsupported": what this path does not run, "entries": every
+ * key read, as text). */
+int dsmd_input_config_json(const dsmd_input_config* config, const char** json);
+
+/* Particle system: coordinates + topology (+ parameters) named by the configuration; recentred into the box; velocities
+ * zero until dsmd_input_system_velocities or dsmd_input_system_apply_restart. */
+int dsmd_input_system_load(const dsmd_input_config* config, dsmd_input_system** out);
+/* The same from explicit file names (parameter_file NULL or "": topology_file is a legacy .top; topology_file NULL or "":
+ * coordinates only). */
+int dsmd_input_system_load_files(const char* coordinate_file, const char* topology_file, const char* parameter_file,
+                                 const double box[3], dsmd_input_system** out);
+void dsmd_input_system_destroy(dsmd_input_system* system);
+int dsmd_input_system_counts(const dsmd_input_system* system, int64_t* atoms, int32_t* types, int64_t* exclusions,
+                             int64_t* constraints, int32_t* explicit_pairs);
+/* Field: 0 x, 1 y, 2 z, 3 vx, 4 vy, 5 vz, 6 mass, 7 charge (double[atoms]). */
+int dsmd_input_system_real(const dsmd_input_system* system, int field, const double** data);
+int dsmd_input_system_types(const dsmd_input_system* system, const int32_t** type);
+/* epsilon and sigma: double[types * types], row-major, symmetric; Mie exponents (12, 6 for Lennard-Jones). */
+int dsmd_input_system_pair_table(const dsmd_input_system* system, const double** epsilon, const double** sigma,
+                                 int32_t* mie_n, int32_t* mie_m);
+/* pairs: int32[2 * exclusions] (smaller id, larger id), sorted, unique: the form dsmd_set_exclusions takes. */
+int dsmd_input_system_exclusions(const dsmd_input_system* system, const int32_t** pairs);
+/* i, j: int32[constraints]; distance: double[constraints]. */
+int dsmd_input_system_constraints(const dsmd_input_system* system, const int32_t** i, const int32_t** j,
+                                  const double** distance);
+/* Maxwell-Boltzmann velocities at the temperature (K) from the seed (A/fs). */
+int dsmd_input_system_velocities(dsmd_input_system* system, double temperature, uint64_t seed);
+
+/* Restart files. read: positions and velocities of the system are replaced (atom counts must agree); step, box (3),
+ * thermostat state xi (0 when the file holds none or another thermostat) are returned. */
+int dsmd_input_restart_read(const char* path, dsmd_input_system* system, int64_t* step, double box[3], double* timestep,
+                            char thermostat_name[64], double* xi);
+int dsmd_input_restart_write(const char* path, int64_t step, double timestep, const double box[3], const int32_t periodic[3],
+                             const char* thermostat_name, const double* thermostat_state, int32_t n_thermostat_state,
+                             int64_t atoms, const double* x, const double* y, const double* z, const double* vx,
+                             const double* vy, const double* vz);
+
+/* One Nose-Hoover application: returns the velocity scale in *scale and advances *xi (kinetic energy of the whole system
+ * in kcal/mol, tau and dt in fs). */
+int dsmd_input_nose_hoover_scale(double kinetic_kcal, int64_t atoms, double target_temperature, double tau, double dt,
+                                 double dof_fraction, double* xi, double* scale);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DSMD_INPUT_H */

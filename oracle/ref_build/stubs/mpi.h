@@ -20,6 +20,9 @@ struct MPI_Status { int unused; };
 #define MPI_CHAR 1
 #define MPI_UNSIGNED_LONG_LONG 9
 #define MPI_LONG_LONG 10
+#define MPI_UINT64_T 11
+#define MPI_INT64_T 12
+#define MPI_BYTE 13
 #define MPI_MAX 1
 #define MPI_SUM 2
 #define MPI_MIN 3
@@ -32,7 +35,7 @@ struct MPI_Status { int unused; };
 
 inline size_t dsmd_stub_mpi_size(MPI_Datatype t) {
     switch (t) {
-        case MPI_DOUBLE: case MPI_UNSIGNED_LONG_LONG: case MPI_LONG_LONG: return 8;
+        case MPI_DOUBLE: case MPI_UNSIGNED_LONG_LONG: case MPI_LONG_LONG: case MPI_UINT64_T: case MPI_INT64_T: return 8;
         case MPI_INT: case MPI_FLOAT: return 4;
         default: return 1;
     }

@@ -1,0 +1,111 @@
+// Test infrastructure: drives the REFERENCE's own Topology reader (src/topology.cpp, compiled where it lies) on a
+// topology / parameter file and returns what it parsed, so that the input layer of this repository can be compared with
+// it. Never part of the product.
+#include <cstdint>
+#include <cstring>
+#include <iostream>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "topology.h"
+
+namespace {
+
+struct Loaded {
+    Topology topology;
+    bool ok = false;
+    std::vector<int> type;
+    std::vector<double> mass, charge, sigma, epsilon, pair_sigma, pair_epsilon, constraint_d;
+    std::vector<int> exclusion_pairs, constraint_i, constraint_j;
+};
+
+// The reference prints progress to std::cout / std::cerr: keep the test output clean.
+struct Quiet {
+    std::streambuf* out;
+    std::streambuf* err;
+    std::ostringstream sink;
+    Quiet() : out(std::cout.rdbuf(sink.rdbuf())), err(std::cerr.rdbuf(sink.rdbuf())) {}
+    ~Quiet() { std::cout.rdbuf(out); std::cerr.rdbuf(err); }
+};
+
+void collect(Loaded& l) {
+    const Topology& t = l.topology;
+    const int n = t.get_num_atoms();
+    for (int i = 0; i < n; ++i) {
+        l.type.push_back(t.get_atom_type_id(i));
+        l.mass.push_back(t.get_atom_mass(i));
+        l.charge.push_back(t.get_atom_charge(i));
+        l.sigma.push_back(t.get_atom_sigma(i));
+        l.epsilon.push_back(t.get_atom_epsilon(i));
+    }
+    for (const auto& row : t.get_pair_sigma()) l.pair_sigma.insert(l.pair_sigma.end(), row.begin(), row.end());
+    for (const auto& row : t.get_pair_epsilon()) l.pair_epsilon.insert(l.pair_epsilon.end(), row.begin(), row.end());
+    for (const std::uint64_t key : t.get_exclusion_keys()) {
+        l.exclusion_pairs.push_back(static_cast<int>(key >> 32));
+        l.exclusion_pairs.push_back(static_cast<int>(key & 0xffffffffu));
+    }
+    for (const Constraint& c : t.get_constraints()) {
+        l.constraint_i.push_back(c.atom1);
+        l.constraint_j.push_back(c.atom2);
+        l.constraint_d.push_back(c.distance);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+// parameter_file empty: legacy .top. Returns null when the reference's reader refuses the files.
+void* dsmd_reftop_load(const char* topology_file, const char* parameter_file) {
+    auto* l = new Loaded();
+    try {
+        Quiet quiet;
+        const std::string prm = parameter_file ? parameter_file : "";
+        l->ok = prm.empty() ? l->topology.load_topology(topology_file, 0) : l->topology.load_canonical(topology_file, prm, 0);
+        if (l->ok) collect(*l);
+    } catch (const std::exception&) {
+        l->ok = false;
+    }
+    if (!l->ok) {
+        delete l;
+        return nullptr;
+    }
+    return l;
+}
+
+void dsmd_reftop_destroy(void* h) { delete static_cast<Loaded*>(h); }
+
+void dsmd_reftop_counts(void* h, long* atoms, long* pair_matrix_entries, long* exclusions, long* constraints, int* mie_n,
+                        int* mie_m) {
+    auto* l = static_cast<Loaded*>(h);
+    *atoms = static_cast<long>(l->type.size());
+    *pair_matrix_entries = static_cast<long>(l->pair_sigma.size());
+    *exclusions = static_cast<long>(l->exclusion_pairs.size() / 2);
+    *constraints = static_cast<long>(l->constraint_i.size());
+    *mie_n = l->topology.get_mie_repulsive_exponent();
+    *mie_m = l->topology.get_mie_attractive_exponent();
+}
+
+void dsmd_reftop_atoms(void* h, int* type, double* mass, double* charge, double* sigma, double* epsilon) {
+    auto* l = static_cast<Loaded*>(h);
+    const size_t n = l->type.size();
+    std::memcpy(type, l->type.data(), n * sizeof(int));
+    std::memcpy(mass, l->mass.data(), n * sizeof(double));
+    std::memcpy(charge, l->charge.data(), n * sizeof(double));
+    std::memcpy(sigma, l->sigma.data(), n * sizeof(double));
+    std::memcpy(epsilon, l->epsilon.data(), n * sizeof(double));
+}
+
+void dsmd_reftop_pairs(void* h, double* pair_sigma, double* pair_epsilon, int* exclusion_pairs, int* constraint_i,
+                       int* constraint_j, double* constraint_d) {
+    auto* l = static_cast<Loaded*>(h);
+    std::memcpy(pair_sigma, l->pair_sigma.data(), l->pair_sigma.size() * sizeof(double));
+    std::memcpy(pair_epsilon, l->pair_epsilon.data(), l->pair_epsilon.size() * sizeof(double));
+    std::memcpy(exclusion_pairs, l->exclusion_pairs.data(), l->exclusion_pairs.size() * sizeof(int));
+    std::memcpy(constraint_i, l->constraint_i.data(), l->constraint_i.size() * sizeof(int));
+    std::memcpy(constraint_j, l->constraint_j.data(), l->constraint_j.size() * sizeof(int));
+    std::memcpy(constraint_d, l->constraint_d.data(), l->constraint_d.size() * sizeof(double));
+}
+
+}  // extern "C"
