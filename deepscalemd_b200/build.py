@@ -53,8 +53,33 @@ def build_host(force: bool = False) -> str:
     return HOST_LIBRARY
 
 
+DRIVER = os.path.join(HERE, "bin", "dsmd_b200_run")
+
+
+def build_driver(force: bool = False) -> str:
+    """The MD driver executable (host C++ over the C ABI; linked against libdsmd_b200.so beside it)."""
+    srcs = [os.path.join(HERE, "csrc", "host", "dsmd_run.cpp")] + [os.path.join(HERE, s) for s in HOST_SOURCES[:-1]]
+    deps = srcs + [LIBRARY, os.path.join(HERE, "..", "include", "dsmd_b200.h")]
+    deps += [os.path.join(HERE, "csrc", "host", f) for f in os.listdir(os.path.join(HERE, "csrc", "host"))]
+    if not force and os.path.exists(DRIVER) and all(os.path.getmtime(d) <= os.path.getmtime(DRIVER) for d in deps):
+        return DRIVER
+    os.makedirs(os.path.dirname(DRIVER), exist_ok=True)
+    cuda_lib = os.path.join(os.path.dirname(os.path.dirname(nvcc_path())), "lib64")
+    cmd = ["/usr/bin/g++", "-std=c++17", "-O2", "-Wall", "-I", os.path.join(HERE, "..", "include"), "-I",
+           os.path.join(HERE, "csrc", "host"), "-o", DRIVER, *srcs, "-L", HERE, "-l:libdsmd_b200.so",
+           "-Wl,-rpath,$ORIGIN/..", f"-Wl,-rpath,{cuda_lib}"]
+    subprocess.run(cmd, check=True, cwd=HERE)
+    return DRIVER
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     build_host(force)
+    library = _build_cuda(force, verbose)
+    build_driver(force)
+    return library
+
+
+def _build_cuda(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIBRARY
     flags = [f for f in FLAGS if f != "--use_fast_math=false"]

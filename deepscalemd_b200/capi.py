@@ -25,7 +25,8 @@ SYMBOLS = [
     "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
     "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned",
     "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq",
-    "dsmd_displacement_word", "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_run_nve",
+    "dsmd_displacement_word", "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_scale_velocities",
+    "dsmd_run_nve",
     "dsmd_forces_host", "dsmd_launch_count", "dsmd_fma_probe", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
     "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_edges_create", "dsmd_edges_destroy",
     "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
@@ -264,6 +265,9 @@ class Context:
     def integrate(self, half, dt, force_to_accel=1.0, stream=None):
         self._check(self.lib.dsmd_integrate(self.h, c_int(half), c_double(dt), c_double(force_to_accel),
                                             _stream_handle(stream)))
+
+    def scale_velocities(self, factor, stream=None):
+        self._check(self.lib.dsmd_scale_velocities(self.h, c_double(factor), _stream_handle(stream)))
 
     def kinetic_energy(self, stream=None):
         v = c_double(0.0)

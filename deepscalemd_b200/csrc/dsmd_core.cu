@@ -320,6 +320,17 @@ __global__ void k_vv2(int n, double half_dt_c, double* __restrict__ vx, double* 
     vz[s] += a * fz[s];
 }
 
+// Thermostat step of the velocity-scaling kind (the reference's nose_hoover_thermostat_kernel,
+// src/thermostat_kernels.cu:68-76): v *= factor.
+__global__ void k_scale_velocities(int n, double factor, double* __restrict__ vx, double* __restrict__ vy,
+                                   double* __restrict__ vz) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n) return;
+    vx[s] *= factor;
+    vy[s] *= factor;
+    vz[s] *= factor;
+}
+
 // Deterministic two-level sums: per-block partials, then one block adds them in a fixed order.
 template <int NV>
 __device__ __forceinline__ void block_sum_to_partials(double (&v)[NV], double* partials) {
@@ -1391,6 +1402,17 @@ int dsmd_kinetic_energy(dsmd_ctx* c, double* out, void* stream) {
     DSMD_CUDA(c, cudaMemcpyAsync(c->h_scalars + 6, c->scalars + 6, sizeof(double), cudaMemcpyDeviceToHost, s));
     DSMD_CUDA(c, cudaStreamSynchronize(s));
     *out = c->h_scalars[6];
+    return DSMD_OK;
+}
+
+int dsmd_scale_velocities(dsmd_ctx* c, double factor, void* stream) {
+    if (!c || !std::isfinite(factor)) return DSMD_ERR_INVALID;
+    if (c->n_owned == 0) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    double** r = c->real[c->cur];
+    k_scale_velocities<<<blocks_for(c->n_owned, kThreads), kThreads, 0, s>>>(static_cast<int>(c->n_owned), factor, r[3], r[4],
+                                                                             r[5]);
+    DSMD_LAUNCHED(c);
     return DSMD_OK;
 }
 

@@ -161,6 +161,11 @@ int dsmd_integrate(dsmd_ctx* ctx, int half, double dt, double force_to_accel, vo
 /* calculate_kinetic_energy (include/force_calculator.h:70): sum 1/2 m v^2 over owned atoms, raw units. Synchronises. */
 int dsmd_kinetic_energy(dsmd_ctx* ctx, double* out, void* stream);
 
+/* Thermostat of the velocity-scaling kind (launch_nose_hoover_thermostat_kernel, src/thermostat_kernels.cu:68-76,
+ * 131-141): multiplies the velocities of the owned atoms by `factor` (which the host computes from the kinetic energy,
+ * src/thermostat.cpp:78-95). */
+int dsmd_scale_velocities(dsmd_ctx* ctx, double factor, void* stream);
+
 /* The MD loop of MDSimulation::single_step (src/md_simulation.cpp:899-941) restricted to this path: n_steps of
  * integrate-1 + pack, rebuild decision (max displacement > (hi_frac skin)^2, or every `every` steps when every > 0;
  * lagged != 0 uses the previous step's read-back, extrapolated, as the reference does on several ranks), list rebuild,

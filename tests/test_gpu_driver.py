@@ -1,0 +1,98 @@
+"""The MD driver executable end to end on a GPU: the reference's input files in, status lines out."""
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+from deepscalemd_b200 import build, input_api, input_files
+from deepscalemd_b200 import synthetic as syn
+from oracle import cpu_oracle as co
+
+pytestmark = pytest.mark.gpu
+
+LINE = re.compile(r"^Step: (\d+), T: ([-\d.eE+]+), KE: ([-\d.eE+]+), PE: ([-\d.eE+]+), Etot: ([-\d.eE+]+)$")
+
+
+def run_driver(yaml_path, timeout=300):
+    r = subprocess.run([build.build_driver(), str(yaml_path)], capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stderr + r.stdout
+    rows = [tuple(float(v) for v in m.groups()) for m in map(LINE.match, r.stdout.splitlines()) if m]
+    return np.array(rows), r.stdout
+
+
+def test_nve_run_from_input_files(cuda_device, tmp_path):
+    """864 argon atoms from XYZ + legacy .top + run description: start energies equal the oracle's for the same positions,
+    the total energy is conserved, the list is rebuilt on the way, the closing lines are the reference's."""
+    s = syn.fcc_lj(6, seed=1)
+    path, scale = input_files.argon_files(str(tmp_path), s, total_steps=200, output_freq=50, update_freq=1000)
+    rows, out = run_driver(path)
+    assert [int(r[0]) for r in rows] == [0, 50, 100, 150, 200]
+    n = s.n
+    target_t = 1.44 * scale["epsilon"] / input_files.KB
+    assert rows[0][2] == pytest.approx(0.5 * (3 * n - 3) * input_files.KB * target_t, rel=1e-9)    # Maxwell-Boltzmann start
+    assert rows[0][1] == pytest.approx(target_t * (3 * n - 3) / (3 * n), rel=1e-9)                 # printed T uses 3N
+    # potential energy of the start configuration: the oracle's, in kcal/mol
+    x, y, z = (np.ascontiguousarray(s.pos[:, k]) for k in range(3))
+    c6, c12 = co.lj_tables(s.eps, s.sig)
+    _, sc = co.forces(x, y, z, n, s.box, co.pairs(x, y, z, n, s.box, search=s.cutoff), c6, c12, s.cutoff)
+    assert rows[0][3] == pytest.approx(sc["pe"] * scale["epsilon"], rel=2e-6)
+    etot = rows[:, 4]
+    # plain truncation: the sampled total energy carries noise from pairs crossing the cutoff (about 4e-4 of the start
+    # kinetic energy for 864 atoms), no drift
+    assert np.abs(etot - etot[0]).max() < 3e-3 * rows[0][2]
+    assert rows[-1][1] < 0.75 * rows[0][1]           # the lattice start gives half its kinetic energy to the potential
+    builds = int(re.search(r"Neighbor list builds = (\d+)", out).group(1))
+    assert builds >= 5
+    assert re.search(r"Performance: [\d.]+ Matom-step/s, [\d.]+ ms/step, [\d.]+ ns/day \(md_loop only, dt=[\d.]+ fs\)", out)
+
+
+def test_nose_hoover_holds_the_target_temperature(cuda_device, tmp_path):
+    s = syn.fcc_lj(6, seed=1)
+    path, scale = input_files.argon_files(str(tmp_path), s, total_steps=3000, output_freq=100, update_freq=1000,
+                                          thermostat="nose_hoover", tau_t=200.0)
+    rows, _ = run_driver(path)
+    target_t = 1.44 * scale["epsilon"] / input_files.KB
+    late = rows[rows[:, 0] >= 1500][:, 1]
+    assert abs(late.mean() - target_t) < 0.05 * target_t
+
+
+def test_restart_continues_the_run(cuda_device, tmp_path):
+    s = syn.fcc_lj(6, seed=1)
+    whole, _ = input_files.argon_files(str(tmp_path / "whole"), s, total_steps=100, output_freq=50, update_freq=1000)
+    rows_whole, _ = run_driver(whole)
+    first, _ = input_files.argon_files(str(tmp_path / "first"), s, total_steps=50, output_freq=50, update_freq=1000,
+                                       restart_output=str(tmp_path / "half.restart"), restart_output_freq=50)
+    rows_first, out_first = run_driver(first)
+    assert "[restart] wrote" in out_first and os.path.exists(tmp_path / "half.restart")
+    second, scale = input_files.argon_files(str(tmp_path / "second"), s, total_steps=50, output_freq=50, update_freq=1000,
+                                            restart_file=str(tmp_path / "half.restart"))
+    rows_second, _ = run_driver(second)
+    assert [int(r[0]) for r in rows_second] == [50, 100]                    # the step counter goes on
+    # same state as where the first half stopped (the list is rebuilt at the restart, so fp32 sums run in another order)
+    assert rows_second[0][2:] == pytest.approx(rows_first[-1][2:], rel=1e-6)
+    assert rows_second[-1][2:] == pytest.approx(rows_whole[-1][2:], rel=1e-5)  # and the same end as the uninterrupted run
+    # the file itself: the layout the reference reads
+    raw = open(tmp_path / "half.restart", "rb").read()
+    assert raw[:8] == b"DSMDRST1" and raw[-8:] == b"DSMDEND1" and len(raw) == 8 + 16 + 32 + 12 + (4 + 4) + 4 + (4 + 4) + 4 + \
+        48 * s.n + 8
+    sys_ = input_api.System(coordinate_file=str(tmp_path / "first" / "argon.xyz"), box=scale["box"])
+    info = sys_.read_restart(tmp_path / "half.restart")
+    assert info["step"] == 50 and info["thermostat"] == "none"
+
+
+def test_velocity_scaling_entry_point(cuda_device):
+    from deepscalemd_b200 import capi
+    s = syn.fcc_lj(4, seed=3)
+    ctx = capi.Context(s.n)
+    ctx.set_box(s.box, (1, 1, 1), (0, 0, 0), (0, 0, 0), 0.0)
+    ctx.set_pair_params(s.eps, s.sig, s.cutoff, s.skin)
+    ctx.upload(s.pos, vel=s.vel, mass=s.mass, types=s.types)
+    before = ctx.kinetic_energy()
+    v_before = np.stack([ctx.download(k, s.n) for k in ("vx", "vy", "vz")], axis=1)
+    ctx.scale_velocities(0.75)
+    v_after = np.stack([ctx.download(k, s.n) for k in ("vx", "vy", "vz")], axis=1)
+    assert np.array_equal(v_after, v_before * 0.75)
+    assert ctx.kinetic_energy() == pytest.approx(before * 0.5625, rel=1e-13)
+    ctx.close()
