@@ -28,7 +28,7 @@ if ROOT not in sys.path:
 DT = 0.005
 ARGON_TAU_FS = 2156.0          # sigma sqrt(m / epsilon) of argon in fs: maps dt = 0.005 tau to 10.78 fs for ns/day
 L2_BYTES = 126e6
-NCU_PAIR_TRAFFIC_BYTES_PER_ATOM = 174.06e6 / 500_000   # measured DRAM bytes per launch / atoms (full list + positions)
+NCU_PAIR_TRAFFIC_BYTES_PER_ATOM = 171.4e6 / 500_000   # measured DRAM bytes per launch / atoms (full list + positions)
 
 
 def measured_peaks():

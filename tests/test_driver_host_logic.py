@@ -97,3 +97,29 @@ def test_restart_continues_the_run(driver, tmp_path):
     sys_ = input_api.System(coordinate_file=str(tmp_path / "first" / "argon.xyz"), box=scale["box"])
     info = sys_.read_restart(tmp_path / "half.restart")
     assert info["step"] == 50 and info["thermostat"] == "nose_hoover" and info["xi"] != 0.0
+
+
+def test_binary_mixture_from_a_dsmd_input_folder(driver, tmp_path):
+    """Two atom types with an explicit pair table (not Lorentz-Berthelot), read through input_system -> manifest ->
+    .dsMDtop / .dsMDprm: the start energy equals the oracle's for the same table, and the run conserves energy."""
+    ka = syn.kob_andersen(256, seed=5)
+    sig, eps, mass = 3.405, 0.238, 39.948
+    box = np.asarray(ka.box) * sig
+    pos = ka.pos * sig
+    pos = pos - box * np.floor(pos / box)
+    pos = pos + (box / 2 - pos.mean(0))
+    manifest = input_files.write_dsmd_input(str(tmp_path / "ka"), "ka", pos, ["Ar" if t == 0 else "Kr" for t in ka.types],
+                                            ka.types, ["A", "B"], ka.mass * mass, ka.charge, np.asarray(ka.sig) * sig,
+                                            np.asarray(ka.eps) * eps)
+    tau = input_files.reduced_time_fs()
+    # cutoff 2.2 sigma_AA: the 256-atom box is 5.98 sigma wide, the test double needs twice the list radius
+    path = input_files.write_run_yaml(tmp_path / "ka.yaml", box=box, total_steps=100, timestep=0.0002 * tau,
+                                      temperature=0.8 * eps / input_files.KB, cutoff=2.2 * sig, skin=0.3 * sig,
+                                      input_system=manifest, output_freq=50, update_freq=1000)
+    rows, _ = run_driver(driver, path)
+    x, y, z = (np.ascontiguousarray(ka.pos[:, k]) for k in range(3))
+    c6, c12 = co.lj_tables(ka.eps, ka.sig)
+    _, sc = co.forces(x, y, z, ka.n, ka.box, co.pairs(x, y, z, ka.n, ka.box, search=2.2), c6, c12, 2.2, types=ka.types)
+    assert rows[0][3] == pytest.approx(sc["pe"] * eps, rel=1e-8)
+    # (the start configuration is unrelaxed, with strongly repulsive contacts: hence the short time step)
+    assert abs(rows[-1][4] - rows[0][4]) < 1e-3 * abs(rows[0][3])
