@@ -213,6 +213,11 @@ class Context:
         self._check(self.lib.dsmd_ghost_slots(self.h, ctypes.byref(p)))
         return p.value
 
+    def ghost_slots(self, n_ghost):
+        """The slot of every ghost atom, in the order the ghosts arrived (int32 device tensor of n_ghost entries)."""
+        import torch
+        return _tensor_from_ptr(self.ghost_slots_ptr(), (int(n_ghost),), torch.int32, torch.device("cuda", self.device))
+
     def list_stats(self):
         e, i = c_int64(0), c_int64(0)
         s, c, r = c_int(0), c_int(0), c_int(0)

@@ -171,16 +171,18 @@ class DomainRunner:
         table = out.cpu().numpy().reshape(self.d.world_size, self.n_dirs)
         return [int(table[dr.src, dr.index]) if dr.src >= 0 else 0 for dr in self.d.directions]
 
-    def _exchange(self, send_chunks, recv_chunks):
-        """One grouped point-to-point round: chunk k travels along direction k."""
+    def _exchange(self, send_chunks, recv_chunks, backwards=False):
+        """One grouped point-to-point round: chunk k travels along direction k (backwards: against it, from the rank that
+        received along k to the rank that sent)."""
         ops = []
         for dr, s, r in zip(self.d.directions, send_chunks, recv_chunks):
             if dr.dest < 0:
                 continue
+            to, frm = (dr.src, dr.dest) if backwards else (dr.dest, dr.src)
             if r is not None and r.numel():
-                ops.append(dist.P2POp(dist.irecv, r, dr.src, group=self.group))
+                ops.append(dist.P2POp(dist.irecv, r, frm, group=self.group))
             if s is not None and s.numel():
-                ops.append(dist.P2POp(dist.isend, s, dr.dest, group=self.group))
+                ops.append(dist.P2POp(dist.isend, s, to, group=self.group))
         if ops:
             for w in dist.batch_isend_irecv(ops):
                 w.wait()
@@ -311,6 +313,43 @@ class DomainRunner:
         """Orders the main stream behind the unpack (ForceCalculatorCUDA::make_force_stream_wait_for_halo)."""
         if self.cuda and self.side is not self.main:
             self.main.wait_stream(self.side)
+
+    # -- per-atom feature fields along the ghost plan ------------------------------------------------------------------------
+    @staticmethod
+    def _row_chunks(rows, counts):
+        out, at = [], 0
+        for n in counts:
+            out.append(rows[at:at + n])
+            at += n
+        return out
+
+    def exchange_field(self, field, reverse=False):
+        """Moves a per-atom field (a contiguous [n_owned + n_ghost, width] float32 / float64 tensor in the context's slot
+        order) along the ghost plan of the last rebuild, as MDSystem::exchange_field_on_device does for the node features
+        of a message-passing model (src/md_system.cpp:1520-1545; contract include/MLIPHaloTransport.h:16-37).
+        forward: the ghost rows are overwritten with the rows of their owners. reverse (its adjoint): the ghost rows are
+        added to the rows of their owners; the ghost rows are not defined afterwards. Collective."""
+        n_owned, n_total = self.ctx.counts()
+        if field.dim() != 2 or not field.is_contiguous() or field.shape[0] != n_total:
+            raise ValueError(f"the field must be a contiguous [{n_total}, width] tensor ({n_owned} owned + "
+                             f"{n_total - n_owned} ghost atoms)")
+        if field.dtype not in (torch.float32, torch.float64):
+            raise ValueError("the field must be float32 or float64")
+        n_send = sum(self.send_counts)
+        plan = self.send_index[:n_send].long()
+        slots = self.ctx.ghost_slots(self.n_ghost).long()
+        width = field.shape[1]
+        if not reverse:
+            out = field.index_select(0, plan)
+            arrived = torch.empty((self.n_ghost, width), dtype=field.dtype, device=field.device)
+            self._exchange(self._row_chunks(out, self.send_counts), self._row_chunks(arrived, self.recv_counts))
+            field.index_copy_(0, slots, arrived)
+        else:
+            back = field.index_select(0, slots)
+            arrived = torch.empty((n_send, width), dtype=field.dtype, device=field.device)
+            self._exchange(self._row_chunks(back, self.recv_counts), self._row_chunks(arrived, self.send_counts), backwards=True)
+            field.index_add_(0, plan, arrived)
+        return field
 
     # -- rebuild vote -----------------------------------------------------------------------------------------------------------
     def vote_rebuild(self, skin, hi_frac=0.5, lagged=True):

@@ -97,6 +97,9 @@ class FakeContext:
         for k, name in enumerate("xyz"):
             self.a[name][s] = b[:, k]
 
+    def ghost_slots(self, n_ghost):
+        return torch.arange(self.n_owned, self.n_owned + n_ghost, dtype=torch.int32)   # ghosts stay in arrival order here
+
     def displacement_word(self):
         return self.word
 

@@ -149,3 +149,79 @@ def test_brick_grids_and_directions():
         for d in decs:
             inside = np.all((w >= d.lo) & (w < d.hi), axis=1)
             assert np.array_equal(inside, owner == d.rank)
+
+
+def field_worker(rank, world, port, dims, out_path):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from fake_context import FakeContext
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    s = syn.fcc_lj(8, seed=33)
+    dec = domain.Decomposition(s.box, world, rank, dims=dims)
+    mine = np.nonzero(dec.owner_of(s.pos) == rank)[0]
+    ctx = FakeContext(s.n, s.box, s.eps, s.sig, s.cutoff, s.skin)
+    ctx.set_split(dec.split)
+    wrapped = s.pos - s.box * np.floor(s.pos / s.box)
+    ctx.upload(wrapped[mine], s.vel[mine], s.mass[mine], mine.astype(np.int32))
+    run = domain.DomainRunner(ctx, dec, s.cutoff + s.skin, "cpu")
+    run.rebuild()
+    n_owned, n_total = ctx.counts()
+    gid = torch.from_numpy(ctx.gid[:n_total].astype(np.int64))
+    # forward: every ghost row becomes its owner's row
+    field = torch.zeros((n_total, 3), dtype=torch.float64)
+    field[:n_owned, 0] = gid[:n_owned].double()
+    field[:n_owned, 1] = 2.0 * gid[:n_owned].double() + 1.0
+    field[:n_owned, 2] = float(rank)
+    run.exchange_field(field)
+    forward_ok = bool(torch.equal(field[:, 0], gid.double()) and torch.equal(field[:, 1], 2.0 * gid.double() + 1.0))
+    owner_rank = torch.from_numpy(dec.owner_of(s.pos)[ctx.gid[:n_total]].astype(np.float64))
+    forward_ok = forward_ok and bool(torch.equal(field[:, 2], owner_rank))
+    # reverse: every ghost row is added to its owner's row (float32 this time)
+    back = torch.zeros((n_total, 2), dtype=torch.float32)
+    back[n_owned:, 0] = 1.0
+    back[n_owned:, 1] = gid[n_owned:].float()
+    back[:n_owned, 0] = 100.0
+    run.exchange_field(back, reverse=True)
+    result = dict(forward_ok=forward_ok, gid=ctx.gid[:n_owned].copy(), copies=back[:n_owned, 0].numpy() - 100.0,
+                  gid_sum=back[:n_owned, 1].numpy(), ghosts=n_total - n_owned)
+    try:
+        run.exchange_field(torch.zeros((n_total + 1, 2), dtype=torch.float64))
+        result["refused"] = False
+    except ValueError:
+        result["refused"] = True
+    gathered = [None] * world
+    dist.all_gather_object(gathered, result)
+    if rank == 0:
+        torch.save(gathered, out_path)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dims", [(2, 1, 1), (2, 2, 2)])
+def test_feature_field_exchange_along_the_ghost_plan(tmp_path, dims):
+    """Forward copies owner rows into every ghost copy; reverse adds every ghost copy's row to its owner (the adjoint):
+    how often an atom is a ghost somewhere follows from the geometry alone (built here independently)."""
+    world = dims[0] * dims[1] * dims[2]
+    out = str(tmp_path / "out.pt")
+    procs = [mp.get_context("spawn").Process(target=field_worker, args=(rank, world, free_port_once(), dims, out))
+             for rank in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.terminate()
+    assert not hung and all(p.exitcode == 0 for p in procs)
+    parts = torch.load(out, weights_only=False)
+    assert all(p["forward_ok"] and p["refused"] for p in parts)
+    s = syn.fcc_lj(8, seed=33)
+    want = np.zeros(s.n)
+    for brick in syn.brick_decompose(s.pos, s.box, dims, s.cutoff + s.skin):
+        want += np.bincount(brick["ghost_src"], minlength=s.n)
+    got = np.zeros(s.n)
+    gid_sum = np.zeros(s.n)
+    for p in parts:
+        got[p["gid"]] = p["copies"]
+        gid_sum[p["gid"]] = p["gid_sum"]
+    assert np.array_equal(got, want) and want.sum() == sum(p["ghosts"] for p in parts) and want.max() >= (1 if world == 2 else 3)
+    assert np.array_equal(gid_sum, want * np.arange(s.n))
