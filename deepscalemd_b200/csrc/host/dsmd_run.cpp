@@ -14,6 +14,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
 #include <iomanip>
 #include <iostream>
 #include <sstream>
@@ -210,6 +211,38 @@ public:
         }
     }
 
+    // One frame "<output_prefix>_<step>.xyz" in the reference's layout (MDSimulation::write_xyz_trajectory,
+    // src/md_simulation.cpp:3819-3863): atom count, a comment line with step, time and energies, then element and
+    // position (and velocity, force when asked for) of every atom in coordinate-file order, six decimals.
+    void write_xyz_frame(long long step, const Metrics& m) {
+        const size_t n = static_cast<size_t>(s_.n);
+        std::vector<int32_t> gid(n);
+        ok(ctx_, dsmd_download(ctx_, DSMD_GLOBAL_ID, s_.n, gid.data(), nullptr), "dsmd_download");
+        std::vector<int> fields = {DSMD_X, DSMD_Y, DSMD_Z};
+        if (c_.trajectory_include_velocities) fields.insert(fields.end(), {DSMD_VX, DSMD_VY, DSMD_VZ});
+        if (c_.trajectory_include_forces) fields.insert(fields.end(), {DSMD_FX, DSMD_FY, DSMD_FZ});
+        std::vector<std::vector<double>> columns(fields.size(), std::vector<double>(n));
+        std::vector<double> buffer(n);
+        for (size_t f = 0; f < fields.size(); ++f) {
+            ok(ctx_, dsmd_download(ctx_, fields[f], s_.n, buffer.data(), nullptr), "dsmd_download");
+            for (size_t k = 0; k < n; ++k) columns[f][static_cast<size_t>(gid[k])] = buffer[k];
+        }
+        const std::string name = c_.output_prefix + "_" + std::to_string(step) + ".xyz";
+        std::ofstream out(name);
+        if (!out.is_open()) {
+            std::cerr << "Warning: Cannot open trajectory file " << name << std::endl;
+            return;
+        }
+        out << n << "\n";
+        out << "Step " << step << " Time " << std::fixed << std::setprecision(3) << static_cast<double>(step) * c_.timestep << " fs"
+            << " KE=" << std::setprecision(6) << m.ke << " PE=" << m.pe << " Total=" << (m.ke + m.pe) << "\n";
+        for (size_t i = 0; i < n; ++i) {
+            out << s_.element[i];
+            for (size_t f = 0; f < fields.size(); ++f) out << " " << columns[f][i];
+            out << "\n";
+        }
+    }
+
     void write_restart_file(long long step) {
         RestartState r;
         r.step = step;
@@ -288,10 +321,12 @@ int run(const Options& opt) {
     md.forces(true);
 
     auto output_due = [&](long long step) { return c.output_freq > 0 && step % c.output_freq == 0; };
+    auto trajectory_due = [&](long long step) { return c.trajectory_output_freq > 0 && step % c.trajectory_output_freq == 0; };
     auto restart_due = [&](long long step) {
         return c.restart_output_freq > 0 && (step % c.restart_output_freq == 0 || step == start_step + c.total_steps);
     };
     if (output_due(start_step)) std::cout << status_line(c.output_info, start_step, md.metrics()) << std::endl;
+    if (trajectory_due(start_step)) md.write_xyz_frame(start_step, md.metrics());
 
     const auto t0 = std::chrono::steady_clock::now();
     const long long last = start_step + c.total_steps;
@@ -302,7 +337,7 @@ int run(const Options& opt) {
         if (!md.nose_hoover_) {
             long long next_event = last;
             for (long long k = step + 1; k <= last; ++k)
-                if (output_due(k) || restart_due(k)) { next_event = k; break; }
+                if (output_due(k) || restart_due(k) || trajectory_due(k)) { next_event = k; break; }
             const long long plain = next_event - 1 - step;
             if (plain > 0) {
                 md.plain_steps(plain);
@@ -310,9 +345,10 @@ int run(const Options& opt) {
             }
         }
         const long long next = step + 1;
-        md.step(step, output_due(next));
+        md.step(step, output_due(next) || trajectory_due(next));
         step = next;
         if (output_due(step)) std::cout << status_line(c.output_info, step, md.metrics()) << std::endl;
+        if (trajectory_due(step)) md.write_xyz_frame(step, md.metrics());
         if (restart_due(step)) md.write_restart_file(step);
     }
     const double seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();

@@ -164,6 +164,9 @@ RunConfig read_run_config(const std::string& path) {
         else if (key == "restart_output") c.restart_output = trimmed(value);
         else if (key == "restart_output_freq") c.restart_output_freq = integer_of(key, value);
         else if (key == "trajectory_output_freq") c.trajectory_output_freq = integer_of(key, value);
+        else if (key == "trajectory_format") c.trajectory_format = value;
+        else if (key == "trajectory_include_velocities") c.trajectory_include_velocities = value == "true";
+        else if (key == "trajectory_include_forces") c.trajectory_include_forces = value == "true";
         else if (key == "energy_output_freq") c.energy_output_freq = integer_of(key, value);
         else if (key == "output_freq") c.output_freq = integer_of(key, value);
         else if (key == "output_info") c.output_info = value;
@@ -245,6 +248,13 @@ RunConfig read_run_config(const std::string& path) {
         c.enable_bonded = any_bonded;
     }
 
+    {
+        std::string formats = trimmed(c.trajectory_format) == "both" ? "xyz,dump" : c.trajectory_format;
+        for (const auto& f : comma_list(formats))
+            if (f != "xyz" && f != "dump" && f != "dcd" && f != "bp" && f != "h5md")
+                throw std::runtime_error("Invalid trajectory_format component: '" + f +
+                                         "'. Supported components are: xyz, dump, dcd, bp, h5md (or legacy 'both')");
+    }
     if (c.total_steps <= 0) throw std::runtime_error("total_steps must be positive");
     if (c.target_temperature < 0.0) throw std::runtime_error("target_temperature must not be negative");
     if (c.neighbor_list_update_freq <= 0) throw std::runtime_error("neighbor_list_update_freq must be positive");
@@ -263,6 +273,11 @@ std::vector<std::string> RunConfig::unsupported() const {
     if (integ == "r_respa") out.push_back("integrator: r_respa");
     const std::string thermo = trimmed(thermostat);
     if (thermo == "langevin" || thermo == "andersen") out.push_back("thermostat: " + thermo + " (none or nose_hoover)");
+    if (trajectory_output_freq > 0) {
+        const std::string formats = trimmed(trajectory_format) == "both" ? "xyz,dump" : trajectory_format;
+        for (const auto& f : comma_list(formats))
+            if (f != "xyz") out.push_back("trajectory_format: " + f + " (xyz frames only)");
+    }
     const std::string baro = trimmed(barostat);
     if (baro == "berendsen" || baro == "parrinello_rahman" || baro == "andersen") out.push_back("barostat: " + baro);
     return out;
@@ -291,6 +306,8 @@ std::string RunConfig::to_json() const {
     boolean("enable_bonded", enable_bonded);
     str("output_prefix", output_prefix); str("output_info", output_info); integer("output_freq", output_freq);
     integer("energy_output_freq", energy_output_freq); integer("trajectory_output_freq", trajectory_output_freq);
+    str("trajectory_format", trajectory_format); boolean("trajectory_include_velocities", trajectory_include_velocities);
+    boolean("trajectory_include_forces", trajectory_include_forces);
     str("restart_file", restart_file); str("restart_output", restart_output);
     integer("restart_output_freq", restart_output_freq); integer("velocity_seed", velocity_seed);
     s << "\"unsupported\": [";

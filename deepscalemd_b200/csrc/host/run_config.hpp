@@ -36,6 +36,8 @@ struct RunConfig {
     // output and restart
     std::string output_prefix = "md_output", output_info = "STEP, T, KE";
     long long output_freq = 10, energy_output_freq = 10, trajectory_output_freq = 100;
+    std::string trajectory_format = "xyz";       // comma list; "both" = xyz,dump
+    bool trajectory_include_velocities = false, trajectory_include_forces = false;
     std::string restart_file, restart_output;
     long long restart_output_freq = 0;
     // keys this implementation adds (the reference ignores unknown keys): seed of the initial velocities

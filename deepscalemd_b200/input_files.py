@@ -79,7 +79,8 @@ def write_dsmd_input(folder, name, pos, elements, type_ids, type_names, mass, ch
 def write_run_yaml(path, *, box, total_steps, timestep, temperature, cutoff, skin, coordinate_file=None, topology_file=None,
                    parameter_file=None, input_system=None, periodic=(True, True, True), force_type="lj", thermostat="none",
                    tau_t=100.0, output_freq=10, output_info="STEP, T, KE, PE, ETOTAL", switch=None, update_freq=10,
-                   restart_file=None, restart_output=None, restart_output_freq=0, output_prefix="md_output", extra=None):
+                   restart_file=None, restart_output=None, restart_output_freq=0, output_prefix="md_output",
+                   trajectory_output_freq=0, extra=None):
     lines = ["# generated run description"]
     if input_system:
         lines.append(f"input_system: {input_system}")
@@ -95,7 +96,8 @@ def write_run_yaml(path, *, box, total_steps, timestep, temperature, cutoff, ski
         lines.append(f"periodic_{axis}: {'true' if p else 'false'}")
     lines += [f"cutoff_distance: {cutoff:.17g}", f"verlet_skin: {skin:.17g}", f"neighbor_list_update_freq: {update_freq}",
               "integrator: velocity_verlet", f"thermostat: {thermostat}", f"tau_t: {tau_t:.17g}", "barostat: none",
-              f"output_freq: {output_freq}", f"output_info: {output_info}", f"output_prefix: {output_prefix}"]
+              f"output_freq: {output_freq}", f"output_info: {output_info}", f"output_prefix: {output_prefix}",
+              f"trajectory_output_freq: {trajectory_output_freq}"]
     if switch is not None:
         lines.append(f"lj_switch_distance: {switch:.17g}")
     if restart_file:

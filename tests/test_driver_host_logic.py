@@ -123,3 +123,24 @@ def test_binary_mixture_from_a_dsmd_input_folder(driver, tmp_path):
     assert rows[0][3] == pytest.approx(sc["pe"] * eps, rel=1e-8)
     # (the start configuration is unrelaxed, with strongly repulsive contacts: hence the short time step)
     assert abs(rows[-1][4] - rows[0][4]) < 1e-3 * abs(rows[0][3])
+
+
+def test_xyz_frames_have_the_reference_layout(driver, tmp_path):
+    s = syn.fcc_lj(4, seed=1)
+    prefix = str(tmp_path / "traj")
+    path, scale = input_files.argon_files(str(tmp_path), s, total_steps=20, output_freq=10, update_freq=1000,
+                                          trajectory_output_freq=10, output_prefix=prefix,
+                                          extra={"trajectory_include_velocities": "true"})
+    rows, _ = run_driver(driver, path)
+    frames = sorted(f for f in os.listdir(tmp_path) if f.startswith("traj_") and f.endswith(".xyz"))
+    assert frames == ["traj_0.xyz", "traj_10.xyz", "traj_20.xyz"]
+    lines = open(tmp_path / "traj_10.xyz").read().splitlines()
+    assert lines[0] == str(s.n) and len(lines) == s.n + 2
+    m = re.match(r"^Step 10 Time ([\d.]+) fs KE=([-\d.]+) PE=([-\d.]+) Total=([-\d.]+)$", lines[1])
+    assert m and float(m.group(1)) == pytest.approx(10 * 0.005 * scale["tau_fs"], abs=1e-3)
+    assert float(m.group(2)) == pytest.approx(rows[1][2], abs=2e-6) and float(m.group(3)) == pytest.approx(rows[1][3], abs=2e-6)
+    first = lines[2].split()
+    assert first[0] == "Ar" and len(first) == 7 and all(re.match(r"^-?\d+\.\d{6}$", v) for v in first[1:])
+    # frame 0 holds the start positions in coordinate-file order
+    start = np.array([[float(v) for v in l.split()[1:4]] for l in open(tmp_path / "traj_0.xyz").read().splitlines()[2:]])
+    assert np.abs(start - scale["positions"]).max() < 1e-6
