@@ -245,6 +245,60 @@ def vv_half(first_half, dt, force_to_accel, pos, vel, frc, mass):
         *[_ptr(a, ctypes.c_double) for a in frc], _ptr(mass, ctypes.c_double))
 
 
+def _constraint_arrays(constraints):
+    a = np.ascontiguousarray([c[0] for c in constraints], dtype=np.int64)
+    b = np.ascontiguousarray([c[1] for c in constraints], dtype=np.int64)
+    d = np.ascontiguousarray([c[2] for c in constraints], dtype=np.float64)
+    return a, b, d
+
+
+def shake(constraints, pos, vel, mass, pre, box, dt, periodic=(1, 1, 1), max_iterations=500, tolerance=1e-8):
+    """SHAKE in place on pos / vel (three contiguous columns each); pre = the positions before the drift. Returns True
+    when converged."""
+    a, b, d = _constraint_arrays(constraints)
+    rc = lib().dsmd_oracle_shake(
+        ctypes.c_long(len(a)), _ptr(a, ctypes.c_long), _ptr(b, ctypes.c_long), _ptr(d, ctypes.c_double),
+        *[_ptr(c, ctypes.c_double) for c in pos], *[_ptr(c, ctypes.c_double) for c in vel], _ptr(_f64(mass), ctypes.c_double),
+        *[_ptr(c, ctypes.c_double) for c in pre], _ptr(_f64(box), ctypes.c_double), _ptr(_i32(periodic), ctypes.c_int),
+        ctypes.c_double(dt), ctypes.c_int(max_iterations), ctypes.c_double(tolerance))
+    return bool(rc)
+
+
+def rattle(constraints, pos, vel, mass, box, dt, force_to_accel, periodic=(1, 1, 1), gid=None, n_local=None,
+           max_iterations=500, tolerance=1e-8):
+    """RATTLE in place on vel. Returns (converged, diagonal of the constraint virial)."""
+    a, b, _ = _constraint_arrays(constraints)
+    n = len(mass)
+    virial = np.zeros(3)
+    g = None if gid is None else _i32(gid)
+    rc = lib().dsmd_oracle_rattle(
+        ctypes.c_long(len(a)), _ptr(a, ctypes.c_long), _ptr(b, ctypes.c_long), *[_ptr(c, ctypes.c_double) for c in pos],
+        *[_ptr(c, ctypes.c_double) for c in vel], _ptr(_f64(mass), ctypes.c_double),
+        _ptr(g, ctypes.c_int) if g is not None else None, ctypes.c_long(n if n_local is None else n_local),
+        _ptr(_f64(box), ctypes.c_double), _ptr(_i32(periodic), ctypes.c_int), ctypes.c_double(dt),
+        ctypes.c_double(force_to_accel), ctypes.c_int(max_iterations), ctypes.c_double(tolerance),
+        _ptr(virial, ctypes.c_double))
+    return bool(rc), virial
+
+
+def ref_constrain(which, constraints, pos, vel, mass, box, dt, pre=None, periodic=(1, 1, 1), max_iterations=500,
+                  tolerance=1e-8):
+    """The REFERENCE's ConstraintSolver (src/constraint_solver.cpp, compiled in place) on the same arrays, in place.
+    which = "shake" or "rattle". Returns (converged, virial diagonal)."""
+    a, b, d = _constraint_arrays(constraints)
+    n = len(mass)
+    virial = np.zeros(3)
+    pre = pos if pre is None else pre
+    L = ref_lib()
+    rc = L.dsmd_ref_constrain(
+        ctypes.c_int(0 if which == "shake" else 1), ctypes.c_long(n), ctypes.c_long(n), *[_ptr(c, ctypes.c_double) for c in pos],
+        *[_ptr(c, ctypes.c_double) for c in vel], _ptr(_f64(mass), ctypes.c_double), None, _ptr(_f64(box), ctypes.c_double),
+        _ptr(_i32(periodic), ctypes.c_int), ctypes.c_long(len(a)), _ptr(a, ctypes.c_long), _ptr(b, ctypes.c_long),
+        _ptr(d, ctypes.c_double), ctypes.c_double(dt), *[_ptr(c, ctypes.c_double) for c in pre], ctypes.c_int(max_iterations),
+        ctypes.c_double(tolerance), _ptr(virial, ctypes.c_double))
+    return bool(rc), virial
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 # brute force (pure numpy, O(N^2): small cases only)
 # ---------------------------------------------------------------------------------------------------------------------

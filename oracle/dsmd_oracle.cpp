@@ -524,4 +524,91 @@ void dsmd_oracle_vv_half(long n, double dt, double force_to_accel, int first_hal
     }
 }
 
+// ---- distance constraints -----------------------------------------------------------------------------------------------
+// SHAKE (positions) and RATTLE (velocities) as the reference's CPU solver does them (src/constraint_solver.cpp:15-146):
+// Gauss-Seidel sweeps over the constraint list until every constraint holds to the tolerance; a constraint already inside
+// the tolerance is left alone in a sweep. Minimum image per periodic axis by one box length (|d| > L / 2).
+namespace {
+inline void min_image(double d[3], const double L[3], const int periodic[3]) {
+    for (int a = 0; a < 3; ++a)
+        if (periodic[a]) {
+            if (d[a] > 0.5 * L[a]) d[a] -= L[a];
+            else if (d[a] < -0.5 * L[a]) d[a] += L[a];
+        }
+}
+}  // namespace
+
+// SHAKE: moves the atoms of every constraint (i, j, distance) along the bond vector the pair had BEFORE the drift
+// (pre_x, pre_y, pre_z) until |r_ij|^2 is within `tolerance` (relative) of distance^2; the velocities take the
+// displacement over dt. Returns 1 when converged within max_iterations sweeps.
+int dsmd_oracle_shake(long n_constraints, const long* atom1, const long* atom2, const double* distance, double* x, double* y,
+                      double* z, double* vx, double* vy, double* vz, const double* mass, const double* pre_x,
+                      const double* pre_y, const double* pre_z, const double L[3], const int periodic[3], double dt,
+                      int max_iterations, double tolerance) {
+    if (n_constraints == 0) return 1;
+    const double inv_dt = 1.0 / dt;
+    for (int sweep = 0; sweep < max_iterations; ++sweep) {
+        double worst = 0.0;
+        for (long c = 0; c < n_constraints; ++c) {
+            const long i = atom1[c], j = atom2[c];
+            const double target2 = distance[c] * distance[c];
+            double d[3] = {x[i] - x[j], y[i] - y[j], z[i] - z[j]};
+            min_image(d, L, periodic);
+            const double excess = (d[0] * d[0] + d[1] * d[1] + d[2] * d[2]) - target2;
+            const double relative = std::fabs(excess) / target2;
+            worst = std::max(worst, relative);
+            if (relative < tolerance) continue;
+            double o[3] = {pre_x[i] - pre_x[j], pre_y[i] - pre_y[j], pre_z[i] - pre_z[j]};
+            min_image(o, L, periodic);
+            const double along = o[0] * d[0] + o[1] * d[1] + o[2] * d[2];
+            if (std::fabs(along) < 1e-12) continue;   // degenerate geometry: try again in the next sweep
+            const double wi = 1.0 / mass[i], wj = 1.0 / mass[j];
+            const double g = excess / (2.0 * (wi + wj) * along);
+            const double cx = g * o[0], cy = g * o[1], cz = g * o[2];
+            x[i] -= cx * wi; y[i] -= cy * wi; z[i] -= cz * wi;
+            x[j] += cx * wj; y[j] += cy * wj; z[j] += cz * wj;
+            vx[i] -= cx * wi * inv_dt; vy[i] -= cy * wi * inv_dt; vz[i] -= cz * wi * inv_dt;
+            vx[j] += cx * wj * inv_dt; vy[j] += cy * wj * inv_dt; vz[j] += cz * wj * inv_dt;
+        }
+        if (worst < tolerance) return 1;
+    }
+    return 0;
+}
+
+// RATTLE: removes the relative velocity along every constrained bond (|r_ij . v_ij| below `tolerance`, absolute).
+// virial_diag (may be null): diagonal of the constraint virial, -2 / (force_to_accel dt) * sum over corrections of
+// k r_a^2, counted for a pair when the atom with the lower global id is owned (index < n_local).
+int dsmd_oracle_rattle(long n_constraints, const long* atom1, const long* atom2, const double* x, const double* y,
+                       const double* z, double* vx, double* vy, double* vz, const double* mass, const int* gid, long n_local,
+                       const double L[3], const int periodic[3], double dt, double force_to_accel, int max_iterations,
+                       double tolerance, double* virial_diag) {
+    double w[3] = {0.0, 0.0, 0.0};
+    int converged = n_constraints == 0 ? 1 : 0;
+    const double prefactor = -2.0 / (force_to_accel * dt);
+    for (int sweep = 0; sweep < max_iterations && !converged; ++sweep) {
+        double worst = 0.0;
+        for (long c = 0; c < n_constraints; ++c) {
+            const long i = atom1[c], j = atom2[c];
+            double d[3] = {x[i] - x[j], y[i] - y[j], z[i] - z[j]};
+            min_image(d, L, periodic);
+            const double r2 = d[0] * d[0] + d[1] * d[1] + d[2] * d[2];
+            if (r2 < 1e-20) continue;
+            const double along = d[0] * (vx[i] - vx[j]) + d[1] * (vy[i] - vy[j]) + d[2] * (vz[i] - vz[j]);
+            worst = std::max(worst, std::fabs(along));
+            if (std::fabs(along) < tolerance) continue;
+            const double wi = 1.0 / mass[i], wj = 1.0 / mass[j];
+            const double k = along / ((wi + wj) * r2);
+            vx[i] -= k * wi * d[0]; vy[i] -= k * wi * d[1]; vz[i] -= k * wi * d[2];
+            vx[j] += k * wj * d[0]; vy[j] += k * wj * d[1]; vz[j] += k * wj * d[2];
+            const long lower = (gid ? gid[i] < gid[j] : i < j) ? i : j;
+            if (lower < n_local)
+                for (int a = 0; a < 3; ++a) w[a] += prefactor * k * d[a] * d[a];
+        }
+        if (worst < tolerance) converged = 1;
+    }
+    if (virial_diag)
+        for (int a = 0; a < 3; ++a) virial_diag[a] = w[a];
+    return converged;
+}
+
 }  // extern "C"

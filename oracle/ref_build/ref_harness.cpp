@@ -26,6 +26,7 @@
 #endif
 
 #include "reference_members.hpp"
+#include "constraint_solver.h"
 
 // ---- the C entry points ----------------------------------------------------------------------------
 
@@ -241,6 +242,48 @@ int dsmd_ref_compute_forces(void* h, int do_lj, int do_coulomb, int tensor, int 
         return 1;
     }
     return 0;
+}
+
+// The reference's CPU constraint solver (src/constraint_solver.cpp) on a system given as plain arrays: positions and
+// velocities are updated in place. which = 0: ConstraintSolver::apply_shake (pre = positions before the drift);
+// which = 1: apply_rattle (virial_out receives the diagonal of the constraint virial). Returns 1 when it converged.
+int dsmd_ref_constrain(int which, long n, long n_local, double* x, double* y, double* z, double* vx, double* vy, double* vz,
+                       const double* mass, const int* gid, const double L[3], const int periodic[3], long n_constraints,
+                       const long* atom1, const long* atom2, const double* distance, double dt, const double* pre_x,
+                       const double* pre_y, const double* pre_z, int max_iterations, double tolerance, double virial_out[3]) {
+    MDSystem system;
+    SimulationBox& b = system.box;
+    b.lx = L[0]; b.ly = L[1]; b.lz = L[2];
+    b.xlo = b.ylo = b.zlo = 0.0;
+    b.xhi = L[0]; b.yhi = L[1]; b.zhi = L[2];
+    b.periodic_x = periodic[0] != 0; b.periodic_y = periodic[1] != 0; b.periodic_z = periodic[2] != 0;
+    b.update_box_length();
+    ParticleData& p = system.particles;
+    p.reset_counts(static_cast<size_t>(n_local), static_cast<size_t>(n - n_local));
+    p.resize(static_cast<size_t>(n));
+    p.reset_counts(static_cast<size_t>(n_local), static_cast<size_t>(n - n_local));
+    for (long i = 0; i < n; ++i) {
+        p.x[i] = x[i]; p.y[i] = y[i]; p.z[i] = z[i];
+        p.vx[i] = vx[i]; p.vy[i] = vy[i]; p.vz[i] = vz[i];
+        p.mass[i] = mass[i];
+        p.global_id[i] = gid ? gid[i] : static_cast<int>(i);
+    }
+    for (long k = 0; k < n_constraints; ++k)
+        system.local_constraints_.push_back({static_cast<size_t>(atom1[k]), static_cast<size_t>(atom2[k]), distance[k]});
+    ConstraintSolver solver(max_iterations, tolerance, tolerance);
+    bool ok = false;
+    if (which == 0) {
+        std::vector<Real> px(pre_x, pre_x + n), py(pre_y, pre_y + n), pz(pre_z, pre_z + n);
+        ok = solver.apply_shake(system, dt, px, py, pz);
+    } else {
+        ok = solver.apply_rattle(system, dt);
+        if (virial_out) solver.get_virial_diag(virial_out);
+    }
+    for (long i = 0; i < n; ++i) {
+        x[i] = p.x[i]; y[i] = p.y[i]; z[i] = p.z[i];
+        vx[i] = p.vx[i]; vy[i] = p.vy[i]; vz[i] = p.vz[i];
+    }
+    return ok ? 1 : 0;
 }
 
 }  // extern "C"

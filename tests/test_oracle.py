@@ -241,3 +241,67 @@ def test_pair_checksum_is_the_same_in_numpy_and_torch():
     b2 = b.copy()
     b2[7] += 1
     assert checksum_numpy(a, b2) != want
+
+
+def _water_constraints(w):
+    """O-H1, O-H2, H1-H2 of every molecule at the lengths the generated (rigid) geometry has."""
+    out = []
+    for m in range(w.n // 3):
+        o, h1, h2 = 3 * m, 3 * m + 1, 3 * m + 2
+        for i, j in ((o, h1), (o, h2), (h1, h2)):
+            r = w.pos[i] - w.pos[j]
+            r -= w.box * np.round(r / w.box)
+            out.append((i, j, float(np.sqrt(r @ r))))
+    return out
+
+
+@pytest.mark.skipif(not co.ref_available(), reason="oracle/_ref is not built")
+def test_shake_and_rattle_match_the_reference_constraint_solver():
+    """Rigid water after an unconstrained drift: the oracle's SHAKE / RATTLE and the reference's own ConstraintSolver
+    (compiled in place) give the same positions, velocities and constraint virial; the constraints hold afterwards."""
+    w = syn.water_box(4, seed=11)
+    cons = _water_constraints(w)
+    rng = np.random.default_rng(5)
+    dt = 2.0
+    vel0 = rng.normal(0.0, 0.004, (w.n, 3)) / np.sqrt(w.mass)[:, None] * 4.0
+    pre = [np.ascontiguousarray(w.pos[:, k]) for k in range(3)]
+    drifted = [p + dt * vel0[:, k] for k, p in enumerate(pre)]
+
+    def copies():
+        return [c.copy() for c in drifted], [np.ascontiguousarray(vel0[:, k]).copy() for k in range(3)]
+
+    def violation(pos):
+        P = np.stack(pos, axis=1)
+        worst = 0.0
+        for i, j, d in cons:
+            r = P[i] - P[j]
+            r -= w.box * np.round(r / w.box)
+            worst = max(worst, abs(r @ r - d * d) / (d * d))
+        return worst
+
+    assert violation(pre) < 1e-12 and violation(drifted) > 1e-4
+    pos_o, vel_o = copies()
+    pos_r, vel_r = copies()
+    assert co.shake(cons, pos_o, vel_o, w.mass, pre, w.box, dt)
+    ok_ref, _ = co.ref_constrain("shake", cons, pos_r, vel_r, w.mass, w.box, dt, pre=pre)
+    assert ok_ref
+    for a, b in zip(pos_o + vel_o, pos_r + vel_r):
+        assert np.abs(a - b).max() < 1e-13
+    assert violation(pos_o) < 1e-8
+    momentum = sum((w.mass * v).sum() for v in vel_o), sum((w.mass * vel0[:, k]).sum() for k in range(3))
+    assert abs(momentum[0] - momentum[1]) < 1e-12
+    # the velocity part
+    ok, virial = co.rattle(cons, pos_o, vel_o, w.mass, w.box, dt, 4.184e-4)
+    ok_ref, virial_ref = co.ref_constrain("rattle", cons, pos_r, vel_r, w.mass, w.box, dt)
+    assert ok and ok_ref
+    for a, b in zip(vel_o, vel_r):
+        assert np.abs(a - b).max() < 1e-13
+    assert np.allclose(virial, virial_ref, rtol=1e-11, atol=0.0) and np.abs(virial).min() > 0.0
+    P, V = np.stack(pos_o, axis=1), np.stack(vel_o, axis=1)
+    for i, j, _ in cons:
+        r = P[i] - P[j]
+        r -= w.box * np.round(r / w.box)
+        assert abs(r @ (V[i] - V[j])) < 1e-8
+    # a solver that cannot converge says so
+    pos_x, vel_x = copies()
+    assert not co.shake(cons, pos_x, vel_x, w.mass, pre, w.box, dt, max_iterations=1)
