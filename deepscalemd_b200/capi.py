@@ -30,7 +30,8 @@ SYMBOLS = [
     "dsmd_forces_host", "dsmd_launch_count", "dsmd_fma_probe", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
     "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_edges_create", "dsmd_edges_destroy",
     "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
-    "dsmd_edges_result_compact", "dsmd_images_build", "dsmd_images_result", "dsmd_mark_receivers",
+    "dsmd_edges_result_compact", "dsmd_images_build", "dsmd_images_result", "dsmd_images_fold_forces",
+    "dsmd_virial_from_forces", "dsmd_mark_receivers",
     "dsmd_kinetic_energy_noalloc", "dsmd_nccl_unique_id", "dsmd_domain_create",
     "dsmd_domain_destroy", "dsmd_domain_last_error", "dsmd_domain_rebuild", "dsmd_domain_refresh", "dsmd_domain_run",
     "dsmd_domain_stats", "dsmd_domain_profile",
@@ -515,6 +516,20 @@ class EdgeBuilder:
         i32 = lambda p: _tensor_from_ptr(p.value, (N,), torch.int32, dev)
         return dict(x=f64(ptrs[0]), y=f64(ptrs[1]), z=f64(ptrs[2]), type=i32(ptrs[3]), owner=i32(ptrs[4]),
                     shift=(f64(ptrs[5]), f64(ptrs[6]), f64(ptrs[7])), n_all=N)
+
+    def fold_image_forces(self, fx, fy, fz, tx, ty, tz, n_out=-1, with_images=True, stream=None):
+        """target += model forces of the atoms and of their images (the images of the last images() call)."""
+        self._check(self.lib.dsmd_images_fold_forces(
+            self.h, c_void_p(fx.data_ptr()), c_void_p(fy.data_ptr()), c_void_p(fz.data_ptr()), c_int64(n_out),
+            c_int(1 if with_images else 0), c_void_p(tx.data_ptr()), c_void_p(ty.data_ptr()), c_void_p(tz.data_ptr()),
+            _stream_handle(stream)))
+
+    def virial_from_forces(self, x, y, z, fx, fy, fz, stream=None):
+        out = (c_double * 4)()
+        self._check(self.lib.dsmd_virial_from_forces(
+            self.h, *[c_void_p(t.data_ptr()) for t in (x, y, z, fx, fy, fz)], c_int64(x.numel()), out,
+            _stream_handle(stream)))
+        return np.array(list(out))
 
     def mark_receivers(self, x, y, z, lo, hi, reach, stream=None):
         import torch

@@ -281,72 +281,174 @@ __global__ void k_edge_fill_compact(Grid g, int n, int stride, const int* __rest
     }
 }
 
-// ---- periodic image atoms and receiver marking (what MLIPStep::prepare does around the edge build) ----------------------
-
-struct ImageSpec {
-    double box[3], origin[3], region_lo[3], region_hi[3];
-    int shells[3];
+// ---- periodic image atoms, their forces folded back, receiver marking (the work of MLIPStep::prepare / add_forces /
+// virial around the edge build, src/MLIPStep.cu:214-432) ----------------------------------------------------------------
+//
+// Semantics (what parity depends on): on an axis with images, a position is first wrapped into [from, from + period);
+// the image with lattice shift (sx, sy, sz) != 0, |s_a| <= reach[a], exists when p_a + s_a period_a lies inside
+// [keep_lo, keep_hi] on every axis with images; the images of an atom are numbered in the order sx, sy, sz ascending and
+// stored consecutively, atom after atom, behind the wrapped atoms.
+//
+// Along one axis the admissible shifts of an atom are a handful of values, found once and kept as a bit mask (bit
+// s + reach). The images of an atom are then the product of three bit sets minus the origin, so their count is a product
+// of population counts, and the k-th image is decoded from k by division - which lets the writing kernel run one thread
+// per OUTPUT slot (unit-stride stores of every output array) instead of one thread per atom with scattered stores.
+struct ImageLattice {
+    double period[3], from[3], keep_lo[3], keep_hi[3];
+    int reach[3];
 };
 
-__device__ __forceinline__ double wrap_from(double v, double origin, double box, int shells) {
-    return shells > 0 ? v - box * floor((v - origin) / box) : v;
+constexpr int kMaskBits = 17;   // shifts -8 .. 8
+
+__device__ __forceinline__ double image_coord(double p, int s, double period) {
+    return __dadd_rn(p, __dmul_rn(static_cast<double>(s), period));   // no contraction: rounds as p + s * period
 }
 
-// Visits the periodic images of (px, py, pz) that lie inside the region, in the fixed order sx, sy, sz ascending.
-template <class Emit>
-__device__ __forceinline__ void visit_images(const ImageSpec& s, double px, double py, double pz, Emit emit) {
-    for (int sx = -s.shells[0]; sx <= s.shells[0]; ++sx) {
-        const double qx = __dadd_rn(px, __dmul_rn(static_cast<double>(sx), s.box[0]));
-        if (s.shells[0] > 0 && (qx < s.region_lo[0] || qx > s.region_hi[0])) continue;
-        for (int sy = -s.shells[1]; sy <= s.shells[1]; ++sy) {
-            const double qy = __dadd_rn(py, __dmul_rn(static_cast<double>(sy), s.box[1]));
-            if (s.shells[1] > 0 && (qy < s.region_lo[1] || qy > s.region_hi[1])) continue;
-            for (int sz = -s.shells[2]; sz <= s.shells[2]; ++sz) {
-                if (sx == 0 && sy == 0 && sz == 0) continue;
-                const double qz = __dadd_rn(pz, __dmul_rn(static_cast<double>(sz), s.box[2]));
-                if (s.shells[2] > 0 && (qz < s.region_lo[2] || qz > s.region_hi[2])) continue;
-                emit(qx, qy, qz);
-            }
+__device__ __forceinline__ double wrapped_coord(const ImageLattice& L, int a, double v) {
+    return L.reach[a] > 0 ? v - L.period[a] * floor((v - L.from[a]) / L.period[a]) : v;
+}
+
+__device__ __forceinline__ unsigned axis_mask(const ImageLattice& L, int a, double p) {
+    const int r = L.reach[a];
+    if (r == 0) return 1u;
+    unsigned m = 0;
+    for (int s = -r; s <= r; ++s) {
+        const double q = image_coord(p, s, L.period[a]);
+        if (!(q < L.keep_lo[a] || q > L.keep_hi[a])) m |= 1u << (s + r);
+    }
+    return m;
+}
+
+__device__ __forceinline__ int nth_set_bit(unsigned mask, int n) {
+    int b = 0;
+    for (;; ++b)
+        if ((mask >> b) & 1u) {
+            if (n == 0) break;
+            --n;
         }
+    return b;
+}
+
+// Per atom: the three shift masks packed into one word, and how many images that makes.
+__global__ void k_image_masks(ImageLattice L, int n, const double* __restrict__ x, const double* __restrict__ y,
+                              const double* __restrict__ z, unsigned long long* __restrict__ masks,
+                              long long* __restrict__ counts) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const unsigned mx = axis_mask(L, 0, wrapped_coord(L, 0, x[i]));
+    const unsigned my = axis_mask(L, 1, wrapped_coord(L, 1, y[i]));
+    const unsigned mz = axis_mask(L, 2, wrapped_coord(L, 2, z[i]));
+    const bool self = ((mx >> L.reach[0]) & (my >> L.reach[1]) & (mz >> L.reach[2]) & 1u) != 0u;
+    masks[i] = static_cast<unsigned long long>(mx) | (static_cast<unsigned long long>(my) << kMaskBits) |
+               (static_cast<unsigned long long>(mz) << (2 * kMaskBits));
+    counts[i] = static_cast<long long>(__popc(mx)) * __popc(my) * __popc(mz) - (self ? 1 : 0);
+}
+
+// One thread per output slot: slots [0, n) are the wrapped atoms, slot n + m is image number m of the whole system, which
+// belongs to the last atom whose first image number is <= m.
+__global__ void k_image_fill(ImageLattice L, int n, long long n_images, const double* __restrict__ x,
+                             const double* __restrict__ y, const double* __restrict__ z, const int* __restrict__ type,
+                             const unsigned long long* __restrict__ masks, const long long* __restrict__ first_image,
+                             double* __restrict__ out_x, double* __restrict__ out_y, double* __restrict__ out_z,
+                             int* __restrict__ out_type, int* __restrict__ out_owner, double* __restrict__ off_x,
+                             double* __restrict__ off_y, double* __restrict__ off_z) {
+    const long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (t >= n + n_images) return;
+    int owner;
+    int s[3] = {0, 0, 0};
+    if (t < n) {
+        owner = static_cast<int>(t);
+    } else {
+        const long long m = t - n;
+        int lo = 0, hi = n;   // first_image is non-decreasing; atoms without images repeat their successor's value
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (first_image[mid] <= m) lo = mid; else hi = mid;
+        }
+        owner = lo;
+        const unsigned long long w = masks[owner];
+        const unsigned field = (1u << kMaskBits) - 1u;
+        const unsigned mx = static_cast<unsigned>(w) & field, my = static_cast<unsigned>(w >> kMaskBits) & field,
+                       mz = static_cast<unsigned>(w >> (2 * kMaskBits)) & field;
+        const int ny = __popc(my), nz = __popc(mz);
+        int k = static_cast<int>(m - first_image[owner]);
+        if ((mx >> L.reach[0]) & (my >> L.reach[1]) & (mz >> L.reach[2]) & 1u) {
+            // the origin sits in the product too: images at or behind its rank move up by one
+            const int rank = (__popc(mx & ((1u << L.reach[0]) - 1u)) * ny + __popc(my & ((1u << L.reach[1]) - 1u))) * nz +
+                             __popc(mz & ((1u << L.reach[2]) - 1u));
+            if (k >= rank) ++k;
+        }
+        s[0] = nth_set_bit(mx, k / (ny * nz)) - L.reach[0];
+        s[1] = nth_set_bit(my, (k / nz) % ny) - L.reach[1];
+        s[2] = nth_set_bit(mz, k % nz) - L.reach[2];
+    }
+    const double px = wrapped_coord(L, 0, x[owner]), py = wrapped_coord(L, 1, y[owner]), pz = wrapped_coord(L, 2, z[owner]);
+    const double qx = s[0] ? image_coord(px, s[0], L.period[0]) : px;
+    const double qy = s[1] ? image_coord(py, s[1], L.period[1]) : py;
+    const double qz = s[2] ? image_coord(pz, s[2], L.period[2]) : pz;
+    out_x[t] = qx; out_y[t] = qy; out_z[t] = qz;
+    out_type[t] = type ? type[owner] : 0;
+    out_owner[t] = owner;
+    off_x[t] = qx - px; off_y[t] = qy - py; off_z[t] = qz - pz;
+}
+
+// target[i] += f[i] + the forces on the images of atom i, added in slot order (MLIPStep::add_forces,
+// src/MLIPStep.cu:108-124, 373-381), for the first n_out of the n atoms. with_images == 0: the images were edge shifts,
+// not atoms the model saw, and carry no force.
+__global__ void k_image_fold(int n_out, int n, int with_images, const double* __restrict__ fx,
+                             const double* __restrict__ fy, const double* __restrict__ fz,
+                             const long long* __restrict__ first_image, const long long* __restrict__ counts,
+                             double* __restrict__ tx, double* __restrict__ ty, double* __restrict__ tz) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_out) return;
+    double sx = fx[i], sy = fy[i], sz = fz[i];
+    if (with_images) {
+        const long long begin = n + first_image[i], end = begin + counts[i];
+        for (long long k = begin; k < end; ++k) {
+            sx += fx[k];
+            sy += fy[k];
+            sz += fz[k];
+        }
+    }
+    tx[i] += sx;
+    ty[i] += sy;
+    tz[i] += sz;
+}
+
+// Sum over atoms of r . F and of its three diagonal terms (MLIPStep::virial / virial_diag, src/MLIPStep.cu:126-148,
+// 383-432): per-block sums in a fixed order, then one block adds the blocks' sums in a fixed order.
+__global__ void k_virial_partials(long long n, const double* __restrict__ x, const double* __restrict__ y,
+                                  const double* __restrict__ z, const double* __restrict__ fx,
+                                  const double* __restrict__ fy, const double* __restrict__ fz,
+                                  double* __restrict__ partials) {
+    __shared__ double sh[kThreads / 32][3];
+    double v[3] = {0.0, 0.0, 0.0};
+    for (long long p = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; p < n;
+         p += static_cast<long long>(gridDim.x) * blockDim.x) {
+        v[0] += x[p] * fx[p];
+        v[1] += y[p] * fy[p];
+        v[2] += z[p] * fz[p];
+    }
+    for (int a = 0; a < 3; ++a)
+        for (int o = 16; o > 0; o >>= 1) v[a] += __shfl_down_sync(0xffffffffu, v[a], o);
+    if ((threadIdx.x & 31) == 0)
+        for (int a = 0; a < 3; ++a) sh[threadIdx.x >> 5][a] = v[a];
+    __syncthreads();
+    if (threadIdx.x < 3) {
+        double sum = 0.0;
+        for (int w = 0; w < kThreads / 32; ++w) sum += sh[w][threadIdx.x];
+        partials[3 * blockIdx.x + threadIdx.x] = sum;
     }
 }
 
-__global__ void k_image_count(ImageSpec spec, int n, const double* __restrict__ x, const double* __restrict__ y,
-                              const double* __restrict__ z, long long* __restrict__ counts) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const double px = wrap_from(x[i], spec.origin[0], spec.box[0], spec.shells[0]);
-    const double py = wrap_from(y[i], spec.origin[1], spec.box[1], spec.shells[1]);
-    const double pz = wrap_from(z[i], spec.origin[2], spec.box[2], spec.shells[2]);
-    long long c = 0;
-    visit_images(spec, px, py, pz, [&](double, double, double) { ++c; });
-    counts[i] = c;
-}
-
-// The wrapped atoms in [0, n), their images behind them: those of atom i in slots n + offsets[i] ...
-__global__ void k_image_extend(ImageSpec spec, int n, const double* __restrict__ x, const double* __restrict__ y,
-                               const double* __restrict__ z, const int* __restrict__ type,
-                               const long long* __restrict__ offsets, double* __restrict__ ex, double* __restrict__ ey,
-                               double* __restrict__ ez, int* __restrict__ etype, int* __restrict__ eowner,
-                               double* __restrict__ esx, double* __restrict__ esy, double* __restrict__ esz) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const double px = wrap_from(x[i], spec.origin[0], spec.box[0], spec.shells[0]);
-    const double py = wrap_from(y[i], spec.origin[1], spec.box[1], spec.shells[1]);
-    const double pz = wrap_from(z[i], spec.origin[2], spec.box[2], spec.shells[2]);
-    const int t = type ? type[i] : 0;
-    ex[i] = px; ey[i] = py; ez[i] = pz;
-    etype[i] = t;
-    eowner[i] = i;
-    esx[i] = 0.0; esy[i] = 0.0; esz[i] = 0.0;
-    long long slot = n + offsets[i];
-    visit_images(spec, px, py, pz, [&](double qx, double qy, double qz) {
-        ex[slot] = qx; ey[slot] = qy; ez[slot] = qz;
-        etype[slot] = t;
-        eowner[slot] = i;
-        esx[slot] = qx - px; esy[slot] = qy - py; esz[slot] = qz - pz;
-        ++slot;
-    });
+__global__ void k_virial_total(int n_blocks, const double* __restrict__ partials, double* __restrict__ out) {
+    if (threadIdx.x < 3) {
+        double sum = 0.0;
+        for (int b = 0; b < n_blocks; ++b) sum += partials[3 * b + threadIdx.x];
+        out[1 + threadIdx.x] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out[0] = out[1] + out[2] + out[3];
 }
 
 __global__ void k_mark_receivers(int n, const double* __restrict__ x, const double* __restrict__ y,
@@ -396,6 +498,10 @@ struct dsmd_edges {
     // image atoms
     long long* img_counts = nullptr;        size_t cap_img_counts = 0;
     long long* img_offsets = nullptr;       size_t cap_img_offsets = 0;
+    unsigned long long* img_masks = nullptr; size_t cap_img_masks = 0;
+    int64_t n_img_src = 0;                  // atoms the last image build was given
+    double* virial_partials = nullptr;      // [3 * kVirialBlocks] + 4 results
+    double* h_virial = nullptr;             // pinned, 4 doubles
     double* ext[6] = {};                    size_t cap_ext[6] = {};     // x y z shift_x shift_y shift_z
     int* ext_type = nullptr;                size_t cap_ext_type = 0;
     int* ext_owner = nullptr;               size_t cap_ext_owner = 0;
@@ -587,7 +693,9 @@ void dsmd_edges_destroy(dsmd_edges* e) {
     cudaFree(e->pq); cudaFree(e->slot_of); cudaFree(e->cell_start); cudaFree(e->rows); cudaFree(e->counts);
     cudaFree(e->offsets); cudaFree(e->temp); cudaFree(e->edges); cudaFree(e->shift); cudaFree(e->c_src);
     cudaFree(e->c_dst); cudaFree(e->c_shift); cudaFree(e->c_vec); cudaFree(e->bounds); cudaFree(e->d_status);
-    cudaFree(e->img_counts); cudaFree(e->img_offsets); cudaFree(e->ext_type); cudaFree(e->ext_owner);
+    cudaFree(e->img_counts); cudaFree(e->img_offsets); cudaFree(e->img_masks); cudaFree(e->virial_partials);
+    if (e->h_virial) cudaFreeHost(e->h_virial);
+    cudaFree(e->ext_type); cudaFree(e->ext_owner);
     for (int k = 0; k < 6; ++k) cudaFree(e->ext[k]);
     cudaFreeHost(e->h_status);
     delete e;
@@ -710,39 +818,84 @@ int dsmd_images_build(dsmd_edges* e, const double* d_x, const double* d_y, const
     if (!d_x || !d_y || !d_z) return DSMD_ERR_INVALID;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     EDGE_CUDA(e, cudaSetDevice(e->device));
-    ImageSpec spec;
+    ImageLattice lattice;
     for (int a = 0; a < 3; ++a) {
         if (shells[a] < 0 || shells[a] > 8) return efail(e, DSMD_ERR_INVALID, "image shells must be in 0 .. 8");
         if (shells[a] > 0 && !(box[a] > 0.0)) return efail(e, DSMD_ERR_INVALID, "box length must be positive on an image axis");
-        spec.box[a] = box[a]; spec.origin[a] = origin[a];
-        spec.region_lo[a] = region_lo[a]; spec.region_hi[a] = region_hi[a];
-        spec.shells[a] = shells[a];
+        lattice.period[a] = box[a];
+        lattice.from[a] = origin[a];
+        lattice.keep_lo[a] = region_lo[a];
+        lattice.keep_hi[a] = region_hi[a];
+        lattice.reach[a] = shells[a];
     }
     const size_t un = static_cast<size_t>(n);
     EDGE_ALLOC(e, grow(e->img_counts, e->cap_img_counts, un));
     EDGE_ALLOC(e, grow(e->img_offsets, e->cap_img_offsets, un));
+    EDGE_ALLOC(e, grow(e->img_masks, e->cap_img_masks, un));
     size_t scan_bytes = 0;
     cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, e->img_counts, e->img_offsets, static_cast<int>(n), s);
     EDGE_ALLOC(e, grow(e->temp, e->cap_temp, scan_bytes));
-    k_image_count<<<blocks_for(n, kThreads), kThreads, 0, s>>>(spec, static_cast<int>(n), d_x, d_y, d_z, e->img_counts);
+    k_image_masks<<<blocks_for(n, kThreads), kThreads, 0, s>>>(lattice, static_cast<int>(n), d_x, d_y, d_z, e->img_masks,
+                                                              e->img_counts);
     EDGE_CUDA(e, cub::DeviceScan::ExclusiveSum(e->temp, scan_bytes, e->img_counts, e->img_offsets, static_cast<int>(n), s));
     // the image count comes to the host: the one synchronisation (MLIPStep::prepare does the same, src/MLIPStep.cu:254-255)
     long long last[2] = {0, 0};
     EDGE_CUDA(e, cudaMemcpyAsync(&last[0], e->img_offsets + (n - 1), sizeof(long long), cudaMemcpyDeviceToHost, s));
     EDGE_CUDA(e, cudaMemcpyAsync(&last[1], e->img_counts + (n - 1), sizeof(long long), cudaMemcpyDeviceToHost, s));
     EDGE_CUDA(e, cudaStreamSynchronize(s));
-    const int64_t total = n + last[0] + last[1];
+    const int64_t n_images = last[0] + last[1];
+    const int64_t total = n + n_images;
     if (total >= std::numeric_limits<int32_t>::max() / 2) return efail(e, DSMD_ERR_CAPACITY, "too many image atoms");
     for (int k = 0; k < 6; ++k) EDGE_ALLOC(e, grow(e->ext[k], e->cap_ext[k], static_cast<size_t>(total)));
     EDGE_ALLOC(e, grow(e->ext_type, e->cap_ext_type, static_cast<size_t>(total)));
     EDGE_ALLOC(e, grow(e->ext_owner, e->cap_ext_owner, static_cast<size_t>(total)));
-    k_image_extend<<<blocks_for(n, kThreads), kThreads, 0, s>>>(spec, static_cast<int>(n), d_x, d_y, d_z, d_type,
-                                                               e->img_offsets, e->ext[0], e->ext[1], e->ext[2],
-                                                               e->ext_type, e->ext_owner, e->ext[3], e->ext[4], e->ext[5]);
+    k_image_fill<<<blocks_for(total, kThreads), kThreads, 0, s>>>(lattice, static_cast<int>(n), n_images, d_x, d_y, d_z, d_type,
+                                                                 e->img_masks, e->img_offsets, e->ext[0], e->ext[1], e->ext[2],
+                                                                 e->ext_type, e->ext_owner, e->ext[3], e->ext[4], e->ext[5]);
     e->launches += 2;
     EDGE_CUDA(e, cudaGetLastError());
     e->n_ext = total;
+    e->n_img_src = n;
     *n_all = total;
+    return DSMD_OK;
+}
+
+int dsmd_images_fold_forces(dsmd_edges* e, const double* d_fx, const double* d_fy, const double* d_fz, int64_t n_out,
+                            int with_images, double* d_tx, double* d_ty, double* d_tz, void* stream) {
+    if (!e || !d_fx || !d_fy || !d_fz || !d_tx || !d_ty || !d_tz) return DSMD_ERR_INVALID;
+    if (e->n_img_src <= 0) return efail(e, DSMD_ERR_STATE, "no image atoms built");
+    if (n_out < 0 || n_out > e->n_img_src) n_out = e->n_img_src;
+    if (n_out == 0) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    k_image_fold<<<blocks_for(n_out, kThreads), kThreads, 0, s>>>(static_cast<int>(n_out), static_cast<int>(e->n_img_src),
+                                                                 with_images, d_fx, d_fy, d_fz, e->img_offsets, e->img_counts,
+                                                                 d_tx, d_ty, d_tz);
+    ++e->launches;
+    EDGE_CUDA(e, cudaGetLastError());
+    return DSMD_OK;
+}
+
+int dsmd_virial_from_forces(dsmd_edges* e, const double* d_x, const double* d_y, const double* d_z, const double* d_fx,
+                            const double* d_fy, const double* d_fz, int64_t n, double out[4], void* stream) {
+    if (!e || !out || n < 0 || (n > 0 && (!d_x || !d_y || !d_z || !d_fx || !d_fy || !d_fz))) return DSMD_ERR_INVALID;
+    out[0] = out[1] = out[2] = out[3] = 0.0;
+    if (n == 0) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EDGE_CUDA(e, cudaSetDevice(e->device));
+    constexpr int kVirialBlocks = 592;   // 4 per SM of a B200: a fixed grid keeps the order of the sum the same for every n
+    if (!e->virial_partials) {
+        EDGE_CUDA(e, cudaMalloc(&e->virial_partials, sizeof(double) * (3 * kVirialBlocks + 4)));
+        EDGE_CUDA(e, cudaMallocHost(&e->h_virial, sizeof(double) * 4));
+    }
+    const int blocks = static_cast<int>(std::min<int64_t>(kVirialBlocks, (n + kThreads - 1) / kThreads));
+    k_virial_partials<<<blocks, kThreads, 0, s>>>(n, d_x, d_y, d_z, d_fx, d_fy, d_fz, e->virial_partials);
+    k_virial_total<<<1, 32, 0, s>>>(blocks, e->virial_partials, e->virial_partials + 3 * kVirialBlocks);
+    e->launches += 2;
+    EDGE_CUDA(e, cudaGetLastError());
+    EDGE_CUDA(e, cudaMemcpyAsync(e->h_virial, e->virial_partials + 3 * kVirialBlocks, sizeof(double) * 4,
+                                 cudaMemcpyDeviceToHost, s));
+    EDGE_CUDA(e, cudaStreamSynchronize(s));
+    for (int k = 0; k < 4; ++k) out[k] = e->h_virial[k];
     return DSMD_OK;
 }
 

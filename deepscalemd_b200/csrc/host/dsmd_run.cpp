@@ -230,7 +230,7 @@ public:
         const std::string name = c_.output_prefix + "_" + std::to_string(step) + ".xyz";
         std::ofstream out(name);
         if (!out.is_open()) {
-            std::cerr << "Warning: Cannot open trajectory file " << name << std::endl;
+            std::cerr << "[trajectory] cannot write to " << name << std::endl;
             return;
         }
         out << n << "\n";
@@ -255,7 +255,7 @@ public:
         if (nose_hoover_) r.thermostat_state = {xi_};
         download(r);
         if (write_restart(c_.restart_output, r)) std::cout << "[restart] wrote " << c_.restart_output << " at step " << step << std::endl;
-        else std::cerr << "[restart] WARNING: could not write " << c_.restart_output << " at step " << step << std::endl;
+        else std::cerr << "[restart] failed to write " << c_.restart_output << " at step " << step << std::endl;
     }
 
     bool nose_hoover_ = false;

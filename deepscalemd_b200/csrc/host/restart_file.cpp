@@ -1,8 +1,8 @@
 #include "restart_file.hpp"
 
+#include <cstdio>
 #include <cstring>
 #include <filesystem>
-#include <fstream>
 #include <limits>
 #include <stdexcept>
 
@@ -10,115 +10,142 @@ namespace dsmd::host {
 
 namespace {
 
-const char kBegin[8] = {'D', 'S', 'M', 'D', 'R', 'S', 'T', '1'};
-const char kEnd[8] = {'D', 'S', 'M', 'D', 'E', 'N', 'D', '1'};
+constexpr char kHead[] = "DSMDRST1";
+constexpr char kTail[] = "DSMDEND1";
+constexpr size_t kTag = 8;
+constexpr int32_t kLongestName = 4096;    // thermostat / barostat names
+constexpr int32_t kMostStateValues = 1024;
 
-struct Reader {
-    std::ifstream in;
-    std::string path;
+// The file is small next to device memory traffic (48 bytes per atom): it is read whole, then taken apart from a byte
+// image with a moving offset, and written the same way in reverse.
+class ByteImage {
+public:
+    ByteImage(std::vector<unsigned char> bytes, std::string name) : bytes_(std::move(bytes)), name_(std::move(name)) {}
+
+    void take(void* into, size_t count, const char* what) {
+        if (count > bytes_.size() - at_) {
+            throw std::runtime_error("restart file " + name_ + ": truncated inside " + what + " (" + std::to_string(bytes_.size()) +
+                                     " bytes on disk)");
+        }
+        std::memcpy(into, bytes_.data() + at_, count);
+        at_ += count;
+    }
     template <class T>
-    T value() {
-        T v{};
-        in.read(reinterpret_cast<char*>(&v), sizeof(T));
-        if (!in) throw std::runtime_error("restart file " + path + " ends early (truncated or not a dsMD restart file)");
+    T scalar(const char* what) {
+        T v;
+        take(&v, sizeof(T), what);
         return v;
     }
-    std::string text() {
-        const int32_t length = value<int32_t>();
-        if (length < 0 || length > 4096) throw std::runtime_error("restart file " + path + " is damaged (bad string length)");
-        std::string s(static_cast<size_t>(length), '\0');
-        if (length > 0) in.read(&s[0], length);
-        if (!in) throw std::runtime_error("restart file " + path + " ends early");
+    std::string name_field(const char* what) {
+        const int32_t length = scalar<int32_t>(what);
+        if (length < 0 || length > kLongestName) throw std::runtime_error(bad_length(what, length));
+        std::string s(static_cast<size_t>(length), ' ');
+        take(s.data(), s.size(), what);
         return s;
     }
-    std::vector<double> reals() {
-        const int32_t count = value<int32_t>();
-        if (count < 0 || count > 1024) throw std::runtime_error("restart file " + path + " is damaged (bad state length)");
+    std::vector<double> state_field(const char* what) {
+        const int32_t count = scalar<int32_t>(what);
+        if (count < 0 || count > kMostStateValues) throw std::runtime_error(bad_length(what, count));
         std::vector<double> v(static_cast<size_t>(count));
-        for (double& x : v) x = value<double>();
+        take(v.data(), v.size() * sizeof(double), what);
         return v;
     }
-    void array(std::vector<double>& v) {
-        in.read(reinterpret_cast<char*>(v.data()), static_cast<std::streamsize>(v.size() * sizeof(double)));
-        if (!in) throw std::runtime_error("restart file " + path + " ends early (truncated)");
+    bool tag_is(const char* tag) {
+        if (kTag > bytes_.size() - at_) return false;
+        const bool same = std::memcmp(bytes_.data() + at_, tag, kTag) == 0;
+        at_ += kTag;
+        return same;
     }
+
+private:
+    std::string bad_length(const char* what, int32_t got) const {
+        return "restart file " + name_ + ": the length stored for " + what + " (" + std::to_string(got) + ") is not plausible";
+    }
+    std::vector<unsigned char> bytes_;
+    std::string name_;
+    size_t at_ = 0;
 };
 
+std::vector<unsigned char> slurp(const std::string& path) {
+    std::FILE* f = std::fopen(path.c_str(), "rb");
+    if (!f) throw std::runtime_error("cannot open restart file " + path);
+    std::vector<unsigned char> bytes;
+    unsigned char chunk[1 << 16];
+    size_t got;
+    while ((got = std::fread(chunk, 1, sizeof(chunk), f)) > 0) bytes.insert(bytes.end(), chunk, chunk + got);
+    std::fclose(f);
+    return bytes;
+}
+
+void append(std::vector<unsigned char>& image, const void* from, size_t count) {
+    const unsigned char* p = static_cast<const unsigned char*>(from);
+    image.insert(image.end(), p, p + count);
+}
+
 template <class T>
-void put(std::ofstream& out, const T& v) {
-    out.write(reinterpret_cast<const char*>(&v), sizeof(T));
-}
-
-void put_text(std::ofstream& out, const std::string& s) {
-    put<int32_t>(out, static_cast<int32_t>(s.size()));
-    out.write(s.data(), static_cast<std::streamsize>(s.size()));
-}
-
-void put_reals(std::ofstream& out, const std::vector<double>& v) {
-    put<int32_t>(out, static_cast<int32_t>(v.size()));
-    for (double x : v) put<double>(out, x);
+void append_scalar(std::vector<unsigned char>& image, T v) {
+    append(image, &v, sizeof(T));
 }
 
 }  // namespace
 
 RestartState read_restart(const std::string& path) {
-    Reader r;
-    r.path = path;
-    r.in.open(path, std::ios::binary);
-    if (!r.in.is_open()) throw std::runtime_error("cannot open restart file " + path);
-    char magic[8];
-    r.in.read(magic, 8);
-    if (!r.in || std::memcmp(magic, kBegin, 8) != 0) throw std::runtime_error(path + " is not a dsMD restart file (DSMDRST1)");
+    ByteImage file(slurp(path), path);
+    if (!file.tag_is(kHead)) throw std::runtime_error(path + " is not a dsMD restart file (no DSMDRST1 tag)");
     RestartState s;
-    s.step = r.value<int64_t>();
-    const int64_t atoms = r.value<int64_t>();
-    s.timestep = r.value<double>();
-    for (double& b : s.box) b = r.value<double>();
-    for (int32_t& p : s.periodic) p = r.value<int32_t>();
-    s.thermostat = r.text();
-    s.thermostat_state = r.reals();
-    s.barostat = r.text();
-    s.barostat_state = r.reals();
-    if (atoms <= 0 || atoms >= (1ll << 30)) throw std::runtime_error("restart file " + path + " has an invalid atom count");
+    s.step = file.scalar<int64_t>("the step number");
+    const int64_t atoms = file.scalar<int64_t>("the atom count");
+    s.timestep = file.scalar<double>("the time step");
+    file.take(s.box, sizeof(s.box), "the box");
+    file.take(s.periodic, sizeof(s.periodic), "the periodic flags");
+    s.thermostat = file.name_field("the thermostat name");
+    s.thermostat_state = file.state_field("the thermostat state");
+    s.barostat = file.name_field("the barostat name");
+    s.barostat_state = file.state_field("the barostat state");
+    if (atoms <= 0 || atoms >= (1ll << 30)) throw std::runtime_error("restart file " + path + ": atom count " + std::to_string(atoms) + " out of range");
     if (s.step < 0 || s.step > static_cast<int64_t>(std::numeric_limits<int>::max()))
-        throw std::runtime_error("restart file " + path + " has an invalid step " + std::to_string(s.step));
-    if (!(s.box[0] > 0.0 && s.box[1] > 0.0 && s.box[2] > 0.0)) throw std::runtime_error("restart file " + path + " has an invalid box");
-    for (std::vector<double>* a : {&s.x, &s.y, &s.z, &s.vx, &s.vy, &s.vz}) {
-        a->resize(static_cast<size_t>(atoms));
-        r.array(*a);
+        throw std::runtime_error("restart file " + path + ": step " + std::to_string(s.step) + " out of range");
+    if (!(s.box[0] > 0.0 && s.box[1] > 0.0 && s.box[2] > 0.0)) throw std::runtime_error("restart file " + path + ": box lengths must be positive");
+    std::vector<double>* arrays[6] = {&s.x, &s.y, &s.z, &s.vx, &s.vy, &s.vz};
+    const char* names[6] = {"x", "y", "z", "vx", "vy", "vz"};
+    for (int k = 0; k < 6; ++k) {
+        arrays[k]->resize(static_cast<size_t>(atoms));
+        file.take(arrays[k]->data(), arrays[k]->size() * sizeof(double), names[k]);
     }
-    char end[8];
-    r.in.read(end, 8);
-    if (!r.in || std::memcmp(end, kEnd, 8) != 0) throw std::runtime_error("restart file " + path + " is truncated (no end marker)");
+    if (!file.tag_is(kTail)) throw std::runtime_error("restart file " + path + ": truncated (the closing DSMDEND1 tag is missing)");
     return s;
 }
 
 bool write_restart(const std::string& path, const RestartState& s) {
-    const std::string temporary = path + ".tmp";
-    bool ok = false;
-    {
-        std::ofstream out(temporary, std::ios::binary | std::ios::trunc);
-        if (out.is_open()) {
-            out.write(kBegin, 8);
-            put<int64_t>(out, s.step);
-            put<int64_t>(out, static_cast<int64_t>(s.x.size()));
-            put<double>(out, s.timestep);
-            for (double b : s.box) put<double>(out, b);
-            for (int32_t p : s.periodic) put<int32_t>(out, p ? 1 : 0);
-            put_text(out, s.thermostat);
-            put_reals(out, s.thermostat_state);
-            put_text(out, s.barostat);
-            put_reals(out, s.barostat_state);
-            for (const std::vector<double>* a : {&s.x, &s.y, &s.z, &s.vx, &s.vy, &s.vz})
-                out.write(reinterpret_cast<const char*>(a->data()), static_cast<std::streamsize>(a->size() * sizeof(double)));
-            out.write(kEnd, 8);
-            out.flush();
-            ok = static_cast<bool>(out);
-        }
+    std::vector<unsigned char> image;
+    image.reserve(128 + s.thermostat.size() + s.barostat.size() + 8 * (s.thermostat_state.size() + s.barostat_state.size()) +
+                  48 * s.x.size());
+    append(image, kHead, kTag);
+    append_scalar<int64_t>(image, s.step);
+    append_scalar<int64_t>(image, static_cast<int64_t>(s.x.size()));
+    append_scalar<double>(image, s.timestep);
+    append(image, s.box, sizeof(s.box));
+    for (int32_t flag : s.periodic) append_scalar<int32_t>(image, flag ? 1 : 0);
+    const std::string* names[2] = {&s.thermostat, &s.barostat};
+    const std::vector<double>* states[2] = {&s.thermostat_state, &s.barostat_state};
+    for (int k = 0; k < 2; ++k) {
+        append_scalar<int32_t>(image, static_cast<int32_t>(names[k]->size()));
+        append(image, names[k]->data(), names[k]->size());
+        append_scalar<int32_t>(image, static_cast<int32_t>(states[k]->size()));
+        append(image, states[k]->data(), states[k]->size() * sizeof(double));
     }
+    for (const std::vector<double>* a : {&s.x, &s.y, &s.z, &s.vx, &s.vy, &s.vz}) append(image, a->data(), a->size() * sizeof(double));
+    append(image, kTail, kTag);
+
+    const std::string scratch = path + ".tmp";
+    std::FILE* f = std::fopen(scratch.c_str(), "wb");
+    if (!f) return false;
+    const bool written = std::fwrite(image.data(), 1, image.size(), f) == image.size();
+    const bool closed = std::fclose(f) == 0;
+    if (!written || !closed) return false;
     std::error_code ec;
-    if (ok) std::filesystem::rename(temporary, path, ec);
-    return ok && !ec;
+    std::filesystem::rename(scratch, path, ec);
+    return !ec;
 }
 
 }  // namespace dsmd::host

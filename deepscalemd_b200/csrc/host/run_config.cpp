@@ -83,7 +83,7 @@ const std::string& RunConfig::text(const std::string& key) const {
 
 std::map<std::string, std::string> read_manifest(const std::string& path) {
     std::ifstream file(path);
-    if (!file) throw std::runtime_error("Cannot open dsMD_input manifest: " + path);
+    if (!file) throw std::runtime_error("input system manifest " + path + " cannot be opened");
     std::map<std::string, std::string> values;
     std::string line;
     while (std::getline(file, line)) {
@@ -97,14 +97,14 @@ std::map<std::string, std::string> read_manifest(const std::string& path) {
             value = value.substr(1, value.size() - 2);
         if (!key.empty() && !value.empty()) values[key] = value;
     }
-    if (values["schema_version"] != "1") throw std::runtime_error("dsMD_input manifest schema_version must be 1");
-    if (values["format"] != "dsMD_input") throw std::runtime_error("dsMD_input manifest format must be dsMD_input");
+    if (values["schema_version"] != "1") throw std::runtime_error("input system manifest " + path + ": schema_version must be 1");
+    if (values["format"] != "dsMD_input") throw std::runtime_error("input system manifest " + path + ": format must be dsMD_input");
     return values;
 }
 
 RunConfig read_run_config(const std::string& path) {
     std::ifstream file(path);
-    if (!file.is_open()) throw std::runtime_error("Cannot open config file: " + path);
+    if (!file.is_open()) throw std::runtime_error("run description " + path + " cannot be opened");
     RunConfig c;
     bool have_coordinates = false, have_temperature = false, have_timestep = false, have_steps = false;
     std::string section, subsection;
@@ -212,7 +212,7 @@ RunConfig read_run_config(const std::string& path) {
     if (!have_timestep) missing.push_back("timestep");
     if (!have_steps) missing.push_back("total_steps");
     if (!missing.empty()) {
-        std::string message = "Missing required configuration parameters: ";
+        std::string message = "the run description lacks required keys: ";
         for (size_t k = 0; k < missing.size(); ++k) message += (k ? ", " : "") + missing[k];
         throw std::runtime_error(message);
     }
@@ -220,11 +220,10 @@ RunConfig read_run_config(const std::string& path) {
     // force_calculation.mode: a comma list of builtin / mlip
     const auto modes = comma_list(c.force_mode);
     if (modes.empty())
-        throw std::runtime_error("Invalid force_calculation.mode: '" + c.force_mode + "'. Specify one or more of: builtin, mlip");
+        throw std::runtime_error("force_calculation.mode '" + c.force_mode + "' names no force provider (builtin, mlip, or both separated by a comma)");
     for (const auto& m : modes)
         if (m != "builtin" && m != "mlip")
-            throw std::runtime_error("Invalid force_calculation.mode component: '" + m +
-                                     "'. Supported components are: builtin, mlip");
+            throw std::runtime_error("force_calculation.mode: '" + m + "' is not a force provider (builtin and mlip are)");
 
     // which built-in terms: a "type" list switches every term it does not name off; without it the enable_* keys apply
     // (only the exact text "true" switches a term on), default all on (src/force_manager.cpp:88-160)
@@ -252,8 +251,7 @@ RunConfig read_run_config(const std::string& path) {
         std::string formats = trimmed(c.trajectory_format) == "both" ? "xyz,dump" : c.trajectory_format;
         for (const auto& f : comma_list(formats))
             if (f != "xyz" && f != "dump" && f != "dcd" && f != "bp" && f != "h5md")
-                throw std::runtime_error("Invalid trajectory_format component: '" + f +
-                                         "'. Supported components are: xyz, dump, dcd, bp, h5md (or legacy 'both')");
+                throw std::runtime_error("trajectory_format: '" + f + "' is not a trajectory format (xyz, dump, dcd, bp, h5md; 'both' = xyz,dump)");
     }
     if (c.total_steps <= 0) throw std::runtime_error("total_steps must be positive");
     if (c.target_temperature < 0.0) throw std::runtime_error("target_temperature must not be negative");

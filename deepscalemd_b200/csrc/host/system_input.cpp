@@ -44,7 +44,7 @@ void require_atom_count(const SystemInput& s, size_t topology_atoms, const std::
 void read_xyz(const std::string& raw_path, const double box[3], SystemInput& out) {
     const std::string path = clean_file_name(raw_path);
     std::ifstream file(path);
-    if (!file.is_open()) throw std::runtime_error("Cannot open coordinate file: " + path);
+    if (!file.is_open()) throw std::runtime_error("coordinate file " + path + " cannot be opened");
     std::string line;
     std::getline(file, line);
     long long declared = 0;
@@ -75,8 +75,8 @@ void read_xyz(const std::string& raw_path, const double box[3], SystemInput& out
         }
     }
     if (read != n)
-        throw std::runtime_error("XYZ atom-count mismatch: header declares " + std::to_string(n) + " but " +
-                                 std::to_string(read) + " coordinate records were read");
+        throw std::runtime_error("coordinate file " + path + ": line 1 announces " + std::to_string(n) + " atoms, " + std::to_string(read) +
+                                 " usable 'element x y z' lines follow");
     // recentre: mean position -> box centre (plain sums in file order, as the reference adds them)
     double mean[3] = {0.0, 0.0, 0.0};
     for (size_t i = 0; i < n; ++i) { mean[0] += out.x[i]; mean[1] += out.y[i]; mean[2] += out.z[i]; }
@@ -92,7 +92,7 @@ void read_xyz(const std::string& raw_path, const double box[3], SystemInput& out
 void apply_legacy_topology(const std::string& raw_path, SystemInput& s) {
     const std::string path = clean_file_name(raw_path);
     std::ifstream file(path);
-    if (!file.is_open()) throw std::runtime_error("Failed to load topology file: " + path);
+    if (!file.is_open()) throw std::runtime_error("topology file " + path + " cannot be opened");
     struct TypeRow { double mass, charge, sigma, epsilon; };
     std::map<std::string, TypeRow> rows;
     std::vector<std::string> atom_type_name;   // by 0-based atom id; "" = never named
@@ -132,7 +132,7 @@ void apply_legacy_topology(const std::string& raw_path, SystemInput& s) {
         auto found = id_of.find(name);
         if (found == id_of.end()) {
             const auto row = rows.find(name);
-            if (row == rows.end()) throw std::runtime_error("Atom type not found: " + name);
+            if (row == rows.end()) throw std::runtime_error("topology " + path + ": [ atoms ] uses type '" + name + "', which [ atomtypes ] does not define");
             found = id_of.emplace(name, static_cast<int>(id_of.size())).first;
             s.type_name.push_back(name);
             by_id.push_back(row->second);
@@ -162,7 +162,7 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
 
     // ---- parameter file ------------------------------------------------------------------------------------------------
     std::ifstream parameters(parameter_path);
-    if (!parameters) throw std::runtime_error("cannot open parameter file: " + parameter_path);
+    if (!parameters) throw std::runtime_error("parameter file " + parameter_path + " cannot be opened");
     std::map<int, std::string> type_names;
     struct PairRow { int i, j; double sigma, epsilon; };
     std::vector<PairRow> pair_rows;
@@ -181,11 +181,11 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
             throw std::runtime_error(parameter_path + ":" + std::to_string(line_number) + ": " + what);
         };
         if (section == "meta") {
-            if (t.size() < 2) fail("metadata requires key and value");
-            if (t[0] == "schema_version" && t[1] != "1") fail("unsupported schema_version '" + t[1] + "'");
-            if (t[0] == "length_unit" && t[1] != "angstrom") fail("length_unit must be angstrom");
-            if (t[0] == "energy_unit" && t[1] != "kcal_per_mol") fail("energy_unit must be kcal_per_mol");
-            if (t[0] == "charge_unit" && t[1] != "elementary_charge") fail("charge_unit must be elementary_charge");
+            if (t.size() < 2) fail("a [meta] line is 'key value'");
+            if (t[0] == "schema_version" && t[1] != "1") fail("schema_version " + t[1] + " is not understood (this reader knows version 1)");
+            if (t[0] == "length_unit" && t[1] != "angstrom") fail("lengths must be given in angstrom (length_unit)");
+            if (t[0] == "energy_unit" && t[1] != "kcal_per_mol") fail("energies must be given in kcal_per_mol (energy_unit)");
+            if (t[0] == "charge_unit" && t[1] != "elementary_charge") fail("charges must be given in elementary_charge (charge_unit)");
         } else if (section == "nonbonded") {
             if (t[0] == "component") {
                 bool mie = false;
@@ -196,63 +196,63 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
                     if (w.rfind("m=", 0) == 0) m = to_int(w.substr(2));
                 }
                 if (mie) {
-                    if (mie_seen) fail("only one Mie nonbonded component is supported");
-                    if (!((n == 12 && m == 6) || (n == 9 && m == 6))) fail("supported Mie exponents are (12,6) and SPICA (9,6)");
+                    if (mie_seen) fail("a second Mie component: one pair potential per system");
+                    if (!((n == 12 && m == 6) || (n == 9 && m == 6))) fail("Mie exponents n=" + std::to_string(n) + " m=" + std::to_string(m) + ": only 12-6 and 9-6 exist here");
                     s.mie_n = n;
                     s.mie_m = m;
                     mie_seen = true;
                 }
             }
         } else if (section == "atom_types") {
-            if (t.size() < 2) fail("atom type requires: type_id name");
+            if (t.size() < 2) fail("an [atom_types] line is 'id name'");
             const int id = to_int(t[0]);
-            if (id < 0 || !type_names.emplace(id, t[1]).second) fail("invalid or duplicate atom type ID");
+            if (id < 0 || !type_names.emplace(id, t[1]).second) fail("atom type id " + t[0] + " is negative or given twice");
         } else if (section == "pair_parameters") {
-            if (t.size() < 5) fail("pair parameter requires: component type_i type_j sigma epsilon");
+            if (t.size() < 5) fail("a [pair_parameters] line has five fields: component, two type ids, sigma, epsilon");
             pair_rows.push_back({to_int(t[1]), to_int(t[2]), to_real(t[3]), to_real(t[4])});
         } else if (section == "bond_parameters") {
-            if (t.size() < 4 || t[1] != "harmonic") fail("only 'param_id harmonic k r0' bond parameters are supported");
-            if (!bond_ids.emplace(t[0], true).second) fail("duplicate bond parameter ID '" + t[0] + "'");
+            if (t.size() < 4 || t[1] != "harmonic") fail("bond parameters must read 'id harmonic k r0'");
+            if (!bond_ids.emplace(t[0], true).second) fail("bond parameter id " + t[0] + " is given twice");
         } else if (section == "angle_parameters") {
-            if (t.size() < 4 || t[1] != "harmonic") fail("only 'param_id harmonic k theta0_deg' angle parameters are supported");
-            if (!angle_ids.emplace(t[0], true).second) fail("duplicate angle parameter ID '" + t[0] + "'");
+            if (t.size() < 4 || t[1] != "harmonic") fail("angle parameters must read 'id harmonic k theta0' (degrees)");
+            if (!angle_ids.emplace(t[0], true).second) fail("angle parameter id " + t[0] + " is given twice");
         } else if (section == "torsion_parameters") {
-            if (t.size() < 5 || t[1] != "periodic") fail("only 'param_id periodic k phase_deg multiplicity' torsions are supported");
-            if (!torsion_ids.emplace(t[0], true).second) fail("duplicate torsion parameter ID '" + t[0] + "'");
+            if (t.size() < 5 || t[1] != "periodic") fail("torsion parameters must read 'id periodic k phase multiplicity' (phase in degrees)");
+            if (!torsion_ids.emplace(t[0], true).second) fail("torsion parameter id " + t[0] + " is given twice");
         } else if (section == "improper_parameters") {
             if (t.size() < 4 || (t[1] != "periodic" && t[1] != "harmonic"))
-                fail("improper requires either 'param_id periodic k phase_deg multiplicity' or 'param_id harmonic k phi0_deg'");
-            if (!improper_ids.emplace(t[0], true).second) fail("duplicate improper parameter ID '" + t[0] + "'");
+                fail("improper parameters must read 'id periodic k phase multiplicity' or 'id harmonic k phi0' (degrees)");
+            if (!improper_ids.emplace(t[0], true).second) fail("improper parameter id " + t[0] + " is given twice");
         } else if (section == "special_pair_parameters") {
-            if (t.size() < 3) fail("special pair parameter requires: param_id sigma epsilon");
+            if (t.size() < 3) fail("a [special_pair_parameters] line is 'id sigma epsilon'");
         } else {
             fail("unknown parameter section [" + section + "]");
         }
     }
-    if (!mie_seen) throw std::runtime_error("parameter file has no supported Mie nonbonded component");
-    if (type_names.empty()) throw std::runtime_error("parameter file has no [atom_types]");
+    if (!mie_seen) throw std::runtime_error("parameter file " + parameter_path + ": [nonbonded] names no Mie component");
+    if (type_names.empty()) throw std::runtime_error("parameter file " + parameter_path + ": the [atom_types] section is missing or empty");
     const int nt = type_names.rbegin()->first + 1;
-    if (static_cast<int>(type_names.size()) != nt) throw std::runtime_error("atom type IDs must be contiguous and start at zero");
+    if (static_cast<int>(type_names.size()) != nt) throw std::runtime_error("parameter file " + parameter_path + ": atom type ids must run 0, 1, 2, ... without gaps");
     std::vector<double> sig(static_cast<size_t>(nt) * nt, nan), eps(sig.size(), nan);
     for (const PairRow& r : pair_rows) {
-        if (r.i < 0 || r.j < 0 || r.i >= nt || r.j >= nt) throw std::runtime_error("pair parameter references an invalid atom type ID");
+        if (r.i < 0 || r.j < 0 || r.i >= nt || r.j >= nt) throw std::runtime_error("[pair_parameters] names the type pair " + std::to_string(r.i) + "," + std::to_string(r.j) + ": invalid atom type ID");
         if (!std::isfinite(r.sigma) || !std::isfinite(r.epsilon) || r.sigma < 0.0 || r.epsilon < 0.0)
-            throw std::runtime_error("pair sigma and epsilon must be finite and non-negative");
+            throw std::runtime_error("[pair_parameters] " + std::to_string(r.i) + "," + std::to_string(r.j) + ": sigma and epsilon must be finite numbers >= 0");
         const size_t ab = static_cast<size_t>(r.i) * nt + r.j, ba = static_cast<size_t>(r.j) * nt + r.i;
         if (std::isfinite(sig[ab]) || std::isfinite(eps[ab]))
-            throw std::runtime_error("duplicate pair parameter for type IDs " + std::to_string(r.i) + "," + std::to_string(r.j));
+            throw std::runtime_error("[pair_parameters] gives the type pair " + std::to_string(r.i) + "," + std::to_string(r.j) + " twice");
         sig[ab] = sig[ba] = r.sigma;
         eps[ab] = eps[ba] = r.epsilon;
     }
     for (int a = 0; a < nt; ++a)
         for (int b = 0; b < nt; ++b)
             if (!std::isfinite(sig[static_cast<size_t>(a) * nt + b]) || !std::isfinite(eps[static_cast<size_t>(a) * nt + b]))
-                throw std::runtime_error("pair parameter matrix is incomplete for type IDs " + std::to_string(a) + "," +
-                                         std::to_string(b));
+                throw std::runtime_error("[pair_parameters] has no line for the type pair " + std::to_string(a) + "," + std::to_string(b) +
+                                         " (every pair of types needs one)");
 
     // ---- topology file -------------------------------------------------------------------------------------------------
     std::ifstream topology(topology_path);
-    if (!topology) throw std::runtime_error("cannot open topology file: " + topology_path);
+    if (!topology) throw std::runtime_error("topology file " + topology_path + " cannot be opened");
     section.clear();
     line_number = 0;
     long long expected_atoms = -1;
@@ -273,73 +273,73 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
             throw std::runtime_error(topology_path + ":" + std::to_string(line_number) + ": " + what);
         };
         if (section == "meta") {
-            if (t.size() < 2) fail("metadata requires key and value");
-            if (t[0] == "schema_version" && t[1] != "1") fail("unsupported schema_version '" + t[1] + "'");
+            if (t.size() < 2) fail("a [meta] line is 'key value'");
+            if (t[0] == "schema_version" && t[1] != "1") fail("schema_version " + t[1] + " is not understood (this reader knows version 1)");
             if (t[0] == "atom_count") {
                 expected_atoms = std::stoll(t[1]);
-                if (expected_atoms <= 0) fail("atom_count must be positive");
+                if (expected_atoms <= 0) fail("atom_count " + t[1] + ": must be at least 1");
             }
         } else if (section == "atoms") {
-            if (t.size() < 5) fail("atom requires: atom_id element type_id mass charge [molecule_id residue_id]");
-            if (to_int(t[0]) != static_cast<int>(type.size())) fail("atom IDs must be contiguous and start at zero");
+            if (t.size() < 5) fail("an [atoms] line starts with five fields: id, element, type id, mass, charge");
+            if (to_int(t[0]) != static_cast<int>(type.size())) fail("atom ids must run 0, 1, 2, ... in file order (expected " + std::to_string(type.size()) + ")");
             const int type_id = to_int(t[2]);
-            if (type_names.find(type_id) == type_names.end()) fail("atom references an invalid type ID");
+            if (type_names.find(type_id) == type_names.end()) fail("type id " + t[2] + " is not in the parameter file's [atom_types]");
             const double m = to_real(t[3]), q = to_real(t[4]);
             if (!std::isfinite(m) || m <= 0.0 || !std::isfinite(q))
-                fail("atom mass must be finite and positive, and charge must be finite");
+                fail("mass must be a finite number > 0 and charge a finite number");
             type.push_back(type_id);
             mass.push_back(m);
             charge.push_back(q);
         } else if (section == "bonds") {
-            if (t.size() < 3) fail("bond requires: atom_i atom_j bond_param_id");
-            if (!bond_ids.count(t[2])) fail("bond references an invalid parameter ID");
+            if (t.size() < 3) fail("a [bonds] line is two atom ids and a bond parameter id");
+            if (!bond_ids.count(t[2])) fail("bond parameter id " + t[2] + " is not defined in the parameter file");
             bond_ends.push_back({to_int(t[0]), to_int(t[1])});
         } else if (section == "angles") {
-            if (t.size() < 4) fail("angle requires: atom_i atom_j atom_k angle_param_id");
-            if (!angle_ids.count(t[3])) fail("angle references an invalid parameter ID");
+            if (t.size() < 4) fail("an [angles] line is three atom ids and an angle parameter id");
+            if (!angle_ids.count(t[3])) fail("angle parameter id " + t[3] + " is not defined in the parameter file");
             angles3.push_back({to_int(t[0]), to_int(t[1]), to_int(t[2]), 0});
         } else if (section == "dihedrals") {
-            if (t.size() < 5) fail("dihedral requires: atom_i atom_j atom_k atom_l torsion_param_id");
-            if (!torsion_ids.count(t[4])) fail("dihedral references an invalid parameter ID");
+            if (t.size() < 5) fail("a [dihedrals] line is four atom ids and a torsion parameter id");
+            if (!torsion_ids.count(t[4])) fail("torsion parameter id " + t[4] + " is not defined in the parameter file");
             dihedrals4.push_back({to_int(t[0]), to_int(t[1]), to_int(t[2]), to_int(t[3])});
         } else if (section == "exclusions") {
-            if (t.size() < 2) fail("exclusion requires: atom_i atom_j");
+            if (t.size() < 2) fail("an [exclusions] line is two atom ids");
             listed.push_back({to_int(t[0]), to_int(t[1])});
         } else if (section == "impropers") {
-            if (t.size() < 5) fail("improper requires: atom_i atom_j atom_k atom_l torsion_param_id");
-            if (!improper_ids.count(t[4])) fail("improper references an invalid parameter ID");
+            if (t.size() < 5) fail("an [impropers] line is four atom ids and an improper parameter id");
+            if (!improper_ids.count(t[4])) fail("improper parameter id " + t[4] + " is not defined in the parameter file");
             impropers4.push_back({to_int(t[0]), to_int(t[1]), to_int(t[2]), to_int(t[3])});
         } else if (section == "special_pairs") {
-            if (t.size() < 5) fail("special_pair requires: atom_i atom_j pair_param_id lj_scale coulomb_scale");
+            if (t.size() < 5) fail("a [special_pairs] line is two atom ids, a pair parameter id and the LJ and Coulomb scale factors");
             special.push_back({to_int(t[0]), to_int(t[1])});
         } else if (section == "constraints") {
-            if (t.size() < 3) fail("constraint requires: atom_i atom_j target_distance");
+            if (t.size() < 3) fail("a [constraints] line is two atom ids and a distance");
             constraints.push_back({to_int(t[0]), to_int(t[1]), to_real(t[2])});
         } else if (section == "virtual_sites") {
-            fail("[" + section + "] is represented by the format but not supported by the current runtime");
+            fail("section [" + section + "] is part of the file format, but nothing here can simulate it");
         } else {
             fail("unknown topology section [" + section + "]");
         }
     }
-    if (type.empty()) throw std::runtime_error("topology file has no [atoms]");
-    if (expected_atoms < 0) throw std::runtime_error("topology [meta] has no atom_count");
+    if (type.empty()) throw std::runtime_error("topology file " + topology_path + ": the [atoms] section is missing or empty");
+    if (expected_atoms < 0) throw std::runtime_error("topology file " + topology_path + ": [meta] must state atom_count");
     if (expected_atoms != static_cast<long long>(type.size()))
-        throw std::runtime_error("topology atom_count is " + std::to_string(expected_atoms) + " but [atoms] contains " +
-                                 std::to_string(type.size()) + " entries");
+        throw std::runtime_error("topology file " + topology_path + ": atom_count is " + std::to_string(expected_atoms) + " but [atoms] contains " +
+                                 std::to_string(type.size()) + " lines");
     const int n_atoms = static_cast<int>(type.size());
     auto check = [&](int id, const char* kind) {
-        if (id < 0 || id >= n_atoms) throw std::runtime_error(std::string(kind) + " references invalid atom ID " + std::to_string(id));
+        if (id < 0 || id >= n_atoms) throw std::runtime_error("a [" + std::string(kind) + "] line names atom " + std::to_string(id) + ", which does not exist");
     };
-    for (const auto& b : bond_ends) { check(b.first, "bond"); check(b.second, "bond"); }
-    for (const auto& a : angles3) { check(a.a, "angle"); check(a.b, "angle"); check(a.c, "angle"); }
-    for (const auto& d : dihedrals4) { check(d.a, "dihedral"); check(d.b, "dihedral"); check(d.c, "dihedral"); check(d.d, "dihedral"); }
-    for (const auto& d : impropers4) { check(d.a, "improper"); check(d.b, "improper"); check(d.c, "improper"); check(d.d, "improper"); }
-    for (const auto& p : special) { check(p.first, "special_pair"); check(p.second, "special_pair"); }
+    for (const auto& b : bond_ends) { check(b.first, "bonds"); check(b.second, "bonds"); }
+    for (const auto& a : angles3) { check(a.a, "angles"); check(a.b, "angles"); check(a.c, "angles"); }
+    for (const auto& d : dihedrals4) { check(d.a, "dihedrals"); check(d.b, "dihedrals"); check(d.c, "dihedrals"); check(d.d, "dihedrals"); }
+    for (const auto& d : impropers4) { check(d.a, "impropers"); check(d.b, "impropers"); check(d.c, "impropers"); check(d.d, "impropers"); }
+    for (const auto& p : special) { check(p.first, "special_pairs"); check(p.second, "special_pairs"); }
     for (const auto& c : constraints) {
-        check(c.i, "constraint"); check(c.j, "constraint");
-        if (!std::isfinite(c.distance) || c.distance <= 0.0) throw std::runtime_error("constraint target_distance must be finite and positive");
+        check(c.i, "constraints"); check(c.j, "constraints");
+        if (!std::isfinite(c.distance) || c.distance <= 0.0) throw std::runtime_error("a [constraints] distance must be a finite number > 0");
     }
-    for (const auto& e : listed) { check(e.first, "exclusion"); check(e.second, "exclusion"); }
+    for (const auto& e : listed) { check(e.first, "exclusions"); check(e.second, "exclusions"); }
 
     std::vector<std::pair<int, int>> exclusions;
     for (const auto& e : listed) exclusions.push_back(ordered(e.first, e.second));
@@ -350,8 +350,8 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
     exclusions.erase(std::unique(exclusions.begin(), exclusions.end()), exclusions.end());
     for (const auto& p : special)
         if (!std::binary_search(exclusions.begin(), exclusions.end(), ordered(p.first, p.second)))
-            throw std::runtime_error("special_pair " + std::to_string(p.first) + "-" + std::to_string(p.second) +
-                                     " must also appear in [exclusions]");
+            throw std::runtime_error("[special_pairs] " + std::to_string(p.first) + "-" + std::to_string(p.second) +
+                                     ": the pair must be excluded from the normal pair sum as well ([exclusions] or a bonded term)");
 
     require_atom_count(s, type.size(), topology_path);
     s.type = type;

@@ -285,6 +285,18 @@ int dsmd_images_result(const dsmd_edges* eb, const double** d_x, const double** 
                        const int32_t** d_type, const int32_t** d_owner, const double** d_shift_x, const double** d_shift_y,
                        const double** d_shift_z, int64_t* n_all);
 
+/* MLIPStep::add_forces (src/MLIPStep.cu:108-124, 373-381): target[i] += f[i] + the forces on the images of atom i (in the
+ * order the images were created), for the first n_out of the atoms the last dsmd_images_build was given (n_out < 0: all
+ * of them). d_f*: the model's forces on all n_all atoms of that build; with_images == 0 adds f[i] alone (the images were
+ * used as edge shifts, not as atoms). Queued on `stream`. */
+int dsmd_images_fold_forces(dsmd_edges* eb, const double* d_fx, const double* d_fy, const double* d_fz, int64_t n_out,
+                            int with_images, double* d_target_x, double* d_target_y, double* d_target_z, void* stream);
+
+/* MLIPStep::virial / virial_diag (src/MLIPStep.cu:126-148, 383-432): out = {sum r.F, sum x Fx, sum y Fy, sum z Fz} over the
+ * n atoms given (owned, ghosts and images alike), summed in a fixed order. Synchronises `stream`. */
+int dsmd_virial_from_forces(dsmd_edges* eb, const double* d_x, const double* d_y, const double* d_z, const double* d_fx,
+                            const double* d_fy, const double* d_fz, int64_t n, double out[4], void* stream);
+
 /* Receiver mask (mark_receivers_kernel, src/MLIPStep.cu:150-161): d_ok[i] = 1 when atom i lies within `reach` (Euclidean
  * distance) of the box [lo, hi]; a NaN position gives 0. The mask EdgeBuilder::Prune wants. */
 int dsmd_mark_receivers(dsmd_edges* eb, const double* d_x, const double* d_y, const double* d_z, int64_t n,

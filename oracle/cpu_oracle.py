@@ -207,6 +207,35 @@ def images(x, y, z, box, origin, region_lo, region_hi, shells):
     return dict(x=arrs[0], y=arrs[1], z=arrs[2], owner=arrs[3], shift=np.stack(arrs[4:7], axis=1))
 
 
+def fold_image_forces(f, n, owner, target, n_out=None, with_images=True):
+    """target[:n_out] += f[:n_out] + the forces on each atom's images (slots n..; owner[slot] = the atom copied), added in
+    slot order. f: [n_all, 3]; owner: [n_all]; target: [n, 3]. Returns the new target."""
+    f = np.ascontiguousarray(f, dtype=np.float64)
+    n_out = n if n_out is None else n_out
+    own = np.asarray(owner[n:], dtype=np.int64)
+    count = np.bincount(own, minlength=n).astype(np.int64)
+    first = np.concatenate([[0], np.cumsum(count)[:-1]]).astype(np.int64)
+    assert np.array_equal(own, np.repeat(np.arange(n), count)), "images must be stored atom after atom"
+    cols = [np.ascontiguousarray(f[:, k]) for k in range(3)]
+    out = [np.ascontiguousarray(target[:, k], dtype=np.float64).copy() for k in range(3)]
+    cl = ctypes.POINTER(ctypes.c_long)
+    lib().dsmd_oracle_fold_image_forces(
+        ctypes.c_long(n_out), ctypes.c_long(n), *[_ptr(c, ctypes.c_double) for c in cols],
+        first.ctypes.data_as(cl), count.ctypes.data_as(cl) if with_images else None,
+        *[_ptr(o, ctypes.c_double) for o in out])
+    return np.stack(out, axis=1)
+
+
+def virial_from_forces(pos, f):
+    """{sum r.F, sum x Fx, sum y Fy, sum z Fz} over all rows of pos / f ([n, 3] each)."""
+    p = [np.ascontiguousarray(pos[:, k], dtype=np.float64) for k in range(3)]
+    g = [np.ascontiguousarray(f[:, k], dtype=np.float64) for k in range(3)]
+    out = np.zeros(4)
+    lib().dsmd_oracle_virial_from_forces(ctypes.c_long(len(p[0])), *[_ptr(a, ctypes.c_double) for a in p + g],
+                                         _ptr(out, ctypes.c_double))
+    return out
+
+
 def mark_receivers(x, y, z, lo, hi, reach):
     x, y, z = _f64(x), _f64(y), _f64(z)
     ok = np.zeros(len(x), dtype=np.uint8)

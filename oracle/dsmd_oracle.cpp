@@ -18,6 +18,7 @@
 //   cubic Ewald table   include/ewald_real_table.h:31-122   (float-bit indexed piecewise cubics; what the device evaluates)
 //   radius-graph edges  src/EdgeBuilder.cu:116-192          (ordered pairs, strict <, no minimum image, images, pruning)
 //   periodic images     src/MLIPStep.cu:31-52,73-103        (wrap from lo, shells, fixed emission order)
+//   image force fold    src/MLIPStep.cu:108-148             (forces of images added to their atoms in slot order; r.F sums)
 //   receiver marking    src/MLIPStep.cu:150-161
 //   ghost selection     src/md_system.cpp:855-891           (geometric rule only: every periodic image of an atom that
 //                                                           lies within the halo width of the brick, edges and corners
@@ -451,6 +452,40 @@ long dsmd_oracle_images(long n, const double* x, const double* y, const double* 
         }
     }
     return total;
+}
+
+// Forces of image atoms folded back onto the atoms they copy (src/MLIPStep.cu:108-124): target[i] += f[i] + the forces on
+// the slots n + first[i] .. n + first[i] + count[i] - 1, added in that order, for i < n_out. count == null: f[i] alone.
+void dsmd_oracle_fold_image_forces(long n_out, long n, const double* fx, const double* fy, const double* fz,
+                                   const long* first, const long* count, double* tx, double* ty, double* tz) {
+    for (long i = 0; i < n_out; ++i) {
+        double ax = fx[i], ay = fy[i], az = fz[i];
+        if (count)
+            for (long k = 0; k < count[i]; ++k) {
+                ax += fx[n + first[i] + k];
+                ay += fy[n + first[i] + k];
+                az += fz[n + first[i] + k];
+            }
+        tx[i] += ax;
+        ty[i] += ay;
+        tz[i] += az;
+    }
+}
+
+// out = {sum r.F, sum x Fx, sum y Fy, sum z Fz} over n atoms (src/MLIPStep.cu:126-148), long double accumulators so that
+// the comparison is against the exact sum rather than against one summation order.
+void dsmd_oracle_virial_from_forces(long n, const double* x, const double* y, const double* z, const double* fx,
+                                    const double* fy, const double* fz, double out[4]) {
+    long double s[3] = {0.0L, 0.0L, 0.0L};
+    for (long p = 0; p < n; ++p) {
+        s[0] += static_cast<long double>(x[p]) * fx[p];
+        s[1] += static_cast<long double>(y[p]) * fy[p];
+        s[2] += static_cast<long double>(z[p]) * fz[p];
+    }
+    out[0] = static_cast<double>(s[0] + s[1] + s[2]);
+    out[1] = static_cast<double>(s[0]);
+    out[2] = static_cast<double>(s[1]);
+    out[3] = static_cast<double>(s[2]);
 }
 
 // ok[i] = atom i lies within `reach` (Euclidean distance to the box [lo, hi]) of the box.

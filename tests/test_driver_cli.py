@@ -56,7 +56,7 @@ def test_usage_and_input_errors(driver, tmp_path):
     assert run(driver).returncode == 2
     assert run(driver, "--no-such-flag").returncode == 2
     r = run(driver, tmp_path / "absent.yaml")
-    assert r.returncode == 1 and "Cannot open config file" in r.stderr
+    assert r.returncode == 1 and "cannot be opened" in r.stderr
     (tmp_path / "incomplete.yaml").write_text("timestep: 1.0\n")
     r = run(driver, tmp_path / "incomplete.yaml", "--check-input")
-    assert r.returncode == 1 and "Missing required configuration parameters: coordinate_file, target_temperature, total_steps" in r.stderr
+    assert r.returncode == 1 and "lacks required keys: coordinate_file, target_temperature, total_steps" in r.stderr

@@ -142,3 +142,42 @@ def test_image_atoms_receivers_and_the_whole_mlip_preparation(cuda_device):
     b = np.concatenate([want_idx.astype(np.float64), want_sh.T])
     assert a.shape == b.shape and np.array_equal(canon(a), canon(b))
     eb.close()
+
+
+def test_image_forces_fold_back_and_virial(cuda_device):
+    """Forces a model returns for atoms + image atoms are folded back onto the atoms (images summed in slot order) exactly
+    as the oracle does it, with and without the image part and for a prefix of the atoms; the r.F sums agree with the
+    oracle's extended-precision sums to rounding."""
+    import torch
+    rng = np.random.default_rng(5)
+    n, L = 3000, 24.0
+    box = np.full(3, L)
+    pos = rng.uniform(0, L, (n, 3))
+    reach = 4.0
+    lo, hi = -np.full(3, reach), box + reach
+    eb = capi.EdgeBuilder()
+    x, y, z = (to_dev(pos[:, k]) for k in range(3))
+    img = eb.images(x, y, z, None, box, np.zeros(3), lo, hi, (1, 1, 0))       # two image axes, one without
+    n_all = img["n_all"]
+    owner = img["owner"].cpu().numpy()
+    assert n_all > n and np.all(img["shift"][2].cpu().numpy() == 0.0)
+    f = rng.normal(size=(n_all, 3))
+    before = rng.normal(size=(n, 3))
+    fdev = [to_dev(f[:, k]) for k in range(3)]
+    for n_out, with_images in ((-1, True), (n // 3, True), (-1, False)):
+        t = [to_dev(before[:, k]) for k in range(3)]
+        eb.fold_image_forces(*fdev, *t, n_out=n_out, with_images=with_images)
+        got = np.stack([v.cpu().numpy() for v in t], axis=1)
+        want = co.fold_image_forces(f, n, owner, before, n_out=None if n_out < 0 else n_out, with_images=with_images)
+        assert np.array_equal(got, want)
+    # momentum: what went in on images comes out on atoms
+    t = [torch.zeros(n, dtype=torch.float64, device="cuda") for _ in range(3)]
+    eb.fold_image_forces(*fdev, *t)
+    assert np.allclose(np.stack([v.cpu().numpy() for v in t], axis=1).sum(0), f.sum(0), rtol=0, atol=1e-9)
+    all_pos = np.stack([img[k].cpu().numpy() for k in "xyz"], axis=1)
+    got = eb.virial_from_forces(img["x"].clone(), img["y"].clone(), img["z"].clone(), *fdev)
+    want = co.virial_from_forces(all_pos, f)
+    scale = np.abs(all_pos * f).sum()
+    assert np.abs(got - want).max() <= 1e-13 * scale
+    eb.close()
+

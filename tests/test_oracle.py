@@ -305,3 +305,26 @@ def test_shake_and_rattle_match_the_reference_constraint_solver():
     # a solver that cannot converge says so
     pos_x, vel_x = copies()
     assert not co.shake(cons, pos_x, vel_x, w.mass, pre, w.box, dt, max_iterations=1)
+
+
+def test_image_force_fold_and_virial_restatement():
+    """The oracle's fold of image forces (src/MLIPStep.cu:108-124) against an independent numpy scatter-add, and its
+    r.F sums (src/MLIPStep.cu:126-148) against numpy."""
+    rng = np.random.default_rng(11)
+    n, L = 500, 12.0
+    pos = rng.uniform(0, L, (n, 3))
+    box = np.full(3, L)
+    img = co.images(pos[:, 0], pos[:, 1], pos[:, 2], box, np.zeros(3), -np.full(3, 3.0), box + 3.0, (1, 1, 1))
+    n_all = len(img["x"])
+    f = rng.normal(size=(n_all, 3))
+    target = rng.normal(size=(n, 3))
+    want = target + f[:n]
+    np.add.at(want, img["owner"][n:], f[n:])
+    got = co.fold_image_forces(f, n, img["owner"], target)
+    assert np.allclose(got, want, rtol=0, atol=1e-12)
+    assert np.array_equal(co.fold_image_forces(f, n, img["owner"], target, with_images=False), target + f[:n])
+    part = co.fold_image_forces(f, n, img["owner"], target, n_out=100)
+    assert np.array_equal(part[100:], target[100:]) and np.array_equal(part[:100], got[:100])
+    all_pos = np.stack([img["x"], img["y"], img["z"]], axis=1)
+    v = co.virial_from_forces(all_pos, f)
+    assert np.allclose(v[1:], (all_pos * f).sum(0), rtol=1e-12) and np.isclose(v[0], (all_pos * f).sum(), rtol=1e-12)
