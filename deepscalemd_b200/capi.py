@@ -23,18 +23,19 @@ FIELD_ID = {name: k for k, name in enumerate(FIELDS)}
 SYMBOLS = [
     "dsmd_create", "dsmd_destroy", "dsmd_last_error", "dsmd_set_box", "dsmd_set_pair_params", "dsmd_set_coulomb",
     "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
-    "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned",
+    "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned", "dsmd_sort_owned_in_brick",
     "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq",
     "dsmd_displacement_word", "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_scale_velocities",
     "dsmd_run_nve",
     "dsmd_forces_host", "dsmd_launch_count", "dsmd_fma_probe", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
-    "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_edges_create", "dsmd_edges_destroy",
+    "dsmd_halo_pack_records", "dsmd_halo_append_records", "dsmd_halo_append_packed", "dsmd_capacity", "dsmd_edges_create", "dsmd_edges_destroy",
     "dsmd_edges_last_error", "dsmd_edges_build", "dsmd_edges_result", "dsmd_edges_build_periodic",
     "dsmd_edges_result_compact", "dsmd_images_build", "dsmd_images_result", "dsmd_images_fold_forces",
     "dsmd_virial_from_forces", "dsmd_mark_receivers",
     "dsmd_kinetic_energy_noalloc", "dsmd_nccl_unique_id", "dsmd_domain_create",
     "dsmd_domain_destroy", "dsmd_domain_last_error", "dsmd_domain_rebuild", "dsmd_domain_refresh", "dsmd_domain_run",
-    "dsmd_domain_stats", "dsmd_domain_profile",
+    "dsmd_domain_stats", "dsmd_domain_profile", "dsmd_domain_set_wait_limit", "dsmd_domain_abort",
+    "dsmd_domain_reverse_forces", "dsmd_domain_exchange_field", "dsmd_domain_peers",
 ]
 
 _lib = None
@@ -392,6 +393,31 @@ class Domain:
     def run(self, n_steps, dt, force_to_accel=1.0, hi_frac=0.5, stream=None):
         self._check(self.lib.dsmd_domain_run(self.h, c_int64(n_steps), c_double(dt), c_double(force_to_accel),
                                              c_double(hi_frac), _stream_handle(stream)))
+
+    def reverse_forces(self, stream=None):
+        """Forces held on ghost atoms go back to, and are added to, their owners."""
+        self._check(self.lib.dsmd_domain_reverse_forces(self.h, _stream_handle(stream)))
+
+    def exchange_field(self, tensor, reverse=False, stream=None):
+        """A [rows, width] float32 / float64 device tensor over owned + ghost atoms: forward copies owners' rows into
+        their ghosts, reverse adds the ghosts' rows to their owners'."""
+        rows, width = tensor.shape
+        self._check(self.lib.dsmd_domain_exchange_field(self.h, c_void_p(tensor.data_ptr()), c_int64(rows), c_int64(width),
+                                                        c_int(tensor.element_size()), c_int(1 if reverse else 0),
+                                                        _stream_handle(stream)))
+
+    def set_wait_limit(self, seconds):
+        self._check(self.lib.dsmd_domain_set_wait_limit(self.h, c_double(seconds)))
+
+    def abort(self):
+        self.lib.dsmd_domain_abort(self.h)
+
+    def peers(self):
+        n = ctypes.c_int32(0)
+        ranks = (ctypes.c_int32 * 26)()
+        msgs = (ctypes.c_int32 * 1)()
+        self._check(self.lib.dsmd_domain_peers(self.h, ctypes.byref(n), ranks, msgs))
+        return dict(ranks=[ranks[k] for k in range(n.value)], messages_per_exchange=msgs[0])
 
     def profile(self, enable=True):
         """Switches per-phase timing on or off; returns the accumulated per-step averages (ms) so far."""

@@ -44,6 +44,8 @@ struct Status {
     unsigned long long entries;    // directed list entries
     unsigned long long interior;   // of which the partner is owned
     unsigned long long select_count;
+    unsigned int dropped;          // owned atoms found outside the brick by a sort that removes them
+    unsigned int reserved;
 };
 
 __host__ __device__ inline unsigned int cell_of(unsigned int fixed, int wrap, int nc) {

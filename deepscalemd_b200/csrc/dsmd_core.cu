@@ -54,21 +54,38 @@ struct RealArrays {
     double* p[kNumReal];
 };
 
-__global__ void k_cell_keys(Grid g, int first, int n_owned, int n_total, const double* __restrict__ x,
+// This rank's brick on the axes that are split between ranks (drop != 0: atoms outside it are to be removed).
+struct Brick {
+    double lo[3], hi[3];
+    int split[3];
+    int drop;
+};
+
+__global__ void k_cell_keys(Grid g, Brick brick, int first, int n_owned, int n_total, const double* __restrict__ x,
                             const double* __restrict__ y, const double* __restrict__ z, unsigned* __restrict__ key,
                             int* __restrict__ val, Status* st) {
     const int s = first + blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= n_total) return;
+    const double p[3] = {x[s], y[s], z[s]};
     unsigned bad = 0;
-    const unsigned fx = dsmd::to_fixed(x[s], 0, g, bad);
-    const unsigned fy = dsmd::to_fixed(y[s], 1, g, bad);
-    const unsigned fz = dsmd::to_fixed(z[s], 2, g, bad);
+    const unsigned fx = dsmd::to_fixed(p[0], 0, g, bad);
+    const unsigned fy = dsmd::to_fixed(p[1], 1, g, bad);
+    const unsigned fz = dsmd::to_fixed(p[2], 2, g, bad);
     if (bad) atomicAdd(&st->out_of_domain, 1u);
     const unsigned cx = dsmd::cell_of(fx, g.wrap[0], g.nc[0]);
     const unsigned cy = dsmd::cell_of(fy, g.wrap[1], g.nc[1]);
     const unsigned cz = dsmd::cell_of(fz, g.wrap[2], g.nc[2]);
     unsigned c = (cz * g.nc[1] + cy) * g.nc[0] + cx;
     if (s >= n_owned) c += g.ncells;
+    if (brick.drop) {   // an atom that left the brick (the same comparisons as the migration's classifier) sorts last
+        bool outside = false;
+        for (int a = 0; a < 3; ++a)
+            if (brick.split[a] && (p[a] < brick.lo[a] || p[a] >= brick.hi[a])) outside = true;
+        if (outside) {
+            c = 2u * static_cast<unsigned>(g.ncells);
+            atomicAdd(&st->dropped, 1u);
+        }
+    }
     key[s - first] = c;
     val[s - first] = s;
 }
@@ -111,6 +128,7 @@ __global__ void k_reorder(Grid g, int first, int n_owned, int n_total, const uns
     // Cell starts. Keys of the sorted range [first, n_total) are key[0 .. n_total - first). When only the owned atoms
     // are sorted (first == 0, n_total == n_owned) the ghost half of the table is filled by the later full build.
     const int k_here = static_cast<int>(key[t]);
+    if (k_here >= 2 * g.ncells) return;   // an atom being removed: behind every cell
     const int k_prev = t == 0 ? (first == 0 ? -1 : g.ncells - 1) : static_cast<int>(key[t - 1]);
     for (int c = k_prev + 1; c <= k_here; ++c) cell_start[c] = s;
 }
@@ -630,6 +648,23 @@ __global__ void k_halo_append_records(int count, int first_slot, const double* _
     gid[s] = int_in[2 * k + 1];
 }
 
+// Full records as one run of nine doubles per atom: x y z vx vy vz mass charge and the two int32 words (type, gid) in the
+// ninth - one message per peer carries every field.
+__global__ void k_halo_append_packed(int count, int first_slot, const double* __restrict__ rec, RealArrays a,
+                                     int* __restrict__ type, int* __restrict__ gid) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= count) return;
+    const int s = first_slot + k;
+    const double* r = rec + 9 * static_cast<size_t>(k);
+    a.p[0][s] = r[0]; a.p[1][s] = r[1]; a.p[2][s] = r[2];
+    a.p[3][s] = r[3]; a.p[4][s] = r[4]; a.p[5][s] = r[5];
+    a.p[6][s] = 0.0; a.p[7][s] = 0.0; a.p[8][s] = 0.0;
+    a.p[9][s] = r[6]; a.p[10][s] = r[7];
+    const long long words = __double_as_longlong(r[8]);
+    type[s] = static_cast<int>(words & 0xFFFFFFFFll);
+    gid[s] = static_cast<int>(words >> 32);
+}
+
 // Dependent-FMA-free throughput probe: 8 independent fp32 FMA chains per thread. The benchmark times it to get the
 // fp32 CUDA-core peak of the device it runs on (the denominator of the pair kernel's compute roofline).
 __global__ void __launch_bounds__(256) k_fma_probe(int iters, float seed, float* out) {
@@ -709,6 +744,7 @@ struct dsmd_ctx {
     unsigned long long* offsets64 = nullptr;
     bool list_valid = false;
     bool owned_sorted_only = false;
+    int64_t expect_dropped = 0;    // atoms the last owned-only sort was told to remove (checked with the build status)
     int64_t stat_entries = 0, stat_interior = 0;
     int stat_rechecked = 0;
 };
@@ -855,8 +891,9 @@ int ensure_partials(dsmd_ctx* c, int64_t blocks) {
     return DSMD_OK;
 }
 
-// Sorts slots [first, n_total) by cell and gathers everything into the other buffer set.
-int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s) {
+// Sorts slots [first, n_total) by cell and gathers everything into the other buffer set. n_removed > 0 (owned-only
+// sorts): that many atoms lie outside the brick; they sort behind every cell and fall off the end.
+int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s, int64_t n_removed = 0, const Brick* bounds = nullptr) {
     const int64_t n = c->n_total - first;
     const int from = c->cur, to = 1 - c->cur;
     if (first > 0) {
@@ -868,20 +905,23 @@ int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s) {
         DSMD_CUDA(c, cudaMemcpyAsync(c->gid[to], c->gid[from], sizeof(int) * first, cudaMemcpyDeviceToDevice, s));
     }
     if (n > 0) {
+        Brick brick{};
+        if (bounds) brick = *bounds;
+        brick.drop = (bounds && n_removed > 0) ? 1 : 0;
         k_cell_keys<<<blocks_for(n, kThreads), kThreads, 0, s>>>(
-            c->grid, static_cast<int>(first), static_cast<int>(c->n_owned), static_cast<int>(c->n_total),
+            c->grid, brick, static_cast<int>(first), static_cast<int>(c->n_owned), static_cast<int>(c->n_total),
             c->real[from][0], c->real[from][1], c->real[from][2], c->key[0], c->val[0], c->status);
         DSMD_LAUNCHED(c);
         int bits = 1;
-        while ((1ll << bits) < 2ll * c->grid.ncells) ++bits;
+        while ((1ll << bits) < 2ll * c->grid.ncells + 1) ++bits;
         size_t need = 0;
         cub::DeviceRadixSort::SortPairs(nullptr, need, c->key[0], c->key[1], c->val[0], c->val[1], static_cast<int>(n), 0,
                                         bits, s);
         if (need > c->cub_temp_bytes) {
             if (c->cub_temp) cudaFree(c->cub_temp);
             c->cub_temp = nullptr;
-            DSMD_CUDA(c, cudaMalloc(&c->cub_temp, need));
-            c->cub_temp_bytes = need;
+            DSMD_CUDA(c, cudaMalloc(&c->cub_temp, need + need / 4));
+            c->cub_temp_bytes = need + need / 4;
         }
         DSMD_CUDA(c, cub::DeviceRadixSort::SortPairs(c->cub_temp, need, c->key[0], c->key[1], c->val[0], c->val[1],
                                                      static_cast<int>(n), 0, bits, s));
@@ -891,9 +931,13 @@ int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s) {
             c->qf, c->ref[0], c->ref[1], c->ref[2], c->cell_start, c->ghost_slot);
         DSMD_LAUNCHED(c);
         const int table = 2 * c->grid.ncells + 1;
-        k_cell_tail<<<blocks_for(table, kThreads), kThreads, 0, s>>>(c->key[1], static_cast<int>(n),
-                                                                  static_cast<int>(c->n_total), table, c->cell_start);
-        DSMD_LAUNCHED(c);
+        const int64_t kept = n - n_removed;
+        if (kept > 0) {
+            k_cell_tail<<<blocks_for(table, kThreads), kThreads, 0, s>>>(c->key[1], static_cast<int>(kept),
+                                                                      static_cast<int>(c->n_total - n_removed), table,
+                                                                      c->cell_start);
+            DSMD_LAUNCHED(c);
+        }
     }
     c->cur = to;
     return DSMD_OK;
@@ -1178,25 +1222,46 @@ int dsmd_set_counts(dsmd_ctx* c, int64_t n_owned, int64_t n_total) {
     return DSMD_OK;
 }
 
-int dsmd_sort_owned(dsmd_ctx* c, void* stream) {
-    if (!c) return DSMD_ERR_INVALID;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+static int sort_owned_impl(dsmd_ctx* c, const Brick* bounds, int64_t n_outside, bool check_now, cudaStream_t s) {
     DSMD_CUDA(c, cudaSetDevice(c->device));
+    if (n_outside < 0 || n_outside >= c->n_owned) return fail(c, DSMD_ERR_INVALID, "sort: bad count of atoms to remove");
     if (!c->grid_valid) { const int rc = make_grid(c); if (rc) return rc; }
     { const int rc = ensure_cells(c); if (rc) return rc; }
     DSMD_CUDA(c, cudaMemsetAsync(c->status, 0, sizeof(Status), s));
     const int64_t keep_total = c->n_total;
     c->n_total = c->n_owned;   // sort the owned segment alone
-    const int rc = sort_range(c, 0, s);
+    const int rc = sort_range(c, 0, s, n_outside, bounds);
     c->n_total = keep_total;
     if (rc) return rc;
+    c->n_owned -= n_outside;
     c->n_total = c->n_owned;   // ghosts (if any were present) are dropped: the caller appends the new ones
     c->list_valid = false;
     c->owned_sorted_only = true;
+    c->expect_dropped = n_outside;
+    if (!check_now) return DSMD_OK;   // the status words stay and are read with the list build's
     { const int rc2 = read_status(c, s); if (rc2) return rc2; }
     if (c->h_status->out_of_domain)
         return fail(c, DSMD_ERR_OUT_OF_DOMAIN, "an atom lies outside the subdomain + halo, or has a NaN position");
+    if (c->h_status->dropped != static_cast<unsigned>(n_outside))
+        return fail(c, DSMD_ERR_STATE, "sort: the number of atoms outside the brick differs from the caller's count");
     return DSMD_OK;
+}
+
+int dsmd_sort_owned(dsmd_ctx* c, void* stream) {
+    if (!c) return DSMD_ERR_INVALID;
+    return sort_owned_impl(c, nullptr, 0, true, static_cast<cudaStream_t>(stream));
+}
+
+int dsmd_sort_owned_in_brick(dsmd_ctx* c, const double lo[3], const double hi[3], const int split[3], int64_t n_outside,
+                             void* stream) {
+    if (!c || !lo || !hi || !split) return DSMD_ERR_INVALID;
+    Brick bounds{};
+    for (int a = 0; a < 3; ++a) {
+        bounds.lo[a] = lo[a];
+        bounds.hi[a] = hi[a];
+        bounds.split[a] = split[a] != 0;
+    }
+    return sort_owned_impl(c, &bounds, n_outside, false, static_cast<cudaStream_t>(stream));
 }
 
 int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
@@ -1206,10 +1271,13 @@ int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
     if (c->n_owned <= 0) return fail(c, DSMD_ERR_STATE, "no atoms uploaded");
     if (!c->grid_valid) { const int rc = make_grid(c); if (rc) return rc; }
     { const int rc = ensure_cells(c); if (rc) return rc; }
-    DSMD_CUDA(c, cudaMemsetAsync(c->status, 0, sizeof(Status), s));
-    // 1. bin + sort + reorder (everything, or only the ghosts when the owned segment was sorted just before)
+    // 1. bin + sort + reorder (everything, or only the ghosts when the owned segment was sorted just before: the
+    //    status words of that sort are then still unread and are kept)
     const int64_t first = c->owned_sorted_only ? c->n_owned : 0;
+    const int64_t expect_dropped = c->owned_sorted_only ? c->expect_dropped : 0;
+    if (!c->owned_sorted_only) DSMD_CUDA(c, cudaMemsetAsync(c->status, 0, sizeof(Status), s));
     c->owned_sorted_only = false;
+    c->expect_dropped = 0;
     if (first == 0 || c->n_total > first) { const int rc = sort_range(c, first, s); if (rc) return rc; }
     // 2. list rows
     if (c->stride == 0) {
@@ -1231,6 +1299,8 @@ int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
         { const int rc = read_status(c, s); if (rc) return rc; }
         if (c->h_status->out_of_domain)
             return fail(c, DSMD_ERR_OUT_OF_DOMAIN, "an atom lies outside the subdomain + halo, or has a NaN position");
+        if (attempt == 0 && c->h_status->dropped != static_cast<unsigned>(expect_dropped))
+            return fail(c, DSMD_ERR_STATE, "sort: the number of atoms outside the brick differs from the caller's count");
         if (c->h_status->need_stride <= static_cast<unsigned>(c->stride)) break;
         // a row overflowed: grow and build again
         c->stride = (static_cast<int>(c->h_status->need_stride * 1.1) + 8 + 3) & ~3;
@@ -1608,6 +1678,26 @@ int dsmd_halo_append_records(dsmd_ctx* c, const double* d_real_in, const int32_t
     DSMD_LAUNCHED(c);
     c->n_total += count;
     c->list_valid = false;
+    return DSMD_OK;
+}
+
+int dsmd_halo_append_packed(dsmd_ctx* c, const double* d_records, int64_t count, void* stream) {
+    if (!c || count < 0 || (count > 0 && !d_records)) return DSMD_ERR_INVALID;
+    if (c->n_total + count > c->capacity) return fail(c, DSMD_ERR_CAPACITY, "atoms exceed the context's capacity");
+    if (count == 0) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    k_halo_append_packed<<<blocks_for(count, kThreads), kThreads, 0, s>>>(
+        static_cast<int>(count), static_cast<int>(c->n_total), d_records, arrays_of(c, c->cur), c->type[c->cur],
+        c->gid[c->cur]);
+    DSMD_LAUNCHED(c);
+    c->n_total += count;
+    c->list_valid = false;
+    return DSMD_OK;
+}
+
+int dsmd_capacity(const dsmd_ctx* c, int64_t* capacity) {
+    if (!c || !capacity) return DSMD_ERR_INVALID;
+    *capacity = c->capacity;
     return DSMD_OK;
 }
 

@@ -8,6 +8,8 @@
 #include <vector>
 
 #include "dynamics.hpp"
+#include "brick_plan.hpp"
+#include "deadline.hpp"
 #include "restart_file.hpp"
 #include "run_config.hpp"
 #include "system_input.hpp"
@@ -231,6 +233,65 @@ int dsmd_input_nose_hoover_scale(double kinetic_kcal, int64_t atoms, double targ
     if (!xi || !scale) return failed(DSMD_INPUT_ERR_INVALID, "null argument");
     *scale = nose_hoover_scale(kinetic_kcal, atoms, target_temperature, tau, dt, *xi, dof_fraction);
     return DSMD_INPUT_OK;
+}
+
+// ---- host logic of the multi-GPU domain code, callable without a GPU (CPU tests) ------------------------------------------
+
+int dsmd_host_brick_plan(const int32_t dims[3], int32_t rank, int32_t* n_dirs, int32_t dir_dest[26], int32_t* n_peers,
+                         int32_t peers[26], int32_t from_count[26]) {
+    if (!dims || !n_dirs || !n_peers || dims[0] < 1 || dims[1] < 1 || dims[2] < 1) return failed(DSMD_INPUT_ERR_INVALID, "null argument");
+    const int world = dims[0] * dims[1] * dims[2];
+    if (rank < 0 || rank >= world) return failed(DSMD_INPUT_ERR_INVALID, "rank outside the grid");
+    const int d[3] = {dims[0], dims[1], dims[2]};
+    std::vector<dsmd::host::RankDirs> all(world);
+    for (int r = 0; r < world; ++r) all[r] = dsmd::host::dirs_of(d, r);
+    const dsmd::host::PeerPlan plan = dsmd::host::peer_plan(all, rank);
+    *n_dirs = all[rank].n;
+    *n_peers = plan.n_peers;
+    for (int k = 0; k < all[rank].n && dir_dest; ++k) dir_dest[k] = all[rank].dest[k];
+    for (int p = 0; p < plan.n_peers; ++p) {
+        if (peers) peers[p] = plan.peer[p];
+        if (from_count) from_count[p] = plan.from_last[p] - plan.from_first[p];
+    }
+    return DSMD_INPUT_OK;
+}
+
+int dsmd_host_counts_verdict(const int32_t dims[3], const int32_t* counts, int64_t scratch_capacity, int32_t* code,
+                             int32_t* about_rank, int32_t messages[64]) {
+    if (!dims || !counts || !code) return failed(DSMD_INPUT_ERR_INVALID, "null argument");
+    const int world = dims[0] * dims[1] * dims[2];
+    const int d[3] = {dims[0], dims[1], dims[2]};
+    std::vector<dsmd::host::RankDirs> all(world);
+    for (int r = 0; r < world; ++r) all[r] = dsmd::host::dirs_of(d, r);
+    const dsmd::host::CountsVerdict v = dsmd::host::counts_verdict(all, counts, scratch_capacity, "atoms");
+    *code = v.code;
+    if (about_rank) *about_rank = v.rank;
+    g_error = v.text;
+    if (messages) {   // messages each rank posts for these counts: one per neighbour rank and way with anything in it
+        for (int r = 0; r < world && r < 64; ++r) {
+            const dsmd::host::PeerPlan plan = dsmd::host::peer_plan(all, r);
+            int send_to[dsmd::host::kMaxDirs], recv_from[dsmd::host::kMaxDirs];
+            long long ns = 0, nr = 0;
+            dsmd::host::per_peer_counts(plan, counts, r, send_to, recv_from, ns, nr);
+            int m = 0;
+            for (int p = 0; p < plan.n_peers; ++p) m += (send_to[p] > 0) + (recv_from[p] > 0);
+            messages[r] = m;
+        }
+    }
+    return DSMD_INPUT_OK;
+}
+
+int dsmd_host_wait_probe(double limit_s, int64_t ready_after_polls, int64_t fail_after_polls) {
+    int64_t polls = 0;
+    const dsmd::host::WaitResult r = dsmd::host::poll_until(
+        [&]() {
+            ++polls;
+            if (fail_after_polls >= 0 && polls > fail_after_polls) return -1;
+            if (ready_after_polls >= 0 && polls > ready_after_polls) return 1;
+            return 0;
+        },
+        limit_s);
+    return r == dsmd::host::WaitResult::kReady ? 0 : (r == dsmd::host::WaitResult::kTimedOut ? 7 : 2);
 }
 
 }  // extern "C"

@@ -73,6 +73,7 @@ def run(args):
     def md(n):
         dom.run(n, bench.DT, 1.0, 0.5, stream)
 
+    md(bench.SETTLE_STEPS)      # set-up: through the first in-loop rebuild with atoms that really migrate
     md(args.warmup)
     sampler = bench.ClockSampler(local) if rank == 0 else None
     if sampler:
@@ -117,20 +118,29 @@ def run(args):
     # end to end: host positions in, forces out, ghost refresh in between (every rank its own atoms)
     host = [torch.from_numpy(ctx.download(k)).pin_memory() for k in ("x", "y", "z")]
     hf = [torch.empty(n_owned, dtype=torch.float64).pin_memory() for _ in range(3)]
-    fptr = [ctx.device_pointer(k) for k in ("fx", "fy", "fz")]
+
+    cadence = max(1, round(args.steps / max(rebuilds, 1)))
+    calls = {"k": 0}
 
     def e2e_call():
+        # what the single-GPU end-to-end call does, per rank: positions in, rebuild (migration, ghost plan, list) at the
+        # MD run's cadence or else pack + ghost refresh, forces, forces out
         ctx.upload_positions_ptr(host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), stream)
-        ctx.pack_positions(0, n_owned, stream)
-        dom.refresh(stream)
+        if calls["k"] % cadence == 0:
+            dom.rebuild(stream)
+        else:
+            ctx.pack_positions(0, n_owned, stream)
+            dom.refresh(stream)
+        calls["k"] += 1
         ctx.compute_forces(capi.PHASE_FULL, False, stream)
         for k in range(3):
-            view = capi._tensor_from_ptr(fptr[k], (n_owned,), torch.float64, device)
+            view = capi._tensor_from_ptr(ctx.device_pointer(("fx", "fy", "fz")[k]), (n_owned,), torch.float64, device)
             hf[k].copy_(view, non_blocking=True)
         torch.cuda.synchronize()
 
     for _ in range(3):
         e2e_call()
+    calls["k"] = 0
     e2e_steps = max(4, min(args.steps, 40))
     dist.barrier()
     t0 = time.perf_counter()
@@ -153,8 +163,7 @@ def run(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
-                "workload": "LJ NVE 4,000,000 atoms (FCC 100^3, rho*=0.8442, T*=1.44, rc=2.5, skin=0.3, dt=0.005)"
-                if args.workload == "lj_4m" else args.workload,
+                "workload": bench.WORKLOAD_NAME if args.workload == "lj_4m" else args.workload,
                 "atoms": s.n, "decomposition": "x".join(str(d) for d in dec.dims) + " bricks",
                 "halo_width": halo, "ns_per_day": bench.ns_per_day(ms_per_step), "rebuilds": rebuilds,
                 "owned_ghost_sentbytes_per_rank": per_rank,
@@ -162,9 +171,10 @@ def run(args):
                 "l2": "inputs larger than L2 on every rank (list %.2f GB on rank 0)" % (4.0 * stats["directed_entries"] / 1e9),
                 "energy_per_atom_before": e0 / s.n, "energy_per_atom_after": e1 / s.n,
                 "phase_ms_per_step_rank0": phases,
-                "exchange": "native loop (dsmd_domain_run): positions-only refresh (24 B/ghost) by grouped ncclSend/ncclRecv "
-                            "on a side stream, overlapped with the interior force pass; 8-byte MAX all-reduce for the "
-                            "rebuild vote; gloo only for set-up and timing reductions",
+                "neighbour_ranks": dom.peers(),
+                "exchange": "native loop (dsmd_domain_run): positions-only refresh (24 B/ghost), one ncclSend/ncclRecv per "
+                            "neighbour rank, on a side stream, overlapped with the interior force pass; 8-byte MAX all-reduce "
+                            "for the rebuild vote on its own communicator and stream; gloo only for set-up and timing reductions",
             },
             "clocks": clocks,
             "roofline": {
@@ -180,7 +190,9 @@ def run(args):
             "cpu_baseline": None,
             "e2e": {"value": s.n * e2e_steps / float(e2e_t.item()), "unit": "atom-steps/s",
                     "h2d_bytes_per_step": 24 * n_total, "d2h_bytes_per_step": 24 * n_owned, "steps": e2e_steps,
-                    "call": "per rank: pinned host positions in, pack, ghost refresh, forces, forces out"},
+                    "rebuild_every": cadence,
+                    "call": "per rank: pinned host positions in, rebuild (migration, ghost plan, list) at the MD run's cadence "
+                            "or pack + ghost refresh, forces, forces out"},
             "gpu_launches": int(launches),
         }
         print(json.dumps(line))

@@ -17,7 +17,7 @@ SYMBOLS = [
     "dsmd_input_system_load", "dsmd_input_system_load_files", "dsmd_input_system_destroy", "dsmd_input_system_counts",
     "dsmd_input_system_real", "dsmd_input_system_types", "dsmd_input_system_pair_table", "dsmd_input_system_exclusions",
     "dsmd_input_system_constraints", "dsmd_input_system_velocities", "dsmd_input_restart_read", "dsmd_input_restart_write",
-    "dsmd_input_nose_hoover_scale",
+    "dsmd_input_nose_hoover_scale", "dsmd_host_brick_plan", "dsmd_host_counts_verdict", "dsmd_host_wait_probe",
 ]
 
 _lib = None
@@ -172,3 +172,37 @@ def nose_hoover_scale(kinetic_kcal, atoms, target_temperature, tau, dt, xi, dof_
     _check(lib().dsmd_input_nose_hoover_scale(c_double(kinetic_kcal), c_int64(atoms), c_double(target_temperature),
                                               c_double(tau), c_double(dt), c_double(dof_fraction), byref(x), byref(s)))
     return s.value, x.value
+
+
+# ---- host logic of the multi-GPU domain code (no GPU needed) ----------------------------------------------------------
+
+BINS = 29          # counts a rank publishes: stays, 26 directions, lost atoms, room
+
+
+def brick_plan(dims, rank):
+    """Neighbour directions (destination rank of each, ordered by destination), distinct neighbour ranks and how many of
+    each neighbour's directions point back at `rank`."""
+    d = (ctypes.c_int32 * 3)(*[int(v) for v in dims])
+    n_dirs, n_peers = ctypes.c_int32(0), ctypes.c_int32(0)
+    dest, peers, back = (ctypes.c_int32 * 26)(), (ctypes.c_int32 * 26)(), (ctypes.c_int32 * 26)()
+    _check(lib().dsmd_host_brick_plan(d, ctypes.c_int32(rank), ctypes.byref(n_dirs), dest, ctypes.byref(n_peers), peers, back))
+    return dict(dir_dest=[dest[k] for k in range(n_dirs.value)], peers=[peers[k] for k in range(n_peers.value)],
+                from_count=[back[k] for k in range(n_peers.value)])
+
+
+def counts_verdict(dims, counts, scratch_capacity=1 << 30):
+    """The status every rank derives from the gathered counts ([world, 29] int32) and the messages each rank posts."""
+    d = (ctypes.c_int32 * 3)(*[int(v) for v in dims])
+    world = int(np.prod(dims))
+    c = np.ascontiguousarray(counts, dtype=np.int32).reshape(world, BINS)
+    code, about = ctypes.c_int32(0), ctypes.c_int32(-1)
+    messages = (ctypes.c_int32 * 64)()
+    _check(lib().dsmd_host_counts_verdict(d, c.ctypes.data_as(ctypes.c_void_p), c_int64(scratch_capacity), ctypes.byref(code),
+                                          ctypes.byref(about), messages))
+    return dict(code=code.value, rank=about.value, text=lib().dsmd_input_last_error().decode(),
+                messages=[messages[r] for r in range(min(world, 64))])
+
+
+def wait_probe(limit_s, ready_after=-1, fail_after=-1):
+    return lib().dsmd_host_wait_probe(c_double(limit_s), c_int64(ready_after), c_int64(fail_after))
+

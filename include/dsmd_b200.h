@@ -112,6 +112,14 @@ int dsmd_build_neighbor_list(dsmd_ctx* ctx, void* stream);
  * their slots stay fixed when the ghosts arrive. */
 int dsmd_sort_owned(dsmd_ctx* ctx, void* stream);
 
+/* The owned-atom sort of a rebuild step that follows a migration (MDSystem::migrate_particles_on_device,
+ * src/md_system.cpp:1495-1509): the n_outside owned atoms that lie outside the brick [lo, hi) on a split axis have been
+ * sent to their new owners and are removed (they sort behind every cell and fall off the end; the owned count shrinks by
+ * n_outside), arrivals that were appended behind the owned atoms are sorted in. Does not synchronise: the status of
+ * this sort is read together with that of the dsmd_build_neighbor_list call that must follow. */
+int dsmd_sort_owned_in_brick(dsmd_ctx* ctx, const double lo[3], const double hi[3], const int split[3], int64_t n_outside,
+                             void* stream);
+
 /* After a build: ghost_slot[k] = the slot, in the sorted arrays, of the k-th ghost as it was handed in (device int32
  * array of n_total - n_owned entries). The halo refresh unpacks through it. */
 int dsmd_ghost_slots(dsmd_ctx* ctx, const int32_t** device_ghost_slot);
@@ -210,6 +218,13 @@ int dsmd_halo_pack_records(dsmd_ctx* ctx, const int32_t* device_send_index, int6
 int dsmd_halo_append_records(dsmd_ctx* ctx, const double* device_real_in, const int32_t* device_int_in, int64_t count,
                              void* stream);
 
+/* The same records as one run of nine doubles per atom - x y z vx vy vz mass charge and, in the ninth, the two int32 words
+ * type (low) and global id (high) - so that one message per neighbour rank carries every field. */
+int dsmd_halo_append_packed(dsmd_ctx* ctx, const double* device_records, int64_t count, void* stream);
+
+/* The capacity the context was created with (ParticleInfo::Provider sizing, src/force_calculator_cuda.cu:4143-4216). */
+int dsmd_capacity(const dsmd_ctx* ctx, int64_t* capacity);
+
 /* -- several GPUs: bricks, migration, ghost plan, MD loop --------------------------------------------------------------- */
 
 typedef struct dsmd_domain dsmd_domain;
@@ -228,20 +243,47 @@ int dsmd_domain_create(dsmd_ctx* ctx, int rank, int world, const int dims[3], co
 void dsmd_domain_destroy(dsmd_domain* dom);
 const char* dsmd_domain_last_error(const dsmd_domain* dom);
 
-/* The rebuild step (MDSimulation::handle_neighbor_phase on a rebuild, src/md_simulation.cpp:1316-1401): migrate atoms that
- * left the brick (MDSystem::migrate_particles_on_device), sort the owned atoms, select and exchange the ghosts' full records
- * (exchange_halo_on_device(rebuild = true)), build the list. Collective; synchronises `stream` three times. */
+/* The rebuild step (MDSimulation::handle_neighbor_phase on a rebuild, src/md_simulation.cpp:1316-1401): send the atoms that
+ * left the brick to their new owners (MDSystem::migrate_particles_on_device; only leavers and arrivals move), sort the
+ * owned atoms, select and exchange the ghosts' full records (exchange_halo_on_device(rebuild = true)), build the list.
+ * One message per neighbour RANK and way (at most 7 ranks on a 2 x 2 x 2 grid), no allocation. Collective; synchronises
+ * `stream` four times (leaver counts, ghost counts, list status, agreement on the status), each wait bounded by the wait
+ * limit. Every rank returns the same status: lost atoms, missing room and a failed list build are decided from values
+ * that all ranks exchange. */
 int dsmd_domain_rebuild(dsmd_domain* dom, void* stream);
+
+/* Host waits of the domain (message sizes, votes) poll against this limit and return DSMD_ERR_TIMEOUT when it runs out
+ * (default 120 s, or the environment's DSMD_WAIT_LIMIT_S). After a time-out the run cannot go on: call dsmd_domain_abort,
+ * which aborts the communicators so that kernels still waiting for the missing rank are released (the reference's
+ * behaviour on a failed rank: exception -> MPI_Abort, src/main.cpp:85-93). */
+int dsmd_domain_set_wait_limit(dsmd_domain* dom, double seconds);
+int dsmd_domain_abort(dsmd_domain* dom);
 
 /* Positions-only ghost refresh (begin + end_halo_exchange_on_device, src/md_system.cpp:1465-1493): pack, grouped
  * ncclSend / ncclRecv with the neighbour directions, unpack, on the domain's side stream; `stream` then waits for it. */
 int dsmd_domain_refresh(dsmd_domain* dom, void* stream);
 
 /* n_steps MD steps (MDSimulation::single_step, src/md_simulation.cpp:899-941, restricted to this path): first
- * velocity-Verlet half + pack, rebuild vote (8-byte MAX all-reduce, read one step late and extrapolated), then either a
- * rebuild + full force pass, or the ghost refresh on the side stream overlapped with the interior force pass followed by
- * the boundary pass; second half. Collective. */
+ * velocity-Verlet half + pack, rebuild vote (8-byte MAX all-reduce on a communicator and stream of its own, read one step
+ * late and extrapolated), then either a rebuild + full force pass, or the ghost refresh on the side stream overlapped
+ * with the interior force pass followed by the boundary pass; second half. Collective. Returns DSMD_ERR_TIMEOUT when a
+ * vote does not arrive within the wait limit. */
 int dsmd_domain_run(dsmd_domain* dom, int64_t n_steps, double dt, double force_to_accel, double hi_frac, void* stream);
+
+/* MDSystem::reverse_halo_on_device (src/md_system.cpp:1511-1518): the forces this rank holds on its ghost atoms travel back
+ * along the ghost plan and are added to the forces of the owners (one message per neighbour rank and way). The force
+ * arrays are the context's (DSMD_FX ...). Queued on `stream`; collective. */
+int dsmd_domain_reverse_forces(dsmd_domain* dom, void* stream);
+
+/* MDSystem::exchange_field_on_device (src/md_system.cpp:1520-1545; contract include/MLIPHaloTransport.h:16-37): a
+ * row-major device array [rows, width] of float (element_bytes 4) or double (8), rows = owned atoms then ghosts in the
+ * context's current order. reverse == 0: the rows of the ghosts are overwritten with the rows of their owners;
+ * reverse != 0: the rows of the ghosts are added to the rows of their owners. Queued on `stream`; collective. */
+int dsmd_domain_exchange_field(dsmd_domain* dom, void* device_data, int64_t rows, int64_t width, int element_bytes,
+                               int reverse, void* stream);
+
+/* The distinct neighbour ranks of this brick and how many messages one exchange of the current ghost plan posts. */
+int dsmd_domain_peers(const dsmd_domain* dom, int32_t* n_peers, int32_t peers[26], int32_t n_messages_per_exchange[1]);
 
 /* Per-phase device times of dsmd_domain_run, accumulated while enabled (profiling mode synchronises every step, so the
  * totals are not a benchmark): phase_ms = {integrate 1 + pack, vote, refresh issue + interior forces (or nothing),

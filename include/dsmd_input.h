@@ -77,6 +77,26 @@ int dsmd_input_restart_write(const char* path, int64_t step, double timestep, co
 int dsmd_input_nose_hoover_scale(double kinetic_kcal, int64_t atoms, double target_temperature, double tau, double dt,
                                  double dof_fraction, double* xi, double* scale);
 
+/* -- host logic of the multi-GPU domain code, without a GPU (what the CPU tests drive) -------------------------------------
+ * The decomposition library of the reference is external (dsDecompX 1.0, CMakeLists.txt:99); these are the host-side
+ * decisions of its replacement, dsmd_domain_* in dsmd_b200.h. */
+
+/* Neighbour directions of `rank` in a dims[0] x dims[1] x dims[2] periodic brick grid, ordered by destination rank
+ * (dir_dest), the distinct neighbour ranks (peers, ascending) and how many of each peer's directions point back here. */
+int dsmd_host_brick_plan(const int32_t dims[3], int32_t rank, int32_t* n_dirs, int32_t dir_dest[26], int32_t* n_peers,
+                         int32_t peers[26], int32_t from_count[26]);
+
+/* The verdict every rank reaches from the counts all ranks publish before a migration or ghost exchange
+ * (counts[r * 29 + 0] stays, [1 + k] atoms along direction k, [27] atoms lost, [28] room left): *code = 0 to go on,
+ * 4 when a rank lost atoms, 5 when arrivals exceed a rank's room; *about_rank says whose counts decided;
+ * messages[r] = point-to-point messages rank r posts for these counts. The sentence is in dsmd_input_last_error(). */
+int dsmd_host_counts_verdict(const int32_t dims[3], const int32_t* counts, int64_t scratch_capacity, int32_t* code,
+                             int32_t* about_rank, int32_t messages[64]);
+
+/* The bounded host wait of the domain code against a stand-in that becomes ready (or fails) after a number of polls,
+ * -1 = never: returns 0 ready, 7 (DSMD_ERR_TIMEOUT) when limit_s ran out, 2 when the stand-in failed. */
+int dsmd_host_wait_probe(double limit_s, int64_t ready_after_polls, int64_t fail_after_polls);
+
 #ifdef __cplusplus
 }
 #endif

@@ -116,12 +116,38 @@ def worker_native(rank, world, port, steps, dt, out_path):
     f_first = np.stack([ctx.download(k, n_owned) for k in ("fx", "fy", "fz")], axis=1)
     dom.run(steps, dt, 1.0, 0.5)
     torch.cuda.synchronize()
-    n_owned, _ = ctx.counts()
+    n_owned, n_total_now = ctx.counts()
     st = dom.stats()
     result = dict(gid_first=gid_first, f_first=f_first, first=dict(pe=float(first[0]), virial=float(first[1])),
                   ghosts=n_total - n_owned, gid=ctx.download("global_id", n_owned),
                   pos=np.stack([ctx.download(k, n_owned) for k in "xyz"], axis=1), rebuilds=st["rebuilds"],
-                  worst=st["worst_disp_sq"])
+                  worst=st["worst_disp_sq"], peers=dom.peers())
+    # -- the exchanges of the MLIP path along the same ghost plan ---------------------------------------------------------
+    device = torch.device("cuda", rank)
+    gid_all = torch.tensor(ctx.download("global_id", n_total_now), device=device, dtype=torch.float64)
+    is_ghost = torch.arange(n_total_now, device=device) >= n_owned
+    # forward: a ghost row becomes a copy of its owner's row (rows carry the global id, so it can be checked locally)
+    for dtype in (torch.float32, torch.float64):
+        field = torch.stack([gid_all + 0.25 * w for w in range(5)], dim=1).to(dtype)
+        want = field.clone()
+        field[is_ghost] = -1.0
+        dom.exchange_field(field, reverse=False)
+        torch.cuda.synchronize()
+        result[f"forward_ok_{field.element_size()}"] = bool(torch.equal(field, want))
+    # reverse: every ghost row holds (1, 2, 3); owners end up with (number of ghost copies elsewhere) x (1, 2, 3)
+    grad = torch.zeros(n_total_now, 3, device=device, dtype=torch.float64)
+    grad[is_ghost] = torch.tensor([1.0, 2.0, 3.0], device=device, dtype=torch.float64)
+    dom.exchange_field(grad, reverse=True)
+    # the force version of the same thing, on the context's own force arrays
+    f = [capi._tensor_from_ptr(ctx.device_pointer(k), (n_total_now,), torch.float64, device) for k in ("fx", "fy", "fz")]
+    for k in range(3):
+        f[k].zero_()
+        f[k][is_ghost] = float(k + 1)
+    dom.reverse_forces()
+    torch.cuda.synchronize()
+    result["reverse_field"] = grad[:n_owned].cpu().numpy()
+    result["reverse_force"] = np.stack([f[k][:n_owned].cpu().numpy() for k in range(3)], axis=1)
+    result["ghost_gid"] = ctx.download("global_id", n_total_now)[n_owned:]
     gathered = [None] * world
     dist.all_gather_object(gathered, result)
     if rank == 0:
@@ -175,3 +201,15 @@ def test_two_gpus_equal_the_undivided_system(tmp_path, which):
     assert np.abs(d).max() < 1e-4      # fp32 pair forces: round-off grows along the (chaotic) trajectory
     assert parts[0]["rebuilds"] >= 4
     assert parts[0]["worst"] <= (0.5 * s.skin) ** 2 * 1.2
+    if which == "native":
+        # two bricks are each other's only neighbour rank: one message each way per exchange
+        assert all(p["peers"]["ranks"] == [1 - r] and p["peers"]["messages_per_exchange"] == 2 for r, p in enumerate(parts))
+        assert all(p["forward_ok_4"] and p["forward_ok_8"] for p in parts)
+        copies = np.zeros(s.n)
+        for p in parts:
+            np.add.at(copies, p["ghost_gid"], 1.0)             # how often each atom is a ghost somewhere
+        assert copies.max() >= 1
+        for p in parts:
+            want = copies[p["gid"]][:, None] * np.array([1.0, 2.0, 3.0])
+            assert np.array_equal(p["reverse_field"], want)
+            assert np.array_equal(p["reverse_force"], want)
