@@ -33,6 +33,7 @@ struct Grid {
     float cellw[3];     // cell width per axis (length units); the x cells are finer than the y and z cells
     float r_pad;        // list radius plus a rounding margin: the reach used to prune cell rows
     float x_reach;      // widest half window along x (stencil * width of an unrefined cell, a hair less)
+    float band_search;  // the band of the list search (fp32 coordinates relative to the grid origin, image shifts added)
 };
 
 struct Status {
@@ -45,7 +46,7 @@ struct Status {
     unsigned long long interior;   // of which the partner is owned
     unsigned long long select_count;
     unsigned int dropped;          // owned atoms found outside the brick by a sort that removes them
-    unsigned int reserved;
+    unsigned int reserved[3];
 };
 
 __host__ __device__ inline unsigned int cell_of(unsigned int fixed, int wrap, int nc) {

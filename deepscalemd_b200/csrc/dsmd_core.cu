@@ -22,6 +22,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -95,7 +96,7 @@ __global__ void k_cell_keys(Grid g, Brick brick, int first, int n_owned, int n_t
 __global__ void k_reorder(Grid g, int first, int n_owned, int n_total, const unsigned* __restrict__ key,
                           const int* __restrict__ val, RealArrays src, RealArrays dst, const int* __restrict__ type_src,
                           const int* __restrict__ gid_src, int* __restrict__ type_dst, int* __restrict__ gid_dst,
-                          int4* __restrict__ pq, float* __restrict__ qf, double* __restrict__ xref,
+                          int4* __restrict__ pq, float4* __restrict__ pf, float* __restrict__ qf, double* __restrict__ xref,
                           double* __restrict__ yref, double* __restrict__ zref, int* __restrict__ cell_start,
                           int* __restrict__ ghost_slot) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -117,6 +118,10 @@ __global__ void k_reorder(Grid g, int first, int n_owned, int n_total, const uns
     p.z = static_cast<int>(dsmd::to_fixed(r[2], 2, g, bad));
     p.w = ty;
     pq[s] = p;
+    // the list search's copy: single-precision offsets from the grid origin (the value of the fixed-point coordinate)
+    pf[s] = make_float4(__uint2float_rn(static_cast<unsigned>(p.x)) * g.scale[0],
+                        __uint2float_rn(static_cast<unsigned>(p.y)) * g.scale[1],
+                        __uint2float_rn(static_cast<unsigned>(p.z)) * g.scale[2], 0.f);
     qf[s] = static_cast<float>(r[10]);
     if (s < n_owned) {
         xref[s] = r[0];
@@ -163,18 +168,24 @@ __device__ __forceinline__ bool within_list_fp64(const Grid& g, const double* __
 }
 
 // One thread per owned atom. The cell rows of the stencil are contiguous runs of slots (cells are sorted x fastest), so
-// a row costs two table reads and a linear scan. The candidate test runs on the fixed-point coordinates in fp32; only
-// results inside the rounding band around the list radius are re-decided in fp64 on the caller's double positions, which
-// makes list membership identical to an fp64 search. Owned partners are scanned first, then ghosts, so the first
-// deg_int entries of a row are the interior part.
-__global__ void __launch_bounds__(kBuildThreads)
-k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, const double* __restrict__ x,
-             const double* __restrict__ y, const double* __restrict__ z, const int* __restrict__ gid,
-             ExclusionTable excl, const int* __restrict__ cell_start, unsigned* __restrict__ nbr, int stride,
-             int* __restrict__ deg, int* __restrict__ deg_int, Status* st) {
+// a row costs two table reads and a linear scan. The candidate test runs in fp32 on `pf`, a copy of the positions as
+// single-precision offsets from the grid origin written at the sort; the periodic image of a cell row (or of the piece
+// of a row window that lies across the box boundary) is one shift of the CENTRE's coordinate per row, so a candidate
+// costs three subtractions, no integer arithmetic and no conversion. Results inside the rounding band around the list
+// radius are re-decided in fp64 on the caller's double positions, which makes list membership identical to an fp64
+// search. Owned partners are scanned first, then ghosts, so the first deg_int entries of a row are the interior part.
+// 16 resident blocks of 64 threads: the 64-register budget that gives is worth more than the registers (measured: 2.76 ms
+// against 4.24 ms per build at 4 M atoms with 110 registers and 8 blocks).
+__global__ void __launch_bounds__(kBuildThreads, 16)
+k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, const float4* __restrict__ pf,
+             const double* __restrict__ x, const double* __restrict__ y, const double* __restrict__ z,
+             const int* __restrict__ gid, ExclusionTable excl, const int* __restrict__ cell_start,
+             unsigned* __restrict__ nbr, int stride, int* __restrict__ deg, int* __restrict__ deg_int, Status* st) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const bool active = i < n_owned;   // lanes past the end stay for the warp sums at the bottom
     const int4 pi = active ? pq[i] : make_int4(0, 0, 0, 0);
+    const float4 fi = active ? pf[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const int cx = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.x), g.wrap[0], g.nc[0]));
     const int cy = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.y), g.wrap[1], g.nc[1]));
     const int cz = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(pi.z), g.wrap[2], g.nc[2]));
     const int S = g.stencil;
@@ -187,51 +198,102 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
             ex_end = excl.offsets[gi + 1];
         }
     }
-    int count = 0, interior = 0;
+    const float hi_band = g.r2_list + g.band_search;
+    const float in_band = g.r2_list - g.band_search;
+    // every hit of an atom with exclusions takes the slow path, which looks the partner up in the exclusion table
+    const float lo_band = ex_end > ex_begin ? -1.0f : in_band;
+    const float box_x = static_cast<float>(g.box[0]), box_y = static_cast<float>(g.box[1]), box_z = static_cast<float>(g.box[2]);
+    unsigned* dst = nbr + base;   // next entry of this atom's row (entries of a row are 32 words apart)
+    unsigned* const dst_end = dst + static_cast<size_t>(stride) * 32;
+    int interior = 0;
     unsigned rechecked = 0;
     const int n_seg = !active ? 0 : (n_total > n_owned ? 2 : 1);
+    // The x window of a cell row is the chord of the list sphere at the row's distance from the atom in the y-z plane
+    // (dsmd::row_window spells the rule out): the distance has one term per axis, each a function of the cell offset and
+    // of the atom's place inside its home cell, so the z term is worked out per layer and the y term per row.
+    const unsigned ux = static_cast<unsigned>(pi.x), uy = static_cast<unsigned>(pi.y), uz = static_cast<unsigned>(pi.z);
+    const float ty = __uint2float_rn(g.wrap[1] ? uy : uy << 1) * (static_cast<float>(g.nc[1]) * 2.3283064e-10f);
+    const float tz = __uint2float_rn(g.wrap[2] ? uz : uz << 1) * (static_cast<float>(g.nc[2]) * 2.3283064e-10f);
+    const float in_y = fminf(fmaxf(ty - static_cast<float>(cy), 0.f), 1.f);   // place inside the home cell, 0 .. 1
+    const float in_z = fminf(fmaxf(tz - static_cast<float>(cz), 0.f), 1.f);
+    const float reach2 = g.r_pad * g.r_pad;
+    const float units_per_length = 1.0f / g.scale[0];
     for (int seg = 0; seg < n_seg; ++seg) {
         for (int dz = -S; dz <= S; ++dz) {
             int zc = cz + dz;
-            if (g.wrap[2]) { if (zc < 0) zc += g.nc[2]; else if (zc >= g.nc[2]) zc -= g.nc[2]; }
+            float zi = fi.z;   // the centre as the atoms of this cell row see it
+            if (g.wrap[2]) { if (zc < 0) { zc += g.nc[2]; zi += box_z; } else if (zc >= g.nc[2]) { zc -= g.nc[2]; zi -= box_z; } }
             else if (zc < 0 || zc >= g.nc[2]) continue;
+            float gz = dz > 0 ? (static_cast<float>(dz) - in_z) : (dz < 0 ? (in_z - static_cast<float>(dz + 1)) : 0.f);
+            gz = fmaxf(gz - 1e-4f, 0.f) * g.cellw[2];   // 1e-4 of a cell: rounding of the in-cell position
+            const float room2 = reach2 - gz * gz;
+            if (room2 <= 0.f) continue;
             for (int dy = -S; dy <= S; ++dy) {
                 int yc = cy + dy;
-                if (g.wrap[1]) { if (yc < 0) yc += g.nc[1]; else if (yc >= g.nc[1]) yc -= g.nc[1]; }
+                float yi = fi.y;
+                if (g.wrap[1]) { if (yc < 0) { yc += g.nc[1]; yi += box_y; } else if (yc >= g.nc[1]) { yc -= g.nc[1]; yi -= box_y; } }
                 else if (yc < 0 || yc >= g.nc[1]) continue;
+                float gy = dy > 0 ? (static_cast<float>(dy) - in_y) : (dy < 0 ? (in_y - static_cast<float>(dy + 1)) : 0.f);
+                gy = fmaxf(gy - 1e-4f, 0.f) * g.cellw[1];
+                const float chord2 = room2 - gy * gy;
+                if (chord2 <= 0.f) continue;
+                // half window: the chord, never wider than the stencil, rounded outwards to whole x cells (r_pad carries
+                // 1e-4 of slack, far more than the approximate square root gives away)
+                const float hw = fminf(chord2 * rsqrtf(chord2), g.x_reach);
+                const unsigned hw_fixed = static_cast<unsigned>(hw * units_per_length) + 2u;
                 const int row = seg * g.ncells + (zc * g.nc[1] + yc) * g.nc[0];
                 dsmd::RowWindow win;
-                if (!dsmd::row_window(g, pi, cy, cz, dy, dz, win)) continue;
-                const int a0 = win.a0, b0 = win.b0, a1 = win.a1, b1 = win.b1;
+                win.a1 = 0;
+                win.b1 = -1;
+                if (g.wrap[0]) {
+                    const int c_lo = static_cast<int>(dsmd::cell_of(ux - hw_fixed, 1, g.nc[0]));
+                    const int c_hi = static_cast<int>(dsmd::cell_of(ux + hw_fixed, 1, g.nc[0]));
+                    if (c_lo <= c_hi) { win.a0 = c_lo; win.b0 = c_hi; }
+                    else { win.a0 = 0; win.b0 = c_hi; win.a1 = c_lo; win.b1 = g.nc[0] - 1; }
+                } else {
+                    const long long lo = static_cast<long long>(ux) - hw_fixed, hi = static_cast<long long>(ux) + hw_fixed;
+                    win.a0 = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(lo < 0 ? 0 : lo), 0, g.nc[0]));
+                    win.b0 = static_cast<int>(dsmd::cell_of(static_cast<unsigned>(hi > 2147483647ll ? 2147483647ll : hi), 0, g.nc[0]));
+                }
+                const bool two = win.b1 >= win.a1;   // the x window crosses the periodic boundary: [0, b0] and [a1, nc - 1]
                 for (int part = 0; part < 2; ++part) {
-                    const int a = part == 0 ? a0 : a1, b = part == 0 ? b0 : b1;
+                    const int a = part == 0 ? win.a0 : win.a1, b = part == 0 ? win.b0 : win.b1;
                     if (b < a) continue;
+                    // the piece the centre's own cell is not in holds images one box length away
+                    float xi = fi.x;
+                    if (two) {
+                        const bool centre_low = cx <= win.b0;
+                        if (part == 0 && !centre_low) xi -= box_x;
+                        if (part == 1 && centre_low) xi += box_x;
+                    }
                     const int s_begin = cell_start[row + a], s_end = cell_start[row + b + 1];
                     for (int s = s_begin; s < s_end; ++s) {
-                        const int4 pj = __ldg(&pq[s]);
-                        const float fx = dsmd::fixed_delta(pj.x, pi.x, g.scale[0]);
-                        const float fy = dsmd::fixed_delta(pj.y, pi.y, g.scale[1]);
-                        const float fz = dsmd::fixed_delta(pj.z, pi.z, g.scale[2]);
-                        const float r2 = fx * fx + fy * fy + fz * fz;
-                        if (r2 >= g.r2_list + g.band || s == i) continue;
-                        if (r2 >= g.r2_list - g.band) {
-                            ++rechecked;
-                            if (!within_list_fp64(g, x, y, z, i, s)) continue;
+                        const float4 c = __ldg(&pf[s]);
+                        const float dx = c.x - xi, ddy = c.y - yi, ddz = c.z - zi;
+                        const float r2 = dx * dx + ddy * ddy + ddz * ddz;
+                        if (r2 < hi_band && s != i) {
+                            unsigned entry = static_cast<unsigned>(s);
+                            if (r2 >= lo_band) {   // inside the rounding band, or an atom with exclusions: the slow, exact way
+                                if (r2 >= in_band) {
+                                    ++rechecked;
+                                    if (!within_list_fp64(g, x, y, z, i, s)) continue;
+                                }
+                                if (ex_end > ex_begin) {
+                                    const int gj = gid[s];
+                                    for (int e = ex_begin; e < ex_end; ++e)
+                                        if (excl.partners[e] == gj) entry |= kExclBit;
+                                }
+                            }
+                            if (dst < dst_end) *dst = entry;
+                            dst += 32;
                         }
-                        unsigned entry = static_cast<unsigned>(s);
-                        if (ex_end > ex_begin) {
-                            const int gj = gid[s];
-                            for (int e = ex_begin; e < ex_end; ++e)
-                                if (excl.partners[e] == gj) entry |= kExclBit;
-                        }
-                        if (count < stride) nbr[base + static_cast<size_t>(count) * 32] = entry;
-                        ++count;
                     }
                 }
             }
         }
-        if (seg == 0) interior = count;
+        if (seg == 0) interior = static_cast<int>((dst - (nbr + base)) >> 5);
     }
+    const int count = static_cast<int>((dst - (nbr + base)) >> 5);
     if (active) {
         deg[i] = min(count, stride);
         deg_int[i] = min(interior, stride);
@@ -713,6 +775,7 @@ struct dsmd_ctx {
     int* gid[2] = {};
     int cur = 0;
     int4* pq = nullptr;
+    float4* pf = nullptr;          // positions as fp32 offsets from the grid origin, as of the last sort (list search)
     float* qf = nullptr;
     double* ref[3] = {};
     unsigned* key[2] = {};
@@ -810,6 +873,8 @@ int make_grid(dsmd_ctx* c) {
     }
     // Cells at least R / stencil wide (a hair more, so that fixed-point rounding cannot push a partner one cell too far).
     int stencil = 2;
+    int x_refine = kXRefine;
+    if (const char* e = std::getenv("DSMD_XREFINE")) x_refine = std::max(1, std::min(8, std::atoi(e)));
     for (int attempt = 0; attempt < 2; ++attempt) {
         bool ok = true;
         for (int a = 0; a < 3; ++a) {
@@ -831,7 +896,7 @@ int make_grid(dsmd_ctx* c) {
     // cells: finer x cells (kXRefine per unrefined cell) make the windows tighter at no cost per row.
     g.x_reach = static_cast<float>(g.stencil * (1.0 / (g.inv_len[0] * g.nc[0])) * 0.9999999);
     {
-        int refine = kXRefine;
+        int refine = x_refine;
         while (refine > 1 && (static_cast<int64_t>(g.nc[0]) * refine > 4096 ||
                               2 * static_cast<int64_t>(g.nc[0]) * refine * g.nc[1] * g.nc[2] + 1 > (1ll << 26)))
             refine >>= 1;
@@ -849,6 +914,10 @@ int make_grid(dsmd_ctx* c) {
         max_len = std::max(max_len, 1.0 / g.inv_len[a]);
     }
     g.r_pad = static_cast<float>(R * (1.0 + 1e-4) + 8.0 * max_len * 1.2e-7);
+    // Rounding band of the fp32 search: a coordinate is an offset of up to max_len from the grid origin, the centre's may
+    // carry one more box length (image shift), so each carries a few ulp of 2 max_len; the squares and sums add a few
+    // ulp of R^2; the fixed-point grid itself one unit per coordinate. Everything inside the band is re-decided in fp64.
+    g.band_search = static_cast<float>(1.1920929e-7 * (24.0 * R * max_len + 16.0 * R * R) + 8.0 * R * max_scale);
     c->grid_valid = true;
     return DSMD_OK;
 }
@@ -928,7 +997,7 @@ int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s, int64_t n_removed = 0
         k_reorder<<<blocks_for(n, kThreads), kThreads, 0, s>>>(
             c->grid, static_cast<int>(first), static_cast<int>(c->n_owned), static_cast<int>(c->n_total), c->key[1],
             c->val[1], arrays_of(c, from), arrays_of(c, to), c->type[from], c->gid[from], c->type[to], c->gid[to], c->pq,
-            c->qf, c->ref[0], c->ref[1], c->ref[2], c->cell_start, c->ghost_slot);
+            c->pf, c->qf, c->ref[0], c->ref[1], c->ref[2], c->cell_start, c->ghost_slot);
         DSMD_LAUNCHED(c);
         const int table = 2 * c->grid.ncells + 1;
         const int64_t kept = n - n_removed;
@@ -996,6 +1065,7 @@ int dsmd_create(int device, int64_t capacity, dsmd_ctx** out) {
         DSMD_CUDA(c, cudaMalloc(&c->val[set], sizeof(int) * capacity));
     }
     DSMD_CUDA(c, cudaMalloc(&c->pq, sizeof(int4) * capacity));
+    DSMD_CUDA(c, cudaMalloc(&c->pf, sizeof(float4) * capacity));
     DSMD_CUDA(c, cudaMalloc(&c->qf, sizeof(float) * capacity));
     for (int a = 0; a < 3; ++a) DSMD_CUDA(c, cudaMalloc(&c->ref[a], sizeof(double) * capacity));
     DSMD_CUDA(c, cudaMalloc(&c->ghost_slot, sizeof(int) * capacity));
@@ -1024,7 +1094,7 @@ void dsmd_destroy(dsmd_ctx* c) {
         for (int f = 0; f < kNumReal; ++f) cudaFree(c->real[set][f]);
         cudaFree(c->type[set]); cudaFree(c->gid[set]); cudaFree(c->key[set]); cudaFree(c->val[set]);
     }
-    cudaFree(c->pq); cudaFree(c->qf);
+    cudaFree(c->pq); cudaFree(c->pf); cudaFree(c->qf);
     for (int a = 0; a < 3; ++a) cudaFree(c->ref[a]);
     cudaFree(c->ghost_slot); cudaFree(c->cell_start); cudaFree(c->nbr); cudaFree(c->deg); cudaFree(c->deg_int);
     cudaFree(c->cub_temp); cudaFree(c->c6c12); cudaFree(c->ewald); cudaFree(c->excl_off); cudaFree(c->excl_partner);
@@ -1292,7 +1362,7 @@ int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
         { const int rc = ensure_list(c, c->stride); if (rc) return rc; }
         ExclusionTable ex{c->excl_off, c->excl_partner, static_cast<int>(c->excl_n_global)};
         k_build_list<<<blocks_for(c->n_owned, kBuildThreads), kBuildThreads, 0, s>>>(
-            c->grid, static_cast<int>(c->n_owned), static_cast<int>(c->n_total), c->pq, c->real[c->cur][0],
+            c->grid, static_cast<int>(c->n_owned), static_cast<int>(c->n_total), c->pq, c->pf, c->real[c->cur][0],
             c->real[c->cur][1], c->real[c->cur][2], c->gid[c->cur], ex, c->cell_start, c->nbr, c->stride, c->deg,
             c->deg_int, c->status);
         DSMD_LAUNCHED(c);
