@@ -95,6 +95,16 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def clocks_max_ghz(device_index: int) -> float:
+    """clocks.max.sm of the device in GHz (for the nominal fp32 peak: SMs x 128 lanes x 2 flops x clock)."""
+    try:
+        out = subprocess.run(["nvidia-smi", f"--id={device_index}", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=10).stdout.strip()
+        return float(out.splitlines()[0]) * 1e-3 if out else 1.965
+    except (OSError, ValueError, subprocess.SubprocessError):
+        return 1.965
+
+
 def fcc_for(workload: str):
     from deepscalemd_b200 import synthetic as syn
     cells = {"lj_4m": 100, "lj_500k": 50, "lj_256k": 40, "lj_108k": 30, "lj_32k": 20}[workload]
@@ -217,7 +227,7 @@ def reference_arm(args):
     if rank != 0:
         return
     use_all_host_cores()
-    base = run_cpu_baseline(args.steps, args.warmup, budget_s=170.0)
+    base = run_cpu_baseline(args.steps, args.warmup, budget_s=args.cpu_budget_s)
     full = base["atoms"] == 4_000_000
     config = {"workload": WORKLOAD_NAME, "ns_per_day": ns_per_day(base["ms_per_step"] * (1.0 if full else 4e6 / base["atoms"]))}
     if not full:
@@ -353,16 +363,53 @@ def single_gpu(args):
                                               "frac_hbm": interface_bytes / (t_interface * 1e-3) / 1e9 / hbm_peak}
         eb.close()
         del sx, sy, sz, ix, iy, iz, owner, shift, img
+    # the other named shapes, kernels only (list build and pair kernel at full size): the 1,048,576-atom binary mixture
+    # (two types, explicit pair table) and the 648,000-atom rigid-water geometry box (LJ + real-space Ewald, exclusions)
+    if args.workload == "lj_4m":
+        from deepscalemd_b200 import synthetic as syn
+        for name, system, coulomb in (("kob_andersen_1m", syn.kob_andersen(1_048_576, seed=5), False),
+                                      ("water_648k", syn.water_box(60, seed=3), True)):
+            c2 = capi.Context(system.n)
+            c2.set_box(system.box)
+            c2.set_pair_params(system.eps, system.sig, system.cutoff, system.skin)
+            if coulomb:
+                c2.set_coulomb(True)
+            if system.exclusions is not None:
+                c2.set_exclusions(system.n, system.exclusions)
+            c2.upload(system.pos, mass=system.mass, types=system.types, charge=system.charge)
+            c2.build_neighbor_list(stream)
+            st2 = c2.list_stats()
+            c2.compute_forces(capi.PHASE_FULL, True, stream)
+            cut2 = c2.read_scalars(stream)["pairs_in_cutoff"]
+            list2 = st2["directed_entries"] / 2
+            tp = time_calls(lambda: c2.compute_forces(capi.PHASE_FULL, False, stream), 10, stream)
+            tb = time_calls(lambda: c2.build_neighbor_list(stream), 3, stream)
+            fl = 8.0 * list2 + (19.0 + (9.0 if coulomb else 0.0)) * cut2
+            by = 16.0 * system.n + 4.0 * list2 + 24.0 * system.n + (4.0 * system.n if coulomb else 0.0)
+            bb = 16.0 * system.n + 4.0 * list2 + 8.0 * system.n / 32
+            kernels[name] = {
+                "atoms": system.n, "pairs_listed": list2, "pairs_in_cutoff": cut2,
+                "pair_forces": {"ms": tp, "tflops": fl / (tp * 1e-3) / 1e12, "frac_fp32": fl / (tp * 1e-3) / 1e12 / fp32_peak_tflops,
+                                "gbs": by / (tp * 1e-3) / 1e9, "frac_hbm": by / (tp * 1e-3) / 1e9 / hbm_peak},
+                "list_build_total": {"ms": tb, "gbs": bb / (tb * 1e-3) / 1e9, "frac_hbm": bb / (tb * 1e-3) / 1e9 / hbm_peak},
+            }
+            c2.close()
     pk = kernels["pair_forces"]
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
     roofline = {
-        "kernel": "k_pair (LJ, full list, forces only)", "bound": "hbm", "achieved": pk["gbs"], "peak": hbm_peak,
-        "unit": "GB/s", "frac": pk["frac_hbm"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
+        "kernel": "k_pair (LJ, full list, forces only)", "bound": "fp32", "achieved": pk["tflops"], "peak": fp32_peak_tflops,
+        "unit": "TFLOP/s", "frac": pk["frac_fp32"],
+        "peak_source": "measured in this run (independent FMA chains on every SM); no fp32 CUDA-core figure in MEASURED_PEAKS.json",
+        "peak_nominal": sms * 128 * 2 * clocks_max_ghz(0) * 1e-3,   # TFLOP/s: SMs x 128 fp32 lanes x 2 flops x max SM clock
         # dram__bytes_read + dram__bytes_write of one k_pair launch, from the ncu capture of the 500,000-atom case
-        # (profiles/k_pair_k_build_list_lj_500k_ncu_full.md: 174.1 MB) scaled by the atom count
+        # (profiles/k_pair_k_build_list_lj_500k_ncu_full.md: 171.4 MB) scaled by the atom count
         "traffic": NCU_PAIR_TRAFFIC_BYTES_PER_ATOM * s.n,
         "algorithmic_bytes_per_launch": pair_bytes, "algorithmic_flops_per_launch": pair_flops,
-        "fp32": {"achieved_tflops": pk["tflops"], "peak_tflops": fp32_peak_tflops,
-                 "peak_source": "measured in this run (independent FMA chains on every SM)", "frac": pk["frac_fp32"]},
+        "hbm": {"achieved": pk["gbs"], "peak": hbm_peak, "unit": "GB/s", "frac": pk["frac_hbm"],
+                "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)"},
+        "list_build": {"kernel": "bin + sort + reorder + k_build_list", "bound": "hbm", "ms": t_build,
+                       "achieved": kernels["list_build_total"]["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                       "frac": kernels["list_build_total"]["frac_hbm"], "algorithmic_bytes_per_launch": build_bytes},
     }
 
     # -- end to end: the host-buffer force call (upload positions, pack or rebuild, forces, download forces) --------------
@@ -431,6 +478,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="lj_4m")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget-s", type=float, default=170.0,
+                    help="time the reference arm may take: it runs the 4,000,000-atom system when that fits, else a smaller sample")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

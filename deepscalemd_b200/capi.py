@@ -24,7 +24,7 @@ SYMBOLS = [
     "dsmd_create", "dsmd_destroy", "dsmd_last_error", "dsmd_set_box", "dsmd_set_pair_params", "dsmd_set_coulomb",
     "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
     "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned", "dsmd_sort_owned_in_brick",
-    "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq",
+    "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq", "dsmd_max_displacement_sq_lagged",
     "dsmd_displacement_word", "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_scale_velocities",
     "dsmd_run_nve",
     "dsmd_forces_host", "dsmd_launch_count", "dsmd_fma_probe", "dsmd_halo_pack", "dsmd_halo_unpack", "dsmd_halo_select",
@@ -35,7 +35,7 @@ SYMBOLS = [
     "dsmd_kinetic_energy_noalloc", "dsmd_nccl_unique_id", "dsmd_domain_create",
     "dsmd_domain_destroy", "dsmd_domain_last_error", "dsmd_domain_rebuild", "dsmd_domain_refresh", "dsmd_domain_run",
     "dsmd_domain_stats", "dsmd_domain_profile", "dsmd_domain_set_wait_limit", "dsmd_domain_abort",
-    "dsmd_domain_reverse_forces", "dsmd_domain_exchange_field", "dsmd_domain_peers",
+    "dsmd_domain_reverse_forces", "dsmd_domain_exchange_field", "dsmd_domain_peers", "dsmd_domain_reduce",
 ]
 
 _lib = None

@@ -384,6 +384,9 @@ __global__ void k_pack(Grid g, int first, int count, int n_owned, double* __rest
         if (s < n_owned) {
             const double ddx = px - xref[s], ddy = py - yref[s], ddz = pz - zref[s];
             d2 = ddx * ddx + ddy * ddy + ddz * ddz;
+            // a position that is no number must not vanish in the block maximum (fmax drops NaN): it forces a rebuild,
+            // and the rebuild reports the atom
+            if (!(d2 == d2)) d2 = __longlong_as_double(0x7FF0000000000000ll);
         }
     }
     block_max_to_status(d2, st);
@@ -802,6 +805,9 @@ struct dsmd_ctx {
     Status* h_status = nullptr;     // pinned
     double* h_scalars = nullptr;    // pinned
     unsigned long long* h_disp[2] = {};   // pinned, lagged displacement read-back
+    long long disp_epoch[2] = {-1, -1};   // list build each read-back slot was measured under
+    int disp_pending = -1;                // slot queued by the previous lagged query
+    long long build_epoch = 0;            // bumped by every list build (new reference positions)
     cudaEvent_t disp_event[2] = {};
     unsigned char* flag = nullptr;
     unsigned long long* offsets64 = nullptr;
@@ -1380,6 +1386,7 @@ int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
     c->stat_entries = static_cast<int64_t>(c->h_status->entries);
     c->stat_interior = static_cast<int64_t>(c->h_status->interior);
     c->stat_rechecked = static_cast<int>(c->h_status->rechecked);
+    ++c->build_epoch;
     DSMD_CUDA(c, cudaMemsetAsync(c->status, 0, sizeof(Status), s));   // displacement word restarts at zero
     c->list_valid = true;
     return DSMD_OK;
@@ -1462,6 +1469,28 @@ int dsmd_max_displacement_sq(dsmd_ctx* c, double* out, void* stream) {
     *out = v;
     if (c->h_status->out_of_domain)
         return fail(c, DSMD_ERR_OUT_OF_DOMAIN, "an atom left the subdomain + halo, or has a NaN position");
+    return DSMD_OK;
+}
+
+int dsmd_max_displacement_sq_lagged(dsmd_ctx* c, double* out, void* stream) {
+    if (!c || !out) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    *out = -1.0;
+    if (c->disp_pending >= 0) {
+        const int slot = c->disp_pending;
+        DSMD_CUDA(c, cudaEventSynchronize(c->disp_event[slot]));   // queued one call ago: long finished
+        if (c->disp_epoch[slot] == c->build_epoch) {   // else it was measured against reference positions that are gone
+            double v;
+            const unsigned long long bits = *c->h_disp[slot];
+            std::memcpy(&v, &bits, sizeof(v));
+            *out = v;
+        }
+    }
+    const int next = c->disp_pending == 0 ? 1 : 0;
+    DSMD_CUDA(c, cudaMemcpyAsync(c->h_disp[next], &c->status->max_disp2, sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaEventRecord(c->disp_event[next], s));
+    c->disp_epoch[next] = c->build_epoch;
+    c->disp_pending = next;
     return DSMD_OK;
 }
 

@@ -892,6 +892,17 @@ int dsmd_domain_exchange_field(dsmd_domain* d, void* device_data, int64_t rows, 
     return exchange_field_typed<double>(d, static_cast<double*>(device_data), static_cast<int>(width), reverse != 0, s);
 }
 
+int dsmd_domain_reduce(dsmd_domain* d, double* values, int n, int op, void* stream) {
+    if (!d || !values || n < 1 || n > 16 || (op != 0 && op != 1)) return DSMD_ERR_INVALID;
+    if (d->world == 1) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    double* scratch = d->send_pos;   // idle between exchanges; ordered on the caller's stream like them
+    DOM_CUDA(d, cudaMemcpyAsync(scratch, values, sizeof(double) * n, cudaMemcpyHostToDevice, s));
+    DOM_NCCL(d, g_nccl.AllReduce(scratch, scratch + 16, n, ncclFloat64, op == 0 ? ncclSum : ncclMax, d->comm, s));
+    DOM_CUDA(d, cudaMemcpyAsync(values, scratch + 16, sizeof(double) * n, cudaMemcpyDeviceToHost, s));
+    return wait_stream(d, s, "reduction over the ranks");
+}
+
 int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_accel, double hi_frac, void* stream) {
     if (!d || n_steps < 0) return DSMD_ERR_INVALID;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -103,6 +103,53 @@ public:
         return d2;
     }
 
+    // ForceCalculatorCUDA::compute_max_displacement_lagged (src/force_calculator_cuda.cu:6723-6764): the value of the
+    // previous call (negative: none yet for the current reference positions); the host does not wait for this step.
+    Real compute_max_displacement_lagged(size_t, const SimulationBox&) {
+        check(ctx_, dsmd_pack_positions(ctx_, 0, owned(), force_stream_), "dsmd_pack_positions");
+        double d2 = -1.0;
+        check(ctx_, dsmd_max_displacement_sq_lagged(ctx_, &d2, force_stream_), "dsmd_max_displacement_sq_lagged");
+        return d2;
+    }
+
+    // ParticleInfo::Provider (ForceCalculatorCUDA::particle_info_view / resize_particle_info,
+    // src/force_calculator_cuda.cu:4143-4216) for an engine that brings its own halo library: the decomposition library's
+    // view / result types are the engine's, so they are template parameters here; a View needs the members count, x, y, z,
+    // vx, vy, vz, fx, fy, fz, mass, charge, type, global_id, a Result the members view and reallocated. The context's
+    // arrays never move (they are allocated for the capacity given at creation), so nothing is ever reallocated; asking
+    // for more than the capacity throws.
+    template <class View>
+    View particle_info_view_as(size_t count) {
+        if (count > capacity()) throw std::runtime_error("particle_info_view: more atoms than the context's capacity");
+        View v{};
+        v.count = count;
+        v.x = get_device_x(); v.y = get_device_y(); v.z = get_device_z();
+        v.vx = get_device_vx(); v.vy = get_device_vy(); v.vz = get_device_vz();
+        v.fx = get_device_fx(); v.fy = get_device_fy(); v.fz = get_device_fz();
+        v.mass = get_device_mass(); v.charge = get_device_charge();
+        v.type = get_device_type(); v.global_id = get_device_global_id();
+        return v;
+    }
+    template <class Result, class View>
+    Result resize_particle_info_as(size_t required, size_t preserve_count) {
+        if (required > capacity()) throw std::runtime_error("resize_particle_info: more atoms than the context's capacity");
+        int64_t n_owned = 0, n_total = 0;
+        dsmd_counts(ctx_, &n_owned, &n_total);
+        if (static_cast<int64_t>(required) != n_total)
+            check(ctx_, dsmd_set_counts(ctx_, std::min<int64_t>(n_owned, static_cast<int64_t>(required)), static_cast<int64_t>(required)),
+                  "dsmd_set_counts");
+        (void)preserve_count;   // every atom below the new count is preserved: the arrays stay where they are
+        Result r{};
+        r.view = particle_info_view_as<View>(required);
+        r.reallocated = false;
+        return r;
+    }
+    size_t capacity() const {
+        int64_t cap = 0;
+        if (ctx_) dsmd_capacity(ctx_, &cap);
+        return static_cast<size_t>(cap);
+    }
+
     // ForceCalculator::compute_forces: device-resident state, FULL phase. Energy and virial are read back only when
     // asked for (set_energy_readback_needed), as the reference does.
     void compute_forces(MDSystem& system) override {
@@ -253,49 +300,79 @@ private:
     ForceCalculatorB200* calc_;
 };
 
-// HaloBackend seam (include/halo_backend.h:10-27). The exchange itself (pack kernel -> NCCL send/recv -> unpack kernel) is
-// supplied as a callable, so that the transport (the engine's communicator) stays the engine's.
+// HaloBackend seam (include/halo_backend.h:10-27) over the native domain code (dsmd_domain_*): on a rebuild step the
+// whole rebuild (migration, owned sort, ghost plan and records, list), otherwise the positions-only refresh. A callable
+// given at construction replaces that (an engine that keeps its own transport).
 class HaloBackendB200 : public HaloBackend {
 public:
     using Exchange = std::function<bool(ForceCalculatorB200&, bool rebuild)>;   // returns: ghost layout changed
+    explicit HaloBackendB200(dsmd_domain* domain) : domain_(domain) {}
     explicit HaloBackendB200(Exchange exchange) : exchange_(std::move(exchange)) {}
     bool try_gpu_direct_halo(MDSystem&, ForceCalculator* force_calc, bool& should_rebuild) override {
         auto* calc = dynamic_cast<ForceCalculatorB200*>(force_calc);
-        if (!calc || !exchange_) return false;
-        if (exchange_(*calc, should_rebuild)) should_rebuild = true;
+        if (!calc) return false;
+        if (exchange_) {
+            if (exchange_(*calc, should_rebuild)) should_rebuild = true;
+            return true;
+        }
+        if (!domain_) return false;
+        if (should_rebuild) {
+            const int rc = dsmd_domain_rebuild(domain_, calc->get_force_stream());
+            if (rc != DSMD_OK) throw std::runtime_error(std::string("dsmd_domain_rebuild: ") + dsmd_domain_last_error(domain_));
+            calc->nlist_dirty_ = false;   // the rebuild ends with the list build
+        } else {
+            const int rc = dsmd_domain_refresh(domain_, calc->get_force_stream());
+            if (rc != DSMD_OK) throw std::runtime_error(std::string("dsmd_domain_refresh: ") + dsmd_domain_last_error(domain_));
+        }
         return true;
     }
     void on_post_halo(MDSystem&, ForceCalculator*, bool, bool) override {}
     const char* name() const override { return "b200-nccl"; }
 
 private:
+    dsmd_domain* domain_ = nullptr;
     Exchange exchange_;
 };
 
-// CommBackend seam (include/comm_backend.h:12-38): scalar reductions through caller-supplied callables (ncclAllReduce on a
-// few doubles, or MPI), single rank by default.
+// CommBackend seam (include/comm_backend.h:12-38) over the native domain code: scalar reductions are dsmd_domain_reduce
+// (NCCL all-reduce of a few doubles); migration is part of the rebuild that HaloBackendB200 runs on the same step, so
+// migrate_particles_if_needed only reports that ownership may change. Callables, when set, replace the reductions.
 class CommBackendB200 : public CommBackend {
 public:
+    CommBackendB200() = default;
+    CommBackendB200(dsmd_domain* domain, bool several_ranks, cudaStream_t stream = nullptr)
+        : distributed(several_ranks), domain_(domain), stream_(stream) {}
     std::function<double(double)> max_fn, sum_fn;
     std::function<bool(MDSystem&, ForceCalculator*)> migrate_fn;
     bool distributed = false;
 
     bool is_distributed() const override { return distributed; }
-    void unify_rebuild_decision(bool& should_rebuild) override {
-        if (max_fn) should_rebuild = max_fn(should_rebuild ? 1.0 : 0.0) > 0.5;
-    }
+    void unify_rebuild_decision(bool& should_rebuild) override { should_rebuild = reduce(should_rebuild ? 1.0 : 0.0, 1) > 0.5; }
     bool migrate_particles_if_needed(MDSystem& system, bool should_rebuild, ForceCalculator* calc) override {
-        return should_rebuild && migrate_fn ? migrate_fn(system, calc) : false;
+        if (migrate_fn) return should_rebuild && migrate_fn(system, calc);
+        return should_rebuild && distributed;
     }
     bool is_gpu_single_rank(bool using_cuda) const override { return using_cuda && !distributed; }
-    Real max_reduce(Real v) const override { return max_fn ? max_fn(v) : v; }
-    Real sum_reduce(Real v) const override { return sum_fn ? sum_fn(v) : v; }
-    int sum_int(int v) const override { return sum_fn ? static_cast<int>(std::lround(sum_fn(v))) : v; }
-    bool all_true(bool v) const override { return max_fn ? max_fn(v ? 0.0 : 1.0) < 0.5 : v; }
+    Real max_reduce(Real v) const override { return reduce(v, 1); }
+    Real sum_reduce(Real v) const override { return reduce(v, 0); }
+    int sum_int(int v) const override { return static_cast<int>(std::lround(reduce(v, 0))); }
+    bool all_true(bool v) const override { return reduce(v ? 0.0 : 1.0, 1) < 0.5; }
     void reduce_max_force_particle(Real f, size_t id, int, Real& gf, size_t& gid) const override {
-        gf = max_fn ? max_fn(f) : f;
+        gf = reduce(f, 1);
         gid = id;   // single rank: the local particle; several ranks: the engine's MAXLOC reduction decides the owner
     }
+
+private:
+    double reduce(double v, int op) const {
+        if (op == 1 && max_fn) return max_fn(v);
+        if (op == 0 && sum_fn) return sum_fn(v);
+        if (!domain_ || !distributed) return v;
+        const int rc = dsmd_domain_reduce(domain_, &v, 1, op, stream_);
+        if (rc != DSMD_OK) throw std::runtime_error(std::string("dsmd_domain_reduce: ") + dsmd_domain_last_error(domain_));
+        return v;
+    }
+    dsmd_domain* domain_ = nullptr;
+    cudaStream_t stream_ = nullptr;
 };
 
 }  // namespace dsmd

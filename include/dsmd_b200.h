@@ -145,6 +145,11 @@ int dsmd_pack_positions(dsmd_ctx* ctx, int64_t first, int64_t count, void* strea
  * Synchronises `stream`. */
 int dsmd_max_displacement_sq(dsmd_ctx* ctx, double* out, void* stream);
 
+/* compute_max_displacement_lagged (src/force_calculator_cuda.cu:6723-6764): queues the read-back of the current value and
+ * returns the one queued by the PREVIOUS call, so the host never waits for the step in flight; negative when there is
+ * none yet, or when the list has been rebuilt since (the reference positions that value was measured against are gone). */
+int dsmd_max_displacement_sq_lagged(dsmd_ctx* ctx, double* out, void* stream);
+
 /* The device word behind it: the bit pattern of that non-negative double, 8 bytes. Bit patterns of non-negative doubles
  * order like the values, so ranks can take a MAX over it as a 64-bit integer (CommBackend::unify_rebuild_decision,
  * src/comm_backend.cpp:85) without a host round trip. Reset to zero by every list build. */
@@ -281,6 +286,10 @@ int dsmd_domain_reverse_forces(dsmd_domain* dom, void* stream);
  * reverse != 0: the rows of the ghosts are added to the rows of their owners. Queued on `stream`; collective. */
 int dsmd_domain_exchange_field(dsmd_domain* dom, void* device_data, int64_t rows, int64_t width, int element_bytes,
                                int reverse, void* stream);
+
+/* CommBackend::max_reduce / sum_reduce / sum_reduce3 (include/comm_backend.h:24-33): n host doubles (n <= 16) combined
+ * over the ranks in place, op 0 = sum, 1 = max; every rank gets the result. Collective; synchronises `stream` (bounded). */
+int dsmd_domain_reduce(dsmd_domain* dom, double* values, int n, int op, void* stream);
 
 /* The distinct neighbour ranks of this brick and how many messages one exchange of the current ghost plan posts. */
 int dsmd_domain_peers(const dsmd_domain* dom, int32_t* n_peers, int32_t peers[26], int32_t n_messages_per_exchange[1]);

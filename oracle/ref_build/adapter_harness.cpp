@@ -17,7 +17,8 @@
 extern "C" {
 
 // One force evaluation through the reference-shaped interface. eps / sig: [ntypes x ntypes]. Forces are returned by
-// global id. out_scalars = {PE, virial, Wxx, Wyy, Wzz, KE, needs_rebuild after moving one atom by 0.6 skin}.
+// global id. out_scalars = {PE, virial, Wxx, Wyy, Wzz, KE, needs_rebuild before / after moving one atom by 0.6 skin,
+// the two lagged displacement answers, PE after a rebuild through HaloBackendB200}.
 int dsmd_adapter_forces(long n, const double* x, const double* y, const double* z, const double* vx, const double* vy,
                         const double* vz, const double* mass, const double* charge, const int* type, const double box[3],
                         int ntypes, const double* eps, const double* sig, double cutoff, double skin, int do_coulomb,
@@ -100,6 +101,48 @@ int dsmd_adapter_forces(long n, const double* x, const double* y, const double* 
         const bool after = nl.needs_rebuild(p, b, static_cast<size_t>(n));
         out_scalars[6] = (before ? 1.0 : 0.0) + (after ? 2.0 : 0.0);   // expected 2
         if (std::fabs(nl.search_cutoff() - (cutoff + skin)) > 1e-12) throw std::runtime_error("search_cutoff");
+        // the lagged displacement query: nothing yet, then the value of the call before (the atom moved 0.6 skin above)
+        const double lag0 = calc.compute_max_displacement_lagged(static_cast<size_t>(n), b);
+        const double lag1 = calc.compute_max_displacement_lagged(static_cast<size_t>(n), b);
+        out_scalars[7] = lag0;
+        out_scalars[8] = lag1;
+        moved -= 0.6 * skin;   // back where it was
+        cudaMemcpy(calc.get_device_x(), &moved, sizeof(double), cudaMemcpyHostToDevice);
+        // the storage provider an external halo library would be given: a view of the device arrays, a resize in place
+        struct View { size_t count; Real *x, *y, *z, *vx, *vy, *vz, *fx, *fy, *fz, *mass, *charge; int *type, *global_id; };
+        struct Resized { View view; bool reallocated; };
+        const View view = calc.particle_info_view_as<View>(static_cast<size_t>(n));
+        const Resized grown = calc.resize_particle_info_as<Resized, View>(static_cast<size_t>(n) + 10, static_cast<size_t>(n));
+        if (view.x != calc.get_device_x() || grown.view.x != view.x || grown.reallocated || grown.view.count != static_cast<size_t>(n) + 10)
+            throw std::runtime_error("particle_info_view / resize_particle_info");
+        calc.resize_particle_info_as<Resized, View>(static_cast<size_t>(n), static_cast<size_t>(n));
+        bool refused = false;
+        try { calc.particle_info_view_as<View>(calc.capacity() + 1); } catch (const std::runtime_error&) { refused = true; }
+        if (!refused) throw std::runtime_error("a view beyond the capacity must throw");
+        // HaloBackend / CommBackend over the native domain code, one rank: a rebuild step rebuilds the list, the
+        // reductions are the identity, the energy afterwards is the one from before
+        {
+            dsmd_domain* dom = nullptr;
+            const int dims[3] = {1, 1, 1};
+            if (dsmd_domain_create(calc.context(), 0, 1, dims, box, cutoff + skin, skin, nullptr, nullptr, &dom) != DSMD_OK)
+                throw std::runtime_error("dsmd_domain_create");
+            dsmd::HaloBackendB200 halo(dom);
+            dsmd::CommBackendB200 comm(dom, false, calc.get_force_stream());
+            HaloBackend& hb = halo;
+            CommBackend& cb = comm;
+            bool rebuild = true;
+            cb.unify_rebuild_decision(rebuild);
+            if (!rebuild || cb.is_distributed() || !cb.is_gpu_single_rank(true)) throw std::runtime_error("CommBackendB200 flags");
+            if (cb.migrate_particles_if_needed(system, rebuild, &calc)) throw std::runtime_error("one rank never migrates");
+            if (!hb.try_gpu_direct_halo(system, &calc, rebuild) || !rebuild) throw std::runtime_error("HaloBackendB200 rebuild");
+            bool no = false;
+            if (!hb.try_gpu_direct_halo(system, &calc, no) || no) throw std::runtime_error("HaloBackendB200 refresh");
+            if (cb.sum_reduce(2.5) != 2.5 || cb.max_reduce(-1.0) != -1.0 || cb.sum_int(7) != 7 || !cb.all_true(true) || cb.all_true(false))
+                throw std::runtime_error("CommBackendB200 reductions");
+            base.compute_forces(system);
+            out_scalars[9] = base.get_potential_energy();
+            dsmd_domain_destroy(dom);
+        }
         base.finalize();
     } catch (const std::exception& e) {
         if (error && error_len > 0) std::snprintf(error, static_cast<size_t>(error_len), "%s", e.what());

@@ -13,8 +13,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.mark.skipif(not co.ref_available(), reason="oracle/_ref is not built")
 def test_reference_arm_prints_one_json_line_with_the_contract_keys():
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "2", "--warmup", "3"],
-                       capture_output=True, text=True, timeout=600, cwd=ROOT)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "2", "--warmup", "3",
+                        "--cpu-budget-s", "6"], capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert r.returncode == 0, r.stderr
     lines = [l for l in r.stdout.splitlines() if l.strip()]
     assert len(lines) == 1
@@ -24,7 +24,7 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
         assert key in line, key
     assert line["impl"] == "reference" and line["metric"] == "atom-steps/s" and line["vs_baseline"] is None
     assert line["value"] > 0 and line["steps"] == 2 and line["warmup"] >= 3 and line["gpu_launches"] == 0
-    assert "workload" in line["config"]
+    assert "workload" in line["config"] and "measured_on" in line["config"]      # a 6-second budget: a sample, and said so
     base = line["cpu_baseline"]
     assert base["kind"] == "reference" and base["cores"] >= 1 and base["value"] == line["value"] and base["sample"]
     assert line["e2e"] == {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}

@@ -1,7 +1,8 @@
 """GPU tests of the C++ adapters that carry the reference's class shapes (include/dsmd/): a harness compiled against the
 reference's own interface headers (oracle/ref_build/adapter_harness.cpp -> oracle/_ref/libdsmd_adapter_check.so) fills an
-MDSystem as the reference's driver would and calls ForceCalculator::compute_forces, NeighborList::needs_rebuild and
-EdgeBuilder::build; results are compared with the CPU oracle. Skipped where the harness was not built (it needs the
+MDSystem as the reference's driver would and calls ForceCalculator::compute_forces, NeighborList::needs_rebuild,
+the lagged displacement query, the storage provider, HaloBackend::try_gpu_direct_halo and the CommBackend reductions
+(over the native domain code, one rank) and EdgeBuilder::build; results are compared with the CPU oracle. Skipped where the harness was not built (it needs the
 reference headers at build time)."""
 import ctypes
 import os
@@ -44,7 +45,7 @@ def test_force_calculator_adapter_matches_oracle(harness, case):
     excl = s.exclusions if s.exclusions is not None else np.zeros((0, 2), dtype=np.int32)
     ea, eb = np.ascontiguousarray(excl[:, 0], dtype=np.int32), np.ascontiguousarray(excl[:, 1], dtype=np.int32)
     out_f = np.zeros((s.n, 3))
-    out_sc = np.zeros(7)
+    out_sc = np.zeros(10)
     err = ctypes.create_string_buffer(512)
     box = np.ascontiguousarray(s.box)
     rc = harness.dsmd_adapter_forces(
@@ -67,6 +68,10 @@ def test_force_calculator_adapter_matches_oracle(harness, case):
     ke = 0.5 * (s.mass[:, None] * s.vel ** 2).sum()
     assert abs(out_sc[5] - ke) <= 1e-12 * ke
     assert out_sc[6] == 2.0          # no rebuild right after a build, rebuild once an atom moved 0.6 skin
+    # lagged displacement: nothing on the first call, then what the call before measured (the atom 0.6 skin away)
+    assert out_sc[7] < 0.0 and out_sc[8] == pytest.approx((0.6 * s.skin) ** 2, rel=1e-9)
+    # a rebuild step through HaloBackendB200 / CommBackendB200 over a one-rank domain leaves the physics alone
+    assert abs(out_sc[9] - sc_o["pe"]) <= 1e-6 * abs(sc_o["pe"])
 
 
 def test_edge_builder_adapter_matches_oracle(harness):
