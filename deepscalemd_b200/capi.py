@@ -22,7 +22,7 @@ FIELD_ID = {name: k for k, name in enumerate(FIELDS)}
 # every symbol include/dsmd_b200.h declares
 SYMBOLS = [
     "dsmd_create", "dsmd_destroy", "dsmd_last_error", "dsmd_set_box", "dsmd_set_pair_params", "dsmd_set_coulomb",
-    "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
+    "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_set_constraints", "dsmd_constraint_failures", "dsmd_rattle", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
     "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned", "dsmd_sort_owned_in_brick",
     "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq", "dsmd_max_displacement_sq_lagged",
     "dsmd_displacement_word", "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_scale_velocities",
@@ -143,6 +143,21 @@ class Context:
         pairs = np.asarray(pairs)
         a, b = _arr(pairs[:, 0], np.int32), _arr(pairs[:, 1], np.int32)
         self._check(self.lib.dsmd_set_exclusions(self.h, c_int64(n_global), c_int64(len(a)), _p(a), _p(b)))
+
+    def set_constraints(self, n_global, constraints, tolerance=0.0, max_iterations=0):
+        """constraints: rows (atom i, atom j, distance) by global id."""
+        if constraints is None or len(constraints) == 0:
+            self._check(self.lib.dsmd_set_constraints(self.h, c_int64(n_global), c_int64(0), None, None, None, c_double(0.0), c_int(0)))
+            return
+        rows = np.asarray(constraints, dtype=np.float64)
+        a, b, d = _arr(rows[:, 0], np.int32), _arr(rows[:, 1], np.int32), _arr(rows[:, 2], np.float64)
+        self._check(self.lib.dsmd_set_constraints(self.h, c_int64(n_global), c_int64(len(a)), _p(a), _p(b), _p(d),
+                                                  c_double(tolerance), c_int(max_iterations)))
+
+    def constraint_failures(self, stream=None):
+        n = c_int64(0)
+        self._check(self.lib.dsmd_constraint_failures(self.h, ctypes.byref(n), _stream_handle(stream)))
+        return n.value
 
     # -- particles ----------------------------------------------------------------------------------------------------
     def upload(self, pos, n_owned=None, vel=None, mass=None, charge=None, types=None, gid=None, stream=None):

@@ -46,7 +46,8 @@ struct Status {
     unsigned long long interior;   // of which the partner is owned
     unsigned long long select_count;
     unsigned int dropped;          // owned atoms found outside the brick by a sort that removes them
-    unsigned int reserved[3];
+    unsigned int constraint_failed;   // constraint clusters whose SHAKE / RATTLE sweeps did not converge
+    unsigned int reserved[2];
 };
 
 __host__ __device__ inline unsigned int cell_of(unsigned int fixed, int wrap, int nc) {

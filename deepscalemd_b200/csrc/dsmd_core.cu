@@ -461,6 +461,12 @@ __global__ void k_kinetic(int n, const double* __restrict__ vx, const double* __
     block_sum_to_partials<1>(v, partials);
 }
 
+}  // namespace
+
+#include "dsmd_constraints.cuh"
+
+namespace {
+
 // ---------------------------------------------------------------------------------------------------------------------
 // kernel: LJ + real-space Ewald over the list
 // ---------------------------------------------------------------------------------------------------------------------
@@ -812,6 +818,18 @@ struct dsmd_ctx {
     unsigned char* flag = nullptr;
     unsigned long long* offsets64 = nullptr;
     bool list_valid = false;
+    // distance constraints (dsmd_constraints.cuh)
+    int n_clusters = 0;
+    int64_t cons_n_global = 0;
+    int* cl_gid = nullptr;
+    unsigned char* cl_a = nullptr;
+    unsigned char* cl_b = nullptr;
+    double* cl_d2 = nullptr;
+    int* slot_of_gid = nullptr;
+    bool slot_map_valid = false;
+    double* pre[3] = {};
+    double cons_tolerance = 1e-8;
+    int cons_max_iterations = 500;
     bool owned_sorted_only = false;
     int64_t expect_dropped = 0;    // atoms the last owned-only sort was told to remove (checked with the build status)
     int64_t stat_entries = 0, stat_interior = 0;
@@ -1015,6 +1033,7 @@ int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s, int64_t n_removed = 0
         }
     }
     c->cur = to;
+    c->slot_map_valid = false;
     return DSMD_OK;
 }
 
@@ -1105,6 +1124,8 @@ void dsmd_destroy(dsmd_ctx* c) {
     cudaFree(c->ghost_slot); cudaFree(c->cell_start); cudaFree(c->nbr); cudaFree(c->deg); cudaFree(c->deg_int);
     cudaFree(c->cub_temp); cudaFree(c->c6c12); cudaFree(c->ewald); cudaFree(c->excl_off); cudaFree(c->excl_partner);
     cudaFree(c->partials); cudaFree(c->scalars); cudaFree(c->status); cudaFree(c->flag); cudaFree(c->offsets64);
+    cudaFree(c->cl_gid); cudaFree(c->cl_a); cudaFree(c->cl_b); cudaFree(c->cl_d2); cudaFree(c->slot_of_gid);
+    for (int a = 0; a < 3; ++a) cudaFree(c->pre[a]);
     cudaFreeHost(c->h_status); cudaFreeHost(c->h_scalars);
     for (int k = 0; k < 2; ++k) {
         cudaFreeHost(c->h_disp[k]);
@@ -1250,6 +1271,7 @@ int dsmd_upload(dsmd_ctx* c, int64_t n_owned, int64_t n_total, const double* x, 
     c->n_owned = n_owned;
     c->n_total = n_total;
     c->list_valid = false;
+    c->slot_map_valid = false;
     return DSMD_OK;
 }
 
@@ -1545,15 +1567,180 @@ int dsmd_read_scalars(dsmd_ctx* c, double out[6], void* stream) {
     return DSMD_OK;
 }
 
+namespace {
+
+ClusterTable cluster_table(const dsmd_ctx* c) {
+    ClusterTable t{};
+    t.n_clusters = c->n_clusters;
+    t.atom_gid = c->cl_gid;
+    t.con_a = c->cl_a;
+    t.con_b = c->cl_b;
+    t.con_d2 = c->cl_d2;
+    t.slot_of_gid = c->slot_of_gid;
+    for (int a = 0; a < 3; ++a) {
+        t.box[a] = c->box[a];
+        t.periodic[a] = c->periodic[a];
+    }
+    return t;
+}
+
+int ensure_slot_map(dsmd_ctx* c, cudaStream_t s) {
+    if (c->slot_map_valid) return DSMD_OK;
+    k_slot_of_gid<<<blocks_for(c->n_owned, kThreads), kThreads, 0, s>>>(static_cast<int>(c->n_owned), c->gid[c->cur],
+                                                                         static_cast<int>(c->cons_n_global), c->slot_of_gid);
+    DSMD_LAUNCHED(c);
+    c->slot_map_valid = true;
+    return DSMD_OK;
+}
+
+// SHAKE after the drift of the first half step (positions before it are in c->pre), then the positions the kernels
+// read are converted again.
+int shake_impl(dsmd_ctx* c, double dt, cudaStream_t s) {
+    { const int rc = ensure_slot_map(c, s); if (rc) return rc; }
+    double** r = c->real[c->cur];
+    k_shake<<<blocks_for(c->n_clusters, 128), 128, 0, s>>>(cluster_table(c), r[0], r[1], r[2], r[3], r[4], r[5], c->pre[0],
+                                                            c->pre[1], c->pre[2], r[9], 1.0 / dt, c->cons_tolerance,
+                                                            c->cons_max_iterations, &c->status->constraint_failed);
+    DSMD_LAUNCHED(c);
+    return DSMD_OK;
+}
+
+int rattle_impl(dsmd_ctx* c, double dt, double f2a, double* d_virial3, cudaStream_t s) {
+    { const int rc = ensure_slot_map(c, s); if (rc) return rc; }
+    double** r = c->real[c->cur];
+    const unsigned blocks = blocks_for(c->n_clusters, 128);
+    double* partials = nullptr;
+    if (d_virial3) {
+        { const int rc = ensure_partials(c, blocks); if (rc) return rc; }
+        partials = c->partials;
+    }
+    k_rattle<<<blocks, 128, 0, s>>>(cluster_table(c), r[0], r[1], r[2], r[3], r[4], r[5], r[9], c->cons_tolerance,
+                                    c->cons_max_iterations, -2.0 / (f2a * dt), partials, &c->status->constraint_failed);
+    DSMD_LAUNCHED(c);
+    if (d_virial3) {
+        k_reduce_partials<3><<<1, kThreads, 0, s>>>(partials, static_cast<int>(blocks), d_virial3, 0);
+        DSMD_LAUNCHED(c);
+    }
+    return DSMD_OK;
+}
+
+}  // namespace
+
+int dsmd_set_constraints(dsmd_ctx* c, int64_t n_global, int64_t n_constraints, const int32_t* a, const int32_t* b,
+                         const double* distance, double tolerance, int max_iterations) {
+    if (!c || n_global < 0 || n_constraints < 0 || (n_constraints > 0 && (!a || !b || !distance))) return DSMD_ERR_INVALID;
+    DSMD_CUDA(c, cudaSetDevice(c->device));
+    cudaFree(c->cl_gid); cudaFree(c->cl_a); cudaFree(c->cl_b); cudaFree(c->cl_d2); cudaFree(c->slot_of_gid);
+    c->cl_gid = c->slot_of_gid = nullptr;
+    c->cl_a = c->cl_b = nullptr;
+    c->cl_d2 = nullptr;
+    c->n_clusters = 0;
+    c->slot_map_valid = false;
+    if (tolerance > 0.0) c->cons_tolerance = tolerance;
+    if (max_iterations > 0) c->cons_max_iterations = max_iterations;
+    if (n_constraints == 0) return DSMD_OK;
+    // clusters = connected groups of constraints (union-find over the atoms), in the order of their first constraint;
+    // inside a cluster the constraints keep their given order
+    std::vector<int> parent(static_cast<size_t>(n_global));
+    for (int64_t g = 0; g < n_global; ++g) parent[g] = static_cast<int>(g);
+    auto find = [&](int v) {
+        while (parent[v] != v) v = parent[v] = parent[parent[v]];
+        return v;
+    };
+    for (int64_t k = 0; k < n_constraints; ++k) {
+        if (a[k] < 0 || b[k] < 0 || a[k] >= n_global || b[k] >= n_global || a[k] == b[k] || !(distance[k] > 0.0))
+            return fail(c, DSMD_ERR_INVALID, "constraint names an atom outside the system, or its distance is not positive");
+        parent[find(a[k])] = find(b[k]);
+    }
+    std::vector<int> cluster_of(static_cast<size_t>(n_global), -1);
+    std::vector<int> gids;
+    std::vector<unsigned char> ca, cb;
+    std::vector<double> d2;
+    std::vector<int> n_atoms, n_cons;
+    for (int64_t k = 0; k < n_constraints; ++k) {
+        const int root = find(a[k]);
+        int cl = cluster_of[root];
+        if (cl < 0) {
+            cl = cluster_of[root] = static_cast<int>(n_atoms.size());
+            n_atoms.push_back(0);
+            n_cons.push_back(0);
+            gids.resize(gids.size() + kClusterAtoms, -1);
+            ca.resize(ca.size() + kClusterCons, 255);
+            cb.resize(cb.size() + kClusterCons, 255);
+            d2.resize(d2.size() + kClusterCons, 1.0);
+        }
+        int local[2];
+        const int ends[2] = {a[k], b[k]};
+        for (int e = 0; e < 2; ++e) {
+            local[e] = -1;
+            for (int q = 0; q < n_atoms[cl]; ++q)
+                if (gids[static_cast<size_t>(cl) * kClusterAtoms + q] == ends[e]) local[e] = q;
+            if (local[e] < 0) {
+                if (n_atoms[cl] == kClusterAtoms)
+                    return fail(c, DSMD_ERR_CAPACITY, "a group of connected constraints has more than 4 atoms");
+                local[e] = n_atoms[cl]++;
+                gids[static_cast<size_t>(cl) * kClusterAtoms + local[e]] = ends[e];
+            }
+        }
+        if (n_cons[cl] == kClusterCons) return fail(c, DSMD_ERR_CAPACITY, "a group of connected constraints has more than 6 constraints");
+        const size_t at = static_cast<size_t>(cl) * kClusterCons + n_cons[cl]++;
+        ca[at] = static_cast<unsigned char>(local[0]);
+        cb[at] = static_cast<unsigned char>(local[1]);
+        d2[at] = distance[k] * distance[k];
+    }
+    const size_t ncl = n_atoms.size();
+    DSMD_CUDA(c, cudaMalloc(&c->cl_gid, sizeof(int) * gids.size()));
+    DSMD_CUDA(c, cudaMalloc(&c->cl_a, ca.size()));
+    DSMD_CUDA(c, cudaMalloc(&c->cl_b, cb.size()));
+    DSMD_CUDA(c, cudaMalloc(&c->cl_d2, sizeof(double) * d2.size()));
+    DSMD_CUDA(c, cudaMalloc(&c->slot_of_gid, sizeof(int) * static_cast<size_t>(n_global)));
+    DSMD_CUDA(c, cudaMemcpy(c->cl_gid, gids.data(), sizeof(int) * gids.size(), cudaMemcpyHostToDevice));
+    DSMD_CUDA(c, cudaMemcpy(c->cl_a, ca.data(), ca.size(), cudaMemcpyHostToDevice));
+    DSMD_CUDA(c, cudaMemcpy(c->cl_b, cb.data(), cb.size(), cudaMemcpyHostToDevice));
+    DSMD_CUDA(c, cudaMemcpy(c->cl_d2, d2.data(), sizeof(double) * d2.size(), cudaMemcpyHostToDevice));
+    for (int ax = 0; ax < 3; ++ax)
+        if (!c->pre[ax]) DSMD_CUDA(c, cudaMalloc(&c->pre[ax], sizeof(double) * c->capacity));
+    c->n_clusters = static_cast<int>(ncl);
+    c->cons_n_global = n_global;
+    return DSMD_OK;
+}
+
+int dsmd_constraint_failures(dsmd_ctx* c, int64_t* failed, void* stream) {
+    if (!c || !failed) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    { const int rc = read_status(c, s); if (rc) return rc; }
+    *failed = c->h_status->constraint_failed;
+    return DSMD_OK;
+}
+
+int dsmd_rattle(dsmd_ctx* c, double dt, double f2a, double* d_virial_diag, void* stream) {
+    if (!c || !(dt > 0.0)) return DSMD_ERR_INVALID;
+    if (c->n_clusters == 0) return DSMD_OK;
+    if (c->n_total != c->n_owned) return fail(c, DSMD_ERR_STATE, "constraints are solved on single-rank systems only");
+    return rattle_impl(c, dt, f2a, d_virial_diag, static_cast<cudaStream_t>(stream));
+}
+
 int dsmd_integrate(dsmd_ctx* c, int half, double dt, double f2a, void* stream) {
     if (!c || (half != 1 && half != 2)) return DSMD_ERR_INVALID;
     if (!c->grid_valid) return fail(c, DSMD_ERR_STATE, "no neighbour list built yet");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (half == 1) return pack_impl(c, 0, c->n_owned, true, dt, f2a, s);
+    const bool constrained = c->n_clusters > 0;
+    if (constrained && c->n_total != c->n_owned)
+        return fail(c, DSMD_ERR_STATE, "constraints are solved on single-rank systems only");
+    if (half == 1) {
+        if (!constrained) return pack_impl(c, 0, c->n_owned, true, dt, f2a, s);
+        // constrained: keep the positions from before the drift, drift, SHAKE, then convert the corrected positions
+        for (int a = 0; a < 3; ++a)
+            DSMD_CUDA(c, cudaMemcpyAsync(c->pre[a], c->real[c->cur][a], sizeof(double) * c->n_owned, cudaMemcpyDeviceToDevice, s));
+        { const int rc = pack_impl(c, 0, c->n_owned, true, dt, f2a, s); if (rc) return rc; }
+        { const int rc = shake_impl(c, dt, s); if (rc) return rc; }
+        return pack_impl(c, 0, c->n_owned, false, 0.0, 0.0, s);
+    }
     double** r = c->real[c->cur];
     k_vv2<<<blocks_for(c->n_owned, kThreads), kThreads, 0, s>>>(static_cast<int>(c->n_owned), 0.5 * dt * f2a, r[3], r[4],
                                                                r[5], r[6], r[7], r[8], r[9]);
     DSMD_LAUNCHED(c);
+    if (constrained) return rattle_impl(c, dt, f2a, nullptr, s);
     return DSMD_OK;
 }
 
@@ -1604,7 +1791,7 @@ int dsmd_run_nve(dsmd_ctx* c, int64_t n_steps, double dt, double f2a, double hi_
     int pending = -1;                      // read-back slot in flight
     auto bits_to_double = [](unsigned long long b) { double v; std::memcpy(&v, &b, sizeof(v)); return v; };
     for (int64_t step = 0; step < n_steps; ++step) {
-        { const int rc = pack_impl(c, 0, c->n_owned, true, dt, f2a, s); if (rc) return rc; }
+        { const int rc = dsmd_integrate(c, 1, dt, f2a, s); if (rc) return rc; }   // with SHAKE when constraints are set
         ++since_build;
         bool rebuild = every > 0 && since_build >= every;
         if (!lagged) {

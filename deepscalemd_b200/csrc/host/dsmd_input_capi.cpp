@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "dynamics.hpp"
+#include "../ewald_table.hpp"
 #include "brick_plan.hpp"
 #include "deadline.hpp"
 #include "restart_file.hpp"
@@ -279,6 +280,14 @@ int dsmd_host_counts_verdict(const int32_t dims[3], const int32_t* counts, int64
         }
     }
     return DSMD_INPUT_OK;
+}
+
+int dsmd_host_ewald_table(double alpha, double cutoff_sq, float* out, int32_t capacity_intervals) {
+    const int intervals = dsmd::ewald_intervals(cutoff_sq);
+    if (!out || capacity_intervals < intervals) return intervals;
+    const std::vector<float> coef = dsmd::ewald_build_table(alpha, intervals);
+    std::copy(coef.begin(), coef.end(), out);
+    return intervals;
 }
 
 int dsmd_host_wait_probe(double limit_s, int64_t ready_after_polls, int64_t fail_after_polls) {

@@ -47,7 +47,6 @@ void ok(dsmd_ctx* ctx, int rc, const char* what) {
 std::vector<std::string> refusals(const RunConfig& c, const SystemInput& s) {
     std::vector<std::string> out = c.unsupported();
     if (s.mie_n != 12 || s.mie_m != 6) out.push_back("Mie exponents other than (12, 6)");
-    if (!s.constraints.empty()) out.push_back("distance constraints (SHAKE/RATTLE is outside the nonbonded path)");
     if (c.enable_bonded && (s.n_bonds || s.n_angles || s.n_dihedrals || s.n_impropers))
         out.push_back("bonded terms (switch them off with force_calculation.type: lj[, PME])");
     if (s.n_special_pairs) out.push_back("special (1-4) pairs");
@@ -128,6 +127,17 @@ public:
             }
             ok(ctx_, dsmd_set_exclusions(ctx_, s_.n, static_cast<int64_t>(a.size()), a.data(), b.data()), "dsmd_set_exclusions");
         }
+        if (!s_.constraints.empty()) {   // rigid groups: SHAKE / RATTLE inside the library's integration halves
+            std::vector<int32_t> a, b;
+            std::vector<double> d;
+            for (const auto& k : s_.constraints) {
+                a.push_back(k.i);
+                b.push_back(k.j);
+                d.push_back(k.distance);
+            }
+            ok(ctx_, dsmd_set_constraints(ctx_, s_.n, static_cast<int64_t>(a.size()), a.data(), b.data(), d.data(), 0.0, 0),
+               "dsmd_set_constraints");
+        }
         std::vector<int32_t> type(s_.type.begin(), s_.type.end());
         ok(ctx_, dsmd_upload(ctx_, s_.n, s_.n, s_.x.data(), s_.y.data(), s_.z.data(), s_.vx.data(), s_.vy.data(), s_.vz.data(),
                              s_.mass.data(), s_.charge.data(), type.data(), nullptr, nullptr),
@@ -192,7 +202,7 @@ public:
         Metrics m;
         m.ke = kinetic_kcal();
         m.pe = pe_;
-        m.temperature = temperature_of(m.ke, s_.n, 0);
+        m.temperature = temperature_of(m.ke, s_.n, static_cast<int64_t>(s_.constraints.size()));
         return m;
     }
 

@@ -17,7 +17,7 @@ SYMBOLS = [
     "dsmd_input_system_load", "dsmd_input_system_load_files", "dsmd_input_system_destroy", "dsmd_input_system_counts",
     "dsmd_input_system_real", "dsmd_input_system_types", "dsmd_input_system_pair_table", "dsmd_input_system_exclusions",
     "dsmd_input_system_constraints", "dsmd_input_system_velocities", "dsmd_input_restart_read", "dsmd_input_restart_write",
-    "dsmd_input_nose_hoover_scale", "dsmd_host_brick_plan", "dsmd_host_counts_verdict", "dsmd_host_wait_probe",
+    "dsmd_input_nose_hoover_scale", "dsmd_host_brick_plan", "dsmd_host_counts_verdict", "dsmd_host_wait_probe", "dsmd_host_ewald_table",
 ]
 
 _lib = None
@@ -205,4 +205,12 @@ def counts_verdict(dims, counts, scratch_capacity=1 << 30):
 
 def wait_probe(limit_s, ready_after=-1, fail_after=-1):
     return lib().dsmd_host_wait_probe(c_double(limit_s), c_int64(ready_after), c_int64(fail_after))
+
+
+def ewald_table(alpha, cutoff):
+    """[intervals, 2, 4] float32: force and energy cubic of every interval of the table the pair kernel evaluates."""
+    n = lib().dsmd_host_ewald_table(c_double(alpha), c_double(cutoff * cutoff), None, ctypes.c_int32(0))
+    out = np.zeros((n, 2, 4), dtype=np.float32)
+    lib().dsmd_host_ewald_table(c_double(alpha), c_double(cutoff * cutoff), out.ctypes.data_as(ctypes.c_void_p), ctypes.c_int32(n))
+    return out
 

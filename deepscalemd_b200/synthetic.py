@@ -25,6 +25,7 @@ class System:
     skin: float
     vel: np.ndarray | None = None        # [N, 3]
     exclusions: np.ndarray | None = None  # [X, 2] global ids
+    constraints: np.ndarray | None = None  # [C, 3] global id, global id, distance
     coulomb: bool = False
     dt: float = 0.005
     force_to_accel: float = 1.0          # 4.184e-4 in the reference's real units, 1 in reduced units
@@ -131,8 +132,12 @@ def water_box(cells: int = 60, *, cutoff=10.0, skin=2.0, seed=4242) -> System:
     excl = np.concatenate([np.stack([o, o + 1], 1), np.stack([o, o + 2], 1), np.stack([o + 1, o + 2], 1)])
     kb = 0.0019872041
     vel = maxwell_boltzmann(n, 300.0, mass, rng, kb=kb / (48.88821291 ** 2))
+    # the rigid geometry as distance constraints, molecule after molecule: O-H, O-H, H-H
+    hh = 2.0 * np.sin(half)
+    cons = np.stack([np.stack([o, o + 1, np.full(nm, 1.0)], 1), np.stack([o, o + 2, np.full(nm, 1.0)], 1),
+                     np.stack([o + 1, o + 2, np.full(nm, hh)], 1)], axis=1).reshape(-1, 3)
     return System(name=f"water_{n}", pos=pos, box=box, types=types, charge=charge, mass=mass, eps=eps, sig=sig,
-                  cutoff=cutoff, skin=skin, vel=vel, exclusions=excl, coulomb=True, dt=2.0, force_to_accel=4.184e-4,
+                  cutoff=cutoff, skin=skin, vel=vel, exclusions=excl, constraints=cons, coulomb=True, dt=2.0, force_to_accel=4.184e-4,
                   meta=dict(seed=seed, molecules=nm))
 
 

@@ -74,6 +74,23 @@ int dsmd_get_ewald_alpha(const dsmd_ctx* ctx, double* alpha);
  * src/force_calculator_cuda.cu:4379-4423). n_global = atoms in the whole system. */
 int dsmd_set_exclusions(dsmd_ctx* ctx, int64_t n_global, int64_t n_pairs, const int32_t* a, const int32_t* b);
 
+/* Distance constraints by global id (Topology constraints -> ConstraintSolver, src/constraint_solver.cpp:15-146; device
+ * kernels shake_cluster_kernel / rattle_cluster_kernel, src/force_calculator_cuda.cu:6168-6333). Connected constraints
+ * form a group solved by one thread (at most 4 atoms and 6 constraints per group: rigid water has 3 and 3). Once set,
+ * dsmd_integrate applies SHAKE after the drift of half 1 and RATTLE after half 2, and so does dsmd_run_nve.
+ * tolerance <= 0 / max_iterations <= 0 keep the reference's defaults (1e-8, 500). n_constraints = 0 removes them.
+ * Single-rank systems only (a group's atoms must all be owned). */
+int dsmd_set_constraints(dsmd_ctx* ctx, int64_t n_global, int64_t n_constraints, const int32_t* a, const int32_t* b,
+                         const double* distance, double tolerance, int max_iterations);
+
+/* Groups whose sweeps did not converge since the last list build (ConstraintSolver::apply_shake / apply_rattle return
+ * false then). Synchronises `stream`. */
+int dsmd_constraint_failures(dsmd_ctx* ctx, int64_t* failed_groups, void* stream);
+
+/* RATTLE alone, with the diagonal of the constraint virial (ForceCalculatorCUDA::apply_rattle_on_device): velocities are
+ * projected; device_virial_diag (3 device doubles, may be NULL) receives -2 / (force_to_accel dt) * sum k r_a^2. */
+int dsmd_rattle(dsmd_ctx* ctx, double dt, double force_to_accel, double* device_virial_diag, void* stream);
+
 /* -- particle storage ----------------------------------------------------------------------------------------------- */
 
 /* ForceCalculatorCUDA::initial_upload_to_device (src/force_calculator_cuda.cu:4281): host arrays, owned atoms first

@@ -93,6 +93,11 @@ int dsmd_host_brick_plan(const int32_t dims[3], int32_t rank, int32_t* n_dirs, i
 int dsmd_host_counts_verdict(const int32_t dims[3], const int32_t* counts, int64_t scratch_capacity, int32_t* code,
                              int32_t* about_rank, int32_t messages[64]);
 
+/* The real-space Ewald table the pair kernel evaluates (the builder behind dsmd_set_coulomb; the reference's is
+ * ewald_real_table_build, include/ewald_real_table.h:41-105): 8 floats per interval, the force cubic then the energy
+ * cubic. Returns the number of intervals; writes nothing when capacity_intervals is smaller. */
+int dsmd_host_ewald_table(double alpha, double cutoff_sq, float* out, int32_t capacity_intervals);
+
 /* The bounded host wait of the domain code against a stand-in that becomes ready (or fails) after a number of polls,
  * -1 = never: returns 0 ready, 7 (DSMD_ERR_TIMEOUT) when limit_s ran out, 2 when the stand-in failed. */
 int dsmd_host_wait_probe(double limit_s, int64_t ready_after_polls, int64_t fail_after_polls);

@@ -109,3 +109,21 @@ void dsmd_reftop_pairs(void* h, double* pair_sigma, double* pair_epsilon, int* e
 }
 
 }  // extern "C"
+
+// The reference's real-space Ewald table builder (include/ewald_real_table.h:41-105), header-only: force and energy cubic
+// coefficients of every interval, interleaved as the device table is laid out ({force cubic, energy cubic} per interval).
+#include "ewald_real_table.h"
+
+extern "C" int dsmd_ref_ewald_table(double alpha, double cutoff_sq, float* out, int capacity_intervals) {
+    const int intervals = ewald_real_table_intervals(cutoff_sq);
+    if (!out || capacity_intervals < intervals) return intervals;
+    std::vector<float> force, energy;
+    ewald_real_table_build(alpha, intervals, force, energy);
+    for (int i = 0; i < intervals; ++i)
+        for (int k = 0; k < 4; ++k) {
+            out[8 * i + k] = force[4 * static_cast<size_t>(i) + k];
+            out[8 * i + 4 + k] = energy[4 * static_cast<size_t>(i) + k];
+        }
+    return intervals;
+}
+

@@ -121,6 +121,10 @@ int dsmd_set_exclusions(dsmd_ctx* c, int64_t, int64_t n_pairs, const int32_t*, c
     return n_pairs ? fail(c, DSMD_ERR_INVALID, "the test double has no exclusions") : DSMD_OK;
 }
 
+int dsmd_set_constraints(dsmd_ctx* c, int64_t, int64_t n_constraints, const int32_t*, const int32_t*, const double*, double, int) {
+    return n_constraints ? fail(c, DSMD_ERR_INVALID, "the test double has no constraints") : DSMD_OK;
+}
+
 int dsmd_upload(dsmd_ctx* c, int64_t n_owned, int64_t n_total, const double* x, const double* y, const double* z,
                 const double* vx, const double* vy, const double* vz, const double* mass, const double* charge,
                 const int32_t* type, const int32_t* gid, void*) {

@@ -103,3 +103,29 @@ def test_velocity_scaling_entry_point(cuda_device):
     assert np.array_equal(v_after, v_before * 0.75)
     assert ctx.kinetic_energy() == pytest.approx(before * 0.5625, rel=1e-13)
     ctx.close()
+
+
+def test_rigid_water_runs_as_md_from_the_reference_input_files(cuda_device, tmp_path):
+    """The rigid-water geometry box through the driver: a dsMD_input folder (manifest, .xyz, .dsMDtop with exclusions and
+    constraints, .dsMDprm with the explicit pair table) and a run description with real_space_only: true. The run
+    finishes; the seeded start (random orientations on a jittered lattice) is far from equilibrium and heats up as it
+    relaxes, but stays finite and bounded with the molecules held rigid by SHAKE / RATTLE (the printed temperature counts
+    the constraints in its degrees of freedom: 450 K at step 0 for velocities drawn at 300 K); the total energy moves by a
+    fraction of the kinetic energy only; the list is rebuilt on the way."""
+    s = syn.water_box(11, seed=3)
+    sigma = [[3.166, 1.583], [1.583, 0.0]]
+    epsilon = [[0.1553, 0.0], [0.0, 0.0]]
+    pos = s.pos - s.box * np.floor(s.pos / s.box)
+    pos = pos + (s.box / 2.0 - pos.mean(0))
+    manifest = input_files.write_dsmd_input(str(tmp_path / "water"), "water", pos, ["O", "H", "H"] * (s.n // 3), s.types,
+                                            ["OW", "HW"], s.mass, s.charge, sigma, epsilon, exclusions=s.exclusions,
+                                            constraints=s.constraints)
+    path = input_files.write_run_yaml(tmp_path / "water.yaml", box=s.box, total_steps=100, timestep=2.0, temperature=300.0,
+                                      cutoff=s.cutoff, skin=s.skin, input_system=manifest, force_type="lj, PME",
+                                      output_freq=25, update_freq=1000, extra={"real_space_only": "true"})
+    rows, out = run_driver(path)
+    assert [int(r[0]) for r in rows] == [0, 25, 50, 75, 100]
+    assert np.all(np.isfinite(rows)) and np.all(rows[:, 1] > 100.0) and np.all(rows[:, 1] < 3000.0)
+    assert rows[0][1] == pytest.approx(300.0 * 9.0 / 6.0, rel=0.05)
+    assert np.abs(rows[1:, 4] - rows[1, 4]).max() < 0.25 * rows[-1][2]
+    assert int(re.search(r"Neighbor list builds = (\d+)", out).group(1)) >= 2

@@ -283,3 +283,31 @@ def test_start_velocities_and_nose_hoover(tmp_path):
     got_scale, got_xi = input_api.nose_hoover_scale(ke, n, T, tau, dt, xi)
     assert got_scale == pytest.approx(scale, rel=1e-15) and got_xi == pytest.approx(xi2, rel=1e-15)
     assert input_api.nose_hoover_scale(ke, n, 0.0, tau, dt, xi) == (1.0, xi)
+
+
+def test_ewald_table_equals_the_reference_builders_coefficient_by_coefficient():
+    """The product's real-space Ewald table builder (Newton divided differences on the Chebyshev nodes) against the
+    reference's own (include/ewald_real_table.h:41-105, a 4 x 4 elimination), compiled from the reference header where
+    it lies: same intervals, and the same cubic in every interval, for the water box's alpha and two others."""
+    import ctypes
+    from tests.input_cases import REF_TOPOLOGY
+    if not os.path.exists(REF_TOPOLOGY):
+        pytest.skip("oracle/_ref is not built")
+    ref = ctypes.CDLL(REF_TOPOLOGY)
+    if not hasattr(ref, "dsmd_ref_ewald_table"):
+        pytest.skip("oracle/_ref predates the Ewald table hook: make -C oracle ref")
+    for alpha, cutoff in ((0.3123, 10.0), (0.25, 12.0), (1.1, 2.5)):
+        mine = input_api.ewald_table(alpha, cutoff)
+        n = ref.dsmd_ref_ewald_table(ctypes.c_double(alpha), ctypes.c_double(cutoff * cutoff), None, ctypes.c_int(0))
+        assert n == mine.shape[0]
+        theirs = np.zeros((n, 2, 4), dtype=np.float32)
+        ref.dsmd_ref_ewald_table(ctypes.c_double(alpha), ctypes.c_double(cutoff * cutoff),
+                                 theirs.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(n))
+        # the cubics are the same polynomial found two ways: equal to a few ulp of the interval's largest coefficient
+        scale = np.abs(theirs).max(axis=2, keepdims=True)
+        assert np.all(np.abs(mine - theirs) <= 4e-6 * scale + 1e-30)
+        # and they evaluate to the same values across every interval
+        t = np.linspace(0.0, 1.0, 9, dtype=np.float32)[None, None, :]
+        ev = lambda c: ((c[..., 3:4] * t + c[..., 2:3]) * t + c[..., 1:2]) * t + c[..., 0:1]
+        va, vb = ev(mine.astype(np.float64)), ev(theirs.astype(np.float64))
+        assert np.all(np.abs(va - vb) <= 2e-6 * np.abs(vb) + 1e-30)
