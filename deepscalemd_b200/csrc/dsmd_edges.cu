@@ -107,7 +107,7 @@ __device__ __forceinline__ bool within_fp64(const Grid& g, const SearchArgs& a, 
 }
 
 // One thread per sorted slot; hits (the neighbour's atom index) go to the slot's column of its 32-atom slice.
-// PERIODIC: all axes wrap, rows are sorted by neighbour index, counts are stored by the centre's atom index.
+// PERIODIC: all axes wrap, counts are stored by the centre's atom index (the expansion sorts every row by neighbour).
 template <bool PERIODIC>
 __global__ void __launch_bounds__(kSearchThreads) k_edge_search(Grid g, SearchArgs a) {
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
@@ -151,20 +151,7 @@ __global__ void __launch_bounds__(kSearchThreads) k_edge_search(Grid g, SearchAr
                             if (!within_fp64<PERIODIC>(g, a, centre, pj.w)) continue;
                         }
                         if (check_nb && !a.ok[a.owner ? a.owner[pj.w] : pj.w]) continue;
-                        if (count < a.stride) {
-                            if (PERIODIC) {   // keep the row sorted by neighbour index (insertion)
-                                int k = count;
-                                while (k > 0) {
-                                    const unsigned prev = a.rows[base + static_cast<size_t>(k - 1) * 32];
-                                    if (prev <= static_cast<unsigned>(pj.w)) break;
-                                    a.rows[base + static_cast<size_t>(k) * 32] = prev;
-                                    --k;
-                                }
-                                a.rows[base + static_cast<size_t>(k) * 32] = static_cast<unsigned>(pj.w);
-                            } else {
-                                a.rows[base + static_cast<size_t>(count) * 32] = static_cast<unsigned>(pj.w);
-                            }
-                        }
+                        if (count < a.stride) a.rows[base + static_cast<size_t>(count) * 32] = static_cast<unsigned>(pj.w);
                         ++count;
                     }
                 }
@@ -198,7 +185,7 @@ __device__ __forceinline__ int owner_lane(int t, int my_prefix) {
 // three output arrays are written with contiguous, coalesced stores.
 __global__ void k_edge_fill(int n, long long n_edges, int stride, const int4* __restrict__ pq,
                             const unsigned* __restrict__ rows, const int* __restrict__ counts,
-                            const long long* __restrict__ offsets, const int* __restrict__ owner,
+                            const long long* __restrict__ offsets, int n_centers, const int* __restrict__ owner,
                             const double* __restrict__ shift_x, const double* __restrict__ shift_y,
                             const double* __restrict__ shift_z, long long* __restrict__ edges,
                             double* __restrict__ shift) {
@@ -226,29 +213,49 @@ __global__ void k_edge_fill(int n, long long n_edges, int stride, const int4* __
             const int k = t - c_prefix;
             const int nb = static_cast<int>(rows[slice + static_cast<size_t>(k) * 32 + c]);
             const long long o = out0 + t;
+            // the first n_centers atoms are real: they stand for themselves and carry no shift (EdgeBuilder::Images'
+            // contract), so only image atoms cost the four scattered reads
+            const bool image = owner && nb >= n_centers;
             edges[o] = c_centre;
-            edges[n_edges + o] = owner ? owner[nb] : nb;
+            edges[n_edges + o] = image ? owner[nb] : nb;
             if (shift) {
-                shift[3 * o] = shift_x[nb];
-                shift[3 * o + 1] = shift_y[nb];
-                shift[3 * o + 2] = shift_z[nb];
+                shift[3 * o] = image ? shift_x[nb] : 0.0;
+                shift[3 * o + 1] = image ? shift_y[nb] : 0.0;
+                shift[3 * o + 2] = image ? shift_z[nb] : 0.0;
             }
         }
     }
 }
 
-// Compact periodic form: a warp takes 32 consecutive atom indices (edges come out sorted by src, then dst).
+// Compact periodic form: a warp takes 32 consecutive atom indices (edges come out sorted by src), copies their rows into
+// shared memory - entry k of lane l at [k * 32 + l], so that every lane works on its own bank - sorting each by neighbour
+// index on the way in (insertion: rows hold a few dozen entries), and streams them out in flat order.
 __global__ void k_edge_fill_compact(Grid g, int n, int stride, const int* __restrict__ slot_of,
                                     const unsigned* __restrict__ rows, const int* __restrict__ counts,
                                     const long long* __restrict__ offsets, const double* __restrict__ x,
                                     const double* __restrict__ y, const double* __restrict__ z, int* __restrict__ src,
                                     int* __restrict__ dst, signed char* __restrict__ shift, float* __restrict__ vec) {
+    extern __shared__ unsigned sorted_rows[];
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
+    unsigned* mine = sorted_rows + static_cast<size_t>(threadIdx.x >> 5) * stride * 32;
     const int i = warp * 32 + lane;
     if (warp * 32 >= n) return;
     const int cnt = i < n ? counts[i] : 0;
-    const int slot = i < n ? slot_of[i] : 0;
+    if (i < n) {
+        const int slot = slot_of[i];
+        const size_t base = (static_cast<size_t>(slot >> 5) * stride) * 32 + (slot & 31);
+        for (int k = 0; k < cnt; ++k) {
+            const unsigned nb = rows[base + static_cast<size_t>(k) * 32];
+            int at = k;
+            while (at > 0 && mine[(at - 1) * 32 + lane] > nb) {
+                mine[at * 32 + lane] = mine[(at - 1) * 32 + lane];
+                --at;
+            }
+            mine[at * 32 + lane] = nb;
+        }
+    }
+    __syncwarp();
     int prefix = cnt;
     for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(0xffffffffu, prefix, o);
@@ -261,11 +268,9 @@ __global__ void k_edge_fill_compact(Grid g, int n, int stride, const int* __rest
         const int t = t0 + lane;
         const int c = owner_lane(min(t, total - 1), prefix);
         const int c_prefix = __shfl_sync(0xffffffffu, prefix, c);
-        const int c_slot = __shfl_sync(0xffffffffu, slot, c);
         if (t < total) {
             const int k = t - c_prefix;
-            const size_t base = (static_cast<size_t>(c_slot >> 5) * stride) * 32 + (c_slot & 31);
-            const int nb = static_cast<int>(rows[base + static_cast<size_t>(k) * 32]);
+            const int nb = static_cast<int>(mine[k * 32 + c]);
             const int centre = warp * 32 + c;
             const long long o = out0 + t;
             double d[3] = {x[nb] - x[centre], y[nb] - y[centre], z[nb] - z[centre]};
@@ -499,6 +504,7 @@ struct dsmd_edges {
     long long* img_counts = nullptr;        size_t cap_img_counts = 0;
     long long* img_offsets = nullptr;       size_t cap_img_offsets = 0;
     unsigned long long* img_masks = nullptr; size_t cap_img_masks = 0;
+    size_t compact_smem = 0;                // dynamic shared memory k_edge_fill_compact is cleared for
     int64_t n_img_src = 0;                  // atoms the last image build was given
     double* virial_partials = nullptr;      // [3 * kVirialBlocks] + 4 results
     double* h_virial = nullptr;             // pinned, 4 doubles
@@ -757,8 +763,8 @@ int dsmd_edges_build(dsmd_edges* e, const double* d_x, const double* d_y, const 
     EDGE_ALLOC(e, grow(e->edges, e->cap_edges, 2 * static_cast<size_t>(E)));
     if (images) EDGE_ALLOC(e, grow(e->shift, e->cap_shift, 3 * static_cast<size_t>(E)));
     k_edge_fill<<<blocks_for(n, kThreads), kThreads, 0, s>>>(static_cast<int>(n), E, e->stride, e->pq, e->rows, e->counts,
-                                                            e->offsets, d_owner, d_shift_x, d_shift_y, d_shift_z,
-                                                            e->edges, images ? e->shift : nullptr);
+                                                            e->offsets, static_cast<int>(n_centers), d_owner, d_shift_x,
+                                                            d_shift_y, d_shift_z, e->edges, images ? e->shift : nullptr);
     ++e->launches;
     EDGE_CUDA(e, cudaGetLastError());
     e->have_shift = images;
@@ -799,9 +805,18 @@ int dsmd_edges_build_periodic(dsmd_edges* e, const double* d_x, const double* d_
     EDGE_ALLOC(e, grow(e->c_dst, e->cap_cdst, static_cast<size_t>(E)));
     EDGE_ALLOC(e, grow(e->c_shift, e->cap_cshift, 3 * static_cast<size_t>(E)));
     EDGE_ALLOC(e, grow(e->c_vec, e->cap_cvec, 3 * static_cast<size_t>(E)));
-    k_edge_fill_compact<<<blocks_for(n, kThreads), kThreads, 0, s>>>(g, static_cast<int>(n), e->stride, e->slot_of,
-                                                                    e->rows, e->counts, e->offsets, d_x, d_y, d_z,
-                                                                    e->c_src, e->c_dst, e->c_shift, e->c_vec);
+    {
+        constexpr int kFillThreads = 128;   // four warps, each with its own rows in shared memory
+        const size_t smem = static_cast<size_t>(kFillThreads / 32) * e->stride * 32 * sizeof(unsigned);
+        if (smem > 200 * 1024) return efail(e, DSMD_ERR_CAPACITY, "rows too long for the compact form (more than 400 neighbours per atom)");
+        if (smem > e->compact_smem) {
+            EDGE_CUDA(e, cudaFuncSetAttribute(k_edge_fill_compact, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            e->compact_smem = smem;
+        }
+        k_edge_fill_compact<<<blocks_for(n, kFillThreads), kFillThreads, smem, s>>>(g, static_cast<int>(n), e->stride, e->slot_of,
+                                                                                  e->rows, e->counts, e->offsets, d_x, d_y, d_z,
+                                                                                  e->c_src, e->c_dst, e->c_shift, e->c_vec);
+    }
     ++e->launches;
     EDGE_CUDA(e, cudaGetLastError());
     return DSMD_OK;

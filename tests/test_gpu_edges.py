@@ -181,3 +181,38 @@ def test_image_forces_fold_back_and_virial(cuda_device):
     assert np.abs(got - want).max() <= 1e-13 * scale
     eb.close()
 
+
+
+@pytest.mark.parametrize("halo_extra", [0.0, 1.3])
+def test_edges_under_an_eight_way_decomposition_equal_the_periodic_graph(cuda_device, halo_extra):
+    """The radius graph of a periodic solid built brick by brick, as the model runner of one rank is fed: 2 x 2 x 2 bricks,
+    each with its owned atoms and the ghost atoms of a halo as wide as the cutoff (second case: the reference's halo,
+    cutoff + skin + 1 A, here + 1.3 A) as explicit, image-shifted atoms, no periodic images (every axis is decomposed).
+    The edges centred on owned atoms, translated to global ids and lattice shifts, are over all bricks exactly the
+    periodic graph of the undivided box."""
+    import torch
+    s = syn.disordered_solid_lattice(28, seed=7)              # 21,952 atoms, box 76 A, cutoff 5 A
+    cutoff = s.cutoff
+    halo = cutoff + halo_extra
+    eb = capi.EdgeBuilder()
+    x, y, z = (to_dev(s.pos[:, k]) for k in range(3))
+    src, dst, shift, _ = eb.build_periodic(x, y, z, s.box, cutoff)
+    whole = np.concatenate([np.stack([src.cpu().numpy(), dst.cpu().numpy()], axis=0).astype(np.int64),
+                            shift.cpu().numpy().T.astype(np.int64)])
+    wrapped = s.pos - s.box * np.floor(s.pos / s.box)
+    parts = []
+    for brick in syn.brick_decompose(s.pos, s.box, (2, 2, 2), halo):
+        own, gsrc, gimg = brick["owned"], brick["ghost_src"], brick["ghost_image"]
+        pos = np.concatenate([wrapped[own], wrapped[gsrc] + gimg * s.box])
+        gid = np.concatenate([own, gsrc])
+        image = np.concatenate([np.zeros((len(own), 3), dtype=np.int64), gimg.astype(np.int64)])
+        cols = [to_dev(pos[:, k]) for k in range(3)]
+        idx, _ = eb.build(*cols, cutoff, lo=brick["lo"] - halo - 1e-9, hi=brick["hi"] + halo + 1e-9)
+        e = idx.cpu().numpy()
+        e = e[:, e[0] < len(own)]                             # the edges an owned atom is the centre of
+        assert len(gsrc) > 0 and e.shape[1] > 0
+        parts.append(np.concatenate([gid[e], image[e[1]].T]))
+    got = np.concatenate(parts, axis=1)
+    assert got.shape == whole.shape
+    assert np.array_equal(canon(got.astype(np.float64)), canon(whole.astype(np.float64)))
+    eb.close()
