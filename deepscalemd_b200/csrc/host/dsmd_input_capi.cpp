@@ -10,6 +10,7 @@
 #include "dynamics.hpp"
 #include "../ewald_table.hpp"
 #include "brick_plan.hpp"
+#include "dart_throw.hpp"
 #include "deadline.hpp"
 #include "restart_file.hpp"
 #include "run_config.hpp"
@@ -288,6 +289,14 @@ int dsmd_host_ewald_table(double alpha, double cutoff_sq, float* out, int32_t ca
     const std::vector<float> coef = dsmd::ewald_build_table(alpha, intervals);
     std::copy(coef.begin(), coef.end(), out);
     return intervals;
+}
+
+int dsmd_host_dart_throw(int64_t n, double box, double min_dist, uint64_t seed, double* xyz, int64_t* draws) {
+    return guarded([&]() {
+        const int64_t used = dart_throw(n, box, min_dist, seed, xyz);
+        if (draws) *draws = used;
+        return 0;
+    });
 }
 
 int dsmd_host_wait_probe(double limit_s, int64_t ready_after_polls, int64_t fail_after_polls) {

@@ -17,7 +17,7 @@ SYMBOLS = [
     "dsmd_input_system_load", "dsmd_input_system_load_files", "dsmd_input_system_destroy", "dsmd_input_system_counts",
     "dsmd_input_system_real", "dsmd_input_system_types", "dsmd_input_system_pair_table", "dsmd_input_system_exclusions",
     "dsmd_input_system_constraints", "dsmd_input_system_velocities", "dsmd_input_restart_read", "dsmd_input_restart_write",
-    "dsmd_input_nose_hoover_scale", "dsmd_host_brick_plan", "dsmd_host_counts_verdict", "dsmd_host_wait_probe", "dsmd_host_ewald_table",
+    "dsmd_input_nose_hoover_scale", "dsmd_host_brick_plan", "dsmd_host_counts_verdict", "dsmd_host_wait_probe", "dsmd_host_ewald_table", "dsmd_host_dart_throw",
 ]
 
 _lib = None
@@ -205,6 +205,14 @@ def counts_verdict(dims, counts, scratch_capacity=1 << 30):
 
 def wait_probe(limit_s, ready_after=-1, fail_after=-1):
     return lib().dsmd_host_wait_probe(c_double(limit_s), c_int64(ready_after), c_int64(fail_after))
+
+
+def dart_throw(n, box, min_dist, seed):
+    """[n, 3] points drawn uniformly in a periodic cube, each at least min_dist from all earlier ones (seeded)."""
+    out = np.zeros((int(n), 3), dtype=np.float64)
+    _check(lib().dsmd_host_dart_throw(c_int64(int(n)), c_double(box), c_double(min_dist), ctypes.c_uint64(int(seed)),
+                                      out.ctypes.data_as(ctypes.c_void_p), None))
+    return out
 
 
 def ewald_table(alpha, cutoff):

@@ -143,31 +143,21 @@ def water_box(cells: int = 60, *, cutoff=10.0, skin=2.0, seed=4242) -> System:
 
 def disordered_solid(n_target=1_000_000, *, density=0.05, min_dist=1.8, cutoff=5.0, seed=99) -> System:
     """Three-species disordered periodic solid for the radius-graph build: uniform random positions with a minimum
-    distance (seeded rejection: points that sit too close to an earlier point are re-drawn until none is left)."""
-    from scipy.spatial import cKDTree
-    rng = np.random.default_rng(seed)
+    distance (seeded dart throwing over a cell grid in the host library: a draw is kept only when it lies min_dist or
+    more from every point kept before it). A million atoms take about a second."""
+    from . import input_api
     L = (n_target / density) ** (1.0 / 3.0)
-    pos = rng.uniform(0.0, L, (n_target, 3))
-    for _ in range(200):
-        tree = cKDTree(pos, boxsize=L)
-        close = tree.query_pairs(min_dist, output_type="ndarray")
-        if len(close) == 0:
-            break
-        bad = np.unique(close[:, 1])          # the later atom of each close pair is re-drawn
-        pos[bad] = rng.uniform(0.0, L, (len(bad), 3))
-    else:
-        raise RuntimeError("minimum-distance rejection did not converge")
-    types = rng.choice(3, size=n_target, p=[0.5, 0.3, 0.2]).astype(np.int32)
+    pos = input_api.dart_throw(n_target, L, min_dist, seed)
+    types = np.random.default_rng(seed).choice(3, size=n_target, p=[0.5, 0.3, 0.2]).astype(np.int32)
     return System(name=f"solid_{n_target}", pos=pos, box=np.full(3, L), types=types, charge=np.zeros(n_target),
                   mass=np.ones(n_target), eps=np.ones((3, 3)), sig=np.ones((3, 3)), cutoff=cutoff, skin=0.0,
                   meta=dict(seed=seed, density=density, min_dist=min_dist))
 
 
 def disordered_solid_lattice(n_side=100, *, density=0.05, jitter=0.45, cutoff=5.0, seed=99) -> System:
-    """The same shape as disordered_solid() in seconds instead of minutes for a million atoms: a simple-cubic lattice at
-    the target density with a seeded uniform jitter per coordinate, which keeps every pair further apart than
-    spacing - 2 * jitter (2.714 - 0.9 = 1.81 A at density 0.05). Used where only sizes and neighbour counts matter (the
-    benchmark's edge-build timing)."""
+    """A second solid of the same density and species mix: a simple-cubic lattice with a seeded uniform jitter per
+    coordinate, which keeps every pair further apart than spacing - 2 * jitter (2.714 - 0.9 = 1.81 A at density 0.05).
+    Used by tests that want a different neighbour-count distribution from disordered_solid()."""
     rng = np.random.default_rng(seed)
     n = n_side ** 3
     a = (1.0 / density) ** (1.0 / 3.0)

@@ -98,6 +98,12 @@ int dsmd_host_counts_verdict(const int32_t dims[3], const int32_t* counts, int64
  * cubic. Returns the number of intervals; writes nothing when capacity_intervals is smaller. */
 int dsmd_host_ewald_table(double alpha, double cutoff_sq, float* out, int32_t capacity_intervals);
 
+/* Seeded random placement with a minimum distance in a periodic cube of edge `box` (uniform draws, a point is kept only
+ * when it lies min_dist or more from every point kept before it): the disordered-solid input of the radius-graph build.
+ * xyz receives n interleaved points; *draws (may be null) the number of draws made. The random stream is counter based, so
+ * a seed gives the same points everywhere. Fails when the density cannot be reached. */
+int dsmd_host_dart_throw(int64_t n, double box, double min_dist, uint64_t seed, double* xyz, int64_t* draws);
+
 /* The bounded host wait of the domain code against a stand-in that becomes ready (or fails) after a number of polls,
  * -1 = never: returns 0 ready, 7 (DSMD_ERR_TIMEOUT) when limit_s ran out, 2 when the stand-in failed. */
 int dsmd_host_wait_probe(double limit_s, int64_t ready_after_polls, int64_t fail_after_polls);

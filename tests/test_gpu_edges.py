@@ -216,3 +216,48 @@ def test_edges_under_an_eight_way_decomposition_equal_the_periodic_graph(cuda_de
     assert got.shape == whole.shape
     assert np.array_equal(canon(got.astype(np.float64)), canon(whole.astype(np.float64)))
     eb.close()
+
+
+def test_full_size_disordered_solid_whole_and_in_eight_bricks(cuda_device):
+    """The 1,000,000-atom disordered solid (uniform random placement with a 1.8 A minimum distance, cutoff 5 A) at full
+    size: the periodic radius graph has the edge count and the order-independent checksum of the (centre, neighbour,
+    lattice shift) set that the CPU oracle gave (tests/golden/make_edge_checksums.py); built brick by brick under a
+    2 x 2 x 2 decomposition with a cutoff-wide halo of explicit ghost atoms, the edges centred on owned atoms, translated
+    to global ids, add up to the same count and checksum, with the fixture's owned and ghost counts per brick."""
+    import json
+    import os
+    import sys
+    import torch
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, here)
+    from pair_checksum import MASK, checksum_torch
+    with open(os.path.join(here, "full_size_edge_checksums.json")) as f:
+        want = json.load(f)
+    s = syn.disordered_solid(want["atoms"])
+    cutoff = want["cutoff"]
+    eb = capi.EdgeBuilder()
+    x, y, z = (to_dev(s.pos[:, k]) for k in range(3))
+    src, dst, shift, vec = eb.build_periodic(x, y, z, s.box, cutoff)
+    sh = shift.to(torch.int64)
+    code = dst.to(torch.int64) * 27 + (sh[:, 0] + 1) * 9 + (sh[:, 1] + 1) * 3 + (sh[:, 2] + 1)
+    got = checksum_torch(src.to(torch.int64), code)
+    assert got == (want["edges"], int(want["sum1"]), int(want["sum2"]))
+    assert float((vec * vec).sum(1).max()) < cutoff * cutoff * (1 + 1e-6)
+    del src, dst, shift, vec, sh, code
+    wrapped = s.pos - s.box * np.floor(s.pos / s.box)
+    count = s1 = s2 = 0
+    for brick, numbers in zip(syn.brick_decompose(s.pos, s.box, (2, 2, 2), cutoff), want["bricks"]):
+        own, gsrc, gimg = brick["owned"], brick["ghost_src"], brick["ghost_image"]
+        assert (len(own), len(gsrc)) == (numbers["owned"], numbers["ghosts"])
+        pos = np.concatenate([wrapped[own], wrapped[gsrc] + gimg * s.box])
+        gid = to_dev(np.concatenate([own, gsrc]), dtype=torch.int64)
+        image = to_dev(np.concatenate([np.zeros((len(own), 3), dtype=np.int64), gimg.astype(np.int64)]), dtype=torch.int64)
+        cols = [to_dev(pos[:, k]) for k in range(3)]
+        idx, _ = eb.build(*cols, cutoff, lo=brick["lo"] - cutoff - 1e-9, hi=brick["hi"] + cutoff + 1e-9)
+        centred = idx[0] < len(own)
+        i, j = idx[0][centred], idx[1][centred]
+        im = image[j]
+        c, a, b = checksum_torch(gid[i], gid[j] * 27 + (im[:, 0] + 1) * 9 + (im[:, 1] + 1) * 3 + (im[:, 2] + 1))
+        count, s1, s2 = count + c, (s1 + a) & MASK, (s2 + b) & MASK
+    assert (count, s1, s2) == (want["edges"], int(want["sum1"]), int(want["sum2"]))
+    eb.close()

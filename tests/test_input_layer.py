@@ -311,3 +311,22 @@ def test_ewald_table_equals_the_reference_builders_coefficient_by_coefficient():
         ev = lambda c: ((c[..., 3:4] * t + c[..., 2:3]) * t + c[..., 1:2]) * t + c[..., 0:1]
         va, vb = ev(mine.astype(np.float64)), ev(theirs.astype(np.float64))
         assert np.all(np.abs(va - vb) <= 2e-6 * np.abs(vb) + 1e-30)
+
+
+def test_dart_throw_keeps_the_minimum_distance_and_repeats_for_a_seed():
+    """The disordered-solid generator: n points in the periodic cube, none closer than the minimum distance to another
+    (images included), the same points for the same seed, other points for another; a density past saturation fails."""
+    from scipy.spatial import cKDTree
+    from deepscalemd_b200 import synthetic as syn
+    s = syn.disordered_solid(20000, seed=5)
+    L = s.box[0]
+    assert s.pos.shape == (20000, 3) and s.pos.min() >= 0.0 and s.pos.max() < L
+    assert abs(20000 / L ** 3 - 0.05) < 1e-12
+    nearest = cKDTree(s.pos, boxsize=L).query(s.pos, k=2)[0][:, 1]
+    assert nearest.min() >= 1.8 and nearest.min() < 1.9          # rejection at work: without it the minimum is ~0.05 A
+    assert np.array_equal(s.pos, syn.disordered_solid(20000, seed=5).pos)
+    assert not np.array_equal(s.pos, syn.disordered_solid(20000, seed=6).pos)
+    assert np.bincount(s.types, minlength=3).tolist() == pytest.approx([10000, 6000, 4000], abs=300)
+    with pytest.raises(input_api.InputError):
+        input_api.dart_throw(1000, 10.0, 1.8, 1)                 # 1000 spheres of 1.8 A do not fit a 10 A cube
+    assert input_api.dart_throw(50, 10.0, 0.0, 1).shape == (50, 3)
