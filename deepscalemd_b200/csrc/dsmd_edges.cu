@@ -56,21 +56,43 @@ __global__ void k_edge_keys(Grid g, int n, const double* __restrict__ x, const d
     val[i] = i;
 }
 
-// Sorted fixed-point atoms (w = the caller's atom index), inverse permutation and cell starts.
+// How many box lengths a coordinate lies from its wrapped place, consistent with to_fixed (which maps a coordinate that
+// rounds up to the upper face onto the lower face of the next image).
+__device__ __forceinline__ int wrap_count(double v, int axis, const Grid& g) {
+    if (!g.wrap[axis]) return 0;
+    const double u = (v - g.org[axis]) * g.inv_len[axis];
+    if (!(u == u) || fabs(u) > 1.0e9) return 0;
+    const double w = floor(u);
+    return static_cast<int>(w) + (u - w >= 1.0 ? 1 : 0);
+}
+
+constexpr int kWrapBits = 10, kWrapBias = 1 << (kWrapBits - 1), kWrapMask = (1 << kWrapBits) - 1;
+
+__device__ __forceinline__ int packed_wraps(int wx, int wy, int wz) {
+    auto field = [](int w) { return min(max(w + kWrapBias, 0), kWrapMask); };
+    return field(wx) | (field(wy) << kWrapBits) | (field(wz) << (2 * kWrapBits));
+}
+
+__device__ __forceinline__ int wrap_field(int packed, int axis) {
+    return ((packed >> (axis * kWrapBits)) & kWrapMask) - kWrapBias;
+}
+
+// Sorted fixed-point atoms (w = the caller's atom index), their wrap counts (periodic form only) and cell starts.
 __global__ void k_edge_gather(Grid g, int n, const unsigned* __restrict__ key, const int* __restrict__ val,
                               const double* __restrict__ x, const double* __restrict__ y, const double* __restrict__ z,
-                              int4* __restrict__ pq, int* __restrict__ slot_of, int* __restrict__ cell_start) {
+                              int4* __restrict__ pq, int* __restrict__ wraps, int* __restrict__ cell_start) {
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= n) return;
     const int a = val[s];
     unsigned bad = 0;
+    const double px = x[a], py = y[a], pz = z[a];
     int4 p;
-    p.x = static_cast<int>(dsmd::to_fixed(x[a], 0, g, bad));
-    p.y = static_cast<int>(dsmd::to_fixed(y[a], 1, g, bad));
-    p.z = static_cast<int>(dsmd::to_fixed(z[a], 2, g, bad));
+    p.x = static_cast<int>(dsmd::to_fixed(px, 0, g, bad));
+    p.y = static_cast<int>(dsmd::to_fixed(py, 1, g, bad));
+    p.z = static_cast<int>(dsmd::to_fixed(pz, 2, g, bad));
     p.w = a;
     pq[s] = p;
-    slot_of[a] = s;
+    if (wraps) wraps[s] = packed_wraps(wrap_count(px, 0, g), wrap_count(py, 1, g), wrap_count(pz, 2, g));
     const int k_here = static_cast<int>(key[s]);
     const int k_prev = s == 0 ? -1 : static_cast<int>(key[s - 1]);
     for (int c = k_prev + 1; c <= k_here; ++c) cell_start[c] = s;
@@ -90,7 +112,7 @@ struct SearchArgs {
     const int* owner;
     const unsigned char* ok;
     unsigned* rows;
-    int* counts;        // by sorted slot (interface form) or by atom index (compact form)
+    int* counts;        // by sorted slot
     EdgeStatus* st;
 };
 
@@ -106,8 +128,8 @@ __device__ __forceinline__ bool within_fp64(const Grid& g, const SearchArgs& a, 
     return r2 < g.r2_list_d;
 }
 
-// One thread per sorted slot; hits (the neighbour's atom index) go to the slot's column of its 32-atom slice.
-// PERIODIC: all axes wrap, counts are stored by the centre's atom index (the expansion sorts every row by neighbour).
+// One thread per sorted slot; hits go to the slot's column of its 32-atom slice: the neighbour's atom index, or, PERIODIC
+// (all axes wrap), its sorted slot (the expansion reads the neighbour's position by slot).
 template <bool PERIODIC>
 __global__ void __launch_bounds__(kSearchThreads) k_edge_search(Grid g, SearchArgs a) {
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
@@ -151,14 +173,14 @@ __global__ void __launch_bounds__(kSearchThreads) k_edge_search(Grid g, SearchAr
                             if (!within_fp64<PERIODIC>(g, a, centre, pj.w)) continue;
                         }
                         if (check_nb && !a.ok[a.owner ? a.owner[pj.w] : pj.w]) continue;
-                        if (count < a.stride) a.rows[base + static_cast<size_t>(count) * 32] = static_cast<unsigned>(pj.w);
+                        if (count < a.stride) a.rows[base + static_cast<size_t>(count) * 32] = static_cast<unsigned>(PERIODIC ? s : pj.w);
                         ++count;
                     }
                 }
             }
         }
     }
-    a.counts[PERIODIC ? centre : p] = min(count, a.stride);
+    a.counts[p] = min(count, a.stride);
     if (count > a.stride) atomicMax(&a.st->need_stride, static_cast<unsigned>(count));
     if (rechecked) atomicAdd(&a.st->rechecked, rechecked);
 }
@@ -227,35 +249,27 @@ __global__ void k_edge_fill(int n, long long n_edges, int stride, const int4* __
     }
 }
 
-// Compact periodic form: a warp takes 32 consecutive atom indices (edges come out sorted by src), copies their rows into
-// shared memory - entry k of lane l at [k * 32 + l], so that every lane works on its own bank - sorting each by neighbour
-// index on the way in (insertion: rows hold a few dozen entries), and streams them out in flat order.
-__global__ void k_edge_fill_compact(Grid g, int n, int stride, const int* __restrict__ slot_of,
+// Compact periodic form: as k_edge_fill, a warp takes 32 consecutive sorted slots and streams their edges out in flat
+// order with contiguous stores (centres in cell order, the neighbours of a centre in the order of the search: the
+// order of the interface form). Rows hold neighbour slots, so positions and wrap counts are read where they lie
+// whatever the caller's atom numbering. Displacements come from the fixed-point coordinates (resolution box / 2^32);
+// the lattice shift refers to the caller's coordinates: x[dst] + shift * box - x[src] = vec.
+__global__ void k_edge_fill_compact(Grid g, int n, int stride, const int4* __restrict__ pq, const int* __restrict__ wraps,
                                     const unsigned* __restrict__ rows, const int* __restrict__ counts,
-                                    const long long* __restrict__ offsets, const double* __restrict__ x,
-                                    const double* __restrict__ y, const double* __restrict__ z, int* __restrict__ src,
-                                    int* __restrict__ dst, signed char* __restrict__ shift, float* __restrict__ vec) {
-    extern __shared__ unsigned sorted_rows[];
+                                    const long long* __restrict__ offsets, int* __restrict__ src, int* __restrict__ dst,
+                                    signed char* __restrict__ shift, float* __restrict__ vec) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    unsigned* mine = sorted_rows + static_cast<size_t>(threadIdx.x >> 5) * stride * 32;
-    const int i = warp * 32 + lane;
+    const int p = warp * 32 + lane;
     if (warp * 32 >= n) return;
-    const int cnt = i < n ? counts[i] : 0;
-    if (i < n) {
-        const int slot = slot_of[i];
-        const size_t base = (static_cast<size_t>(slot >> 5) * stride) * 32 + (slot & 31);
-        for (int k = 0; k < cnt; ++k) {
-            const unsigned nb = rows[base + static_cast<size_t>(k) * 32];
-            int at = k;
-            while (at > 0 && mine[(at - 1) * 32 + lane] > nb) {
-                mine[at * 32 + lane] = mine[(at - 1) * 32 + lane];
-                --at;
-            }
-            mine[at * 32 + lane] = nb;
-        }
+    int4 pi = make_int4(0, 0, 0, 0);
+    int cnt = 0, wi = 0;
+    if (p < n) {
+        pi = pq[p];
+        cnt = counts[p];
+        wi = wraps[p];
     }
-    __syncwarp();
+    const long long out0 = offsets[warp * 32];
     int prefix = cnt;
     for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(0xffffffffu, prefix, o);
@@ -263,25 +277,35 @@ __global__ void k_edge_fill_compact(Grid g, int n, int stride, const int* __rest
     }
     const int total = __shfl_sync(0xffffffffu, prefix, 31);
     prefix -= cnt;
-    const long long out0 = offsets[warp * 32];
+    const size_t slice = static_cast<size_t>(warp) * stride * 32;
+    const double unit[3] = {g.box[0] / 4294967296.0, g.box[1] / 4294967296.0, g.box[2] / 4294967296.0};
     for (int t0 = 0; t0 < total; t0 += 32) {
         const int t = t0 + lane;
         const int c = owner_lane(min(t, total - 1), prefix);
         const int c_prefix = __shfl_sync(0xffffffffu, prefix, c);
+        const int c_wraps = __shfl_sync(0xffffffffu, wi, c);
+        const int ci[4] = {__shfl_sync(0xffffffffu, pi.x, c), __shfl_sync(0xffffffffu, pi.y, c),
+                           __shfl_sync(0xffffffffu, pi.z, c), __shfl_sync(0xffffffffu, pi.w, c)};
         if (t < total) {
             const int k = t - c_prefix;
-            const int nb = static_cast<int>(mine[k * 32 + c]);
-            const int centre = warp * 32 + c;
+            const unsigned slot = rows[slice + static_cast<size_t>(k) * 32 + c];
+            const int4 pj = __ldg(&pq[slot]);
+            const int wj = __ldg(&wraps[slot]);
             const long long o = out0 + t;
-            double d[3] = {x[nb] - x[centre], y[nb] - y[centre], z[nb] - z[centre]};
+            const int cj[3] = {pj.x, pj.y, pj.z};
 #pragma unroll
             for (int a = 0; a < 3; ++a) {
-                const double image = -rint(d[a] / g.box[a]);   // lattice shift that brings the neighbour closest
-                shift[3 * o + a] = static_cast<signed char>(image);
-                vec[3 * o + a] = static_cast<float>(d[a] + image * g.box[a]);
+                // the wrapped 32-bit difference is the minimum image; comparing it with the plain difference of the
+                // wrapped coordinates tells which image of the neighbour that is
+                const int nearest = static_cast<int>(static_cast<unsigned>(cj[a]) - static_cast<unsigned>(ci[a]));
+                const long long plain = static_cast<long long>(static_cast<unsigned>(cj[a])) -
+                                        static_cast<long long>(static_cast<unsigned>(ci[a]));
+                const int image = static_cast<int>((static_cast<long long>(nearest) - plain) >> 32);
+                shift[3 * o + a] = static_cast<signed char>(image - (wrap_field(wj, a) - wrap_field(c_wraps, a)));
+                vec[3 * o + a] = static_cast<float>(static_cast<double>(nearest) * unit[a]);
             }
-            src[o] = centre;
-            dst[o] = nb;
+            src[o] = ci[3];
+            dst[o] = pj.w;
         }
     }
 }
@@ -488,7 +512,7 @@ struct dsmd_edges {
     unsigned* key[2] = {nullptr, nullptr};  size_t cap_key[2] = {0, 0};
     int* val[2] = {nullptr, nullptr};       size_t cap_val[2] = {0, 0};
     int4* pq = nullptr;                     size_t cap_pq = 0;
-    int* slot_of = nullptr;                 size_t cap_slot = 0;
+    int* wraps = nullptr;                   size_t cap_wraps = 0;     // per sorted slot, periodic form
     int* cell_start = nullptr;              size_t cap_cells = 0;
     unsigned* rows = nullptr;               size_t cap_rows = 0;
     int* counts = nullptr;                  size_t cap_counts = 0;
@@ -504,7 +528,6 @@ struct dsmd_edges {
     long long* img_counts = nullptr;        size_t cap_img_counts = 0;
     long long* img_offsets = nullptr;       size_t cap_img_offsets = 0;
     unsigned long long* img_masks = nullptr; size_t cap_img_masks = 0;
-    size_t compact_smem = 0;                // dynamic shared memory k_edge_fill_compact is cleared for
     int64_t n_img_src = 0;                  // atoms the last image build was given
     double* virial_partials = nullptr;      // [3 * kVirialBlocks] + 4 results
     double* h_virial = nullptr;             // pinned, 4 doubles
@@ -625,7 +648,7 @@ int edge_search(dsmd_edges* e, const Grid& g, const double* d_x, const double* d
         EDGE_ALLOC(e, grow(e->val[k], e->cap_val[k], un));
     }
     EDGE_ALLOC(e, grow(e->pq, e->cap_pq, un));
-    EDGE_ALLOC(e, grow(e->slot_of, e->cap_slot, un));
+    if (PERIODIC) EDGE_ALLOC(e, grow(e->wraps, e->cap_wraps, un));
     EDGE_ALLOC(e, grow(e->cell_start, e->cap_cells, static_cast<size_t>(g.ncells) + 1));
     EDGE_ALLOC(e, grow(e->counts, e->cap_counts, un));
     EDGE_ALLOC(e, grow(e->offsets, e->cap_offsets, un));
@@ -643,7 +666,7 @@ int edge_search(dsmd_edges* e, const Grid& g, const double* d_x, const double* d
     EDGE_CUDA(e, cub::DeviceRadixSort::SortPairs(e->temp, sort_bytes, e->key[0], e->key[1], e->val[0], e->val[1],
                                                  static_cast<int>(n), 0, bits, s));
     k_edge_gather<<<blocks_for(n, kThreads), kThreads, 0, s>>>(g, static_cast<int>(n), e->key[1], e->val[1], d_x, d_y,
-                                                              d_z, e->pq, e->slot_of, e->cell_start);
+                                                              d_z, e->pq, PERIODIC ? e->wraps : nullptr, e->cell_start);
     k_edge_cell_tail<<<blocks_for(g.ncells + 1, kThreads), kThreads, 0, s>>>(e->key[1], static_cast<int>(n), g.ncells + 1,
                                                                            e->cell_start);
     e->launches += 3;
@@ -696,7 +719,7 @@ void dsmd_edges_destroy(dsmd_edges* e) {
     if (!e) return;
     cudaSetDevice(e->device);
     for (int k = 0; k < 2; ++k) { cudaFree(e->key[k]); cudaFree(e->val[k]); }
-    cudaFree(e->pq); cudaFree(e->slot_of); cudaFree(e->cell_start); cudaFree(e->rows); cudaFree(e->counts);
+    cudaFree(e->pq); cudaFree(e->wraps); cudaFree(e->cell_start); cudaFree(e->rows); cudaFree(e->counts);
     cudaFree(e->offsets); cudaFree(e->temp); cudaFree(e->edges); cudaFree(e->shift); cudaFree(e->c_src);
     cudaFree(e->c_dst); cudaFree(e->c_shift); cudaFree(e->c_vec); cudaFree(e->bounds); cudaFree(e->d_status);
     cudaFree(e->img_counts); cudaFree(e->img_offsets); cudaFree(e->img_masks); cudaFree(e->virial_partials);
@@ -806,16 +829,9 @@ int dsmd_edges_build_periodic(dsmd_edges* e, const double* d_x, const double* d_
     EDGE_ALLOC(e, grow(e->c_shift, e->cap_cshift, 3 * static_cast<size_t>(E)));
     EDGE_ALLOC(e, grow(e->c_vec, e->cap_cvec, 3 * static_cast<size_t>(E)));
     {
-        constexpr int kFillThreads = 128;   // four warps, each with its own rows in shared memory
-        const size_t smem = static_cast<size_t>(kFillThreads / 32) * e->stride * 32 * sizeof(unsigned);
-        if (smem > 200 * 1024) return efail(e, DSMD_ERR_CAPACITY, "rows too long for the compact form (more than 400 neighbours per atom)");
-        if (smem > e->compact_smem) {
-            EDGE_CUDA(e, cudaFuncSetAttribute(k_edge_fill_compact, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-            e->compact_smem = smem;
-        }
-        k_edge_fill_compact<<<blocks_for(n, kFillThreads), kFillThreads, smem, s>>>(g, static_cast<int>(n), e->stride, e->slot_of,
-                                                                                  e->rows, e->counts, e->offsets, d_x, d_y, d_z,
-                                                                                  e->c_src, e->c_dst, e->c_shift, e->c_vec);
+        k_edge_fill_compact<<<blocks_for(n, kThreads), kThreads, 0, s>>>(g, static_cast<int>(n), e->stride, e->pq, e->wraps,
+                                                                         e->rows, e->counts, e->offsets, e->c_src, e->c_dst,
+                                                                         e->c_shift, e->c_vec);
     }
     ++e->launches;
     EDGE_CUDA(e, cudaGetLastError());

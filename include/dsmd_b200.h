@@ -371,8 +371,11 @@ int dsmd_mark_receivers(dsmd_edges* eb, const double* d_x, const double* d_y, co
                         const double lo[3], const double hi[3], double reach, unsigned char* d_ok, void* stream);
 
 /* Compact periodic radius graph (no image atoms): n atoms in an orthorhombic periodic box; directed edges as
- * int32 src / dst, int8 lattice shift [E * 3] (dst image = pos[dst] + shift * box) and fp32 edge vectors [E * 3],
- * sorted by (src, dst, shift). No counterpart in the reference, which feeds images as explicit atoms. */
+ * int32 src / dst, int8 lattice shift [E * 3] (dst image = pos[dst] + shift * box, in the coordinates as given, which
+ * need not be wrapped into the box; shifts beyond +-127 do not fit) and fp32 edge vectors [E * 3]. Edges are grouped by
+ * src, centres in cell order and the neighbours of a centre in the order of the search, as in the interface form (the
+ * same order for the same input).
+ * No counterpart in the reference, which feeds images as explicit atoms. */
 int dsmd_edges_build_periodic(dsmd_edges* eb, const double* d_x, const double* d_y, const double* d_z, int64_t n,
                               const double box[3], double cutoff, int64_t* n_edges, void* stream);
 int dsmd_edges_result_compact(const dsmd_edges* eb, const int32_t** d_src, const int32_t** d_dst,

@@ -97,11 +97,20 @@ def test_compact_periodic_graph(cuda_device):
     want = np.stack([want_idx[0], want_idx[1], *(np.rint(want_sh[:, k] / L).astype(np.int64) for k in range(3))])
     got = np.stack([src.astype(np.int64), dst.astype(np.int64), *(sh[:, k].astype(np.int64) for k in range(3))])
     assert np.array_equal(canon(got), canon(want))
-    # already sorted by (src, dst, shift)
-    assert np.array_equal(got, canon(got))
+    # grouped by centre: row 0 changes value n - 1 times at most
+    assert (np.diff(src) != 0).sum() <= s.n - 1
     d = s.pos[dst] + sh * s.box - s.pos[src]
     assert np.abs(vec - d).max() < 1e-5
-    assert abs(len(src) / s.n - 4.18879 * 125 * 0.05) < 1.0      # 26.2 neighbours per atom
+    assert 24.0 < len(src) / s.n < 26.2      # 26.2 neighbours per atom at this density, less what the minimum distance excludes
+    # positions given some box lengths away from the box: the same edges in the same order, the same displacements, and
+    # lattice shifts that refer to the coordinates as given
+    moved = s.pos + np.random.default_rng(3).integers(-3, 4, s.pos.shape) * s.box
+    src2, dst2, sh2, vec2 = eb.build_periodic(*(to_dev(moved[:, k]) for k in range(3)), s.box, s.cutoff)
+    src2, dst2, sh2, vec2 = src2.cpu().numpy(), dst2.cpu().numpy(), sh2.cpu().numpy(), vec2.cpu().numpy()
+    assert np.array_equal(src2, src) and np.array_equal(dst2, dst)
+    assert np.abs(vec2 - vec).max() < 1e-5
+    assert np.abs(moved[dst2] + sh2 * s.box - moved[src2] - vec2).max() < 1e-5
+    assert np.abs(sh2).max() > 1
     eb.close()
 
 
