@@ -589,8 +589,12 @@ int edge_grid(dsmd_edges* e, Grid& g, const double lo[3], const double hi[3], bo
         g.inv_len[a] = 1.0 / len[a];
     }
     const long long max_cells = std::max<long long>(64, 2 * static_cast<long long>(n));
+    // Half-width cells (25 cell rows around an atom) pay when a row holds a few atoms; in a sparse system the cost of
+    // opening a row outweighs the tighter windows and 9 rows of full-width cells are faster (measured on 1,000,000
+    // atoms at 0.05 / A^3, cutoff 5 A, 0.8 atoms per half-width cell: 0.79 ms against 0.89 ms per build).
+    const double per_half_cell = static_cast<double>(n) / (len[0] * len[1] * len[2]) * (cutoff * cutoff * cutoff / 8.0);
     bool done = false;
-    for (int stencil = 2; stencil >= 1 && !done; --stencil) {
+    for (int stencil = per_half_cell >= 1.0 ? 2 : 1; stencil >= 1 && !done; --stencil) {
         double width = cutoff / stencil * (1.0 + 1e-6);
         for (int tries = 0; tries < 64; ++tries) {
             long long cells = 1;
