@@ -149,6 +149,54 @@ __global__ void k_cell_tail(const unsigned* __restrict__ key, int n_sorted, int 
 // kernel: Verlet list build
 // ---------------------------------------------------------------------------------------------------------------------
 
+// Where the ghosts of a cell row sit: lo_end = one past the last x cell of the row's lower half that holds a ghost (0:
+// none), hi_begin = the first x cell of its upper half that holds one (nc[0]: none). One warp per (y, z) row.
+__global__ void k_ghost_row_extent(Grid g, const int* __restrict__ ghost_cell_start, int* __restrict__ lo_end,
+                                   int* __restrict__ hi_begin) {
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= g.nc[1] * g.nc[2]) return;
+    const int* cells = ghost_cell_start + static_cast<size_t>(row) * g.nc[0];
+    const int half = g.nc[0] >> 1;
+    int lo = 0, hi = g.nc[0];
+    for (int c = lane; c < g.nc[0]; c += 32) {
+        if (cells[c + 1] > cells[c]) {
+            if (c < half) lo = max(lo, c + 1);
+            else hi = min(hi, c);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        lo = max(lo, __shfl_down_sync(0xffffffffu, lo, o));
+        hi = min(hi, __shfl_down_sync(0xffffffffu, hi, o));
+    }
+    if (lane == 0) { lo_end[row] = lo; hi_begin[row] = hi; }
+}
+
+// The same over the rows a centre of row (yc, zc) searches (stencil reach in y and z, wrapping where the axis does): an
+// owned atom whose x window stays inside [near_lo, near_hi) of its row cannot have a ghost partner and skips the ghost
+// pass of the list build altogether.
+__global__ void k_ghost_rows_near(Grid g, const int* __restrict__ lo_end, const int* __restrict__ hi_begin,
+                                  int* __restrict__ near_lo, int* __restrict__ near_hi) {
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= g.nc[1] * g.nc[2]) return;
+    const int yc0 = row % g.nc[1], zc0 = row / g.nc[1];
+    int lo = 0, hi = g.nc[0];
+    for (int dz = -g.stencil; dz <= g.stencil; ++dz) {
+        int zc = zc0 + dz;
+        if (g.wrap[2]) zc = (zc + g.nc[2]) % g.nc[2];
+        else if (zc < 0 || zc >= g.nc[2]) continue;
+        for (int dy = -g.stencil; dy <= g.stencil; ++dy) {
+            int yc = yc0 + dy;
+            if (g.wrap[1]) yc = (yc + g.nc[1]) % g.nc[1];
+            else if (yc < 0 || yc >= g.nc[1]) continue;
+            lo = max(lo, lo_end[zc * g.nc[1] + yc]);
+            hi = min(hi, hi_begin[zc * g.nc[1] + yc]);
+        }
+    }
+    near_lo[row] = lo;
+    near_hi[row] = hi;
+}
+
 struct ExclusionTable {
     const int* offsets;    // [n_global + 1] by global id, or null
     const int* partners;   // sorted per atom
@@ -180,6 +228,7 @@ __global__ void __launch_bounds__(kBuildThreads, 16)
 k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, const float4* __restrict__ pf,
              const double* __restrict__ x, const double* __restrict__ y, const double* __restrict__ z,
              const int* __restrict__ gid, ExclusionTable excl, const int* __restrict__ cell_start,
+             const int* __restrict__ ghost_near_lo, const int* __restrict__ ghost_near_hi,
              unsigned* __restrict__ nbr, int stride, int* __restrict__ deg, int* __restrict__ deg_int, Status* st) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const bool active = i < n_owned;   // lanes past the end stay for the warp sums at the bottom
@@ -207,7 +256,16 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
     unsigned* const dst_end = dst + static_cast<size_t>(stride) * 32;
     int interior = 0;
     unsigned rechecked = 0;
-    const int n_seg = !active ? 0 : (n_total > n_owned ? 2 : 1);
+    // the ghost pass only for atoms whose x window reaches an x cell with ghosts in one of the rows they search (on an
+    // axis that wraps the window may come round the box: any ghost in those rows counts)
+    int n_seg = active ? 1 : 0;
+    if (active && n_total > n_owned) {
+        const int row_yz = cz * g.nc[1] + cy;
+        const int near_lo = ghost_near_lo[row_yz], near_hi = ghost_near_hi[row_yz];
+        const int reach_cells = static_cast<int>(g.x_reach / g.cellw[0]) + 2;
+        if (g.wrap[0] ? (near_lo > 0 || near_hi < g.nc[0]) : (cx - reach_cells < near_lo || cx + reach_cells >= near_hi))
+            n_seg = 2;
+    }
     // The x window of a cell row is the chord of the list sphere at the row's distance from the atom in the y-z plane
     // (dsmd::row_window spells the rule out): the distance has one term per axis, each a function of the cell offset and
     // of the atom's place inside its home cell, so the z term is worked out per layer and the y term per row.
@@ -352,14 +410,16 @@ __device__ __forceinline__ void block_max_to_status(double v, Status* st) {
     }
 }
 
-// INTEGRATE: first velocity-Verlet half before the pack (v += dt/2 a, x += dt v).
+// INTEGRATE: kick and drift before the pack (v += kick_c f / m, x += dt v): the first velocity-Verlet half with
+// kick_c = dt/2 (times the force-to-acceleration factor), or, with kick_c = dt, the second half of the previous step and
+// the first half of this one in one pass (both use the same forces).
 template <bool INTEGRATE>
 __global__ void k_pack(Grid g, int first, int count, int n_owned, double* __restrict__ x, double* __restrict__ y,
                        double* __restrict__ z, double* __restrict__ vx, double* __restrict__ vy,
                        double* __restrict__ vz, const double* __restrict__ fx, const double* __restrict__ fy,
                        const double* __restrict__ fz, const double* __restrict__ mass, const int* __restrict__ type,
                        const double* __restrict__ xref, const double* __restrict__ yref,
-                       const double* __restrict__ zref, int4* __restrict__ pq, double dt, double half_dt_c,
+                       const double* __restrict__ zref, int4* __restrict__ pq, double dt, double kick_c,
                        Status* st) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     const int s = first + t;
@@ -367,7 +427,7 @@ __global__ void k_pack(Grid g, int first, int count, int n_owned, double* __rest
     if (t < count) {
         double px = x[s], py = y[s], pz = z[s];
         if (INTEGRATE) {
-            const double a = half_dt_c / mass[s];
+            const double a = kick_c / mass[s];
             const double ux = vx[s] + a * fx[s], uy = vy[s] + a * fy[s], uz = vz[s] + a * fz[s];
             vx[s] = ux; vy[s] = uy; vz[s] = uz;
             px += dt * ux; py += dt * uy; pz += dt * uz;
@@ -792,6 +852,8 @@ struct dsmd_ctx {
     int* ghost_slot = nullptr;
     int* cell_start = nullptr;
     int64_t cell_capacity = 0;
+    int* ghost_rows = nullptr;        // [4 * rows]: lo_end, hi_begin per (y, z) row, then the same over the rows searched
+    int64_t ghost_rows_capacity = 0;
     unsigned* nbr = nullptr;
     size_t nbr_capacity = 0;   // entries
     int stride = 0;
@@ -1121,7 +1183,7 @@ void dsmd_destroy(dsmd_ctx* c) {
     }
     cudaFree(c->pq); cudaFree(c->pf); cudaFree(c->qf);
     for (int a = 0; a < 3; ++a) cudaFree(c->ref[a]);
-    cudaFree(c->ghost_slot); cudaFree(c->cell_start); cudaFree(c->nbr); cudaFree(c->deg); cudaFree(c->deg_int);
+    cudaFree(c->ghost_slot); cudaFree(c->cell_start); cudaFree(c->ghost_rows); cudaFree(c->nbr); cudaFree(c->deg); cudaFree(c->deg_int);
     cudaFree(c->cub_temp); cudaFree(c->c6c12); cudaFree(c->ewald); cudaFree(c->excl_off); cudaFree(c->excl_partner);
     cudaFree(c->partials); cudaFree(c->scalars); cudaFree(c->status); cudaFree(c->flag); cudaFree(c->offsets64);
     cudaFree(c->cl_gid); cudaFree(c->cl_a); cudaFree(c->cl_b); cudaFree(c->cl_d2); cudaFree(c->slot_of_gid);
@@ -1386,13 +1448,28 @@ int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
         c->stride = std::max(32, static_cast<int>(expect * 1.3) + 24);
         c->stride = (c->stride + 3) & ~3;
     }
+    const int64_t rows = static_cast<int64_t>(c->grid.nc[1]) * c->grid.nc[2];
+    if (4 * rows > c->ghost_rows_capacity) {
+        if (c->ghost_rows) cudaFree(c->ghost_rows);
+        c->ghost_rows = nullptr;
+        DSMD_CUDA(c, cudaMalloc(&c->ghost_rows, sizeof(int) * 4 * rows));
+        c->ghost_rows_capacity = 4 * rows;
+    }
+    if (c->n_total > c->n_owned) {
+        k_ghost_row_extent<<<blocks_for(rows * 32, kThreads), kThreads, 0, s>>>(c->grid, c->cell_start + c->grid.ncells,
+                                                                               c->ghost_rows, c->ghost_rows + rows);
+        DSMD_LAUNCHED(c);
+        k_ghost_rows_near<<<blocks_for(rows, kThreads), kThreads, 0, s>>>(c->grid, c->ghost_rows, c->ghost_rows + rows,
+                                                                         c->ghost_rows + 2 * rows, c->ghost_rows + 3 * rows);
+        DSMD_LAUNCHED(c);
+    }
     for (int attempt = 0; attempt < 4; ++attempt) {
         { const int rc = ensure_list(c, c->stride); if (rc) return rc; }
         ExclusionTable ex{c->excl_off, c->excl_partner, static_cast<int>(c->excl_n_global)};
         k_build_list<<<blocks_for(c->n_owned, kBuildThreads), kBuildThreads, 0, s>>>(
             c->grid, static_cast<int>(c->n_owned), static_cast<int>(c->n_total), c->pq, c->pf, c->real[c->cur][0],
-            c->real[c->cur][1], c->real[c->cur][2], c->gid[c->cur], ex, c->cell_start, c->nbr, c->stride, c->deg,
-            c->deg_int, c->status);
+            c->real[c->cur][1], c->real[c->cur][2], c->gid[c->cur], ex, c->cell_start, c->ghost_rows + 2 * rows,
+            c->ghost_rows + 3 * rows, c->nbr, c->stride, c->deg, c->deg_int, c->status);
         DSMD_LAUNCHED(c);
         { const int rc = read_status(c, s); if (rc) return rc; }
         if (c->h_status->out_of_domain)
@@ -1458,14 +1535,16 @@ int dsmd_list_export(dsmd_ctx* c, int32_t* d_i, int32_t* d_j, uint8_t* d_flags, 
     return DSMD_OK;
 }
 
-static int pack_impl(dsmd_ctx* c, int64_t first, int64_t count, bool integrate, double dt, double f2a, cudaStream_t s) {
+// kick: 0.5 for the first velocity-Verlet half, 1.0 for the merged second-and-first half.
+static int pack_impl(dsmd_ctx* c, int64_t first, int64_t count, bool integrate, double dt, double f2a, cudaStream_t s,
+                     double kick = 0.5) {
     if (count <= 0) return DSMD_OK;
     double** r = c->real[c->cur];
     if (integrate)
         k_pack<true><<<blocks_for(count, kThreads), kThreads, 0, s>>>(
             c->grid, static_cast<int>(first), static_cast<int>(count), static_cast<int>(c->n_owned), r[0], r[1], r[2],
             r[3], r[4], r[5], r[6], r[7], r[8], r[9], c->type[c->cur], c->ref[0], c->ref[1], c->ref[2], c->pq, dt,
-            0.5 * dt * f2a, c->status);
+            kick * dt * f2a, c->status);
     else
         k_pack<false><<<blocks_for(count, kThreads), kThreads, 0, s>>>(
             c->grid, static_cast<int>(first), static_cast<int>(count), static_cast<int>(c->n_owned), r[0], r[1], r[2],
@@ -1721,12 +1800,16 @@ int dsmd_rattle(dsmd_ctx* c, double dt, double f2a, double* d_virial_diag, void*
 }
 
 int dsmd_integrate(dsmd_ctx* c, int half, double dt, double f2a, void* stream) {
-    if (!c || (half != 1 && half != 2)) return DSMD_ERR_INVALID;
+    if (!c || half < 1 || half > 3) return DSMD_ERR_INVALID;
     if (!c->grid_valid) return fail(c, DSMD_ERR_STATE, "no neighbour list built yet");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool constrained = c->n_clusters > 0;
     if (constrained && c->n_total != c->n_owned)
         return fail(c, DSMD_ERR_STATE, "constraints are solved on single-rank systems only");
+    if (half == 3) {
+        if (constrained) return fail(c, DSMD_ERR_STATE, "the merged half steps are not available with constraints");
+        return pack_impl(c, 0, c->n_owned, true, dt, f2a, s, 1.0);
+    }
     if (half == 1) {
         if (!constrained) return pack_impl(c, 0, c->n_owned, true, dt, f2a, s);
         // constrained: keep the positions from before the drift, drift, SHAKE, then convert the corrected positions
@@ -1790,8 +1873,11 @@ int dsmd_run_nve(dsmd_ctx* c, int64_t n_steps, double dt, double f2a, double hi_
     double d_prev = 0.0, d_prev2 = 0.0;   // displacement (not squared) seen one and two steps ago (lagged mode)
     int pending = -1;                      // read-back slot in flight
     auto bits_to_double = [](unsigned long long b) { double v; std::memcpy(&v, &b, sizeof(v)); return v; };
+    // Between two steps of this loop nobody reads the velocities, so the second half of one step and the first half of the
+    // next (the same forces) are one pass over the atoms; with constraints RATTLE sits between them and they stay apart.
+    const bool merge = c->n_clusters == 0;
     for (int64_t step = 0; step < n_steps; ++step) {
-        { const int rc = dsmd_integrate(c, 1, dt, f2a, s); if (rc) return rc; }   // with SHAKE when constraints are set
+        { const int rc = dsmd_integrate(c, merge && step > 0 ? 3 : 1, dt, f2a, s); if (rc) return rc; }   // with SHAKE when constraints are set
         ++since_build;
         bool rebuild = every > 0 && since_build >= every;
         if (!lagged) {
@@ -1827,7 +1913,7 @@ int dsmd_run_nve(dsmd_ctx* c, int64_t n_steps, double dt, double f2a, double hi_
             pending = -1;   // the copy queued above predates the new reference positions
         }
         { const int rc = dsmd_compute_forces(c, DSMD_PHASE_FULL, 0, s); if (rc) return rc; }
-        { const int rc = dsmd_integrate(c, 2, dt, f2a, s); if (rc) return rc; }
+        if (!merge || step + 1 == n_steps) { const int rc = dsmd_integrate(c, 2, dt, f2a, s); if (rc) return rc; }
     }
     if (lagged && pending >= 0) {
         DSMD_CUDA(c, cudaEventSynchronize(c->disp_event[pending]));

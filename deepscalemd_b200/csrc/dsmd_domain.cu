@@ -913,7 +913,9 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
     auto mark = [&](int k) { if (d->profile) cudaEventRecord(d->ev_phase[k], s); };
     for (int64_t step = 0; step < n_steps; ++step) {
         mark(0);
-        DOM_CTX(d, dsmd_integrate(d->ctx, 1, dt, force_to_accel, s));   // v += dt/2 a, x += dt v, pack owned, displacement
+        // v += dt/2 a, x += dt v, pack owned, displacement; after the first step of the call the kick is a whole dt: the
+        // second half of the previous step (left out below) and this first half use the same forces
+        DOM_CTX(d, dsmd_integrate(d->ctx, step > 0 ? 3 : 1, dt, force_to_accel, s));
         mark(1);
         // The vote: all ranks take the MAX of their displacement words; the host reads the result of the PREVIOUS step (its
         // copy finished long ago) and extrapolates by its last growth (src/md_simulation.cpp:1232-1245). The word is copied
@@ -965,7 +967,7 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
             DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_BOUNDARY, 0, s));
             mark(4);
         }
-        DOM_CTX(d, dsmd_integrate(d->ctx, 2, dt, force_to_accel, s));
+        if (step + 1 == n_steps) DOM_CTX(d, dsmd_integrate(d->ctx, 2, dt, force_to_accel, s));
         mark(5);
         if (d->profile) {
             { const int rc = wait_stream(d, s, "profiled step"); if (rc) return rc; }

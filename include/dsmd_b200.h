@@ -185,7 +185,10 @@ int dsmd_compute_forces(dsmd_ctx* ctx, int phase, int want_energy, void* stream)
 int dsmd_read_scalars(dsmd_ctx* ctx, double out[6], void* stream);
 
 /* Velocity Verlet halves (launch_vv_step1_kernel / launch_vv_step2_kernel, src/integrator_kernels.cu:149-208):
- * half 1: v += dt/2 f/m c; x += dt v (and packs positions, see dsmd_pack_positions); half 2: v += dt/2 f/m c. */
+ * half 1: v += dt/2 f/m c; x += dt v (and packs positions, see dsmd_pack_positions); half 2: v += dt/2 f/m c;
+ * half 3: half 2 of the previous step and half 1 of this one in one pass (v += dt f/m c; x += dt v; pack), for loops in
+ * which nobody reads the velocities between two steps (dsmd_run_nve and dsmd_domain_run use it after their first step
+ * and end on a plain half 2); not available with constraints, where RATTLE sits between the two. */
 int dsmd_integrate(dsmd_ctx* ctx, int half, double dt, double force_to_accel, void* stream);
 
 /* calculate_kinetic_energy (include/force_calculator.h:70): sum 1/2 m v^2 over owned atoms, raw units. Synchronises. */
