@@ -22,7 +22,8 @@ FIELD_ID = {name: k for k, name in enumerate(FIELDS)}
 # every symbol include/dsmd_b200.h declares
 SYMBOLS = [
     "dsmd_create", "dsmd_destroy", "dsmd_last_error", "dsmd_set_box", "dsmd_set_pair_params", "dsmd_set_coulomb",
-    "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_set_constraints", "dsmd_constraint_failures", "dsmd_rattle", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
+    "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_set_constraints", "dsmd_constraint_failures", "dsmd_rattle",
+    "dsmd_set_bonded", "dsmd_compute_bonded", "dsmd_read_bonded_scalars", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
     "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned", "dsmd_sort_owned_in_brick",
     "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq", "dsmd_max_displacement_sq_lagged",
     "dsmd_displacement_word", "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_scale_velocities",
@@ -153,6 +154,43 @@ class Context:
         a, b, d = _arr(rows[:, 0], np.int32), _arr(rows[:, 1], np.int32), _arr(rows[:, 2], np.float64)
         self._check(self.lib.dsmd_set_constraints(self.h, c_int64(n_global), c_int64(len(a)), _p(a), _p(b), _p(d),
                                                   c_double(tolerance), c_int(max_iterations)))
+
+    def set_bonded(self, n_global, terms):
+        """terms: a mapping (or object) with bonds [nb, 2], bond_k, bond_r0, angles [na, 3], angle_k, angle_theta0 (radians),
+        torsions [nt, 4], torsion_k, torsion_phi0 (radians), torsion_n, specials [ns, 2], special_sigma, special_epsilon,
+        special_lj_scale, special_coulomb_scale; atoms by global id; what is absent counts as empty. None clears."""
+        def get(name):
+            if terms is None:
+                return None
+            return terms.get(name) if isinstance(terms, dict) else getattr(terms, name, None)
+
+        def table(name, width):
+            a = get(name)
+            return np.zeros((0, width), dtype=np.int32) if a is None else _arr(np.asarray(a).reshape(-1, width), np.int32)
+
+        def column(name, n, dtype=np.float64):
+            a = get(name)
+            a = np.zeros(n, dtype=dtype) if a is None else _arr(a, dtype)
+            if len(a) != n:
+                raise ValueError(f"{name}: {len(a)} values for {n} terms")
+            return a
+        b, a, t, sp = table("bonds", 2), table("angles", 3), table("torsions", 4), table("specials", 2)
+        cols = [column("bond_k", len(b)), column("bond_r0", len(b)), column("angle_k", len(a)), column("angle_theta0", len(a)),
+                column("torsion_k", len(t)), column("torsion_phi0", len(t)), column("torsion_n", len(t), np.int32),
+                column("special_sigma", len(sp)), column("special_epsilon", len(sp)), column("special_lj_scale", len(sp)),
+                column("special_coulomb_scale", len(sp))]
+        self._check(self.lib.dsmd_set_bonded(self.h, c_int64(n_global), c_int64(len(b)), _p(b), _p(cols[0]), _p(cols[1]),
+                                             c_int64(len(a)), _p(a), _p(cols[2]), _p(cols[3]), c_int64(len(t)), _p(t),
+                                             _p(cols[4]), _p(cols[5]), _p(cols[6]), c_int64(len(sp)), _p(sp), _p(cols[7]),
+                                             _p(cols[8]), _p(cols[9]), _p(cols[10])))
+
+    def compute_bonded(self, stream=None):
+        self._check(self.lib.dsmd_compute_bonded(self.h, _stream_handle(stream)))
+
+    def read_bonded_scalars(self, stream=None):
+        out = (c_double * 5)()
+        self._check(self.lib.dsmd_read_bonded_scalars(self.h, out, _stream_handle(stream)))
+        return dict(pe=out[0], virial=out[1], virial_diag=np.array([out[2], out[3], out[4]]))
 
     def constraint_failures(self, stream=None):
         n = c_int64(0)

@@ -524,6 +524,7 @@ __global__ void k_kinetic(int n, const double* __restrict__ vx, const double* __
 }  // namespace
 
 #include "dsmd_constraints.cuh"
+#include "dsmd_bonded.cuh"
 
 namespace {
 
@@ -881,6 +882,22 @@ struct dsmd_ctx {
     unsigned long long* offsets64 = nullptr;
     bool list_valid = false;
     // distance constraints (dsmd_constraints.cuh)
+    // bonded terms (dsmd_set_bonded)
+    struct Bonded {
+        int64_t n_global = 0, n_bonds = 0, n_angles = 0, n_torsions = 0, n_specials = 0, n_entries = 0, blocks = 0;
+        int *bond_atoms = nullptr, *angle_atoms = nullptr, *torsion_atoms = nullptr, *torsion_n = nullptr, *special_atoms = nullptr;
+        double *bond_par = nullptr, *angle_par = nullptr, *torsion_par = nullptr, *special_par = nullptr;
+        int* slot_of_gid = nullptr;          // [n_global]
+        long long* entries_of = nullptr;     // [n_global + 1]
+        int* entry = nullptr;                // [n_entries]
+        double* contrib = nullptr;           // [3 * n_entries]
+        double* partials = nullptr;          // [5 * blocks]
+        double* scalars = nullptr;           // device: PE, W, Wxx, Wyy, Wzz
+        unsigned* missing = nullptr;         // device: terms with an owned atom and a partner that is not on this rank
+        double* h_scalars = nullptr;         // pinned: 5 scalars + the missing count
+        int64_t map_epoch = -1;              // list build the gid -> slot map belongs to
+        int64_t terms() const { return n_bonds + n_angles + n_torsions + n_specials; }
+    } bonded;
     int n_clusters = 0;
     int64_t cons_n_global = 0;
     int* cl_gid = nullptr;
@@ -918,6 +935,16 @@ namespace {
             return DSMD_ERR_CUDA;                                                                  \
         }                                                                                          \
     } while (0)
+
+void free_bonded(dsmd_ctx* c) {
+    dsmd_ctx::Bonded& b = c->bonded;
+    cudaFree(b.bond_atoms); cudaFree(b.angle_atoms); cudaFree(b.torsion_atoms); cudaFree(b.torsion_n); cudaFree(b.special_atoms);
+    cudaFree(b.bond_par); cudaFree(b.angle_par); cudaFree(b.torsion_par); cudaFree(b.special_par);
+    cudaFree(b.slot_of_gid); cudaFree(b.entries_of); cudaFree(b.entry); cudaFree(b.contrib); cudaFree(b.partials);
+    cudaFree(b.scalars); cudaFree(b.missing);
+    if (b.h_scalars) cudaFreeHost(b.h_scalars);
+    b = dsmd_ctx::Bonded();
+}
 
 int fail(dsmd_ctx* ctx, int code, const std::string& what) {
     ctx->error = what;
@@ -1187,6 +1214,7 @@ void dsmd_destroy(dsmd_ctx* c) {
     cudaFree(c->cub_temp); cudaFree(c->c6c12); cudaFree(c->ewald); cudaFree(c->excl_off); cudaFree(c->excl_partner);
     cudaFree(c->partials); cudaFree(c->scalars); cudaFree(c->status); cudaFree(c->flag); cudaFree(c->offsets64);
     cudaFree(c->cl_gid); cudaFree(c->cl_a); cudaFree(c->cl_b); cudaFree(c->cl_d2); cudaFree(c->slot_of_gid);
+    free_bonded(c);
     for (int a = 0; a < 3; ++a) cudaFree(c->pre[a]);
     cudaFreeHost(c->h_status); cudaFreeHost(c->h_scalars);
     for (int k = 0; k < 2; ++k) {
@@ -1827,6 +1855,148 @@ int dsmd_integrate(dsmd_ctx* c, int half, double dt, double f2a, void* stream) {
     return DSMD_OK;
 }
 
+// ---- bonded terms ------------------------------------------------------------------------------------------------------
+
+
+static int to_device_bytes(dsmd_ctx* c, void** dst, const void* src, size_t bytes) {
+    *dst = nullptr;
+    if (bytes == 0) return DSMD_OK;
+    DSMD_CUDA(c, cudaMalloc(dst, bytes));
+    DSMD_CUDA(c, cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice));
+    return DSMD_OK;
+}
+#define DSMD_TO_DEVICE(c, dst, vec)                                                                                    \
+    do {                                                                                                               \
+        const int rc_ = to_device_bytes(c, reinterpret_cast<void**>(&(dst)), (vec).data(), sizeof((vec)[0]) * (vec).size()); \
+        if (rc_) return rc_;                                                                                           \
+    } while (0)
+
+int dsmd_set_bonded(dsmd_ctx* c, int64_t n_global, int64_t n_bonds, const int32_t* bond_atoms, const double* bond_k,
+                    const double* bond_r0, int64_t n_angles, const int32_t* angle_atoms, const double* angle_k,
+                    const double* angle_theta0, int64_t n_torsions, const int32_t* torsion_atoms, const double* torsion_k,
+                    const double* torsion_phi0, const int32_t* torsion_n, int64_t n_specials, const int32_t* special_atoms,
+                    const double* special_sigma, const double* special_epsilon, const double* special_lj_scale,
+                    const double* special_coulomb_scale) {
+    if (!c || n_global < 0 || n_bonds < 0 || n_angles < 0 || n_torsions < 0 || n_specials < 0) return DSMD_ERR_INVALID;
+    if ((n_bonds > 0 && (!bond_atoms || !bond_k || !bond_r0)) || (n_angles > 0 && (!angle_atoms || !angle_k || !angle_theta0)) ||
+        (n_torsions > 0 && (!torsion_atoms || !torsion_k || !torsion_phi0 || !torsion_n)) ||
+        (n_specials > 0 && (!special_atoms || !special_sigma || !special_epsilon || !special_lj_scale || !special_coulomb_scale)))
+        return DSMD_ERR_INVALID;
+    DSMD_CUDA(c, cudaSetDevice(c->device));
+    free_bonded(c);
+    const int64_t terms = n_bonds + n_angles + n_torsions + n_specials;
+    if (terms == 0) return DSMD_OK;
+    if (n_global >= (1ll << 31) || terms >= (1ll << 29)) return fail(c, DSMD_ERR_INVALID, "too many atoms or bonded terms");
+    // term tables, and for every global id the places (3-double groups of the scratch array) its forces are written to,
+    // in the order bonds, angles, torsions, specials and, inside a kind, term by term: the order the forces are added in
+    std::vector<int> ba(bond_atoms, bond_atoms + 2 * n_bonds), aa(angle_atoms, angle_atoms + 3 * n_angles),
+        ta(torsion_atoms, torsion_atoms + 4 * n_torsions), tn(torsion_n, torsion_n + n_torsions),
+        sa(special_atoms, special_atoms + 2 * n_specials);
+    std::vector<double> bp(2 * n_bonds), ap(2 * n_angles), tp(2 * n_torsions), sp(4 * n_specials);
+    for (int64_t k = 0; k < n_bonds; ++k) { bp[2 * k] = bond_k[k]; bp[2 * k + 1] = bond_r0[k]; }
+    for (int64_t k = 0; k < n_angles; ++k) { ap[2 * k] = angle_k[k]; ap[2 * k + 1] = angle_theta0[k]; }
+    for (int64_t k = 0; k < n_torsions; ++k) { tp[2 * k] = torsion_k[k]; tp[2 * k + 1] = torsion_phi0[k]; }
+    for (int64_t k = 0; k < n_specials; ++k) {
+        sp[4 * k] = special_sigma[k]; sp[4 * k + 1] = special_epsilon[k];
+        sp[4 * k + 2] = special_lj_scale[k]; sp[4 * k + 3] = special_coulomb_scale[k];
+    }
+    const int64_t n_entries = 2 * n_bonds + 3 * n_angles + 4 * n_torsions + 2 * n_specials;
+    std::vector<long long> entries_of(static_cast<size_t>(n_global) + 1, 0);
+    const std::vector<int>* tables[4] = {&ba, &aa, &ta, &sa};
+    for (const std::vector<int>* t : tables)
+        for (int g : *t) {
+            if (g < 0 || g >= n_global) return fail(c, DSMD_ERR_INVALID, "a bonded term names an atom id outside [0, n_global)");
+            ++entries_of[static_cast<size_t>(g) + 1];
+        }
+    for (int64_t g = 0; g < n_global; ++g) entries_of[g + 1] += entries_of[g];
+    std::vector<int> entry(static_cast<size_t>(n_entries));
+    {
+        std::vector<long long> next(entries_of.begin(), entries_of.end() - 1);
+        int place = 0;
+        for (const std::vector<int>* t : tables)
+            for (int g : *t) entry[static_cast<size_t>(next[g]++)] = place++;
+    }
+    dsmd_ctx::Bonded& b = c->bonded;
+    DSMD_TO_DEVICE(c, b.bond_atoms, ba);
+    DSMD_TO_DEVICE(c, b.angle_atoms, aa);
+    DSMD_TO_DEVICE(c, b.torsion_atoms, ta);
+    DSMD_TO_DEVICE(c, b.torsion_n, tn);
+    DSMD_TO_DEVICE(c, b.special_atoms, sa);
+    DSMD_TO_DEVICE(c, b.bond_par, bp);
+    DSMD_TO_DEVICE(c, b.angle_par, ap);
+    DSMD_TO_DEVICE(c, b.torsion_par, tp);
+    DSMD_TO_DEVICE(c, b.special_par, sp);
+    DSMD_TO_DEVICE(c, b.entries_of, entries_of);
+    DSMD_TO_DEVICE(c, b.entry, entry);
+    b.blocks = blocks_for(terms, kThreads);
+    DSMD_CUDA(c, cudaMalloc(&b.slot_of_gid, sizeof(int) * std::max<int64_t>(n_global, 1)));
+    DSMD_CUDA(c, cudaMalloc(&b.contrib, sizeof(double) * 3 * n_entries));
+    DSMD_CUDA(c, cudaMalloc(&b.partials, sizeof(double) * 5 * b.blocks));
+    DSMD_CUDA(c, cudaMalloc(&b.scalars, sizeof(double) * 5));
+    DSMD_CUDA(c, cudaMemset(b.scalars, 0, sizeof(double) * 5));
+    DSMD_CUDA(c, cudaMalloc(&b.missing, sizeof(unsigned)));
+    DSMD_CUDA(c, cudaMemset(b.missing, 0, sizeof(unsigned)));
+    DSMD_CUDA(c, cudaMallocHost(&b.h_scalars, sizeof(double) * 6));
+    b.n_global = n_global;
+    b.n_bonds = n_bonds; b.n_angles = n_angles; b.n_torsions = n_torsions; b.n_specials = n_specials;
+    b.n_entries = n_entries;
+    b.map_epoch = -1;
+    return DSMD_OK;
+}
+
+int dsmd_compute_bonded(dsmd_ctx* c, void* stream) {
+    if (!c) return DSMD_ERR_INVALID;
+    dsmd_ctx::Bonded& b = c->bonded;
+    if (b.terms() == 0) return DSMD_OK;
+    if (!c->list_valid) return fail(c, DSMD_ERR_STATE, "no neighbour list built yet (bonded terms find their atoms through the sorted arrays)");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (b.map_epoch != c->build_epoch) {   // the sort of a list build moved the atoms
+        DSMD_CUDA(c, cudaMemsetAsync(b.slot_of_gid, 0x7F, sizeof(int) * b.n_global, s));   // 0x7F7F7F7F: beyond any slot
+        k_bonded_slot_map<<<blocks_for(c->n_total, kThreads), kThreads, 0, s>>>(static_cast<int>(c->n_total), c->gid[c->cur],
+                                                                               static_cast<int>(b.n_global), b.slot_of_gid);
+        DSMD_LAUNCHED(c);
+        b.map_epoch = c->build_epoch;
+    }
+    BondedTable t{};
+    t.n_bonds = static_cast<int>(b.n_bonds); t.n_angles = static_cast<int>(b.n_angles);
+    t.n_torsions = static_cast<int>(b.n_torsions); t.n_specials = static_cast<int>(b.n_specials);
+    t.bond_atoms = b.bond_atoms; t.bond_par = b.bond_par; t.angle_atoms = b.angle_atoms; t.angle_par = b.angle_par;
+    t.torsion_atoms = b.torsion_atoms; t.torsion_par = b.torsion_par; t.torsion_n = b.torsion_n;
+    t.special_atoms = b.special_atoms; t.special_par = b.special_par;
+    t.slot_of_gid = b.slot_of_gid;
+    t.n_global = static_cast<int>(b.n_global);
+    t.n_owned = static_cast<int>(c->n_owned);
+    for (int a = 0; a < 3; ++a) { t.box[a] = c->box[a]; t.periodic[a] = c->periodic[a]; }
+    double** r = c->real[c->cur];
+    k_bonded_terms<<<static_cast<unsigned>(b.blocks), kThreads, 0, s>>>(t, r[0], r[1], r[2], r[10], b.contrib, b.partials, b.missing);
+    DSMD_LAUNCHED(c);
+    k_bonded_gather<<<blocks_for(c->n_owned, kThreads), kThreads, 0, s>>>(static_cast<int>(c->n_owned), c->gid[c->cur],
+                                                                         static_cast<int>(b.n_global), b.entries_of, b.entry,
+                                                                         b.contrib, r[6], r[7], r[8]);
+    DSMD_LAUNCHED(c);
+    k_reduce_partials<5><<<1, kThreads, 0, s>>>(b.partials, static_cast<int>(b.blocks), b.scalars, 0);
+    DSMD_LAUNCHED(c);
+    return DSMD_OK;
+}
+
+int dsmd_read_bonded_scalars(dsmd_ctx* c, double out[5], void* stream) {
+    if (!c || !out) return DSMD_ERR_INVALID;
+    dsmd_ctx::Bonded& b = c->bonded;
+    for (int k = 0; k < 5; ++k) out[k] = 0.0;
+    if (b.terms() == 0) return DSMD_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned* h_missing = reinterpret_cast<unsigned*>(b.h_scalars + 5);
+    DSMD_CUDA(c, cudaMemcpyAsync(b.h_scalars, b.scalars, sizeof(double) * 5, cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaMemcpyAsync(h_missing, b.missing, sizeof(unsigned), cudaMemcpyDeviceToHost, s));
+    DSMD_CUDA(c, cudaMemsetAsync(b.missing, 0, sizeof(unsigned), s));
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    for (int k = 0; k < 5; ++k) out[k] = b.h_scalars[k];
+    if (*h_missing)
+        return fail(c, DSMD_ERR_STATE, std::to_string(*h_missing) + " bonded term(s) have an owned atom whose partner is not on "
+                                       "this rank: the halo is narrower than the term is long");
+    return DSMD_OK;
+}
+
 int dsmd_kinetic_energy(dsmd_ctx* c, double* out, void* stream) {
     if (!c || !out) return DSMD_ERR_INVALID;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1865,6 +2035,8 @@ int dsmd_run_nve(dsmd_ctx* c, int64_t n_steps, double dt, double f2a, double hi_
         if (rc) return rc;
         const int rc2 = dsmd_compute_forces(c, DSMD_PHASE_FULL, 0, s);
         if (rc2) return rc2;
+        const int rc3 = dsmd_compute_bonded(c, s);
+        if (rc3) return rc3;
     }
     const double limit2 = (hi_frac * c->skin) * (hi_frac * c->skin);
     int64_t rebuilds = 0;
@@ -1913,6 +2085,7 @@ int dsmd_run_nve(dsmd_ctx* c, int64_t n_steps, double dt, double f2a, double hi_
             pending = -1;   // the copy queued above predates the new reference positions
         }
         { const int rc = dsmd_compute_forces(c, DSMD_PHASE_FULL, 0, s); if (rc) return rc; }
+        { const int rc = dsmd_compute_bonded(c, s); if (rc) return rc; }
         if (!merge || step + 1 == n_steps) { const int rc = dsmd_integrate(c, 2, dt, f2a, s); if (rc) return rc; }
     }
     if (lagged && pending >= 0) {

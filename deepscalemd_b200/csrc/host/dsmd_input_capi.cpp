@@ -178,6 +178,30 @@ int dsmd_input_system_constraints(const dsmd_input_system* system, const int32_t
     return DSMD_INPUT_OK;
 }
 
+int dsmd_input_system_bonded(const dsmd_input_system* system, int64_t counts[5], const int32_t** atoms[4],
+                             const double** parameters[10], const int32_t** torsion_multiplicity) {
+    if (!system || !counts) return failed(DSMD_INPUT_ERR_INVALID, "null argument");
+    const BondedInput& b = system->s.bonded;
+    counts[0] = static_cast<int64_t>(b.bond_k.size());
+    counts[1] = static_cast<int64_t>(b.angle_k.size());
+    counts[2] = static_cast<int64_t>(b.torsion_k.size());
+    counts[3] = b.torsion_k.empty() ? 0 : system->s.n_dihedrals;
+    counts[4] = static_cast<int64_t>(b.special_sigma.size());
+    if (atoms) {
+        const std::vector<int32_t>* a[4] = {&b.bond_atoms, &b.angle_atoms, &b.torsion_atoms, &b.special_atoms};
+        for (int k = 0; k < 4; ++k)
+            if (atoms[k]) *atoms[k] = a[k]->data();
+    }
+    if (parameters) {
+        const std::vector<double>* p[10] = {&b.bond_k, &b.bond_r0, &b.angle_k, &b.angle_theta0, &b.torsion_k, &b.torsion_phi0,
+                                            &b.special_sigma, &b.special_epsilon, &b.special_lj_scale, &b.special_coulomb_scale};
+        for (int k = 0; k < 10; ++k)
+            if (parameters[k]) *parameters[k] = p[k]->data();
+    }
+    if (torsion_multiplicity) *torsion_multiplicity = b.torsion_n.data();
+    return DSMD_INPUT_OK;
+}
+
 int dsmd_input_system_velocities(dsmd_input_system* system, double temperature, uint64_t seed) {
     if (!system) return failed(DSMD_INPUT_ERR_INVALID, "null argument");
     if (!(temperature >= 0.0)) return failed(DSMD_INPUT_ERR_INVALID, "temperature must not be negative");

@@ -47,9 +47,10 @@ void ok(dsmd_ctx* ctx, int rc, const char* what) {
 std::vector<std::string> refusals(const RunConfig& c, const SystemInput& s) {
     std::vector<std::string> out = c.unsupported();
     if (s.mie_n != 12 || s.mie_m != 6) out.push_back("Mie exponents other than (12, 6)");
-    if (c.enable_bonded && (s.n_bonds || s.n_angles || s.n_dihedrals || s.n_impropers))
-        out.push_back("bonded terms (switch them off with force_calculation.type: lj[, PME])");
-    if (s.n_special_pairs) out.push_back("special (1-4) pairs");
+    // the bonded terms of a dsMD_input system run on the device; a legacy topology's are only counted by the reader
+    if (c.enable_bonded() && (s.n_bonds || s.n_angles || s.n_dihedrals || s.n_impropers || s.n_special_pairs) && s.bonded.empty())
+        out.push_back("bonded terms of a legacy topology file (switch them off with force_calculation.type: lj[, PME], or "
+                      "give the system as a dsMD_input folder)");
     const bool charged = std::any_of(s.charge.begin(), s.charge.end(), [](double q) { return q != 0.0; });
     if (c.enable_coulomb && charged && c.text("real_space_only") != "true")
         out.push_back("electrostatics of a charged system: reciprocal-space PME stays on the reference's path "
@@ -138,6 +139,26 @@ public:
             ok(ctx_, dsmd_set_constraints(ctx_, s_.n, static_cast<int64_t>(a.size()), a.data(), b.data(), d.data(), 0.0, 0),
                "dsmd_set_constraints");
         }
+        if (!s_.bonded.empty()) {
+            const BondedInput& b = s_.bonded;
+            // each kind follows its own switch (force_calculation.type / enable_bonds / enable_angles / enable_dihedrals:
+            // src/force_manager.cpp:88-160); impropers go with the dihedrals (src/force_calculator_cpu.cpp:798-803)
+            const int64_t n_bonds = c_.enable_bonds ? static_cast<int64_t>(b.bond_k.size()) : 0;
+            const int64_t n_angles = c_.enable_angles ? static_cast<int64_t>(b.angle_k.size()) : 0;
+            const int64_t n_torsions = c_.enable_dihedrals ? static_cast<int64_t>(b.torsion_k.size()) : 0;
+            const int64_t n_specials = (c_.enable_lennard_jones || c_.enable_coulomb) ? static_cast<int64_t>(b.special_sigma.size()) : 0;
+            // special pairs follow the nonbonded switches: no Lennard-Jones -> epsilon 0, no Coulomb -> scale 0
+            std::vector<double> eps14 = b.special_epsilon, coul14 = b.special_coulomb_scale;
+            if (!c_.enable_lennard_jones) std::fill(eps14.begin(), eps14.end(), 0.0);
+            if (!c_.enable_coulomb) std::fill(coul14.begin(), coul14.end(), 0.0);
+            ok(ctx_, dsmd_set_bonded(ctx_, s_.n, n_bonds, b.bond_atoms.data(), b.bond_k.data(), b.bond_r0.data(), n_angles,
+                                     b.angle_atoms.data(), b.angle_k.data(), b.angle_theta0.data(), n_torsions,
+                                     b.torsion_atoms.data(), b.torsion_k.data(), b.torsion_phi0.data(), b.torsion_n.data(),
+                                     n_specials, b.special_atoms.data(), b.special_sigma.data(), eps14.data(),
+                                     b.special_lj_scale.data(), coul14.data()),
+               "dsmd_set_bonded");
+            bonded_ = n_bonds + n_angles + n_torsions + n_specials > 0;
+        }
         std::vector<int32_t> type(s_.type.begin(), s_.type.end());
         ok(ctx_, dsmd_upload(ctx_, s_.n, s_.n, s_.x.data(), s_.y.data(), s_.z.data(), s_.vx.data(), s_.vy.data(), s_.vz.data(),
                              s_.mass.data(), s_.charge.data(), type.data(), nullptr, nullptr),
@@ -151,10 +172,16 @@ public:
 
     void forces(bool want_energy) {
         ok(ctx_, dsmd_compute_forces(ctx_, DSMD_PHASE_FULL, want_energy ? 1 : 0, nullptr), "dsmd_compute_forces");
+        if (bonded_) ok(ctx_, dsmd_compute_bonded(ctx_, nullptr), "dsmd_compute_bonded");
         if (want_energy) {
             double out[6];
             ok(ctx_, dsmd_read_scalars(ctx_, out, nullptr), "dsmd_read_scalars");
             pe_ = out[0];
+            if (bonded_) {
+                double terms[5];
+                ok(ctx_, dsmd_read_bonded_scalars(ctx_, terms, nullptr), "dsmd_read_bonded_scalars");
+                pe_ += terms[0];
+            }
         }
     }
 
@@ -269,6 +296,7 @@ public:
     }
 
     bool nose_hoover_ = false;
+    bool bonded_ = false;
     double xi_ = 0.0;
     long long builds_ = 0;
     double box_[3] = {0.0, 0.0, 0.0};

@@ -229,22 +229,22 @@ RunConfig read_run_config(const std::string& path) {
     // (only the exact text "true" switches a term on), default all on (src/force_manager.cpp:88-160)
     const auto types = comma_list(c.force_type);
     if (!types.empty()) {
-        c.enable_lennard_jones = c.enable_coulomb = c.enable_bonded = false;
+        c.enable_lennard_jones = c.enable_coulomb = c.enable_bonds = c.enable_angles = c.enable_dihedrals = false;
         for (std::string t : types) {
             t = trimmed(t, " \t\r\n\"");
             if (t == "lj" || t == "lennard_jones" || t == "LJ") c.enable_lennard_jones = true;
             else if (t == "coulomb" || t == "PME" || t == "electrostatic") c.enable_coulomb = true;
-            else if (t == "bonds" || t == "bond" || t == "angles" || t == "angle" || t == "dihedrals" || t == "dihedral")
-                c.enable_bonded = true;
+            else if (t == "bonds" || t == "bond") c.enable_bonds = true;
+            else if (t == "angles" || t == "angle") c.enable_angles = true;
+            else if (t == "dihedrals" || t == "dihedral") c.enable_dihedrals = true;
         }
     } else {
         if (c.has("force_calculation.enable_lennard_jones"))
             c.enable_lennard_jones = c.text("force_calculation.enable_lennard_jones") == "true";
         if (c.has("force_calculation.enable_coulomb")) c.enable_coulomb = c.text("force_calculation.enable_coulomb") == "true";
-        bool any_bonded = true;
-        for (const char* k : {"enable_bonds", "enable_angles", "enable_dihedrals"})
-            if (c.has(std::string("force_calculation.") + k)) any_bonded = any_bonded && c.text(std::string("force_calculation.") + k) == "true";
-        c.enable_bonded = any_bonded;
+        if (c.has("force_calculation.enable_bonds")) c.enable_bonds = c.text("force_calculation.enable_bonds") == "true";
+        if (c.has("force_calculation.enable_angles")) c.enable_angles = c.text("force_calculation.enable_angles") == "true";
+        if (c.has("force_calculation.enable_dihedrals")) c.enable_dihedrals = c.text("force_calculation.enable_dihedrals") == "true";
     }
 
     {
@@ -301,7 +301,10 @@ std::string RunConfig::to_json() const {
     str("force_mode", force_mode); str("force_type", force_type); str("force_precision", force_precision);
     str("nonbonded_kernel", nonbonded_kernel);
     boolean("enable_lennard_jones", enable_lennard_jones); boolean("enable_coulomb", enable_coulomb);
-    boolean("enable_bonded", enable_bonded);
+    boolean("enable_bonded", enable_bonded());
+    boolean("enable_bonds", enable_bonds);
+    boolean("enable_angles", enable_angles);
+    boolean("enable_dihedrals", enable_dihedrals);
     str("output_prefix", output_prefix); str("output_info", output_info); integer("output_freq", output_freq);
     integer("energy_output_freq", energy_output_freq); integer("trajectory_output_freq", trajectory_output_freq);
     str("trajectory_format", trajectory_format); boolean("trajectory_include_velocities", trajectory_include_velocities);

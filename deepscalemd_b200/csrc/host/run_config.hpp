@@ -32,7 +32,9 @@ struct RunConfig {
     double neighbor_rebuild_hi_frac = 0.5, neighbor_rebuild_lo_frac = 0.4;
     // force_calculation section
     std::string force_mode = "builtin", force_type, force_precision = "double", nonbonded_kernel = "tiled";
-    bool enable_lennard_jones = true, enable_coulomb = true, enable_bonded = true;
+    bool enable_lennard_jones = true, enable_coulomb = true;
+    bool enable_bonds = true, enable_angles = true, enable_dihedrals = true;   // dihedrals: impropers with them
+    bool enable_bonded() const { return enable_bonds || enable_angles || enable_dihedrals; }
     // output and restart
     std::string output_prefix = "md_output", output_info = "STEP, T, KE";
     long long output_freq = 10, energy_output_freq = 10, trajectory_output_freq = 100;

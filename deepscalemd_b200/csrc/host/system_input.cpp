@@ -166,7 +166,12 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
     std::map<int, std::string> type_names;
     struct PairRow { int i, j; double sigma, epsilon; };
     std::vector<PairRow> pair_rows;
-    std::map<std::string, bool> bond_ids, angle_ids, torsion_ids, improper_ids;
+    struct Harmonic { double k, at; };
+    struct Periodic { double k, phase; int n; };
+    std::map<std::string, Harmonic> bond_ids, angle_ids;
+    std::map<std::string, Periodic> torsion_ids, improper_ids;
+    std::map<int, std::pair<double, double>> special_ids;   // sigma, epsilon
+    const double degree = 3.14159265358979323846 / 180.0;
     bool mie_seen = false;
     std::string line, section;
     size_t line_number = 0;
@@ -212,19 +217,35 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
             pair_rows.push_back({to_int(t[1]), to_int(t[2]), to_real(t[3]), to_real(t[4])});
         } else if (section == "bond_parameters") {
             if (t.size() < 4 || t[1] != "harmonic") fail("bond parameters must read 'id harmonic k r0'");
-            if (!bond_ids.emplace(t[0], true).second) fail("bond parameter id " + t[0] + " is given twice");
+            const double k = to_real(t[2]), r0 = to_real(t[3]);
+            if (!std::isfinite(k) || !std::isfinite(r0) || k < 0.0 || r0 <= 0.0) fail("a bond needs a finite k >= 0 and a finite r0 > 0");
+            if (!bond_ids.emplace(t[0], Harmonic{k, r0}).second) fail("bond parameter id " + t[0] + " is given twice");
         } else if (section == "angle_parameters") {
             if (t.size() < 4 || t[1] != "harmonic") fail("angle parameters must read 'id harmonic k theta0' (degrees)");
-            if (!angle_ids.emplace(t[0], true).second) fail("angle parameter id " + t[0] + " is given twice");
+            const double k = to_real(t[2]), theta = to_real(t[3]) * degree;
+            if (!std::isfinite(k) || !std::isfinite(theta) || k < 0.0) fail("an angle needs a finite k >= 0 and a finite theta0");
+            if (!angle_ids.emplace(t[0], Harmonic{k, theta}).second) fail("angle parameter id " + t[0] + " is given twice");
         } else if (section == "torsion_parameters") {
             if (t.size() < 5 || t[1] != "periodic") fail("torsion parameters must read 'id periodic k phase multiplicity' (phase in degrees)");
-            if (!torsion_ids.emplace(t[0], true).second) fail("torsion parameter id " + t[0] + " is given twice");
+            const double k = to_real(t[2]), phase = to_real(t[3]) * degree;
+            const int multiplicity = to_int(t[4]);
+            if (!std::isfinite(k) || !std::isfinite(phase) || multiplicity <= 0) fail("a torsion needs finite k and phase and a multiplicity > 0");
+            if (!torsion_ids.emplace(t[0], Periodic{k, phase, multiplicity}).second) fail("torsion parameter id " + t[0] + " is given twice");
         } else if (section == "improper_parameters") {
             if (t.size() < 4 || (t[1] != "periodic" && t[1] != "harmonic"))
                 fail("improper parameters must read 'id periodic k phase multiplicity' or 'id harmonic k phi0' (degrees)");
-            if (!improper_ids.emplace(t[0], true).second) fail("improper parameter id " + t[0] + " is given twice");
+            const double k = to_real(t[2]), phase = to_real(t[3]) * degree;
+            const int multiplicity = t[1] == "harmonic" ? 0 : (t.size() >= 5 ? to_int(t[4]) : -1);
+            if (!std::isfinite(k) || !std::isfinite(phase) || k < 0.0 || (t[1] == "periodic" && multiplicity <= 0))
+                fail("an improper needs a finite k >= 0, a finite phase and, in the periodic form, a multiplicity > 0");
+            if (!improper_ids.emplace(t[0], Periodic{k, phase, multiplicity}).second) fail("improper parameter id " + t[0] + " is given twice");
         } else if (section == "special_pair_parameters") {
             if (t.size() < 3) fail("a [special_pair_parameters] line is 'id sigma epsilon'");
+            const int id = to_int(t[0]);
+            const double sigma = to_real(t[1]), epsilon = to_real(t[2]);
+            if (id < 0 || !std::isfinite(sigma) || !std::isfinite(epsilon) || sigma < 0.0 || epsilon < 0.0 ||
+                !special_ids.emplace(id, std::make_pair(sigma, epsilon)).second)
+                fail("a special pair parameter needs an id >= 0 given once and finite sigma, epsilon >= 0");
         } else {
             fail("unknown parameter section [" + section + "]");
         }
@@ -259,6 +280,9 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
     std::vector<int> type;
     std::vector<double> mass, charge;
     std::vector<std::pair<int, int>> listed, bond_ends, angle_ends, dihedral_ends, improper_atoms, special;
+    std::vector<std::string> bond_par, angle_par, dihedral_par, improper_par;
+    struct SpecialRow { int param; double lj_scale, coulomb_scale; };
+    std::vector<SpecialRow> special_rows;
     std::vector<Constraint> constraints;
     struct Quad { int a, b, c, d; };
     std::vector<Quad> angles3, dihedrals4, impropers4;
@@ -294,14 +318,17 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
             if (t.size() < 3) fail("a [bonds] line is two atom ids and a bond parameter id");
             if (!bond_ids.count(t[2])) fail("bond parameter id " + t[2] + " is not defined in the parameter file");
             bond_ends.push_back({to_int(t[0]), to_int(t[1])});
+            bond_par.push_back(t[2]);
         } else if (section == "angles") {
             if (t.size() < 4) fail("an [angles] line is three atom ids and an angle parameter id");
             if (!angle_ids.count(t[3])) fail("angle parameter id " + t[3] + " is not defined in the parameter file");
             angles3.push_back({to_int(t[0]), to_int(t[1]), to_int(t[2]), 0});
+            angle_par.push_back(t[3]);
         } else if (section == "dihedrals") {
             if (t.size() < 5) fail("a [dihedrals] line is four atom ids and a torsion parameter id");
             if (!torsion_ids.count(t[4])) fail("torsion parameter id " + t[4] + " is not defined in the parameter file");
             dihedrals4.push_back({to_int(t[0]), to_int(t[1]), to_int(t[2]), to_int(t[3])});
+            dihedral_par.push_back(t[4]);
         } else if (section == "exclusions") {
             if (t.size() < 2) fail("an [exclusions] line is two atom ids");
             listed.push_back({to_int(t[0]), to_int(t[1])});
@@ -309,9 +336,11 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
             if (t.size() < 5) fail("an [impropers] line is four atom ids and an improper parameter id");
             if (!improper_ids.count(t[4])) fail("improper parameter id " + t[4] + " is not defined in the parameter file");
             impropers4.push_back({to_int(t[0]), to_int(t[1]), to_int(t[2]), to_int(t[3])});
+            improper_par.push_back(t[4]);
         } else if (section == "special_pairs") {
             if (t.size() < 5) fail("a [special_pairs] line is two atom ids, a pair parameter id and the LJ and Coulomb scale factors");
             special.push_back({to_int(t[0]), to_int(t[1])});
+            special_rows.push_back({to_int(t[2]), to_real(t[3]), to_real(t[4])});
         } else if (section == "constraints") {
             if (t.size() < 3) fail("a [constraints] line is two atom ids and a distance");
             constraints.push_back({to_int(t[0]), to_int(t[1]), to_real(t[2])});
@@ -370,6 +399,37 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
     s.n_dihedrals = static_cast<int64_t>(dihedrals4.size());
     s.n_impropers = static_cast<int64_t>(impropers4.size());
     s.n_special_pairs = static_cast<int64_t>(special.size());
+
+    // every term with its own parameters, as the device library takes them
+    BondedInput& b = s.bonded;
+    b = BondedInput();
+    for (size_t k = 0; k < bond_ends.size(); ++k) {
+        b.bond_atoms.push_back(bond_ends[k].first); b.bond_atoms.push_back(bond_ends[k].second);
+        const Harmonic& h = bond_ids.at(bond_par[k]);
+        b.bond_k.push_back(h.k); b.bond_r0.push_back(h.at);
+    }
+    for (size_t k = 0; k < angles3.size(); ++k) {
+        b.angle_atoms.push_back(angles3[k].a); b.angle_atoms.push_back(angles3[k].b); b.angle_atoms.push_back(angles3[k].c);
+        const Harmonic& h = angle_ids.at(angle_par[k]);
+        b.angle_k.push_back(h.k); b.angle_theta0.push_back(h.at);
+    }
+    auto torsion = [&](const Quad& q, const Periodic& par) {
+        b.torsion_atoms.push_back(q.a); b.torsion_atoms.push_back(q.b); b.torsion_atoms.push_back(q.c); b.torsion_atoms.push_back(q.d);
+        b.torsion_k.push_back(par.k); b.torsion_phi0.push_back(par.phase); b.torsion_n.push_back(par.n);
+    };
+    for (size_t k = 0; k < dihedrals4.size(); ++k) torsion(dihedrals4[k], torsion_ids.at(dihedral_par[k]));
+    for (size_t k = 0; k < impropers4.size(); ++k) torsion(impropers4[k], improper_ids.at(improper_par[k]));
+    for (size_t k = 0; k < special.size(); ++k) {
+        b.special_atoms.push_back(special[k].first); b.special_atoms.push_back(special[k].second);
+        // a pair whose parameter id is not listed takes the pair matrix of its two atom types (the reference hands the
+        // kernel -1 for such a pair and looks the matrix up there: src/force_calculator_cpu.cpp:2820-2821)
+        const auto par = special_ids.find(special_rows[k].param);
+        const size_t ab = static_cast<size_t>(type[special[k].first]) * nt + type[special[k].second];
+        b.special_sigma.push_back(par != special_ids.end() ? par->second.first : sig[ab]);
+        b.special_epsilon.push_back(par != special_ids.end() ? par->second.second : eps[ab]);
+        b.special_lj_scale.push_back(special_rows[k].lj_scale);
+        b.special_coulomb_scale.push_back(special_rows[k].coulomb_scale);
+    }
 }
 
 }  // namespace dsmd::host

@@ -1,7 +1,8 @@
 // The particle system of a run as the input files describe it: coordinates (XYZ), atom types / masses / charges and the
 // pair-parameter matrix from a legacy .top file or a dsMD_input pair (.dsMDtop + .dsMDprm), exclusions and constraints.
 // Formats and rules follow the reference's readers (src/md_system.cpp:562-671, src/topology.cpp:335-881,
-// src/md_system.cpp:730-766); only what the nonbonded path needs is kept (bonded terms are counted, not stored).
+// src/md_system.cpp:730-766). The bonded terms of a dsMD_input pair are kept with their parameters resolved per term; those
+// of a legacy .top file are counted only.
 #pragma once
 
 #include <cstdint>
@@ -14,6 +15,15 @@ namespace dsmd::host {
 struct Constraint {
     int i, j;
     double distance;
+};
+
+// Bonded terms with the parameters of every term written out (angles in radians), in the form dsmd_set_bonded takes.
+// Torsions: the proper dihedrals first, the impropers behind them; multiplicity 0 marks the harmonic form.
+struct BondedInput {
+    std::vector<int32_t> bond_atoms, angle_atoms, torsion_atoms, torsion_n, special_atoms;
+    std::vector<double> bond_k, bond_r0, angle_k, angle_theta0, torsion_k, torsion_phi0;
+    std::vector<double> special_sigma, special_epsilon, special_lj_scale, special_coulomb_scale;
+    bool empty() const { return bond_k.empty() && angle_k.empty() && torsion_k.empty() && special_sigma.empty(); }
 };
 
 struct SystemInput {
@@ -29,6 +39,7 @@ struct SystemInput {
     std::vector<std::pair<int, int>> exclusions;   // (smaller id, larger id), sorted, unique
     std::vector<Constraint> constraints;
     int64_t n_bonds = 0, n_angles = 0, n_dihedrals = 0, n_impropers = 0, n_special_pairs = 0;
+    BondedInput bonded;                    // filled by apply_dsmd_input; a legacy topology leaves it empty
     double shift[3] = {0.0, 0.0, 0.0};     // what recentring added to every coordinate
 };
 

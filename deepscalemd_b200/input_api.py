@@ -16,7 +16,7 @@ SYMBOLS = [
     "dsmd_input_last_error", "dsmd_input_config_read", "dsmd_input_config_destroy", "dsmd_input_config_json",
     "dsmd_input_system_load", "dsmd_input_system_load_files", "dsmd_input_system_destroy", "dsmd_input_system_counts",
     "dsmd_input_system_real", "dsmd_input_system_types", "dsmd_input_system_pair_table", "dsmd_input_system_exclusions",
-    "dsmd_input_system_constraints", "dsmd_input_system_velocities", "dsmd_input_restart_read", "dsmd_input_restart_write",
+    "dsmd_input_system_constraints", "dsmd_input_system_bonded", "dsmd_input_system_velocities", "dsmd_input_restart_read", "dsmd_input_restart_write",
     "dsmd_input_nose_hoover_scale", "dsmd_host_brick_plan", "dsmd_host_counts_verdict", "dsmd_host_wait_probe", "dsmd_host_ewald_table", "dsmd_host_dart_throw",
 ]
 
@@ -131,6 +131,33 @@ class System:
         _check(lib().dsmd_input_system_constraints(self.h, byref(i), byref(j), byref(d)))
         return (np.ctypeslib.as_array(i, shape=(n,)).copy(), np.ctypeslib.as_array(j, shape=(n,)).copy(),
                 np.ctypeslib.as_array(d, shape=(n,)).copy())
+
+    def bonded(self):
+        """The bonded terms with per-term parameters as a mapping of arrays (the keys Context.set_bonded reads), plus
+        n_dihedrals: how many of the torsions are proper dihedrals (they come first)."""
+        counts = (c_int64 * 5)()
+        atom_ptrs = [POINTER(c_int32)() for _ in range(4)]
+        par_ptrs = [POINTER(c_double)() for _ in range(10)]
+        mult = POINTER(c_int32)()
+        atoms = (POINTER(POINTER(c_int32)) * 4)(*[ctypes.pointer(p) for p in atom_ptrs])
+        pars = (POINTER(POINTER(c_double)) * 10)(*[ctypes.pointer(p) for p in par_ptrs])
+        _check(lib().dsmd_input_system_bonded(self.h, counts, atoms, pars, byref(mult)))
+        nb, na, nt, nd, ns = (int(v) for v in counts)
+
+        def ints(p, n, width):
+            p = p.contents if hasattr(p, "contents") and not isinstance(p, POINTER(c_int32)) else p
+            return np.ctypeslib.as_array(p, shape=(n * width,)).copy().reshape(n, width) if n else np.zeros((0, width), np.int32)
+
+        def reals(p, n):
+            return np.ctypeslib.as_array(p, shape=(n,)).copy() if n else np.zeros(0)
+        a = [atoms[k].contents for k in range(4)]
+        q = [pars[k].contents for k in range(10)]
+        return dict(bonds=ints(a[0], nb, 2), bond_k=reals(q[0], nb), bond_r0=reals(q[1], nb),
+                    angles=ints(a[1], na, 3), angle_k=reals(q[2], na), angle_theta0=reals(q[3], na),
+                    torsions=ints(a[2], nt, 4), torsion_k=reals(q[4], nt), torsion_phi0=reals(q[5], nt),
+                    torsion_n=(np.ctypeslib.as_array(mult, shape=(nt,)).copy() if nt else np.zeros(0, np.int32)),
+                    n_dihedrals=nd, specials=ints(a[3], ns, 2), special_sigma=reals(q[6], ns), special_epsilon=reals(q[7], ns),
+                    special_lj_scale=reals(q[8], ns), special_coulomb_scale=reals(q[9], ns))
 
     def init_velocities(self, temperature, seed):
         _check(lib().dsmd_input_system_velocities(self.h, c_double(temperature), c_uint64(seed)))

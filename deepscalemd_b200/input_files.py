@@ -43,9 +43,10 @@ def write_legacy_top(path, type_rows, atom_types):
 
 
 def write_dsmd_input(folder, name, pos, elements, type_ids, type_names, mass, charge, pair_sigma, pair_epsilon,
-                     exclusions=None, constraints=None):
+                     exclusions=None, constraints=None, bonded=None):
     """A dsMD_input folder: manifest.yaml, <name>.xyz, <name>.dsMDtop, <name>.dsMDprm. pair_sigma / pair_epsilon:
-    [ntypes, ntypes] symmetric (the upper triangle is written)."""
+    [ntypes, ntypes] symmetric (the upper triangle is written). bonded: the mapping synthetic.chain_fluid() makes (every
+    term gets a parameter id of its own; angles and phases are written in degrees, as the format wants them)."""
     os.makedirs(folder, exist_ok=True)
     write_xyz(os.path.join(folder, name + ".xyz"), pos, elements)
     nt = len(type_names)
@@ -58,6 +59,26 @@ def write_dsmd_input(folder, name, pos, elements, type_ids, type_names, mass, ch
         for a in range(nt):
             for b in range(a, nt):
                 f.write(f"lj {a} {b} {pair_sigma[a][b]:.17g} {pair_epsilon[a][b]:.17g}\n")
+        if bonded is not None:
+            nd = int(bonded["n_dihedrals"])
+            f.write("\n[bond_parameters]\n")
+            for k, (kk, r0) in enumerate(zip(bonded["bond_k"], bonded["bond_r0"])):
+                f.write(f"{k} harmonic {kk:.17g} {r0:.17g}\n")
+            f.write("\n[angle_parameters]\n")
+            for k, (kk, th) in enumerate(zip(bonded["angle_k"], np.rad2deg(bonded["angle_theta0"]))):
+                f.write(f"{k} harmonic {kk:.17g} {th:.17g}\n")
+            f.write("\n[torsion_parameters]\n")
+            for k in range(nd):
+                f.write(f"{k} periodic {bonded['torsion_k'][k]:.17g} {np.rad2deg(bonded['torsion_phi0'][k]):.17g} "
+                        f"{int(bonded['torsion_n'][k])}\n")
+            f.write("\n[improper_parameters]\n")
+            for k in range(nd, len(bonded["torsions"])):
+                form = "harmonic" if int(bonded["torsion_n"][k]) == 0 else "periodic"
+                tail = "" if form == "harmonic" else f" {int(bonded['torsion_n'][k])}"
+                f.write(f"{k - nd} {form} {bonded['torsion_k'][k]:.17g} {np.rad2deg(bonded['torsion_phi0'][k]):.17g}{tail}\n")
+            f.write("\n[special_pair_parameters]\n")
+            for k, (sg, ep) in enumerate(zip(bonded["special_sigma"], bonded["special_epsilon"])):
+                f.write(f"{k} {sg:.17g} {ep:.17g}\n")
     with open(os.path.join(folder, name + ".dsMDtop"), "w") as f:
         f.write(f"[meta]\nschema_version 1\natom_count {len(pos)}\n\n[atoms]\n; atom_id element type_id mass charge\n")
         for i in range(len(pos)):
@@ -70,6 +91,23 @@ def write_dsmd_input(folder, name, pos, elements, type_ids, type_names, mass, ch
             f.write("\n[constraints]\n")
             for a, b, d in constraints:
                 f.write(f"{int(a)} {int(b)} {d:.17g}\n")
+        if bonded is not None:
+            nd = int(bonded["n_dihedrals"])
+            f.write("\n[bonds]\n")
+            for k, (a, b) in enumerate(bonded["bonds"]):
+                f.write(f"{int(a)} {int(b)} {k}\n")
+            f.write("\n[angles]\n")
+            for k, (a, b, c) in enumerate(bonded["angles"]):
+                f.write(f"{int(a)} {int(b)} {int(c)} {k}\n")
+            f.write("\n[dihedrals]\n")
+            for k, (a, b, c, d) in enumerate(bonded["torsions"][:nd]):
+                f.write(f"{int(a)} {int(b)} {int(c)} {int(d)} {k}\n")
+            f.write("\n[impropers]\n")
+            for k, (a, b, c, d) in enumerate(bonded["torsions"][nd:]):
+                f.write(f"{int(a)} {int(b)} {int(c)} {int(d)} {k}\n")
+            f.write("\n[special_pairs]\n")
+            for k, (a, b) in enumerate(bonded["specials"]):
+                f.write(f"{int(a)} {int(b)} {k} {bonded['special_lj_scale'][k]:.17g} {bonded['special_coulomb_scale'][k]:.17g}\n")
     with open(os.path.join(folder, "manifest.yaml"), "w") as f:
         f.write("schema_version: 1\nformat: dsMD_input\n")
         f.write(f"coordinate_file: {name}.xyz\ntopology_file: {name}.dsMDtop\nparameter_file: {name}.dsMDprm\n")

@@ -26,6 +26,7 @@ class System:
     vel: np.ndarray | None = None        # [N, 3]
     exclusions: np.ndarray | None = None  # [X, 2] global ids
     constraints: np.ndarray | None = None  # [C, 3] global id, global id, distance
+    bonded: dict | None = None           # bonds / angles / torsions / specials with their parameters (chain_fluid)
     coulomb: bool = False
     dt: float = 0.005
     force_to_accel: float = 1.0          # 4.184e-4 in the reference's real units, 1 in reduced units
@@ -139,6 +140,88 @@ def water_box(cells: int = 60, *, cutoff=10.0, skin=2.0, seed=4242) -> System:
     return System(name=f"water_{n}", pos=pos, box=box, types=types, charge=charge, mass=mass, eps=eps, sig=sig,
                   cutoff=cutoff, skin=skin, vel=vel, exclusions=excl, constraints=cons, coulomb=True, dt=2.0, force_to_accel=4.184e-4,
                   meta=dict(seed=seed, molecules=nm))
+
+
+def _torsion_angle(p0, p1, p2, p3):
+    """The torsion angle the bonded kernels use (atan2 form over the normals of the two planes), for arrays of points."""
+    ij, jk, kl = p0 - p1, p1 - p2, p2 - p3
+    n1, n2 = np.cross(ij, jk), np.cross(jk, kl)
+    jkm = np.linalg.norm(jk, axis=-1)
+    return np.arctan2((np.cross(n1, n2) * jk).sum(-1), (n1 * n2).sum(-1) * jkm)
+
+
+def chain_fluid(cells: int = 6, length: int = 8, *, spacing=9.0, cutoff=9.0, skin=1.5, seed=77) -> System:
+    """Flexible chain molecules for the bonded terms: cells^3 chains of `length` united atoms (bond 1.53 A, bend near
+    112 degrees, torsions within 35 degrees of trans, so that a chain does not fold onto itself) grown roughly along x
+    from the sites of a cubic lattice and wrapped into the periodic box, so that terms cross the box boundary. With the
+    default spacing neighbouring chains overlap here and there (fine for force parity with the pair terms switched off);
+    spacing >= 14 keeps them apart for dynamics. Two atom types (chain ends and inner atoms), small alternating charges,
+    and every kind of bonded term the reference evaluates: harmonic bonds and angles, periodic dihedrals of multiplicity
+    1 to 3, harmonic (n = 0) impropers on every other quadruple with a rest angle near the actual one, and 1-4 special
+    pairs with scaled Lennard-Jones and Coulomb parts. 1-2, 1-3 and 1-4 pairs are excluded from the nonbonded list."""
+    rng = np.random.default_rng(seed)
+    nm = cells ** 3
+    g = np.arange(cells, dtype=np.float64)
+    start = (np.stack(np.meshgrid(g, g, g, indexing="ij"), axis=-1).reshape(-1, 3) + 0.15) * spacing
+    start += rng.uniform(-0.5, 0.5, start.shape)
+    pos = np.zeros((nm, length, 3))
+    bond = 1.53
+    for m in range(nm):
+        d = np.array([1.0, 0.0, 0.0]) + rng.uniform(-0.25, 0.25, 3)
+        d /= np.linalg.norm(d)
+        p = [start[m], start[m] + bond * d]
+        for k in range(2, length):
+            c_, b_ = p[-1], p[-2]
+            bc = (c_ - b_) / np.linalg.norm(c_ - b_)
+            if k == 2:
+                ref = rng.normal(size=3)
+            else:
+                ref = b_ - p[-3]
+            n = np.cross(ref, bc)
+            n /= np.linalg.norm(n)
+            mvec = np.cross(n, bc)
+            theta = np.deg2rad(112.0 + rng.uniform(-10.0, 10.0))
+            phi = np.pi + np.deg2rad(rng.uniform(-35.0, 35.0)) if k > 2 else 0.0
+            step = -np.cos(theta) * bc + np.sin(theta) * (np.cos(phi) * mvec + np.sin(phi) * n)
+            p.append(c_ + bond * step)
+        pos[m] = np.array(p)
+    box = np.full(3, cells * spacing)
+    unwrapped = pos.reshape(-1, 3).copy()
+    pos = unwrapped - box * np.floor(unwrapped / box)
+    n = nm * length
+    first = (np.arange(nm) * length)[:, None]
+    k = np.arange(length)
+    ids = first + k[None, :]
+    types = np.tile(np.where((k == 0) | (k == length - 1), 0, 1).astype(np.int32), nm)
+    charge = np.tile(np.where(k % 2 == 0, 0.12, -0.12) * (1.0 if length % 2 == 0 else 0.0), nm)
+    mass = np.tile(np.where((k == 0) | (k == length - 1), 15.035, 14.027), nm)
+    eps, sig = lorentz_berthelot([0.175, 0.118], [3.905, 3.905])
+    bonds = np.stack([ids[:, :-1], ids[:, 1:]], axis=-1).reshape(-1, 2)
+    angles = np.stack([ids[:, :-2], ids[:, 1:-1], ids[:, 2:]], axis=-1).reshape(-1, 3)
+    quads = np.stack([ids[:, :-3], ids[:, 1:-2], ids[:, 2:-1], ids[:, 3:]], axis=-1).reshape(-1, 4)
+    impropers = quads[::2]
+    nd, ni = len(quads), len(impropers)
+    actual = _torsion_angle(*(unwrapped[impropers[:, q]] for q in range(4)))
+    rest = actual + rng.uniform(-0.3, 0.3, ni)
+    rest = rest - 2.0 * np.pi * np.round(rest / (2.0 * np.pi))
+    bonded = dict(
+        bonds=bonds, bond_k=rng.uniform(400.0, 640.0, len(bonds)), bond_r0=rng.uniform(1.50, 1.56, len(bonds)),
+        angles=angles, angle_k=rng.uniform(80.0, 130.0, len(angles)),
+        angle_theta0=np.deg2rad(rng.uniform(107.0, 117.0, len(angles))),
+        torsions=np.concatenate([quads, impropers]),
+        torsion_k=np.concatenate([rng.uniform(0.2, 2.5, nd), rng.uniform(5.0, 40.0, ni)]),
+        torsion_phi0=np.concatenate([rng.choice([0.0, np.pi], nd), rest]),
+        torsion_n=np.concatenate([rng.integers(1, 4, nd), np.zeros(ni, dtype=np.int64)]).astype(np.int32),
+        n_dihedrals=nd,
+        specials=np.stack([quads[:, 0], quads[:, 3]], axis=1), special_sigma=np.full(nd, 3.905),
+        special_epsilon=rng.uniform(0.05, 0.2, nd), special_lj_scale=np.full(nd, 0.5),
+        special_coulomb_scale=np.full(nd, 0.8333))
+    excl = np.concatenate([bonds, angles[:, [0, 2]], quads[:, [0, 3]]]).astype(np.int32)
+    kb = 0.0019872041
+    vel = maxwell_boltzmann(n, 300.0, mass, rng, kb=kb / (48.88821291 ** 2))
+    return System(name=f"chains_{n}", pos=pos, box=box, types=types, charge=charge, mass=mass, eps=eps, sig=sig,
+                  cutoff=cutoff, skin=skin, vel=vel, exclusions=excl, coulomb=True, dt=1.0, force_to_accel=4.184e-4,
+                  bonded=bonded, meta=dict(seed=seed, molecules=nm, length=length))
 
 
 def disordered_solid(n_target=1_000_000, *, density=0.05, min_dist=1.8, cutoff=5.0, seed=99) -> System:

@@ -184,6 +184,35 @@ int dsmd_compute_forces(dsmd_ctx* ctx, int phase, int want_energy, void* stream)
  * Synchronises `stream`. */
 int dsmd_read_scalars(dsmd_ctx* ctx, double out[6], void* stream);
 
+/* Bonded terms and scaled special (1-4) pairs (compute_bond_forces_kernel, compute_angle_forces_kernel,
+ * compute_dihedral_forces_kernel, compute_improper_forces_kernel, compute_special_pair_forces_kernel,
+ * src/force_calculator_cuda.cu:2703-3170; MDSystem::LocalBond ... LocalSpecialPair, include/md_system.h:22-42). Atoms are
+ * named by global id (< n_global); every term carries its own parameters:
+ *   bonds     U = k/2 (r - r0)^2;   angles   U = k/2 (theta - theta0)^2 (radians, vertex = the second atom);
+ *   torsions  (proper dihedrals and impropers alike) n > 0: U = k (1 + cos(n phi - phi0)); n = 0: U = k (phi - phi0)^2 with
+ *             the difference wrapped to (-pi, pi];
+ *   specials  4 eps ((sigma/r)^12 - (sigma/r)^6) lj_scale + 332.0636 qi qj / r coulomb_scale (charges from the context).
+ * Replaces any earlier set; all counts zero clears. On several ranks give every rank the whole table: a term is evaluated
+ * where one of its atoms is owned, forces go to owned atoms only, energy and virial where the lowest global id is owned
+ * (the reference's rule). */
+int dsmd_set_bonded(dsmd_ctx* ctx, int64_t n_global, int64_t n_bonds, const int32_t* bond_atoms, const double* bond_k,
+                    const double* bond_r0, int64_t n_angles, const int32_t* angle_atoms, const double* angle_k,
+                    const double* angle_theta0, int64_t n_torsions, const int32_t* torsion_atoms, const double* torsion_k,
+                    const double* torsion_phi0, const int32_t* torsion_n, int64_t n_specials, const int32_t* special_atoms,
+                    const double* special_sigma, const double* special_epsilon, const double* special_lj_scale,
+                    const double* special_coulomb_scale);
+
+/* ADDS the forces of the bonded terms to the force arrays of the owned atoms (call after dsmd_compute_forces of the FULL
+ * or BOUNDARY phase, when ghost positions are current) and leaves their energy and virial for dsmd_read_bonded_scalars.
+ * Forces are summed per atom in a fixed order (bitwise reproducible). Needs a list build since the last change of the
+ * atom set (terms find their atoms through the sorted arrays). dsmd_run_nve calls it every step. */
+int dsmd_compute_bonded(dsmd_ctx* ctx, void* stream);
+
+/* out = {PE, W, Wxx, Wyy, Wzz} of the last dsmd_compute_bonded on this rank (bonds and specials contribute to W and the
+ * diagonal, angles and torsions to the diagonal only: their trace is zero). Synchronises `stream`. DSMD_ERR_STATE when
+ * a term had an owned atom whose partner was not on this rank (halo narrower than the term is long). */
+int dsmd_read_bonded_scalars(dsmd_ctx* ctx, double out[5], void* stream);
+
 /* Velocity Verlet halves (launch_vv_step1_kernel / launch_vv_step2_kernel, src/integrator_kernels.cu:149-208):
  * half 1: v += dt/2 f/m c; x += dt v (and packs positions, see dsmd_pack_positions); half 2: v += dt/2 f/m c;
  * half 3: half 2 of the previous step and half 1 of this one in one pass (v += dt f/m c; x += dt v; pack), for loops in

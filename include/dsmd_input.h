@@ -60,6 +60,15 @@ int dsmd_input_system_exclusions(const dsmd_input_system* system, const int32_t*
 /* i, j: int32[constraints]; distance: double[constraints]. */
 int dsmd_input_system_constraints(const dsmd_input_system* system, const int32_t** i, const int32_t** j,
                                   const double** distance);
+/* The bonded terms of a dsMD_input system with the parameters of every term written out, in the form dsmd_set_bonded
+ * takes (Topology::load_canonical, src/topology.cpp:601-665, 760-796: angles and phases converted to radians, a harmonic
+ * improper = multiplicity 0, a special pair without a listed parameter id takes the pair matrix of its atom types).
+ * counts = {bonds, angles, torsions (dihedrals + impropers), dihedrals among them (they come first), special pairs};
+ * atoms = {bond, angle, torsion, special} atom ids (2, 3, 4, 2 per term); parameters = {bond k, r0, angle k, theta0,
+ * torsion k, phi0, special sigma, epsilon, LJ scale, Coulomb scale}. Null entries are skipped. A legacy .top system gives
+ * zero counts (its bonded sections are counted by dsmd_input_system_counts only). */
+int dsmd_input_system_bonded(const dsmd_input_system* system, int64_t counts[5], const int32_t** atoms[4],
+                             const double** parameters[10], const int32_t** torsion_multiplicity);
 /* Maxwell-Boltzmann velocities at the temperature (K) from the seed (A/fs). */
 int dsmd_input_system_velocities(dsmd_input_system* system, double temperature, uint64_t seed);
 

@@ -236,6 +236,62 @@ def virial_from_forces(pos, f):
     return out
 
 
+def _i64(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.int64)
+
+
+class BondedTerms:
+    """Plain arrays of the bonded terms of a system: bonds [nb, 2] + k, r0; angles [na, 3] + k, theta0 (radians);
+    torsions [nt, 4] + k, phi0 (radians), n (dihedrals first, impropers behind: n_dihedrals tells where they start);
+    specials [ns, 2] + sigma, epsilon, lj_scale, coulomb_scale. Atom numbers are indices into the arrays handed to the
+    evaluation (for the device library: global ids)."""
+
+    def __init__(self, bonds=None, bond_k=None, bond_r0=None, angles=None, angle_k=None, angle_theta0=None, torsions=None,
+                 torsion_k=None, torsion_phi0=None, torsion_n=None, n_dihedrals=None, specials=None, special_sigma=None,
+                 special_epsilon=None, special_lj_scale=None, special_coulomb_scale=None):
+        def table(a, width):
+            return np.zeros((0, width), dtype=np.int64) if a is None else _i64(np.asarray(a).reshape(-1, width))
+
+        def column(a, n, dtype=np.float64):
+            return np.zeros(n, dtype=dtype) if a is None else np.ascontiguousarray(a, dtype=dtype)
+        self.bonds = table(bonds, 2)
+        self.bond_k, self.bond_r0 = column(bond_k, len(self.bonds)), column(bond_r0, len(self.bonds))
+        self.angles = table(angles, 3)
+        self.angle_k, self.angle_theta0 = column(angle_k, len(self.angles)), column(angle_theta0, len(self.angles))
+        self.torsions = table(torsions, 4)
+        self.torsion_k, self.torsion_phi0 = column(torsion_k, len(self.torsions)), column(torsion_phi0, len(self.torsions))
+        self.torsion_n = column(torsion_n, len(self.torsions), np.int32)
+        self.n_dihedrals = len(self.torsions) if n_dihedrals is None else int(n_dihedrals)
+        self.specials = table(specials, 2)
+        ns = len(self.specials)
+        self.special_sigma, self.special_epsilon = column(special_sigma, ns), column(special_epsilon, ns)
+        self.special_lj_scale, self.special_coulomb_scale = column(special_lj_scale, ns), column(special_coulomb_scale, ns)
+
+
+def bonded(pos, n_local, box, terms, *, periodic=(1, 1, 1), gid=None, charge=None):
+    """Forces [n_local, 3] of the bonded terms and scaled special pairs on the owned atoms, and {pe, virial, virial_diag}:
+    the restatement of the reference's bond / angle / torsion / special-pair routines with the ownership rule of its
+    GPU kernels (a term with no owned atom is skipped; energy where the lowest global id is owned)."""
+    x, y, z = (_f64(pos[:, k]) for k in range(3))
+    f = [np.zeros(len(x)) for _ in range(3)]
+    out = np.zeros(5)
+    Lv, per, g, q = _f64(box), _i32(periodic), _i32(gid), _f64(charge)
+    t = terms
+    lib().dsmd_oracle_bonded(
+        ctypes.c_long(n_local), _ptr(x, ctypes.c_double), _ptr(y, ctypes.c_double), _ptr(z, ctypes.c_double),
+        _ptr(g, ctypes.c_int), _ptr(Lv, ctypes.c_double), _ptr(per, ctypes.c_int),
+        ctypes.c_long(len(t.bonds)), _ptr(t.bonds, ctypes.c_long), _ptr(t.bond_k, ctypes.c_double), _ptr(t.bond_r0, ctypes.c_double),
+        ctypes.c_long(len(t.angles)), _ptr(t.angles, ctypes.c_long), _ptr(t.angle_k, ctypes.c_double),
+        _ptr(t.angle_theta0, ctypes.c_double),
+        ctypes.c_long(len(t.torsions)), _ptr(t.torsions, ctypes.c_long), _ptr(t.torsion_k, ctypes.c_double),
+        _ptr(t.torsion_phi0, ctypes.c_double), _ptr(t.torsion_n, ctypes.c_int),
+        ctypes.c_long(len(t.specials)), _ptr(t.specials, ctypes.c_long), _ptr(t.special_sigma, ctypes.c_double),
+        _ptr(t.special_epsilon, ctypes.c_double), _ptr(t.special_lj_scale, ctypes.c_double),
+        _ptr(t.special_coulomb_scale, ctypes.c_double), _ptr(q, ctypes.c_double),
+        *[_ptr(a, ctypes.c_double) for a in f], _ptr(out, ctypes.c_double))
+    return np.stack(f, axis=1)[:n_local], dict(pe=out[0], virial=out[1], virial_diag=out[2:5].copy())
+
+
 def mark_receivers(x, y, z, lo, hi, reach):
     x, y, z = _f64(x), _f64(y), _f64(z)
     ok = np.zeros(len(x), dtype=np.uint8)
@@ -460,6 +516,25 @@ class RefCase:
             raise RuntimeError("reference compute_forces failed")
         return np.stack([fx, fy, fz], axis=1), dict(pe=sc[0], virial=sc[1], virial_diag=sc[2:5].copy(), alpha=sc[5],
                                                     self_energy=sc[6], pe_real=sc[0] - sc[6])
+
+    def bonded(self, terms, *, do_lj=True, do_coulomb=True):
+        """The reference's own bond / angle / dihedral / improper / special-pair routines on this case's atoms."""
+        fx, fy, fz = np.zeros(self.n_local), np.zeros(self.n_local), np.zeros(self.n_local)
+        sc = np.zeros(5)
+        t = terms
+        rc = self.L.dsmd_ref_bonded(
+            self.h, ctypes.c_long(len(t.bonds)), _ptr(t.bonds, ctypes.c_long), _ptr(t.bond_k, ctypes.c_double),
+            _ptr(t.bond_r0, ctypes.c_double), ctypes.c_long(len(t.angles)), _ptr(t.angles, ctypes.c_long),
+            _ptr(t.angle_k, ctypes.c_double), _ptr(t.angle_theta0, ctypes.c_double), ctypes.c_long(len(t.torsions)),
+            ctypes.c_long(t.n_dihedrals), _ptr(t.torsions, ctypes.c_long), _ptr(t.torsion_k, ctypes.c_double),
+            _ptr(t.torsion_phi0, ctypes.c_double), _ptr(t.torsion_n, ctypes.c_int), ctypes.c_long(len(t.specials)),
+            _ptr(t.specials, ctypes.c_long), _ptr(t.special_sigma, ctypes.c_double), _ptr(t.special_epsilon, ctypes.c_double),
+            _ptr(t.special_lj_scale, ctypes.c_double), _ptr(t.special_coulomb_scale, ctypes.c_double), int(do_lj),
+            int(do_coulomb), _ptr(fx, ctypes.c_double), _ptr(fy, ctypes.c_double), _ptr(fz, ctypes.c_double),
+            _ptr(sc, ctypes.c_double))
+        if rc != 0:
+            raise RuntimeError("reference bonded routines failed")
+        return np.stack([fx, fy, fz], axis=1), dict(pe=sc[0], virial=sc[1], virial_diag=sc[2:5].copy())
 
     def close(self):
         if self.h:

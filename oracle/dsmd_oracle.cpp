@@ -646,4 +646,174 @@ int dsmd_oracle_rattle(long n_constraints, const long* atom1, const long* atom2,
     return converged;
 }
 
+// ---- bonded terms and scaled special pairs ------------------------------------------------------------------------------
+// Restates ForceCalculatorCPU::compute_bond_forces / compute_angle_forces / compute_torsion_forces /
+// compute_special_pair_forces (src/force_calculator_cpu.cpp:2437-2895), with the ownership rule of the reference's GPU
+// kernels (src/force_calculator_cuda.cu:2703-3170): a term is evaluated when at least one of its atoms is owned
+// (index < n_local), forces go to owned atoms only, energy and virial are counted where the atom with the lowest global
+// id is owned. Minimum image per displacement on the periodic axes (one wrap, include/md_types.h:57-70).
+//
+//   bonds      U = k/2 (r - r0)^2                                 (k, r0)
+//   angles     U = k/2 (theta - theta0)^2, theta at atom 2        (k, theta0 in radians)
+//   torsions   n > 0: U = k (1 + cos(n phi - phi0));  n = 0: U = k (phi - phi0)^2 with the difference wrapped to
+//              (-pi, pi]  (dihedrals and impropers alike)         (k, phi0 in radians, n)
+//   specials   scaled 12-6 LJ (4 eps ((s/r)^12 - (s/r)^6) lj_scale) + plain Coulomb 332.0636 qi qj / r coulomb_scale
+//
+// Forces are ADDED to fx, fy, fz. out = {PE, W, Wxx, Wyy, Wzz}: bonds and specials contribute to W and the diagonal,
+// angles and torsions to the diagonal only (their trace is zero).
+namespace {
+inline bool owns_term(const long* atoms, int count, const int* gid, long n_local) {
+    long lowest = atoms[0];
+    for (int k = 1; k < count; ++k)
+        if ((gid ? gid[atoms[k]] < gid[lowest] : atoms[k] < lowest)) lowest = atoms[k];
+    return lowest < n_local;
+}
+inline bool any_local(const long* atoms, int count, long n_local) {
+    for (int k = 0; k < count; ++k)
+        if (atoms[k] < n_local) return true;
+    return false;
+}
+inline void add_force(double* fx, double* fy, double* fz, long i, long n_local, double x, double y, double z) {
+    if (i < n_local) { fx[i] += x; fy[i] += y; fz[i] += z; }
+}
+}  // namespace
+
+void dsmd_oracle_bonded(long n_local, const double* x, const double* y, const double* z, const int* gid, const double L[3],
+                        const int periodic[3],
+                        long n_bonds, const long* bond_atoms, const double* bond_k, const double* bond_r0,
+                        long n_angles, const long* angle_atoms, const double* angle_k, const double* angle_theta0,
+                        long n_torsions, const long* torsion_atoms, const double* torsion_k, const double* torsion_phi0,
+                        const int* torsion_n,
+                        long n_specials, const long* special_atoms, const double* special_sigma,
+                        const double* special_epsilon, const double* special_lj_scale, const double* special_coulomb_scale,
+                        const double* charge, double* fx, double* fy, double* fz, double out[5]) {
+    double pe = 0.0, w = 0.0, wd[3] = {0.0, 0.0, 0.0};
+    for (long b = 0; b < n_bonds; ++b) {
+        const long* a = bond_atoms + 2 * b;
+        if (!any_local(a, 2, n_local)) continue;
+        double d[3] = {x[a[0]] - x[a[1]], y[a[0]] - y[a[1]], z[a[0]] - z[a[1]]};
+        min_image(d, L, periodic);
+        const double r = std::sqrt(d[0] * d[0] + d[1] * d[1] + d[2] * d[2]);
+        if (r < 1e-10) continue;
+        const double dr = r - bond_r0[b];
+        const double fm = -bond_k[b] * dr / r;
+        add_force(fx, fy, fz, a[0], n_local, fm * d[0], fm * d[1], fm * d[2]);
+        add_force(fx, fy, fz, a[1], n_local, -fm * d[0], -fm * d[1], -fm * d[2]);
+        if (owns_term(a, 2, gid, n_local)) {
+            pe += 0.5 * bond_k[b] * dr * dr;
+            w += fm * (d[0] * d[0] + d[1] * d[1] + d[2] * d[2]);
+            for (int c = 0; c < 3; ++c) wd[c] += fm * d[c] * d[c];
+        }
+    }
+    for (long t = 0; t < n_angles; ++t) {
+        const long* a = angle_atoms + 3 * t;
+        if (!any_local(a, 3, n_local)) continue;
+        double u[3] = {x[a[0]] - x[a[1]], y[a[0]] - y[a[1]], z[a[0]] - z[a[1]]};
+        double v[3] = {x[a[2]] - x[a[1]], y[a[2]] - y[a[1]], z[a[2]] - z[a[1]]};
+        min_image(u, L, periodic);
+        min_image(v, L, periodic);
+        const double ru = std::sqrt(u[0] * u[0] + u[1] * u[1] + u[2] * u[2]);
+        const double rv = std::sqrt(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
+        if (ru < 1e-10 || rv < 1e-10) continue;
+        double c = (u[0] * v[0] + u[1] * v[1] + u[2] * v[2]) / (ru * rv);
+        c = std::min(1.0, std::max(-1.0, c));
+        const double dtheta = std::acos(c) - angle_theta0[t];
+        const bool owner = owns_term(a, 3, gid, n_local);
+        if (owner) pe += 0.5 * angle_k[t] * dtheta * dtheta;
+        if (std::fabs(dtheta) < 1e-10) continue;
+        const double sine = std::sqrt(1.0 - c * c);
+        if (sine < 1e-10) continue;
+        const double fc = angle_k[t] * dtheta / sine;
+        double fi[3], fk[3];
+        for (int q = 0; q < 3; ++q) {
+            fi[q] = fc * (v[q] / (ru * rv) - u[q] * c / (ru * ru));
+            fk[q] = fc * (u[q] / (ru * rv) - v[q] * c / (rv * rv));
+        }
+        add_force(fx, fy, fz, a[0], n_local, fi[0], fi[1], fi[2]);
+        add_force(fx, fy, fz, a[2], n_local, fk[0], fk[1], fk[2]);
+        add_force(fx, fy, fz, a[1], n_local, -(fi[0] + fk[0]), -(fi[1] + fk[1]), -(fi[2] + fk[2]));
+        if (owner)
+            for (int q = 0; q < 3; ++q) wd[q] += u[q] * fi[q] + v[q] * fk[q];
+    }
+    for (long t = 0; t < n_torsions; ++t) {
+        const long* a = torsion_atoms + 4 * t;
+        if (!any_local(a, 4, n_local)) continue;
+        double ij[3] = {x[a[0]] - x[a[1]], y[a[0]] - y[a[1]], z[a[0]] - z[a[1]]};
+        double jk[3] = {x[a[1]] - x[a[2]], y[a[1]] - y[a[2]], z[a[1]] - z[a[2]]};
+        double kl[3] = {x[a[2]] - x[a[3]], y[a[2]] - y[a[3]], z[a[2]] - z[a[3]]};
+        min_image(ij, L, periodic);
+        min_image(jk, L, periodic);
+        min_image(kl, L, periodic);
+        const double n1[3] = {ij[1] * jk[2] - ij[2] * jk[1], ij[2] * jk[0] - ij[0] * jk[2], ij[0] * jk[1] - ij[1] * jk[0]};
+        const double n2[3] = {jk[1] * kl[2] - jk[2] * kl[1], jk[2] * kl[0] - jk[0] * kl[2], jk[0] * kl[1] - jk[1] * kl[0]};
+        const double n1sq = n1[0] * n1[0] + n1[1] * n1[1] + n1[2] * n1[2];
+        const double n2sq = n2[0] * n2[0] + n2[1] * n2[1] + n2[2] * n2[2];
+        const double jksq = jk[0] * jk[0] + jk[1] * jk[1] + jk[2] * jk[2];
+        if (n1sq < 1e-20 || n2sq < 1e-20 || jksq < 1e-20) continue;
+        const double jkm = std::sqrt(jksq);
+        const double cosine = n1[0] * n2[0] + n1[1] * n2[1] + n1[2] * n2[2];
+        const double sine = (n1[1] * n2[2] - n1[2] * n2[1]) * jk[0] + (n1[2] * n2[0] - n1[0] * n2[2]) * jk[1] +
+                            (n1[0] * n2[1] - n1[1] * n2[0]) * jk[2];
+        const double phi = std::atan2(sine, cosine * jkm);
+        const bool owner = owns_term(a, 4, gid, n_local);
+        double slope;
+        if (torsion_n[t] == 0) {
+            const double dphi = std::remainder(phi - torsion_phi0[t], 2.0 * M_PI);
+            if (owner) pe += torsion_k[t] * dphi * dphi;
+            slope = 2.0 * torsion_k[t] * dphi;
+        } else {
+            const double dphi = torsion_n[t] * phi - torsion_phi0[t];
+            if (owner) pe += torsion_k[t] * (1.0 + std::cos(dphi));
+            slope = -torsion_k[t] * torsion_n[t] * std::sin(dphi);
+        }
+        const double si = -slope * jkm / n1sq, sl = slope * jkm / n2sq;
+        const double pp = -(ij[0] * jk[0] + ij[1] * jk[1] + ij[2] * jk[2]) / jksq;
+        const double qq = -(kl[0] * jk[0] + kl[1] * jk[1] + kl[2] * jk[2]) / jksq;
+        double fi[3], fj[3], fk[3], fl[3];
+        for (int q = 0; q < 3; ++q) {
+            fi[q] = si * n1[q];
+            fl[q] = sl * n2[q];
+            fj[q] = (pp - 1.0) * fi[q] - qq * fl[q];
+            fk[q] = -pp * fi[q] + (qq - 1.0) * fl[q];
+        }
+        add_force(fx, fy, fz, a[0], n_local, fi[0], fi[1], fi[2]);
+        add_force(fx, fy, fz, a[1], n_local, fj[0], fj[1], fj[2]);
+        add_force(fx, fy, fz, a[2], n_local, fk[0], fk[1], fk[2]);
+        add_force(fx, fy, fz, a[3], n_local, fl[0], fl[1], fl[2]);
+        if (owner)
+            for (int q = 0; q < 3; ++q) wd[q] += ij[q] * fi[q] - jk[q] * fk[q] - (jk[q] + kl[q]) * fl[q];
+    }
+    for (long s = 0; s < n_specials; ++s) {
+        const long* a = special_atoms + 2 * s;
+        if (!any_local(a, 2, n_local)) continue;
+        double d[3] = {x[a[0]] - x[a[1]], y[a[0]] - y[a[1]], z[a[0]] - z[a[1]]};
+        min_image(d, L, periodic);
+        const double r2 = d[0] * d[0] + d[1] * d[1] + d[2] * d[2];
+        if (r2 < 1e-10) continue;
+        double fm = 0.0, u = 0.0;
+        if (special_epsilon[s] != 0.0) {
+            const double r2inv = 1.0 / r2, sig2 = special_sigma[s] * special_sigma[s];
+            const double att = sig2 * sig2 * sig2 * r2inv * r2inv * r2inv, rep = att * att;
+            fm += 4.0 * special_epsilon[s] * r2inv * (12.0 * rep - 6.0 * att) * special_lj_scale[s];
+            u += 4.0 * special_epsilon[s] * (rep - att) * special_lj_scale[s];
+        }
+        if (charge && charge[a[0]] != 0.0 && charge[a[1]] != 0.0) {
+            const double r = std::sqrt(r2);
+            const double qq = 332.0636 * charge[a[0]] * charge[a[1]] * special_coulomb_scale[s];
+            fm += qq / (r2 * r);
+            u += qq / r;
+        }
+        const bool owner = owns_term(a, 2, gid, n_local);
+        if (owner) pe += u;
+        if (fm == 0.0) continue;
+        add_force(fx, fy, fz, a[0], n_local, fm * d[0], fm * d[1], fm * d[2]);
+        add_force(fx, fy, fz, a[1], n_local, -fm * d[0], -fm * d[1], -fm * d[2]);
+        if (owner) {
+            w += r2 * fm;
+            for (int c = 0; c < 3; ++c) wd[c] += fm * d[c] * d[c];
+        }
+    }
+    out[0] = pe; out[1] = w; out[2] = wd[0]; out[3] = wd[1]; out[4] = wd[2];
+}
+
 }  // extern "C"

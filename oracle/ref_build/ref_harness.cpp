@@ -286,4 +286,75 @@ int dsmd_ref_constrain(int which, long n, long n_local, double* x, double* y, do
     return ok ? 1 : 0;
 }
 
+// The reference's bonded terms and scaled special pairs on the particles and box of this case (one rank: every atom is
+// owned): ForceCalculatorCPU::compute_bond_forces, compute_angle_forces, compute_torsion_forces (dihedrals and impropers
+// share it) and compute_special_pair_forces (src/force_calculator_cpu.cpp:2437-2895), called one after the other on
+// cleared force arrays. Every term carries its own parameters (a type per term). Torsions: the first n_dihedrals entries
+// go in as dihedrals, the rest as impropers. special_sigma / special_epsilon < 0: the mixing tables of the force field.
+// out_scalars = {PE, virial, Wxx, Wyy, Wzz}.
+int dsmd_ref_bonded(void* h, long n_bonds, const long* bond_atoms, const double* bond_k, const double* bond_r0,
+                    long n_angles, const long* angle_atoms, const double* angle_k, const double* angle_theta0,
+                    long n_torsions, long n_dihedrals, const long* torsion_atoms, const double* torsion_k,
+                    const double* torsion_phi0, const int* torsion_n,
+                    long n_specials, const long* special_atoms, const double* special_sigma, const double* special_epsilon,
+                    const double* special_lj_scale, const double* special_coulomb_scale, int do_lj, int do_coulomb,
+                    double* fx, double* fy, double* fz, double* out_scalars) {
+    auto* c = static_cast<RefCase*>(h);
+    try {
+        if (!c->calc) c->calc = std::make_unique<ForceCalculatorCPU>();
+        c->calc->set_virial_tensor_enabled(true);
+        MDSystem& sys = c->system;
+        g_ref_bond_types.clear(); g_ref_angle_types.clear(); g_ref_dihedral_types.clear();
+        sys.local_bonds_.clear(); sys.local_angles_.clear(); sys.local_dihedrals_.clear(); sys.local_impropers_.clear();
+        sys.local_special_pairs_.clear();
+        for (long b = 0; b < n_bonds; ++b) {
+            g_ref_bond_types.push_back(BondType{"b", bond_k[b], bond_r0[b]});
+            sys.local_bonds_.push_back({static_cast<size_t>(bond_atoms[2 * b]), static_cast<size_t>(bond_atoms[2 * b + 1]),
+                                        static_cast<int>(b), bond_k[b], bond_r0[b]});
+        }
+        for (long a = 0; a < n_angles; ++a) {
+            g_ref_angle_types.push_back(AngleType{"a", angle_k[a], angle_theta0[a]});
+            sys.local_angles_.push_back({static_cast<size_t>(angle_atoms[3 * a]), static_cast<size_t>(angle_atoms[3 * a + 1]),
+                                         static_cast<size_t>(angle_atoms[3 * a + 2]), static_cast<int>(a), angle_k[a],
+                                         angle_theta0[a]});
+        }
+        for (long t = 0; t < n_torsions; ++t) {
+            g_ref_dihedral_types.push_back(DihedralType{"d", torsion_k[t], torsion_phi0[t], torsion_n[t]});
+            MDSystem::LocalDihedral d{static_cast<size_t>(torsion_atoms[4 * t]), static_cast<size_t>(torsion_atoms[4 * t + 1]),
+                                      static_cast<size_t>(torsion_atoms[4 * t + 2]), static_cast<size_t>(torsion_atoms[4 * t + 3]),
+                                      static_cast<int>(t), torsion_k[t], torsion_phi0[t], torsion_n[t]};
+            (t < n_dihedrals ? sys.local_dihedrals_ : sys.local_impropers_).push_back(d);
+        }
+        for (long s = 0; s < n_specials; ++s)
+            sys.local_special_pairs_.push_back({static_cast<size_t>(special_atoms[2 * s]), static_cast<size_t>(special_atoms[2 * s + 1]),
+                                                special_lj_scale[s], special_coulomb_scale[s], special_sigma[s],
+                                                special_epsilon[s]});
+        ForceManager::ForceConfig& cfg = sys.force_manager->config;
+        cfg.enable_lennard_jones = do_lj != 0;
+        cfg.enable_coulomb = do_coulomb != 0;
+        ParticleData& p = sys.particles;
+        std::fill(p.fx.begin(), p.fx.end(), 0.0);
+        std::fill(p.fy.begin(), p.fy.end(), 0.0);
+        std::fill(p.fz.begin(), p.fz.end(), 0.0);
+        c->calc->last_potential_energy = 0.0;
+        c->calc->last_virial = 0.0;
+        for (int a = 0; a < 3; ++a) c->calc->last_virial_diag[a] = 0.0;
+        c->calc->compute_bond_forces(sys);
+        c->calc->compute_angle_forces(sys);
+        c->calc->compute_dihedral_forces(sys);
+        c->calc->compute_improper_forces(sys);
+        c->calc->compute_special_pair_forces(sys);
+        for (size_t i = 0; i < c->n_local; ++i) { fx[i] = p.fx[i]; fy[i] = p.fy[i]; fz[i] = p.fz[i]; }
+        out_scalars[0] = c->calc->last_potential_energy;
+        out_scalars[1] = c->calc->last_virial;
+        for (int a = 0; a < 3; ++a) out_scalars[2 + a] = c->calc->last_virial_diag[a];
+        sys.local_bonds_.clear(); sys.local_angles_.clear(); sys.local_dihedrals_.clear(); sys.local_impropers_.clear();
+        sys.local_special_pairs_.clear();
+    } catch (const std::exception& e) {
+        std::cerr << "dsmd_ref_bonded: " << e.what() << std::endl;
+        return 1;
+    }
+    return 0;
+}
+
 }  // extern "C"

@@ -43,9 +43,14 @@ void MDSystem::finalize() {}
 
 Topology::Topology() : rank(0) {}
 Topology::~Topology() = default;
-const BondType& Topology::get_bond_type(int) const { throw std::runtime_error("oracle: no bonded terms"); }
-const AngleType& Topology::get_angle_type(int) const { throw std::runtime_error("oracle: no bonded terms"); }
-const DihedralType& Topology::get_dihedral_type(int) const { throw std::runtime_error("oracle: no bonded terms"); }
+// Bonded parameters by type id: the harness keeps them in plain tables (one entry per term is enough for a check); the
+// reference's own tables are string-keyed maps filled by its file reader.
+inline std::vector<BondType> g_ref_bond_types;
+inline std::vector<AngleType> g_ref_angle_types;
+inline std::vector<DihedralType> g_ref_dihedral_types;
+const BondType& Topology::get_bond_type(int id) const { return g_ref_bond_types.at(static_cast<size_t>(id)); }
+const AngleType& Topology::get_angle_type(int id) const { return g_ref_angle_types.at(static_cast<size_t>(id)); }
+const DihedralType& Topology::get_dihedral_type(int id) const { return g_ref_dihedral_types.at(static_cast<size_t>(id)); }
 
 ForceManager::ForceManager() : backend_type("cpu") {}
 

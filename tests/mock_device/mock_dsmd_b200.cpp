@@ -125,6 +125,21 @@ int dsmd_set_constraints(dsmd_ctx* c, int64_t, int64_t n_constraints, const int3
     return n_constraints ? fail(c, DSMD_ERR_INVALID, "the test double has no constraints") : DSMD_OK;
 }
 
+int dsmd_set_bonded(dsmd_ctx* c, int64_t, int64_t n_bonds, const int32_t*, const double*, const double*, int64_t n_angles,
+                    const int32_t*, const double*, const double*, int64_t n_torsions, const int32_t*, const double*,
+                    const double*, const int32_t*, int64_t n_specials, const int32_t*, const double*, const double*,
+                    const double*, const double*) {
+    return (n_bonds || n_angles || n_torsions || n_specials) ? fail(c, DSMD_ERR_INVALID, "the test double has no bonded terms")
+                                                             : DSMD_OK;
+}
+
+int dsmd_compute_bonded(dsmd_ctx*, void*) { return DSMD_OK; }
+
+int dsmd_read_bonded_scalars(dsmd_ctx*, double out[5], void*) {
+    for (int k = 0; k < 5; ++k) out[k] = 0.0;
+    return DSMD_OK;
+}
+
 int dsmd_upload(dsmd_ctx* c, int64_t n_owned, int64_t n_total, const double* x, const double* y, const double* z,
                 const double* vx, const double* vy, const double* vz, const double* mass, const double* charge,
                 const int32_t* type, const int32_t* gid, void*) {

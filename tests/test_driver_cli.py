@@ -61,3 +61,26 @@ def test_usage_and_input_errors(driver, tmp_path):
     (tmp_path / "incomplete.yaml").write_text("timestep: 1.0\n")
     r = run(driver, tmp_path / "incomplete.yaml", "--check-input")
     assert r.returncode == 1 and "lacks required keys: coordinate_file, target_temperature, total_steps" in r.stderr
+
+
+def test_bonded_terms_of_a_dsmd_input_system_are_accepted_and_those_of_a_legacy_topology_refused(driver, tmp_path):
+    s = syn.chain_fluid(3, 8, seed=5)
+    manifest = input_files.write_dsmd_input(str(tmp_path / "chains"), "chains", s.pos, ["C"] * s.n, s.types, ["CH3", "CH2"],
+                                            s.mass, s.charge, s.sig, s.eps, bonded=s.bonded)
+    common = dict(box=s.box, total_steps=10, timestep=0.5, temperature=300.0, cutoff=s.cutoff, skin=s.skin,
+                  extra={"real_space_only": "true"})
+    y = input_files.write_run_yaml(tmp_path / "chains.yaml", input_system=manifest,
+                                   force_type="lj, PME, bonds, angles, dihedrals", **common)
+    r = run(driver, y, "--check-input")
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout)
+    assert out["refused"] == [] and out["system"]["bonds"] == 27 * 7
+    assert out["config"]["enable_bonds"] and out["config"]["enable_angles"] and out["config"]["enable_dihedrals"]
+    y = input_files.write_run_yaml(tmp_path / "bonds_only.yaml", input_system=manifest, force_type="lj, bonds", **common)
+    cfg = json.loads(run(driver, y, "--check-input").stdout)["config"]
+    assert cfg["enable_bonds"] and not cfg["enable_angles"] and not cfg["enable_dihedrals"] and not cfg["enable_coulomb"]
+    legacy = input_cases.topology_cases(str(tmp_path / "cases"))["legacy_mixed"]       # a legacy .top with a [bonds] section
+    y = input_files.write_run_yaml(tmp_path / "legacy.yaml", coordinate_file=legacy["coordinate_file"],
+                                   topology_file=legacy["topology_file"], force_type="lj, bonds", **dict(common, box=legacy["box"]))
+    refused = json.loads(run(driver, y, "--check-input").stdout)["refused"]
+    assert any("legacy topology" in t for t in refused)

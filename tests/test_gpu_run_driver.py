@@ -129,3 +129,36 @@ def test_rigid_water_runs_as_md_from_the_reference_input_files(cuda_device, tmp_
     assert rows[0][1] == pytest.approx(300.0 * 9.0 / 6.0, rel=0.05)
     assert np.abs(rows[1:, 4] - rows[1, 4]).max() < 0.25 * rows[-1][2]
     assert int(re.search(r"Neighbor list builds = (\d+)", out).group(1)) >= 2
+
+
+def test_flexible_chains_run_from_dsmd_input_files(cuda_device, tmp_path):
+    """Bonded terms through the driver: flexible chains as a dsMD_input folder (bonds, angles, dihedrals, impropers and
+    special pairs with their parameter sections), force_calculation.type naming every kind. The potential energy printed
+    at step 0 is the pair energy plus the oracle's bonded energy, and the total energy holds over 200 steps of 0.5 fs."""
+    from deepscalemd_b200 import capi
+    from oracle import cpu_oracle as co
+    s = syn.chain_fluid(4, 8, spacing=14.0, seed=14)
+    pos = s.pos + (s.box / 2.0 - s.pos.mean(0))             # the reader centres the atoms in the box: write them so
+    manifest = input_files.write_dsmd_input(str(tmp_path / "chains"), "chains", pos, ["C"] * s.n, s.types, ["CH3", "CH2"],
+                                            s.mass, s.charge, s.sig, s.eps, bonded=s.bonded)
+    path = input_files.write_run_yaml(tmp_path / "chains.yaml", box=s.box, total_steps=200, timestep=0.5, temperature=300.0,
+                                      cutoff=s.cutoff, skin=s.skin, input_system=manifest,
+                                      force_type="lj, PME, bonds, angles, dihedrals", output_freq=50, update_freq=1000,
+                                      extra={"real_space_only": "true", "velocity_seed": "7"})
+    rows, out = run_driver(path)
+    assert [int(r[0]) for r in rows] == [0, 50, 100, 150, 200] and np.all(np.isfinite(rows))
+    _, bonded = co.bonded(pos, s.n, s.box, co.BondedTerms(**s.bonded), charge=s.charge)
+    ctx = capi.Context(s.n)
+    ctx.set_box(s.box)
+    ctx.set_pair_params(s.eps, s.sig, s.cutoff, s.skin)
+    ctx.set_coulomb(True)
+    ctx.set_exclusions(s.n, s.exclusions)
+    ctx.upload(pos, mass=s.mass, types=s.types, charge=s.charge)
+    ctx.build_neighbor_list()
+    ctx.compute_forces(capi.PHASE_FULL, want_energy=True)
+    pair = ctx.read_scalars()["pe"]
+    ctx.close()
+    assert bonded["pe"] > 10.0
+    assert rows[0][3] == pytest.approx(pair + bonded["pe"], rel=1e-5)
+    assert np.abs(rows[:, 4] - rows[0, 4]).max() < 0.02 * rows[0][2]
+    assert np.abs(rows[1:, 3] - rows[0, 3]).max() > 0.05 * rows[0][2]      # energy moves between kinetic and potential

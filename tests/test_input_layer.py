@@ -330,3 +330,40 @@ def test_dart_throw_keeps_the_minimum_distance_and_repeats_for_a_seed():
     with pytest.raises(input_api.InputError):
         input_api.dart_throw(1000, 10.0, 1.8, 1)                 # 1000 spheres of 1.8 A do not fit a 10 A cube
     assert input_api.dart_throw(50, 10.0, 0.0, 1).shape == (50, 3)
+
+
+def test_bonded_sections_of_a_dsmd_input_system_come_back_term_by_term(tmp_path):
+    """Flexible chains written as a dsMD_input folder: the reader returns every bond, angle, dihedral, improper and special
+    pair with its own parameters (angles and phases converted to radians, a harmonic improper as multiplicity 0), in the
+    form the device library takes; 1-2, 1-3 and 1-4 pairs become exclusions; a special pair whose parameter id is not
+    listed takes the pair matrix of its two atom types."""
+    s = syn.chain_fluid(3, 8, seed=5)
+    elements = ["C"] * s.n
+    manifest = input_files.write_dsmd_input(str(tmp_path / "chains"), "chains", s.pos, elements, s.types, ["CH3", "CH2"], s.mass,
+                                            s.charge, s.sig, s.eps, bonded=s.bonded)
+    folder = os.path.dirname(manifest)
+    files = dict(coordinate_file=os.path.join(folder, "chains.xyz"), topology_file=os.path.join(folder, "chains.dsMDtop"),
+                 parameter_file=os.path.join(folder, "chains.dsMDprm"), box=s.box)
+    system = input_api.System(**files)
+    got = system.bonded()
+    want = s.bonded
+    assert got["n_dihedrals"] == want["n_dihedrals"] == 27 * 5
+    for key in ("bonds", "angles", "torsions", "specials", "torsion_n"):
+        assert np.array_equal(got[key], np.asarray(want[key])), key
+    for key in ("bond_k", "bond_r0", "angle_k", "torsion_k", "special_sigma", "special_epsilon", "special_lj_scale",
+                "special_coulomb_scale"):
+        assert np.array_equal(got[key], want[key]), key
+    for key in ("angle_theta0", "torsion_phi0"):
+        assert np.abs(got[key] - want[key]).max() < 1e-14, key
+    assert (len(got["bonds"]), len(got["angles"]), len(got["torsions"]), len(got["specials"])) == (
+        27 * 7, 27 * 6, len(want["torsions"]), 27 * 5)
+    excl = {tuple(sorted(p)) for p in s.exclusions.tolist()}
+    assert {tuple(p) for p in system.exclusions().tolist()} == excl
+    # unlisted special-pair parameter id: the pair matrix stands in
+    text = open(os.path.join(folder, "chains.dsMDprm")).read()
+    head, tail = text.split("[special_pair_parameters]\n")
+    open(os.path.join(folder, "chains.dsMDprm"), "w").write(head + "[special_pair_parameters]\n" + "\n".join(tail.split("\n")[1:]))
+    again = input_api.System(**files).bonded()
+    i, j = want["specials"][0]
+    assert again["special_sigma"][0] == s.sig[s.types[i], s.types[j]] and again["special_epsilon"][0] == s.eps[s.types[i], s.types[j]]
+    assert np.array_equal(again["special_sigma"][1:], want["special_sigma"][1:])

@@ -328,3 +328,46 @@ def test_image_force_fold_and_virial_restatement():
     all_pos = np.stack([img["x"], img["y"], img["z"]], axis=1)
     v = co.virial_from_forces(all_pos, f)
     assert np.allclose(v[1:], (all_pos * f).sum(0), rtol=1e-12) and np.isclose(v[0], (all_pos * f).sum(), rtol=1e-12)
+
+
+@pytest.mark.skipif(not co.ref_available(), reason="oracle/_ref is not built")
+def test_bonded_terms_match_the_reference_routines():
+    """Bonds, angles, periodic and harmonic torsions (dihedrals and impropers) and scaled special pairs of the restatement
+    against the reference's own compute_bond_forces / compute_angle_forces / compute_torsion_forces /
+    compute_special_pair_forces (compiled in place) on flexible chains wrapped into a periodic box; then the ownership
+    rule: with only part of the atoms owned, owned atoms keep their forces and the energies of the two halves add up."""
+    s = syn.chain_fluid(4, 8, seed=11)
+    t = co.BondedTerms(**s.bonded)
+    assert len(t.bonds) == 64 * 7 and len(t.angles) == 64 * 6 and len(t.torsions) == 64 * 5 + 160 and t.n_dihedrals == 320
+    f, sc = co.bonded(s.pos, s.n, s.box, t, charge=s.charge)
+    ref = co.RefCase(s.pos[:, 0], s.pos[:, 1], s.pos[:, 2], s.n, s.box, s.cutoff, s.skin, charge=s.charge, types=s.types,
+                     eps=s.eps, sig=s.sig)
+    fr, rsc = ref.bonded(t)
+    ref.close()
+    scale = np.sqrt((fr * fr).sum(1).mean())
+    assert scale > 1.0
+    assert np.abs(f - fr).max() <= 1e-11 * scale
+    assert abs(sc["pe"] - rsc["pe"]) <= 1e-12 * abs(rsc["pe"])
+    assert abs(sc["virial"] - rsc["virial"]) <= 1e-11 * abs(rsc["virial"])
+    assert np.abs(sc["virial_diag"] - rsc["virial_diag"]).max() <= 1e-11 * np.abs(rsc["virial_diag"]).max()
+    assert np.abs(f.sum(0)).max() <= 1e-9 * scale                      # Newton's third law over all terms
+    # every kind of term contributes
+    for part in (dict(bonds=s.bonded["bonds"], bond_k=s.bonded["bond_k"], bond_r0=s.bonded["bond_r0"]),
+                 dict(angles=s.bonded["angles"], angle_k=s.bonded["angle_k"], angle_theta0=s.bonded["angle_theta0"]),
+                 dict(torsions=s.bonded["torsions"], torsion_k=s.bonded["torsion_k"], torsion_phi0=s.bonded["torsion_phi0"],
+                      torsion_n=s.bonded["torsion_n"]),
+                 dict(specials=s.bonded["specials"], special_sigma=s.bonded["special_sigma"],
+                      special_epsilon=s.bonded["special_epsilon"], special_lj_scale=s.bonded["special_lj_scale"],
+                      special_coulomb_scale=s.bonded["special_coulomb_scale"])):
+        fp, _ = co.bonded(s.pos, s.n, s.box, co.BondedTerms(**part), charge=s.charge)
+        assert np.sqrt((fp * fp).sum(1).mean()) > 1e-2
+    # ownership: the first 300 atoms owned (chains are cut), then the others owned (atoms reordered so that they come first)
+    n_a = 300
+    fa, sa = co.bonded(s.pos, n_a, s.box, t, charge=s.charge, gid=np.arange(s.n))
+    order = np.concatenate([np.arange(n_a, s.n), np.arange(n_a)])
+    inverse = np.argsort(order)
+    moved = {k: (inverse[v] if k in ("bonds", "angles", "torsions", "specials") else v) for k, v in s.bonded.items()}
+    fb, sb = co.bonded(s.pos[order], s.n - n_a, s.box, co.BondedTerms(**moved), charge=s.charge[order], gid=order)
+    assert np.abs(fa - f[:n_a]).max() <= 1e-12 * scale and np.abs(fb - f[n_a:]).max() <= 1e-12 * scale
+    assert abs(sa["pe"] + sb["pe"] - sc["pe"]) <= 1e-12 * abs(sc["pe"])
+    assert np.abs(sa["virial_diag"] + sb["virial_diag"] - sc["virial_diag"]).max() <= 1e-10 * np.abs(sc["virial_diag"]).max()
