@@ -171,7 +171,8 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
     std::map<std::string, Harmonic> bond_ids, angle_ids;
     std::map<std::string, Periodic> torsion_ids, improper_ids;
     std::map<int, std::pair<double, double>> special_ids;   // sigma, epsilon
-    const double degree = 3.14159265358979323846 / 180.0;
+    // degrees to radians as the reference writes it, (value * pi) / 180: the same roundings, the same bits
+    auto radians = [](double degrees) { return degrees * 3.14159265358979323846 / 180.0; };
     bool mie_seen = false;
     std::string line, section;
     size_t line_number = 0;
@@ -222,19 +223,19 @@ void apply_dsmd_input(const std::string& raw_topology, const std::string& raw_pa
             if (!bond_ids.emplace(t[0], Harmonic{k, r0}).second) fail("bond parameter id " + t[0] + " is given twice");
         } else if (section == "angle_parameters") {
             if (t.size() < 4 || t[1] != "harmonic") fail("angle parameters must read 'id harmonic k theta0' (degrees)");
-            const double k = to_real(t[2]), theta = to_real(t[3]) * degree;
+            const double k = to_real(t[2]), theta = radians(to_real(t[3]));
             if (!std::isfinite(k) || !std::isfinite(theta) || k < 0.0) fail("an angle needs a finite k >= 0 and a finite theta0");
             if (!angle_ids.emplace(t[0], Harmonic{k, theta}).second) fail("angle parameter id " + t[0] + " is given twice");
         } else if (section == "torsion_parameters") {
             if (t.size() < 5 || t[1] != "periodic") fail("torsion parameters must read 'id periodic k phase multiplicity' (phase in degrees)");
-            const double k = to_real(t[2]), phase = to_real(t[3]) * degree;
+            const double k = to_real(t[2]), phase = radians(to_real(t[3]));
             const int multiplicity = to_int(t[4]);
             if (!std::isfinite(k) || !std::isfinite(phase) || multiplicity <= 0) fail("a torsion needs finite k and phase and a multiplicity > 0");
             if (!torsion_ids.emplace(t[0], Periodic{k, phase, multiplicity}).second) fail("torsion parameter id " + t[0] + " is given twice");
         } else if (section == "improper_parameters") {
             if (t.size() < 4 || (t[1] != "periodic" && t[1] != "harmonic"))
                 fail("improper parameters must read 'id periodic k phase multiplicity' or 'id harmonic k phi0' (degrees)");
-            const double k = to_real(t[2]), phase = to_real(t[3]) * degree;
+            const double k = to_real(t[2]), phase = radians(to_real(t[3]));
             const int multiplicity = t[1] == "harmonic" ? 0 : (t.size() >= 5 ? to_int(t[4]) : -1);
             if (!std::isfinite(k) || !std::isfinite(phase) || k < 0.0 || (t[1] == "periodic" && multiplicity <= 0))
                 fail("an improper needs a finite k >= 0, a finite phase and, in the periodic form, a multiplicity > 0");

@@ -144,20 +144,19 @@ class System:
         _check(lib().dsmd_input_system_bonded(self.h, counts, atoms, pars, byref(mult)))
         nb, na, nt, nd, ns = (int(v) for v in counts)
 
-        def ints(p, n, width):
-            p = p.contents if hasattr(p, "contents") and not isinstance(p, POINTER(c_int32)) else p
-            return np.ctypeslib.as_array(p, shape=(n * width,)).copy().reshape(n, width) if n else np.zeros((0, width), np.int32)
+        def ints(k, n, width):
+            if n == 0:
+                return np.zeros((0, width), dtype=np.int32)
+            return np.ctypeslib.as_array(atom_ptrs[k], shape=(n * width,)).copy().reshape(n, width)
 
-        def reals(p, n):
-            return np.ctypeslib.as_array(p, shape=(n,)).copy() if n else np.zeros(0)
-        a = [atoms[k].contents for k in range(4)]
-        q = [pars[k].contents for k in range(10)]
-        return dict(bonds=ints(a[0], nb, 2), bond_k=reals(q[0], nb), bond_r0=reals(q[1], nb),
-                    angles=ints(a[1], na, 3), angle_k=reals(q[2], na), angle_theta0=reals(q[3], na),
-                    torsions=ints(a[2], nt, 4), torsion_k=reals(q[4], nt), torsion_phi0=reals(q[5], nt),
+        def reals(k, n):
+            return np.ctypeslib.as_array(par_ptrs[k], shape=(n,)).copy() if n else np.zeros(0)
+        return dict(bonds=ints(0, nb, 2), bond_k=reals(0, nb), bond_r0=reals(1, nb),
+                    angles=ints(1, na, 3), angle_k=reals(2, na), angle_theta0=reals(3, na),
+                    torsions=ints(2, nt, 4), torsion_k=reals(4, nt), torsion_phi0=reals(5, nt),
                     torsion_n=(np.ctypeslib.as_array(mult, shape=(nt,)).copy() if nt else np.zeros(0, np.int32)),
-                    n_dihedrals=nd, specials=ints(a[3], ns, 2), special_sigma=reals(q[6], ns), special_epsilon=reals(q[7], ns),
-                    special_lj_scale=reals(q[8], ns), special_coulomb_scale=reals(q[9], ns))
+                    n_dihedrals=nd, specials=ints(3, ns, 2), special_sigma=reals(6, ns), special_epsilon=reals(7, ns),
+                    special_lj_scale=reals(8, ns), special_coulomb_scale=reals(9, ns))
 
     def init_velocities(self, temperature, seed):
         _check(lib().dsmd_input_system_velocities(self.h, c_double(temperature), c_uint64(seed)))

@@ -18,6 +18,10 @@ struct Loaded {
     std::vector<int> type;
     std::vector<double> mass, charge, sigma, epsilon, pair_sigma, pair_epsilon, constraint_d;
     std::vector<int> exclusion_pairs, constraint_i, constraint_j;
+    // bonded terms with the parameters the reader resolved for each of them
+    std::vector<int> bond_atoms, angle_atoms, torsion_atoms, torsion_n, special_atoms;
+    std::vector<double> bond_par, angle_par, torsion_par, special_par;
+    long n_dihedrals = 0;
 };
 
 // The reference prints progress to std::cout / std::cerr: keep the test output clean.
@@ -49,6 +53,34 @@ void collect(Loaded& l) {
         l.constraint_i.push_back(c.atom1);
         l.constraint_j.push_back(c.atom2);
         l.constraint_d.push_back(c.distance);
+    }
+    for (const Bond& b : t.get_bonds()) {
+        const BondType& p = t.get_bond_type(b.type);
+        l.bond_atoms.insert(l.bond_atoms.end(), {b.atom1, b.atom2});
+        l.bond_par.insert(l.bond_par.end(), {p.k, p.r0});
+    }
+    for (const Angle& a : t.get_angles()) {
+        const AngleType& p = t.get_angle_type(a.type);
+        l.angle_atoms.insert(l.angle_atoms.end(), {a.atom1, a.atom2, a.atom3});
+        l.angle_par.insert(l.angle_par.end(), {p.k, p.theta0});
+    }
+    auto torsion = [&](const Dihedral& d) {
+        const DihedralType& p = t.get_dihedral_type(d.type);
+        l.torsion_atoms.insert(l.torsion_atoms.end(), {d.atom1, d.atom2, d.atom3, d.atom4});
+        l.torsion_par.insert(l.torsion_par.end(), {p.k, p.phi0});
+        l.torsion_n.push_back(p.n);
+    };
+    for (const Dihedral& d : t.get_dihedrals()) torsion(d);
+    l.n_dihedrals = static_cast<long>(t.get_dihedrals().size());
+    for (const Dihedral& d : t.get_impropers()) torsion(d);
+    for (const SpecialPair& p : t.get_special_pairs()) {
+        // sigma / epsilon below zero: the force routines look the pair matrix of the two atom types up
+        // (src/force_calculator_cpu.cpp:2820-2821); the same is done here
+        const int ti = t.get_atom_type_id(p.atom1), tj = t.get_atom_type_id(p.atom2);
+        const double sigma = p.sigma >= 0.0 ? p.sigma : t.get_pair_sigma()[ti][tj];
+        const double epsilon = p.epsilon >= 0.0 ? p.epsilon : t.get_pair_epsilon()[ti][tj];
+        l.special_atoms.insert(l.special_atoms.end(), {p.atom1, p.atom2});
+        l.special_par.insert(l.special_par.end(), {sigma, epsilon, p.lj_scale, p.coulomb_scale});
     }
 }
 
@@ -106,6 +138,28 @@ void dsmd_reftop_pairs(void* h, double* pair_sigma, double* pair_epsilon, int* e
     std::memcpy(constraint_i, l->constraint_i.data(), l->constraint_i.size() * sizeof(int));
     std::memcpy(constraint_j, l->constraint_j.data(), l->constraint_j.size() * sizeof(int));
     std::memcpy(constraint_d, l->constraint_d.data(), l->constraint_d.size() * sizeof(double));
+}
+
+// counts = {bonds, angles, torsions (dihedrals, then impropers), dihedrals, special pairs}
+void dsmd_reftop_bonded_counts(void* h, long counts[5]) {
+    auto* l = static_cast<Loaded*>(h);
+    counts[0] = static_cast<long>(l->bond_atoms.size() / 2);
+    counts[1] = static_cast<long>(l->angle_atoms.size() / 3);
+    counts[2] = static_cast<long>(l->torsion_n.size());
+    counts[3] = l->n_dihedrals;
+    counts[4] = static_cast<long>(l->special_atoms.size() / 2);
+}
+
+// atoms: 2, 3, 4, 2 ids per term; parameters: (k, r0), (k, theta0), (k, phi0), (sigma, epsilon, LJ scale, Coulomb scale).
+void dsmd_reftop_bonded(void* h, int* bond_atoms, double* bond_par, int* angle_atoms, double* angle_par, int* torsion_atoms,
+                        double* torsion_par, int* torsion_n, int* special_atoms, double* special_par) {
+    auto* l = static_cast<Loaded*>(h);
+    auto copy_i = [](int* dst, const std::vector<int>& v) { if (!v.empty()) std::memcpy(dst, v.data(), v.size() * sizeof(int)); };
+    auto copy_d = [](double* dst, const std::vector<double>& v) { if (!v.empty()) std::memcpy(dst, v.data(), v.size() * sizeof(double)); };
+    copy_i(bond_atoms, l->bond_atoms); copy_d(bond_par, l->bond_par);
+    copy_i(angle_atoms, l->angle_atoms); copy_d(angle_par, l->angle_par);
+    copy_i(torsion_atoms, l->torsion_atoms); copy_d(torsion_par, l->torsion_par); copy_i(torsion_n, l->torsion_n);
+    copy_i(special_atoms, l->special_atoms); copy_d(special_par, l->special_par);
 }
 
 }  // extern "C"

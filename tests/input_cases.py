@@ -67,6 +67,15 @@ def topology_cases(folder):
                                parameter_file=os.path.join(sub, "water.dsMDprm"),
                                coordinate_file=os.path.join(sub, "water.xyz"), box=np.asarray(w.box), n=w.n,
                                manifest=os.path.join(sub, "manifest.yaml"))
+    # 5. dsMD_input: flexible chains with every bonded section (each term with a parameter id of its own)
+    c = syn.chain_fluid(3, 8, seed=5)
+    sub = os.path.join(folder, "chains")
+    input_files.write_dsmd_input(sub, "chains", c.pos, ["C"] * c.n, c.types, ["CH3", "CH2"], c.mass, c.charge, np.asarray(c.sig),
+                                 np.asarray(c.eps), bonded=c.bonded)
+    cases["dsmd_chains"] = dict(topology_file=os.path.join(sub, "chains.dsMDtop"),
+                                parameter_file=os.path.join(sub, "chains.dsMDprm"),
+                                coordinate_file=os.path.join(sub, "chains.xyz"), box=np.asarray(c.box), n=c.n,
+                                manifest=os.path.join(sub, "manifest.yaml"))
     return cases
 
 
@@ -97,8 +106,19 @@ def reference_topology(topology_file, parameter_file=None):
     ci, cj = np.zeros(max(cons.value, 1), dtype=np.int32), np.zeros(max(cons.value, 1), dtype=np.int32)
     cd = np.zeros(max(cons.value, 1))
     L.dsmd_reftop_pairs(h, dp(ps), dp(pe), ip(ex), ip(ci), ip(cj), dp(cd))
+    counts = (ctypes.c_long * 5)()
+    L.dsmd_reftop_bonded_counts(h, counts)
+    nb, na, nt, nd, ns = (int(v) for v in counts)
+    ib = lambda k: np.zeros(max(k, 1), dtype=np.int32)
+    db = lambda k: np.zeros(max(k, 1))
+    ba, bp, aa, ap, ta, tp, tn, sa, sp = ib(2 * nb), db(2 * nb), ib(3 * na), db(2 * na), ib(4 * nt), db(2 * nt), ib(nt), ib(2 * ns), db(4 * ns)
+    L.dsmd_reftop_bonded(h, ip(ba), dp(bp), ip(aa), dp(ap), ip(ta), dp(tp), ip(tn), ip(sa), dp(sp))
+    bonded = dict(counts=[nb, na, nt, nd, ns], bond_atoms=ba[:2 * nb].tolist(), bond_par=bp[:2 * nb].tolist(),
+                  angle_atoms=aa[:3 * na].tolist(), angle_par=ap[:2 * na].tolist(), torsion_atoms=ta[:4 * nt].tolist(),
+                  torsion_par=tp[:2 * nt].tolist(), torsion_n=tn[:nt].tolist(), special_atoms=sa[:2 * ns].tolist(),
+                  special_par=sp[:4 * ns].tolist())
     L.dsmd_reftop_destroy(h)
-    return dict(atoms=n, type=type_.tolist(), mass=mass.tolist(), charge=charge.tolist(), sigma=sigma.tolist(),
+    return dict(bonded=bonded, atoms=n, type=type_.tolist(), mass=mass.tolist(), charge=charge.tolist(), sigma=sigma.tolist(),
                 epsilon=eps.tolist(), pair_sigma=ps[:entries.value].tolist(), pair_epsilon=pe[:entries.value].tolist(),
                 exclusions=ex[:2 * excl.value].tolist(), constraint_i=ci[:cons.value].tolist(),
                 constraint_j=cj[:cons.value].tolist(), constraint_d=cd[:cons.value].tolist(), mie=[mn.value, mm.value])

@@ -155,9 +155,21 @@ def compare_with_reference(system, want):
     assert np.array_equal(ci, np.array(want["constraint_i"], dtype=np.int32))
     assert np.array_equal(cj, np.array(want["constraint_j"], dtype=np.int32))
     assert np.array_equal(cd, np.array(want["constraint_d"]))
+    if c["explicit_pairs"] and "bonded" in want:      # dsMD_input: every bonded term with the parameters resolved for it
+        b, got = want["bonded"], system.bonded()
+        assert [len(got["bonds"]), len(got["angles"]), len(got["torsions"]), got["n_dihedrals"], len(got["specials"])] == b["counts"]
+        for mine, atoms in (("bonds", "bond_atoms"), ("angles", "angle_atoms"), ("torsions", "torsion_atoms"),
+                            ("specials", "special_atoms")):
+            assert np.array_equal(got[mine].ravel(), np.array(b[atoms], dtype=np.int32)), mine
+        assert np.array_equal(np.stack([got["bond_k"], got["bond_r0"]], 1).ravel(), np.array(b["bond_par"]))
+        assert np.array_equal(np.stack([got["angle_k"], got["angle_theta0"]], 1).ravel(), np.array(b["angle_par"]))
+        assert np.array_equal(np.stack([got["torsion_k"], got["torsion_phi0"]], 1).ravel(), np.array(b["torsion_par"]))
+        assert np.array_equal(got["torsion_n"], np.array(b["torsion_n"], dtype=np.int32))
+        assert np.array_equal(np.stack([got["special_sigma"], got["special_epsilon"], got["special_lj_scale"],
+                                        got["special_coulomb_scale"]], 1).ravel(), np.array(b["special_par"]))
 
 
-@pytest.mark.parametrize("name", ["legacy_argon", "legacy_mixed", "dsmd_binary", "dsmd_water"])
+@pytest.mark.parametrize("name", ["legacy_argon", "legacy_mixed", "dsmd_binary", "dsmd_water", "dsmd_chains"])
 def test_topology_readers_match_the_reference_reader(tmp_path, name):
     case = input_cases.topology_cases(str(tmp_path))[name]
     system = input_api.System(coordinate_file=case["coordinate_file"], topology_file=case["topology_file"],
@@ -172,6 +184,8 @@ def test_topology_readers_match_the_reference_reader(tmp_path, name):
     if name == "dsmd_water":
         c = system.counts()
         assert c["exclusions"] == 81 and c["constraints"] == 81
+    if name == "dsmd_chains":
+        assert len(system.bonded()["bonds"]) == 27 * 7 and len(system.bonded()["specials"]) == 27 * 5
 
 
 def test_coordinates_are_recentred_into_the_box(tmp_path):
