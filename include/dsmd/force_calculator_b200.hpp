@@ -157,6 +157,7 @@ public:
         if (nlist_dirty_) build_neighbor_list_on_device(system);
         else check(ctx_, dsmd_pack_positions(ctx_, 0, total(), force_stream_), "dsmd_pack_positions");
         check(ctx_, dsmd_compute_forces(ctx_, DSMD_PHASE_FULL, energy_needed_ ? 1 : 0, force_stream_), "dsmd_compute_forces");
+        if (bonded_) check(ctx_, dsmd_compute_bonded(ctx_, force_stream_), "dsmd_compute_bonded");
         if (energy_needed_) read_scalars();
     }
     bool supports_overlapped_forces(MDSystem&) const { return true; }
@@ -166,6 +167,7 @@ public:
     }
     void finish_forces_boundary(MDSystem&) {
         check(ctx_, dsmd_compute_forces(ctx_, DSMD_PHASE_BOUNDARY, energy_needed_ ? 1 : 0, force_stream_), "boundary");
+        if (bonded_) check(ctx_, dsmd_compute_bonded(ctx_, force_stream_), "dsmd_compute_bonded");   // ghost positions are in
         if (energy_needed_) read_scalars();
     }
     void make_force_stream_wait_for_halo() {
@@ -248,7 +250,55 @@ private:
             }
             check(ctx_, dsmd_set_exclusions(ctx_, system.get_topology().get_num_atoms(), static_cast<int64_t>(keys.size()),
                                             a.data(), c.data()), "dsmd_set_exclusions");
+            upload_bonded_terms(system);
         }
+    }
+    // The bonded terms of the whole topology, by global atom id, each with the parameters of its type (what the
+    // reference copies per rank from MDSystem::get_local_bonds() ... get_local_special_pairs(), include/md_system.h:162-166;
+    // here every rank holds the whole table and evaluates the terms one of whose atoms it owns). Each kind follows its
+    // switch in the force configuration; special pairs run with the pair forces (src/force_calculator_cpu.cpp:792-815).
+    void upload_bonded_terms(MDSystem& system) {
+        const Topology& t = system.get_topology();
+        const auto& cfg = system.get_force_manager().get_config();
+        const ForceFieldParams& ff = system.get_ff_params();
+        std::vector<int32_t> ba, aa, ta, tn, sa;
+        std::vector<double> bk, br, ak, at, tk, tp, ss, se, sl, sc;
+        if (cfg.enable_bonds)
+            for (const Bond& b : t.get_bonds()) {
+                const BondType& p = t.get_bond_type(b.type);
+                ba.insert(ba.end(), {b.atom1, b.atom2});
+                bk.push_back(p.k); br.push_back(p.r0);
+            }
+        if (cfg.enable_angles)
+            for (const Angle& a : t.get_angles()) {
+                const AngleType& p = t.get_angle_type(a.type);
+                aa.insert(aa.end(), {a.atom1, a.atom2, a.atom3});
+                ak.push_back(p.k); at.push_back(p.theta0);
+            }
+        if (cfg.enable_dihedrals) {
+            auto torsion = [&](const Dihedral& d) {
+                const DihedralType& p = t.get_dihedral_type(d.type);
+                ta.insert(ta.end(), {d.atom1, d.atom2, d.atom3, d.atom4});
+                tk.push_back(p.k); tp.push_back(p.phi0); tn.push_back(p.n);
+            };
+            for (const Dihedral& d : t.get_dihedrals()) torsion(d);
+            for (const Dihedral& d : t.get_impropers()) torsion(d);
+        }
+        if (cfg.enable_lennard_jones || cfg.enable_coulomb)
+            for (const SpecialPair& p : t.get_special_pairs()) {
+                const int ti = t.get_atom_type_id(p.atom1), tj = t.get_atom_type_id(p.atom2);
+                sa.insert(sa.end(), {p.atom1, p.atom2});
+                ss.push_back(p.sigma >= 0.0 ? p.sigma : ff.sigma_mixed[ti][tj]);
+                se.push_back(!cfg.enable_lennard_jones ? 0.0 : (p.epsilon >= 0.0 ? p.epsilon : ff.epsilon_mixed[ti][tj]));
+                sl.push_back(p.lj_scale);
+                sc.push_back(cfg.enable_coulomb ? p.coulomb_scale : 0.0);
+            }
+        bonded_ = !bk.empty() || !ak.empty() || !tk.empty() || !ss.empty();
+        check(ctx_, dsmd_set_bonded(ctx_, t.get_num_atoms(), static_cast<int64_t>(bk.size()), ba.data(), bk.data(), br.data(),
+                                    static_cast<int64_t>(ak.size()), aa.data(), ak.data(), at.data(),
+                                    static_cast<int64_t>(tk.size()), ta.data(), tk.data(), tp.data(), tn.data(),
+                                    static_cast<int64_t>(ss.size()), sa.data(), ss.data(), se.data(), sl.data(), sc.data()),
+              "dsmd_set_bonded");
     }
     void read_scalars() {
         double s[6];
@@ -256,6 +306,13 @@ private:
         last_potential_energy = s[0];        // this rank's share; MDSimulation reduces through CommBackend::sum_reduce
         last_virial = s[1];
         for (int a = 0; a < 3; ++a) last_virial_diag[a] = s[2 + a];
+        if (bonded_) {
+            double b[5];
+            check(ctx_, dsmd_read_bonded_scalars(ctx_, b, force_stream_), "dsmd_read_bonded_scalars");
+            last_potential_energy += b[0];
+            last_virial += b[1];
+            for (int a = 0; a < 3; ++a) last_virial_diag[a] += b[2 + a];
+        }
     }
 
 public:
@@ -268,6 +325,7 @@ private:
     cudaStream_t force_stream_ = nullptr, halo_stream_ = nullptr;
     cudaEvent_t halo_done_ = nullptr;
     bool energy_needed_ = true;
+    bool bonded_ = false;
     Real verlet_skin_ = 2.0;
 };
 

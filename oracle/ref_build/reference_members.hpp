@@ -48,6 +48,7 @@ Topology::~Topology() = default;
 inline std::vector<BondType> g_ref_bond_types;
 inline std::vector<AngleType> g_ref_angle_types;
 inline std::vector<DihedralType> g_ref_dihedral_types;
+int Topology::get_atom_type_id(int atom_id) const { return atom_type_ids.at(static_cast<size_t>(atom_id)); }
 const BondType& Topology::get_bond_type(int id) const { return g_ref_bond_types.at(static_cast<size_t>(id)); }
 const AngleType& Topology::get_angle_type(int id) const { return g_ref_angle_types.at(static_cast<size_t>(id)); }
 const DihedralType& Topology::get_dihedral_type(int id) const { return g_ref_dihedral_types.at(static_cast<size_t>(id)); }

@@ -46,3 +46,16 @@ def test_product_does_not_reach_the_oracle():
                 if f.endswith((".py", ".cu", ".cuh", ".hpp", ".h", ".cpp")):
                     text = open(os.path.join(base, f)).read()
                     assert "cpu_oracle" not in text and "dsmd_oracle" not in text and "oracle/" not in text, f
+
+
+def test_adapter_check_library_resolves_every_symbol():
+    """The C++ adapters compiled against the reference's headers (oracle/_ref/libdsmd_adapter_check.so, what the GPU
+    adapter tests drive) load without an unresolved symbol: no compute call is made."""
+    import ctypes
+    import os
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(here, "oracle", "_ref", "libdsmd_adapter_check.so")
+    if not os.path.exists(path):
+        import pytest
+        pytest.skip("adapter check library not built (needs the reference headers)")
+    ctypes.CDLL(path, mode=os.RTLD_NOW)
