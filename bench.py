@@ -311,9 +311,9 @@ def single_gpu(args):
     ctx.compute_forces(capi.PHASE_FULL, True, stream)
     p_cut = ctx.read_scalars(stream)["pairs_in_cutoff"]
     p_list = stats["directed_entries"] / 2
-    t_pair = time_calls(lambda: ctx.compute_forces(capi.PHASE_FULL, False, stream), 20, stream)
-    t_pack = time_calls(lambda: ctx.pack_positions(0, None, stream), 20, stream)
-    t_build = time_calls(lambda: ctx.build_neighbor_list(stream), 5, stream)
+    t_pair = time_calls(lambda: ctx.compute_forces(capi.PHASE_FULL, False, stream), 100, stream)
+    t_pack = time_calls(lambda: ctx.pack_positions(0, None, stream), 100, stream)
+    t_build = time_calls(lambda: ctx.build_neighbor_list(stream), 20, stream)
     flops = ctx.fma_probe(1, stream)
     iters = 20000
     t_probe = time_calls(lambda: ctx.fma_probe(iters, stream), 3, stream)
@@ -333,13 +333,13 @@ def single_gpu(args):
     }
     # radius-graph edge build on the 1,000,000-atom disordered solid (cutoff 5 A): compact periodic form, and the
     # reference's interface form (int64 [2, E] + double [E, 3]) over explicit image atoms
-    if args.workload == "lj_4m":
+    if args.workload == "lj_4m" or args.edges:
         from deepscalemd_b200 import synthetic as syn
         solid = syn.disordered_solid(1_000_000)
         sx, sy, sz = (torch.tensor(np.ascontiguousarray(solid.pos[:, k]), device="cuda") for k in range(3))
         eb = capi.EdgeBuilder()
         eb.build_periodic(sx, sy, sz, solid.box, solid.cutoff, stream)
-        t_compact = time_calls(lambda: eb.build_periodic(sx, sy, sz, solid.box, solid.cutoff, stream), 5, stream)
+        t_compact = time_calls(lambda: eb.build_periodic(sx, sy, sz, solid.box, solid.cutoff, stream), 20, stream)
         n_edges = int(eb.build_periodic(sx, sy, sz, solid.box, solid.cutoff, stream)[0].numel())
         reach = solid.cutoff + 1e-8
         img = eb.images(sx, sy, sz, None, solid.box, np.zeros(3), -np.full(3, reach), solid.box + reach, (1, 1, 1), stream)
@@ -352,7 +352,7 @@ def single_gpu(args):
                             stream=stream)
 
         interface_build()
-        t_interface = time_calls(interface_build, 5, stream)
+        t_interface = time_calls(interface_build, 20, stream)
         e_interface = int(interface_build()[0].shape[1])
         compact_bytes = 24.0 * solid.n + 23.0 * n_edges
         interface_bytes = 24.0 * img["n_all"] + 40.0 * e_interface
@@ -383,8 +383,8 @@ def single_gpu(args):
             c2.compute_forces(capi.PHASE_FULL, True, stream)
             cut2 = c2.read_scalars(stream)["pairs_in_cutoff"]
             list2 = st2["directed_entries"] / 2
-            tp = time_calls(lambda: c2.compute_forces(capi.PHASE_FULL, False, stream), 10, stream)
-            tb = time_calls(lambda: c2.build_neighbor_list(stream), 3, stream)
+            tp = time_calls(lambda: c2.compute_forces(capi.PHASE_FULL, False, stream), 50, stream)
+            tb = time_calls(lambda: c2.build_neighbor_list(stream), 10, stream)
             fl = 8.0 * list2 + (19.0 + (9.0 if coulomb else 0.0)) * cut2
             by = 16.0 * system.n + 4.0 * list2 + 24.0 * system.n + (4.0 * system.n if coulomb else 0.0)
             bb = 16.0 * system.n + 4.0 * list2 + 8.0 * system.n / 32
@@ -479,6 +479,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="lj_4m")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--edges", action="store_true",
+                    help="time the radius-graph build of the 1,000,000-atom solid with a smaller --workload too (it always runs with lj_4m)")
     ap.add_argument("--cpu-budget-s", type=float, default=170.0,
                     help="time the reference arm may take: it runs the 4,000,000-atom system when that fits, else a smaller sample")
     args = ap.parse_args()

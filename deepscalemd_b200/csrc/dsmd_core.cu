@@ -118,10 +118,11 @@ __global__ void k_reorder(Grid g, int first, int n_owned, int n_total, const uns
     p.z = static_cast<int>(dsmd::to_fixed(r[2], 2, g, bad));
     p.w = ty;
     pq[s] = p;
-    // the list search's copy: single-precision offsets from the grid origin (the value of the fixed-point coordinate)
+    // the list search's copy: single-precision offsets from the grid origin (the value of the fixed-point coordinate);
+    // the fourth word carries the global id, so that the exclusion test of a hit needs no second gather
     pf[s] = make_float4(__uint2float_rn(static_cast<unsigned>(p.x)) * g.scale[0],
                         __uint2float_rn(static_cast<unsigned>(p.y)) * g.scale[1],
-                        __uint2float_rn(static_cast<unsigned>(p.z)) * g.scale[2], 0.f);
+                        __uint2float_rn(static_cast<unsigned>(p.z)) * g.scale[2], __int_as_float(gid_src[from]));
     qf[s] = static_cast<float>(r[10]);
     if (s < n_owned) {
         xref[s] = r[0];
@@ -337,7 +338,7 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
                                     if (!within_list_fp64(g, x, y, z, i, s)) continue;
                                 }
                                 if (ex_end > ex_begin) {
-                                    const int gj = gid[s];
+                                    const int gj = __float_as_int(c.w);
                                     for (int e = ex_begin; e < ex_end; ++e)
                                         if (excl.partners[e] == gj) entry |= kExclBit;
                                 }

@@ -205,14 +205,18 @@ __device__ __forceinline__ int owner_lane(int t, int my_prefix) {
 
 // Interface form. A warp takes 32 consecutive sorted slots and streams their edges out in flat order, so that the
 // three output arrays are written with contiguous, coalesced stores.
-__global__ void k_edge_fill(int n, long long n_edges, int stride, const int4* __restrict__ pq,
+__global__ void __launch_bounds__(kThreads) k_edge_fill(int n, long long n_edges, int stride, const int4* __restrict__ pq,
                             const unsigned* __restrict__ rows, const int* __restrict__ counts,
                             const long long* __restrict__ offsets, int n_centers, const int* __restrict__ owner,
                             const double* __restrict__ shift_x, const double* __restrict__ shift_y,
                             const double* __restrict__ shift_z, long long* __restrict__ edges,
                             double* __restrict__ shift) {
+    // the three shift components of 32 edges are 96 consecutive doubles of the output: they pass through shared memory
+    // so that the warp stores them as three unit-stride runs instead of three runs of stride 24 bytes
+    __shared__ double stage[kThreads / 32][96];
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
+    double* mine = stage[threadIdx.x >> 5];
     const int p = warp * 32 + lane;
     if (warp * 32 >= n) return;
     const int cnt = p < n ? counts[p] : 0;
@@ -241,10 +245,17 @@ __global__ void k_edge_fill(int n, long long n_edges, int stride, const int4* __
             edges[o] = c_centre;
             edges[n_edges + o] = image ? owner[nb] : nb;
             if (shift) {
-                shift[3 * o] = image ? shift_x[nb] : 0.0;
-                shift[3 * o + 1] = image ? shift_y[nb] : 0.0;
-                shift[3 * o + 2] = image ? shift_z[nb] : 0.0;
+                mine[3 * lane] = image ? shift_x[nb] : 0.0;
+                mine[3 * lane + 1] = image ? shift_y[nb] : 0.0;
+                mine[3 * lane + 2] = image ? shift_z[nb] : 0.0;
             }
+        }
+        if (shift) {
+            __syncwarp();
+            const int filled = 3 * min(32, total - t0);
+            double* out = shift + 3 * (out0 + t0);
+            for (int q = lane; q < filled; q += 32) out[q] = mine[q];
+            __syncwarp();
         }
     }
 }
@@ -254,12 +265,18 @@ __global__ void k_edge_fill(int n, long long n_edges, int stride, const int4* __
 // order of the interface form). Rows hold neighbour slots, so positions and wrap counts are read where they lie
 // whatever the caller's atom numbering. Displacements come from the fixed-point coordinates (resolution box / 2^32);
 // the lattice shift refers to the caller's coordinates: x[dst] + shift * box - x[src] = vec.
-__global__ void k_edge_fill_compact(Grid g, int n, int stride, const int4* __restrict__ pq, const int* __restrict__ wraps,
-                                    const unsigned* __restrict__ rows, const int* __restrict__ counts,
-                                    const long long* __restrict__ offsets, int* __restrict__ src, int* __restrict__ dst,
-                                    signed char* __restrict__ shift, float* __restrict__ vec) {
+__global__ void __launch_bounds__(kThreads) k_edge_fill_compact(
+    Grid g, int n, int stride, const int4* __restrict__ pq, const int* __restrict__ wraps,
+    const unsigned* __restrict__ rows, const int* __restrict__ counts, const long long* __restrict__ offsets,
+    int* __restrict__ src, int* __restrict__ dst, signed char* __restrict__ shift, float* __restrict__ vec) {
+    // shift bytes and vector components of 32 edges are 96 consecutive bytes / floats of the output: staged in shared
+    // memory and stored as unit-stride runs
+    __shared__ float stage_vec[kThreads / 32][96];
+    __shared__ signed char stage_shift[kThreads / 32][96];
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
+    float* my_vec = stage_vec[threadIdx.x >> 5];
+    signed char* my_shift = stage_shift[threadIdx.x >> 5];
     const int p = warp * 32 + lane;
     if (warp * 32 >= n) return;
     int4 pi = make_int4(0, 0, 0, 0);
@@ -301,12 +318,21 @@ __global__ void k_edge_fill_compact(Grid g, int n, int stride, const int4* __res
                 const long long plain = static_cast<long long>(static_cast<unsigned>(cj[a])) -
                                         static_cast<long long>(static_cast<unsigned>(ci[a]));
                 const int image = static_cast<int>((static_cast<long long>(nearest) - plain) >> 32);
-                shift[3 * o + a] = static_cast<signed char>(image - (wrap_field(wj, a) - wrap_field(c_wraps, a)));
-                vec[3 * o + a] = static_cast<float>(static_cast<double>(nearest) * unit[a]);
+                my_shift[3 * lane + a] = static_cast<signed char>(image - (wrap_field(wj, a) - wrap_field(c_wraps, a)));
+                my_vec[3 * lane + a] = static_cast<float>(static_cast<double>(nearest) * unit[a]);
             }
             src[o] = ci[3];
             dst[o] = pj.w;
         }
+        __syncwarp();
+        const int filled = 3 * min(32, total - t0);
+        float* out_vec = vec + 3 * (out0 + t0);
+        signed char* out_shift = shift + 3 * (out0 + t0);
+        for (int q = lane; q < filled; q += 32) {
+            out_vec[q] = my_vec[q];
+            out_shift[q] = my_shift[q];
+        }
+        __syncwarp();
     }
 }
 
