@@ -967,6 +967,9 @@ int dsmd_domain_run(dsmd_domain* d, int64_t n_steps, double dt, double force_to_
             DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_BOUNDARY, 0, s));
             mark(4);
         }
+        // bonded terms (none set: returns at once): ghost positions are current after the boundary pass; a term is
+        // evaluated on every rank that owns one of its atoms, forces go to owned atoms only
+        DOM_CTX(d, dsmd_compute_bonded(d->ctx, s));
         if (step + 1 == n_steps) DOM_CTX(d, dsmd_integrate(d->ctx, 2, dt, force_to_accel, s));
         mark(5);
         if (d->profile) {

@@ -157,6 +157,111 @@ def worker_native(rank, world, port, steps, dt, out_path):
     dist.destroy_process_group()
 
 
+def chain_system():
+    return syn.chain_fluid(4, 8, spacing=14.0, seed=14)      # 64 flexible chains, box 56 A
+
+
+def chain_setup(ctx, s, n_global):
+    ctx.set_pair_params(s.eps, s.sig, s.cutoff, s.skin)
+    ctx.set_coulomb(True)
+    ctx.set_exclusions(n_global, s.exclusions)
+    ctx.set_bonded(n_global, s.bonded)
+
+
+def worker_chains(rank, world, port, steps, dt, out_path):
+    """Flexible chains over two bricks: pair and bonded forces of the first evaluation, then `steps` steps of the native loop."""
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch.distributed as dist
+    from deepscalemd_b200 import capi, domain
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    s = chain_system()
+    dec = domain.Decomposition(s.box, world, rank)
+    mine = np.nonzero(dec.owner_of(s.pos) == rank)[0]
+    halo = s.cutoff + s.skin
+    ctx = capi.Context(s.n * 2, device=rank)
+    lo = [dec.lo[a] if dec.split[a] else 0.0 for a in range(3)]
+    hi = [dec.hi[a] if dec.split[a] else 0.0 for a in range(3)]
+    ctx.set_box(s.box, (1, 1, 1), lo, hi, halo + 2 * s.skin)
+    chain_setup(ctx, s, s.n)
+    wrapped = s.pos - s.box * np.floor(s.pos / s.box)
+    ctx.upload(wrapped[mine], vel=s.vel[mine], mass=s.mass[mine], types=s.types[mine], charge=s.charge[mine],
+               gid=mine.astype(np.int32))
+    uid = [capi.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    dom = capi.Domain(ctx, rank, world, dec.dims, s.box, halo, s.skin, uid[0])
+    dom.rebuild()
+
+    def energies():
+        ctx.compute_forces(capi.PHASE_FULL, True)
+        ctx.compute_bonded()
+        v = torch.tensor([ctx.read_scalars()["pe"], ctx.read_bonded_scalars()["pe"], ctx.kinetic_energy() / s.force_to_accel],
+                         dtype=torch.float64)
+        dist.all_reduce(v)
+        return v.tolist()
+
+    first = energies()
+    n_owned, _ = ctx.counts()
+    result = dict(first=first, gid_first=ctx.download("global_id", n_owned),
+                  f_first=np.stack([ctx.download(k, n_owned) for k in ("fx", "fy", "fz")], axis=1))
+    dom.run(steps, dt, s.force_to_accel, 0.5)
+    torch.cuda.synchronize()
+    result["last"] = energies()
+    result["rebuilds"] = dom.stats()["rebuilds"]
+    gathered = [None] * world
+    dist.all_gather_object(gathered, result)
+    if rank == 0:
+        torch.save(gathered, out_path)
+    dom.close()
+    ctx.close()
+    dist.destroy_process_group()
+
+
+def test_bonded_terms_on_two_gpus_equal_one_gpu(tmp_path):
+    """Flexible chains cut by a brick boundary: the first evaluation's forces (pair + bonded) and energies equal the
+    one-GPU values, and after 100 steps of the native loop the two runs' energies still agree (terms that cross the
+    boundary are evaluated on both ranks, each keeping the forces of its own atoms)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    from deepscalemd_b200 import capi
+    steps, dt = 100, 0.5
+    out = str(tmp_path / "chains.pt")
+    run_ranks(worker_chains, (2, free_port(), steps, dt, out), 2)
+    parts = torch.load(out, weights_only=False)
+    s = chain_system()
+    ctx = capi.Context(s.n)
+    ctx.set_box(s.box)
+    chain_setup(ctx, s, s.n)
+    ctx.upload(s.pos, vel=s.vel, mass=s.mass, types=s.types, charge=s.charge)
+    ctx.build_neighbor_list()
+
+    def energies():
+        ctx.compute_forces(capi.PHASE_FULL, True)
+        ctx.compute_bonded()
+        return [ctx.read_scalars()["pe"], ctx.read_bonded_scalars()["pe"], ctx.kinetic_energy() / s.force_to_accel]
+
+    want = energies()
+    gid = ctx.download("global_id", s.n)
+    f_want = np.empty((s.n, 3))
+    f_want[gid] = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
+    f_got = np.empty_like(f_want)
+    for p in parts:
+        f_got[p["gid_first"]] = p["f_first"]
+    rms = lambda a: np.sqrt((a * a).sum(1).mean())
+    assert rms(f_got - f_want) <= 1e-5 * rms(f_want)
+    got = parts[0]["first"]
+    assert abs(got[0] - want[0]) <= 1e-5 * abs(want[1]) and abs(got[1] - want[1]) <= 1e-10 * abs(want[1])
+    assert abs(got[2] - want[2]) <= 1e-10 * want[2]
+    ctx.run_nve(steps, dt, s.force_to_accel, 0.5, 0, True)
+    after = energies()
+    last = parts[0]["last"]
+    total0 = sum(want)
+    assert abs(sum(last) - total0) < 0.02 * want[2] and abs(sum(after) - total0) < 0.02 * want[2]
+    assert abs(last[1] - after[1]) < 0.05 * want[2]          # the same physics: bonded energy after 100 steps agrees closely
+    assert abs(after[1] - want[1]) > 0.05 * want[2]
+    ctx.close()
+
+
 @pytest.mark.parametrize("which", ["torch_distributed", "native"])
 def test_two_gpus_equal_the_undivided_system(tmp_path, which):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
