@@ -394,6 +394,14 @@ def single_gpu(args):
                                 "gbs": by / (tp * 1e-3) / 1e9, "frac_hbm": by / (tp * 1e-3) / 1e9 / hbm_peak},
                 "list_build_total": {"ms": tb, "gbs": bb / (tb * 1e-3) / 1e9, "frac_hbm": bb / (tb * 1e-3) / 1e9 / hbm_peak},
             }
+            if coulomb:
+                # the charges of this system are a function of the atom type (O, H): the table form of the kernel
+                by_type = [float(system.charge[system.types == t][0]) for t in range(int(system.types.max()) + 1)]
+                c2.set_type_charges(by_type)
+                tq = time_calls(lambda: c2.compute_forces(capi.PHASE_FULL, False, stream), 50, stream)
+                kernels[name]["pair_forces_charges_by_type"] = {
+                    "ms": tq, "tflops": fl / (tq * 1e-3) / 1e12, "frac_fp32": fl / (tq * 1e-3) / 1e12 / fp32_peak_tflops,
+                    "note": "dsmd_set_type_charges: partner charges from a table in shared memory instead of a gather"}
             c2.close()
     pk = kernels["pair_forces"]
     sms = torch.cuda.get_device_properties(0).multi_processor_count

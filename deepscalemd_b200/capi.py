@@ -23,7 +23,7 @@ FIELD_ID = {name: k for k, name in enumerate(FIELDS)}
 SYMBOLS = [
     "dsmd_create", "dsmd_destroy", "dsmd_last_error", "dsmd_set_box", "dsmd_set_pair_params", "dsmd_set_coulomb",
     "dsmd_get_ewald_alpha", "dsmd_set_exclusions", "dsmd_set_constraints", "dsmd_constraint_failures", "dsmd_rattle",
-    "dsmd_set_bonded", "dsmd_compute_bonded", "dsmd_read_bonded_scalars", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
+    "dsmd_set_bonded", "dsmd_compute_bonded", "dsmd_read_bonded_scalars", "dsmd_set_type_charges", "dsmd_upload", "dsmd_upload_positions", "dsmd_download",
     "dsmd_device_pointer", "dsmd_counts", "dsmd_set_counts", "dsmd_build_neighbor_list", "dsmd_sort_owned", "dsmd_sort_owned_in_brick",
     "dsmd_ghost_slots", "dsmd_list_stats", "dsmd_list_export", "dsmd_pack_positions", "dsmd_max_displacement_sq", "dsmd_max_displacement_sq_lagged",
     "dsmd_displacement_word", "dsmd_compute_forces", "dsmd_read_scalars", "dsmd_integrate", "dsmd_kinetic_energy", "dsmd_scale_velocities",
@@ -154,6 +154,15 @@ class Context:
         a, b, d = _arr(rows[:, 0], np.int32), _arr(rows[:, 1], np.int32), _arr(rows[:, 2], np.float64)
         self._check(self.lib.dsmd_set_constraints(self.h, c_int64(n_global), c_int64(len(a)), _p(a), _p(b), _p(d),
                                                   c_double(tolerance), c_int(max_iterations)))
+
+    def set_type_charges(self, charge_of_type):
+        """Every atom's charge is the charge of its type: the pair kernel reads a table instead of the per-atom array.
+        None switches back to per-atom charges."""
+        if charge_of_type is None:
+            self._check(self.lib.dsmd_set_type_charges(self.h, c_int(0), None))
+            return
+        q = _arr(charge_of_type, np.float64)
+        self._check(self.lib.dsmd_set_type_charges(self.h, c_int(len(q)), _p(q)))
 
     def set_bonded(self, n_global, terms):
         """terms: a mapping (or object) with bonds [nb, 2], bond_k, bond_r0, angles [na, 3], angle_k, angle_theta0 (radians),

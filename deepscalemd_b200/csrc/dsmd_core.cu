@@ -559,6 +559,7 @@ struct PairParams {
     int ewald_intervals;
     const float2* c6c12;         // [ntypes * ntypes]
     const float4* ewald;         // [2 * intervals]: force cubic, energy cubic
+    const float* type_charge;    // [ntypes] when every atom's charge is that of its type (dsmd_set_type_charges), else null
 };
 
 // 1 / v: the hardware approximation (1 ulp) for the force-only kernels, one Newton step more (full single precision)
@@ -653,7 +654,7 @@ struct PairAccumulator {
 // forces need no scatter and no atomics, and the summation order is fixed (bitwise reproducible). Energy and virial
 // take half of every directed entry; an owned-ghost pair is then counted half on each rank, as the reference's list
 // kernel does (src/force_calculator_cuda.cu:1784-1789).
-template <bool COULOMB, bool ENERGY, bool MULTI, bool SWITCH, bool EXCL>
+template <bool COULOMB, bool ENERGY, bool MULTI, bool SWITCH, bool EXCL, bool QTYPE>
 __global__ void __launch_bounds__(kPairThreads)
 k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __restrict__ qf,
        const unsigned* __restrict__ nbr, int stride, const int* __restrict__ deg, const int* __restrict__ deg_int,
@@ -662,17 +663,23 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
     extern __shared__ float4 smem[];
     float2* s_c6c12 = reinterpret_cast<float2*>(smem);
     float4* s_ewald = smem + (MULTI ? (p.ntypes * p.ntypes + 1) / 2 : 0);
+    // charges by type: the partner's charge comes out of a small table in shared memory (its type arrives with its
+    // position) instead of a second gather from global memory
+    constexpr bool by_type = COULOMB && QTYPE;   // QTYPE: launched when dsmd_set_type_charges gave a table
+    float* s_type_charge = reinterpret_cast<float*>(s_ewald + (COULOMB ? 2 * p.ewald_intervals : 0));
     if (MULTI)
         for (int k = threadIdx.x; k < p.ntypes * p.ntypes; k += blockDim.x) s_c6c12[k] = p.c6c12[k];
     if (COULOMB)
         for (int k = threadIdx.x; k < 2 * p.ewald_intervals; k += blockDim.x) s_ewald[k] = p.ewald[k];
+    if (by_type)
+        for (int k = threadIdx.x; k < p.ntypes; k += blockDim.x) s_type_charge[k] = p.type_charge[k];
     if (MULTI || COULOMB) __syncthreads();
 
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     PairAccumulator<COULOMB, ENERGY, MULTI, SWITCH> acc;
     if (i < n_owned) {
         const int4 pi = pq[i];
-        const float qi = COULOMB ? p.kq * qf[i] : 0.f;
+        const float qi = COULOMB ? p.kq * (by_type ? s_type_charge[pi.w] : qf[i]) : 0.f;
         const float2 single = MULTI ? make_float2(0.f, 0.f) : p.c6c12[0];
         const int trow = MULTI ? pi.w * p.ntypes : 0;
         const int k_begin = phase == DSMD_PHASE_BOUNDARY ? deg_int[i] : 0;
@@ -690,15 +697,15 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
             for (int u = 0; u < U; ++u) {
                 e[u] = e_next[u];
                 pj[u] = __ldg(&pq[EXCL ? (e[u] & kIndexMask) : e[u]]);
-                if (COULOMB) qj[u] = __ldg(&qf[EXCL ? (e[u] & kIndexMask) : e[u]]);
+                if (COULOMB && !by_type) qj[u] = __ldg(&qf[EXCL ? (e[u] & kIndexMask) : e[u]]);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u)
                 e_next[u] = (k + U + u < k_end) ? __ldcs(row + static_cast<size_t>(k + U + u) * 32) : self;
 #pragma unroll
             for (int u = 0; u < U; ++u)
-                acc.add(p, pi, pj[u], qi, COULOMB ? qj[u] : 0.f, EXCL && (e[u] & kExclBit) != 0u, s_c6c12, s_ewald, single,
-                        trow);
+                acc.add(p, pi, pj[u], qi, COULOMB ? (by_type ? s_type_charge[pj[u].w] : qj[u]) : 0.f,
+                        EXCL && (e[u] & kExclBit) != 0u, s_c6c12, s_ewald, single, trow);
         }
         if (phase == DSMD_PHASE_BOUNDARY) {
             if (k_end > k_begin) {   // most atoms of a brick have no ghost partner: leave their forces alone
@@ -868,6 +875,7 @@ struct dsmd_ctx {
     unsigned* key[2] = {};
     int* val[2] = {};
     int* ghost_slot = nullptr;
+    float* type_charge = nullptr;     // [ntypes] charges by type (dsmd_set_type_charges), or null: per-atom charges
     int* cell_start = nullptr;
     int64_t cell_capacity = 0;
     int* ghost_rows = nullptr;        // [4 * rows]: lo_end, hi_begin per (y, z) row, then the same over the rows searched
@@ -1155,16 +1163,22 @@ void launch_pair(dsmd_ctx* c, const PairParams& p, int phase, bool sw, cudaStrea
     size_t smem = 0;
     if (MULTI) smem += sizeof(float4) * ((p.ntypes * p.ntypes + 1) / 2);
     if (COULOMB) smem += sizeof(float4) * 2 * p.ewald_intervals;
+    if (COULOMB && p.type_charge) smem += sizeof(float4) * ((p.ntypes + 3) / 4);
     double* fx = c->real[c->cur][DSMD_FX];
     double* fy = c->real[c->cur][DSMD_FY];
     double* fz = c->real[c->cur][DSMD_FZ];
     const bool ex = c->excl_off != nullptr;
-#define DSMD_PAIR_LAUNCH(SW, EX)                                                                                      \
-    k_pair<COULOMB, ENERGY, MULTI, SW, EX><<<blocks, kPairThreads, smem, s>>>(                                          \
+#define DSMD_PAIR_LAUNCH(SW, EX, QT)                                                                                  \
+    k_pair<COULOMB, ENERGY, MULTI, SW, EX, QT><<<blocks, kPairThreads, smem, s>>>(                                      \
         p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, fx, fy, fz,        \
         c->partials)
-    if (sw) { if (ex) DSMD_PAIR_LAUNCH(true, true); else DSMD_PAIR_LAUNCH(true, false); }
-    else    { if (ex) DSMD_PAIR_LAUNCH(false, true); else DSMD_PAIR_LAUNCH(false, false); }
+    if (COULOMB && p.type_charge) {   // charges by type: only the kernels with Coulomb have this form
+        if (sw) { if (ex) DSMD_PAIR_LAUNCH(true, true, COULOMB); else DSMD_PAIR_LAUNCH(true, false, COULOMB); }
+        else    { if (ex) DSMD_PAIR_LAUNCH(false, true, COULOMB); else DSMD_PAIR_LAUNCH(false, false, COULOMB); }
+    } else {
+        if (sw) { if (ex) DSMD_PAIR_LAUNCH(true, true, false); else DSMD_PAIR_LAUNCH(true, false, false); }
+        else    { if (ex) DSMD_PAIR_LAUNCH(false, true, false); else DSMD_PAIR_LAUNCH(false, false, false); }
+    }
 #undef DSMD_PAIR_LAUNCH
 }
 
@@ -1225,7 +1239,7 @@ void dsmd_destroy(dsmd_ctx* c) {
         for (int f = 0; f < kNumReal; ++f) cudaFree(c->real[set][f]);
         cudaFree(c->type[set]); cudaFree(c->gid[set]); cudaFree(c->key[set]); cudaFree(c->val[set]);
     }
-    cudaFree(c->pq); cudaFree(c->pf); cudaFree(c->qf);
+    cudaFree(c->pq); cudaFree(c->pf); cudaFree(c->qf); cudaFree(c->type_charge);
     for (int a = 0; a < 3; ++a) cudaFree(c->ref[a]);
     cudaFree(c->ghost_slot); cudaFree(c->cell_start); cudaFree(c->ghost_rows); cudaFree(c->nbr); cudaFree(c->deg); cudaFree(c->deg_int);
     cudaFree(c->cub_temp); cudaFree(c->c6c12); cudaFree(c->ewald); cudaFree(c->excl_off); cudaFree(c->excl_partner);
@@ -1668,6 +1682,7 @@ int dsmd_compute_forces(dsmd_ctx* c, int phase, int want_energy, void* stream) {
     p.ewald_intervals = c->ewald_intervals;
     p.c6c12 = c->c6c12;
     p.ewald = c->ewald;
+    p.type_charge = c->coulomb ? c->type_charge : nullptr;
     const bool multi = c->ntypes > 1;
     const int64_t blocks = blocks_for(c->n_owned, kPairThreads);
     if (want_energy) { const int rc = ensure_partials(c, blocks); if (rc) return rc; }
@@ -1893,6 +1908,31 @@ static int to_device_bytes(dsmd_ctx* c, void** dst, const void* src, size_t byte
         const int rc_ = to_device_bytes(c, reinterpret_cast<void**>(&(dst)), (vec).data(), sizeof((vec)[0]) * (vec).size()); \
         if (rc_) return rc_;                                                                                           \
     } while (0)
+
+int dsmd_set_type_charges(dsmd_ctx* c, int ntypes, const double* charge_of_type) {
+    if (!c) return DSMD_ERR_INVALID;
+    DSMD_CUDA(c, cudaSetDevice(c->device));
+    cudaFree(c->type_charge);
+    c->type_charge = nullptr;
+    if (!charge_of_type || ntypes <= 0) return DSMD_OK;
+    if (!c->params_set || ntypes != c->ntypes)
+        return fail(c, DSMD_ERR_INVALID, "dsmd_set_type_charges: the number of types differs from dsmd_set_pair_params'");
+    // the atoms already on the device must agree with the table (those that arrive later are the caller's word)
+    if (c->n_total > 0) {
+        std::vector<double> q(static_cast<size_t>(c->n_total));
+        std::vector<int> t(static_cast<size_t>(c->n_total));
+        DSMD_CUDA(c, cudaMemcpy(q.data(), c->real[c->cur][10], sizeof(double) * q.size(), cudaMemcpyDeviceToHost));
+        DSMD_CUDA(c, cudaMemcpy(t.data(), c->type[c->cur], sizeof(int) * t.size(), cudaMemcpyDeviceToHost));
+        for (size_t k = 0; k < q.size(); ++k)
+            if (t[k] < 0 || t[k] >= ntypes || q[k] != charge_of_type[t[k]])
+                return fail(c, DSMD_ERR_INVALID, "dsmd_set_type_charges: an atom's charge is not the charge given for its type");
+    }
+    std::vector<float> table(static_cast<size_t>(ntypes));
+    for (int k = 0; k < ntypes; ++k) table[static_cast<size_t>(k)] = static_cast<float>(charge_of_type[k]);
+    DSMD_CUDA(c, cudaMalloc(&c->type_charge, sizeof(float) * table.size()));
+    DSMD_CUDA(c, cudaMemcpy(c->type_charge, table.data(), sizeof(float) * table.size(), cudaMemcpyHostToDevice));
+    return DSMD_OK;
+}
 
 int dsmd_set_bonded(dsmd_ctx* c, int64_t n_global, int64_t n_bonds, const int32_t* bond_atoms, const double* bond_k,
                     const double* bond_r0, int64_t n_angles, const int32_t* angle_atoms, const double* angle_k,

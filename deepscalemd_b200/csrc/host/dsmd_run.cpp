@@ -163,6 +163,19 @@ public:
         ok(ctx_, dsmd_upload(ctx_, s_.n, s_.n, s_.x.data(), s_.y.data(), s_.z.data(), s_.vx.data(), s_.vy.data(), s_.vz.data(),
                              s_.mass.data(), s_.charge.data(), type.data(), nullptr, nullptr),
            "dsmd_upload");
+        // where every atom of a type carries the same charge (water models, ions, united-atom chains with typed charges)
+        // the pair kernel reads the charges from a table by type
+        if (c_.enable_coulomb && charged) {
+            std::vector<double> by_type(static_cast<size_t>(s_.ntypes), 0.0);
+            std::vector<char> seen(by_type.size(), 0);
+            bool function_of_type = true;
+            for (size_t i = 0; i < s_.type.size() && function_of_type; ++i) {
+                const size_t t = static_cast<size_t>(s_.type[i]);
+                if (!seen[t]) { seen[t] = 1; by_type[t] = s_.charge[i]; }
+                else if (by_type[t] != s_.charge[i]) function_of_type = false;
+            }
+            if (function_of_type) ok(ctx_, dsmd_set_type_charges(ctx_, s_.ntypes, by_type.data()), "dsmd_set_type_charges");
+        }
     }
 
     void build_list() {

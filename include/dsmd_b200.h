@@ -184,6 +184,15 @@ int dsmd_compute_forces(dsmd_ctx* ctx, int phase, int want_energy, void* stream)
  * Synchronises `stream`. */
 int dsmd_read_scalars(dsmd_ctx* ctx, double out[6], void* stream);
 
+/* Optional: declares that every atom's charge is a function of its type (rigid water models, ions, united-atom and
+ * coarse-grained force fields) and gives that function. The pair kernel then takes a partner's charge from a table in
+ * shared memory, indexed by the type that arrives with the partner's position, instead of gathering it from the per-atom
+ * array. ntypes must equal dsmd_set_pair_params'; atoms already uploaded are checked against the table
+ * (DSMD_ERR_INVALID on a mismatch), atoms that arrive later (ghosts, migrated atoms) are the caller's word. The per-atom
+ * charges stay in place for everything else (special pairs, downloads). Null or ntypes <= 0 switches back. No counterpart
+ * in the reference, whose kernels read per-atom charges (src/force_calculator_cuda.cu:1604-1860). */
+int dsmd_set_type_charges(dsmd_ctx* ctx, int ntypes, const double* charge_of_type);
+
 /* Bonded terms and scaled special (1-4) pairs (compute_bond_forces_kernel, compute_angle_forces_kernel,
  * compute_dihedral_forces_kernel, compute_improper_forces_kernel, compute_special_pair_forces_kernel,
  * src/force_calculator_cuda.cu:2703-3170; MDSystem::LocalBond ... LocalSpecialPair, include/md_system.h:22-42). Atoms are

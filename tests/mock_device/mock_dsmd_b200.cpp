@@ -135,6 +135,8 @@ int dsmd_set_bonded(dsmd_ctx* c, int64_t, int64_t n_bonds, const int32_t*, const
 
 int dsmd_compute_bonded(dsmd_ctx*, void*) { return DSMD_OK; }
 
+int dsmd_set_type_charges(dsmd_ctx*, int, const double*) { return DSMD_OK; }
+
 int dsmd_read_bonded_scalars(dsmd_ctx*, double out[5], void*) {
     for (int k = 0; k < 5; ++k) out[k] = 0.0;
     return DSMD_OK;

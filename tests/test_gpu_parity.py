@@ -538,3 +538,32 @@ def test_full_size_properties_kob_andersen_1m(cuda_device):
     assert np.abs(f.sum(0)).max() <= 2e-6 * np.abs(f).sum(0).max()
     full_size_force_parity(ctx, s, "kob_andersen_1m", sc)
     ctx.close()
+
+
+def test_charges_by_type_give_the_same_bits_as_per_atom_charges(cuda_device):
+    """dsmd_set_type_charges: the partner's charge from a table by type instead of the per-atom array. The table holds the
+    same single-precision values, so forces, energy and virial are bit for bit those of the per-atom path; a table that
+    disagrees with the uploaded atoms is refused."""
+    s = syn.water_box(11, seed=3)
+    ctx = make_context(s)
+    ctx.build_neighbor_list()
+    ctx.compute_forces(capi.PHASE_FULL)                      # the force-only kernel (its reciprocal is the 1-ulp one)
+    f_only = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
+    ctx.compute_forces(capi.PHASE_FULL, want_energy=True)
+    sc = ctx.read_scalars()
+    f = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
+    ctx.set_type_charges([-0.8476, 0.4238])
+    ctx.compute_forces(capi.PHASE_FULL, want_energy=True)
+    sc_table = ctx.read_scalars()
+    f_table = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
+    assert np.array_equal(f_table, f) and np.abs(f).max() > 1.0
+    assert sc_table["pe"] == sc["pe"] and sc_table["virial"] == sc["virial"]
+    ctx.compute_forces(capi.PHASE_FULL)
+    assert np.array_equal(np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1), f_only)
+    ctx.set_type_charges(None)
+    with pytest.raises(capi.DsmdError) as err:
+        ctx.set_type_charges([-0.8476, 0.5])
+    assert err.value.code == capi.ERR_INVALID and "not the charge given for its type" in str(err.value)
+    with pytest.raises(capi.DsmdError):
+        ctx.set_type_charges([-0.8476, 0.4238, 0.0])          # three entries for two types
+    ctx.close()
