@@ -47,7 +47,8 @@ struct Status {
     unsigned long long select_count;
     unsigned int dropped;          // owned atoms found outside the brick by a sort that removes them
     unsigned int constraint_failed;   // constraint clusters whose SHAKE / RATTLE sweeps did not converge
-    unsigned int reserved[2];
+    unsigned int boundary_atoms;      // owned atoms with a ghost partner in their list row (the boundary pass runs over them)
+    unsigned int reserved;
 };
 
 __host__ __device__ inline unsigned int cell_of(unsigned int fixed, int wrap, int nc) {

@@ -235,7 +235,8 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
              const double* __restrict__ x, const double* __restrict__ y, const double* __restrict__ z,
              const int* __restrict__ gid, ExclusionTable excl, const int* __restrict__ cell_start,
              const int* __restrict__ ghost_near_lo, const int* __restrict__ ghost_near_hi,
-             unsigned* __restrict__ nbr, int stride, int* __restrict__ deg, int* __restrict__ deg_int, Status* st) {
+             unsigned* __restrict__ nbr, int stride, int* __restrict__ deg, int* __restrict__ deg_int,
+             int* __restrict__ boundary_list, Status* st) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const bool active = i < n_owned;   // lanes past the end stay for the warp sums at the bottom
     const int4 pi = active ? pq[i] : make_int4(0, 0, 0, 0);
@@ -373,6 +374,19 @@ k_build_list(Grid g, int n_owned, int n_total, const int4* __restrict__ pq, cons
         deg[i] = min(count, stride);
         deg_int[i] = min(interior, stride);
         if (count > stride) atomicMax(&st->need_stride, static_cast<unsigned>(count));
+    }
+    // atoms with a ghost partner, collected for the boundary pass of the pair kernel (one atomic per warp; the order of
+    // the collection does not matter: every atom's sum is its own thread's)
+    {
+        const bool has_ghost_partner = active && count > interior;
+        const unsigned ballot = __ballot_sync(0xffffffffu, has_ghost_partner);
+        if (ballot) {
+            const int lane = threadIdx.x & 31;
+            unsigned first = 0;
+            if (lane == 0) first = atomicAdd(&st->boundary_atoms, static_cast<unsigned>(__popc(ballot)));
+            first = __shfl_sync(0xffffffffu, first, 0);
+            if (has_ghost_partner) boundary_list[first + __popc(ballot & ((1u << lane) - 1u))] = i;
+        }
     }
     // statistics: one atomic per warp
     unsigned long long c64 = count, i64 = interior;
@@ -658,8 +672,8 @@ template <bool COULOMB, bool ENERGY, bool MULTI, bool SWITCH, bool EXCL, bool QT
 __global__ void __launch_bounds__(kPairThreads)
 k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __restrict__ qf,
        const unsigned* __restrict__ nbr, int stride, const int* __restrict__ deg, const int* __restrict__ deg_int,
-       int phase, double* __restrict__ fx, double* __restrict__ fy, double* __restrict__ fz,
-       double* __restrict__ partials) {
+       int phase, const int* __restrict__ atom_list, int n_threads, double* __restrict__ fx, double* __restrict__ fy,
+       double* __restrict__ fz, double* __restrict__ partials) {
     extern __shared__ float4 smem[];
     float2* s_c6c12 = reinterpret_cast<float2*>(smem);
     float4* s_ewald = smem + (MULTI ? (p.ntypes * p.ntypes + 1) / 2 : 0);
@@ -675,7 +689,9 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
         for (int k = threadIdx.x; k < p.ntypes; k += blockDim.x) s_type_charge[k] = p.type_charge[k];
     if (MULTI || COULOMB) __syncthreads();
 
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    // atom_list (boundary pass): the atoms that have a ghost partner, a small part of a brick; null: every owned atom
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int i = t < n_threads ? (atom_list ? atom_list[t] : t) : n_owned;
     PairAccumulator<COULOMB, ENERGY, MULTI, SWITCH> acc;
     if (i < n_owned) {
         const int4 pi = pq[i];
@@ -875,6 +891,8 @@ struct dsmd_ctx {
     unsigned* key[2] = {};
     int* val[2] = {};
     int* ghost_slot = nullptr;
+    int* boundary_list = nullptr;     // [capacity] owned atoms with a ghost partner, as the last list build found them
+    int64_t n_boundary = 0;
     float* type_charge = nullptr;     // [ntypes] charges by type (dsmd_set_type_charges), or null: per-atom charges
     int* cell_start = nullptr;
     int64_t cell_capacity = 0;
@@ -1159,7 +1177,10 @@ int read_status(dsmd_ctx* c, cudaStream_t s) {
 
 template <bool COULOMB, bool ENERGY, bool MULTI>
 void launch_pair(dsmd_ctx* c, const PairParams& p, int phase, bool sw, cudaStream_t s) {
-    const unsigned blocks = blocks_for(c->n_owned, kPairThreads);
+    const bool listed = phase == DSMD_PHASE_BOUNDARY;
+    const int n_threads = static_cast<int>(listed ? c->n_boundary : c->n_owned);
+    const int* atom_list = listed ? c->boundary_list : nullptr;
+    const unsigned blocks = blocks_for(n_threads, kPairThreads);
     size_t smem = 0;
     if (MULTI) smem += sizeof(float4) * ((p.ntypes * p.ntypes + 1) / 2);
     if (COULOMB) smem += sizeof(float4) * 2 * p.ewald_intervals;
@@ -1170,8 +1191,8 @@ void launch_pair(dsmd_ctx* c, const PairParams& p, int phase, bool sw, cudaStrea
     const bool ex = c->excl_off != nullptr;
 #define DSMD_PAIR_LAUNCH(SW, EX, QT)                                                                                  \
     k_pair<COULOMB, ENERGY, MULTI, SW, EX, QT><<<blocks, kPairThreads, smem, s>>>(                                      \
-        p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, fx, fy, fz,        \
-        c->partials)
+        p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, atom_list,         \
+        n_threads, fx, fy, fz, c->partials)
     if (COULOMB && p.type_charge) {   // charges by type: only the kernels with Coulomb have this form
         if (sw) { if (ex) DSMD_PAIR_LAUNCH(true, true, COULOMB); else DSMD_PAIR_LAUNCH(true, false, COULOMB); }
         else    { if (ex) DSMD_PAIR_LAUNCH(false, true, COULOMB); else DSMD_PAIR_LAUNCH(false, false, COULOMB); }
@@ -1216,6 +1237,7 @@ int dsmd_create(int device, int64_t capacity, dsmd_ctx** out) {
     DSMD_CUDA(c, cudaMalloc(&c->ghost_slot, sizeof(int) * capacity));
     DSMD_CUDA(c, cudaMalloc(&c->deg, sizeof(int) * capacity));
     DSMD_CUDA(c, cudaMalloc(&c->deg_int, sizeof(int) * capacity));
+    DSMD_CUDA(c, cudaMalloc(&c->boundary_list, sizeof(int) * capacity));
     DSMD_CUDA(c, cudaMalloc(&c->flag, capacity));
     DSMD_CUDA(c, cudaMalloc(&c->offsets64, sizeof(unsigned long long) * capacity));
     DSMD_CUDA(c, cudaMalloc(&c->scalars, sizeof(double) * 8));
@@ -1242,6 +1264,7 @@ void dsmd_destroy(dsmd_ctx* c) {
     cudaFree(c->pq); cudaFree(c->pf); cudaFree(c->qf); cudaFree(c->type_charge);
     for (int a = 0; a < 3; ++a) cudaFree(c->ref[a]);
     cudaFree(c->ghost_slot); cudaFree(c->cell_start); cudaFree(c->ghost_rows); cudaFree(c->nbr); cudaFree(c->deg); cudaFree(c->deg_int);
+    cudaFree(c->boundary_list);
     cudaFree(c->cub_temp); cudaFree(c->c6c12); cudaFree(c->ewald); cudaFree(c->excl_off); cudaFree(c->excl_partner);
     cudaFree(c->partials); cudaFree(c->scalars); cudaFree(c->status); cudaFree(c->flag); cudaFree(c->offsets64);
     cudaFree(c->cl_gid); cudaFree(c->cl_a); cudaFree(c->cl_b); cudaFree(c->cl_d2); cudaFree(c->slot_of_gid);
@@ -1529,12 +1552,12 @@ int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
             k_build_list<true><<<blocks_for(c->n_owned, kBuildThreads), kBuildThreads, 0, s>>>(
                 c->grid, static_cast<int>(c->n_owned), static_cast<int>(c->n_total), c->pq, c->pf, c->real[c->cur][0],
                 c->real[c->cur][1], c->real[c->cur][2], c->gid[c->cur], ex, c->cell_start, c->ghost_rows + 2 * rows,
-                c->ghost_rows + 3 * rows, c->nbr, c->stride, c->deg, c->deg_int, c->status);
+                c->ghost_rows + 3 * rows, c->nbr, c->stride, c->deg, c->deg_int, c->boundary_list, c->status);
         else
             k_build_list<false><<<blocks_for(c->n_owned, kBuildThreads), kBuildThreads, 0, s>>>(
                 c->grid, static_cast<int>(c->n_owned), static_cast<int>(c->n_total), c->pq, c->pf, c->real[c->cur][0],
                 c->real[c->cur][1], c->real[c->cur][2], c->gid[c->cur], ex, c->cell_start, c->ghost_rows + 2 * rows,
-                c->ghost_rows + 3 * rows, c->nbr, c->stride, c->deg, c->deg_int, c->status);
+                c->ghost_rows + 3 * rows, c->nbr, c->stride, c->deg, c->deg_int, c->boundary_list, c->status);
         DSMD_LAUNCHED(c);
         { const int rc = read_status(c, s); if (rc) return rc; }
         if (c->h_status->out_of_domain)
@@ -1550,6 +1573,7 @@ int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
     c->stat_entries = static_cast<int64_t>(c->h_status->entries);
     c->stat_interior = static_cast<int64_t>(c->h_status->interior);
     c->stat_rechecked = static_cast<int>(c->h_status->rechecked);
+    c->n_boundary = static_cast<int64_t>(c->h_status->boundary_atoms);
     ++c->build_epoch;
     DSMD_CUDA(c, cudaMemsetAsync(c->status, 0, sizeof(Status), s));   // displacement word restarts at zero
     c->list_valid = true;
@@ -1684,18 +1708,22 @@ int dsmd_compute_forces(dsmd_ctx* c, int phase, int want_energy, void* stream) {
     p.ewald = c->ewald;
     p.type_charge = c->coulomb ? c->type_charge : nullptr;
     const bool multi = c->ntypes > 1;
-    const int64_t blocks = blocks_for(c->n_owned, kPairThreads);
-    if (want_energy) { const int rc = ensure_partials(c, blocks); if (rc) return rc; }
+    // the boundary pass runs over the atoms the list build found a ghost partner for (none: nothing to launch)
+    const int64_t pair_threads = phase == DSMD_PHASE_BOUNDARY ? c->n_boundary : c->n_owned;
+    const int64_t blocks = blocks_for(pair_threads, kPairThreads);
+    if (want_energy) { const int rc = ensure_partials(c, std::max<int64_t>(blocks, 1)); if (rc) return rc; }
     const bool e = want_energy != 0;
-    if (c->coulomb) {
+    if (pair_threads == 0) {
+        // nothing to add to the forces; the energy sums of a boundary pass stay as the interior pass left them
+    } else if (c->coulomb) {
         if (e) { if (multi) launch_pair<true, true, true>(c, p, phase, sw, s); else launch_pair<true, true, false>(c, p, phase, sw, s); }
         else   { if (multi) launch_pair<true, false, true>(c, p, phase, sw, s); else launch_pair<true, false, false>(c, p, phase, sw, s); }
     } else {
         if (e) { if (multi) launch_pair<false, true, true>(c, p, phase, sw, s); else launch_pair<false, true, false>(c, p, phase, sw, s); }
         else   { if (multi) launch_pair<false, false, true>(c, p, phase, sw, s); else launch_pair<false, false, false>(c, p, phase, sw, s); }
     }
-    DSMD_LAUNCHED(c);
-    if (e) {
+    if (pair_threads > 0) DSMD_LAUNCHED(c);
+    if (e && (pair_threads > 0 || phase != DSMD_PHASE_BOUNDARY)) {
         k_reduce_partials<6><<<1, kThreads, 0, s>>>(c->partials, static_cast<int>(blocks), c->scalars,
                                                    phase == DSMD_PHASE_BOUNDARY ? 1 : 0);
         DSMD_LAUNCHED(c);
