@@ -150,6 +150,19 @@ __global__ void k_cell_tail(const unsigned* __restrict__ key, int n_sorted, int 
 // kernel: Verlet list build
 // ---------------------------------------------------------------------------------------------------------------------
 
+// A ghost-only sort gathers the ghosts into the other buffer set; this brings them back, so that the owned atoms
+// (already in place) need not be copied across: one thread per ghost, all per-atom arrays.
+__global__ void k_copy_back(int first, int count, RealArrays from, RealArrays to, const int* __restrict__ type_from,
+                            const int* __restrict__ gid_from, int* __restrict__ type_to, int* __restrict__ gid_to) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= count) return;
+    const int s = first + t;
+#pragma unroll
+    for (int f = 0; f < kNumReal; ++f) to.p[f][s] = from.p[f][s];
+    type_to[s] = type_from[s];
+    gid_to[s] = gid_from[s];
+}
+
 // Where the ghosts of a cell row sit: lo_end = one past the last x cell of the row's lower half that holds a ghost (0:
 // none), hi_begin = the first x cell of its upper half that holds one (nc[0]: none). One warp per (y, z) row.
 __global__ void k_ghost_row_extent(Grid g, const int* __restrict__ ghost_cell_start, int* __restrict__ lo_end,
@@ -1121,14 +1134,6 @@ int ensure_partials(dsmd_ctx* c, int64_t blocks) {
 int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s, int64_t n_removed = 0, const Brick* bounds = nullptr) {
     const int64_t n = c->n_total - first;
     const int from = c->cur, to = 1 - c->cur;
-    if (first > 0) {
-        // The owned atoms are already in place: carry them over unchanged.
-        for (int f = 0; f < kNumReal; ++f)
-            DSMD_CUDA(c, cudaMemcpyAsync(c->real[to][f], c->real[from][f], sizeof(double) * first,
-                                         cudaMemcpyDeviceToDevice, s));
-        DSMD_CUDA(c, cudaMemcpyAsync(c->type[to], c->type[from], sizeof(int) * first, cudaMemcpyDeviceToDevice, s));
-        DSMD_CUDA(c, cudaMemcpyAsync(c->gid[to], c->gid[from], sizeof(int) * first, cudaMemcpyDeviceToDevice, s));
-    }
     if (n > 0) {
         Brick brick{};
         if (bounds) brick = *bounds;
@@ -1164,7 +1169,18 @@ int sort_range(dsmd_ctx* c, int64_t first, cudaStream_t s, int64_t n_removed = 0
             DSMD_LAUNCHED(c);
         }
     }
-    c->cur = to;
+    if (first > 0) {
+        // a ghost-only sort: the owned atoms are in place in the current set, the sorted ghosts come back to it (far
+        // fewer bytes than carrying the owned atoms across, and one launch instead of thirteen copies)
+        if (n > 0) {
+            k_copy_back<<<blocks_for(n, kThreads), kThreads, 0, s>>>(static_cast<int>(first), static_cast<int>(n),
+                                                                    arrays_of(c, to), arrays_of(c, from), c->type[to],
+                                                                    c->gid[to], c->type[from], c->gid[from]);
+            DSMD_LAUNCHED(c);
+        }
+    } else {
+        c->cur = to;
+    }
     c->slot_map_valid = false;
     return DSMD_OK;
 }
