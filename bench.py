@@ -44,17 +44,45 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML polled every 2 ms from a thread (the timed
+    call runs in native code with the interpreter lock released), or, where the NVML binding is missing, nvidia-smi at its
+    fastest rate. Reading only: no setting of the GPU is touched."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    # bits of the clocks-event (throttle) reasons word
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, device_index: int):
         self.device_index = device_index
         self.proc = None
         self.lines = []
+        self.nvml = None
+        self.samples = []        # (sm MHz, reasons word)
+        self.sm_max = None
+        self.running = False
+
+    def _visible_index(self):
+        """The NVML index of the CUDA device (CUDA_VISIBLE_DEVICES may renumber)."""
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        ids = [v for v in visible.split(",") if v.strip()]
+        if ids and self.device_index < len(ids) and ids[self.device_index].strip().isdigit():
+            return int(ids[self.device_index])
+        return self.device_index
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._visible_index())
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.running = True
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
@@ -64,11 +92,38 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        nv = self.nvml
+        reasons_of = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while self.running:
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                word = int(reasons_of(self.handle)) if reasons_of else 0
+                self.samples.append((mhz, word))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self.running = False
+            self.thread.join(timeout=1.0)
+            sm = [m for m, _ in self.samples]
+            word = 0
+            for _, w in self.samples:
+                word |= w
+            reasons = sorted(name for name, bit in self.REASON_BITS.items() if word & bit)
+            try:
+                self.nvml.nvmlShutdown()
+            except Exception:
+                pass
+            return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": self.sm_max, "samples": len(sm),
+                    "reasons": reasons, "source": "NVML, every 2 ms"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -92,7 +147,7 @@ class ClockSampler:
                 if f[5 + k].lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi -lms 100"}
 
 
 def clocks_max_ghz(device_index: int) -> float:
