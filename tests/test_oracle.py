@@ -371,3 +371,23 @@ def test_bonded_terms_match_the_reference_routines():
     assert np.abs(fa - f[:n_a]).max() <= 1e-12 * scale and np.abs(fb - f[n_a:]).max() <= 1e-12 * scale
     assert abs(sa["pe"] + sb["pe"] - sc["pe"]) <= 1e-12 * abs(sc["pe"])
     assert np.abs(sa["virial_diag"] + sb["virial_diag"] - sc["virial_diag"]).max() <= 1e-10 * np.abs(sc["virial_diag"]).max()
+
+
+@pytest.mark.parametrize("kind", ["all", "bonds", "angles", "torsions", "specials"])
+def test_bonded_restatement_matches_the_golden_reference_output(kind):
+    """The same check against the committed output of the reference's routines (tests/golden/make_bonded_golden.py), which
+    needs no compiled reference: all kinds of term together and each alone."""
+    import os
+    sys_path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "chains_bonded_512.npz")
+    g = np.load(sys_path)
+    s = syn.chain_fluid(4, 8, seed=11)
+    keys = dict(all=None, bonds=("bonds", "bond_k", "bond_r0"), angles=("angles", "angle_k", "angle_theta0"),
+                torsions=("torsions", "torsion_k", "torsion_phi0", "torsion_n", "n_dihedrals"),
+                specials=("specials", "special_sigma", "special_epsilon", "special_lj_scale", "special_coulomb_scale"))[kind]
+    terms = co.BondedTerms(**(s.bonded if keys is None else {k: s.bonded[k] for k in keys}))
+    f, sc = co.bonded(s.pos, s.n, s.box, terms, charge=s.charge)
+    want_f, want = g[f"f_{kind}"], g[f"scalars_{kind}"]
+    scale = np.sqrt((want_f * want_f).sum(1).mean())
+    assert scale > 1e-2 and np.abs(f - want_f).max() <= 1e-11 * max(scale, 1.0)
+    got = np.array([sc["pe"], sc["virial"], *sc["virial_diag"]])
+    assert np.abs(got - want).max() <= 1e-11 * np.abs(want).max()
