@@ -163,6 +163,12 @@ __global__ void k_copy_back(int first, int count, RealArrays from, RealArrays to
     gid_to[s] = gid_from[s];
 }
 
+// First slot of every z layer of (owned) cells, and the end: what lets a caller cut the sorted atoms into slabs.
+__global__ void k_layer_starts(const int* __restrict__ cell_start, int cells_per_layer, int layers, int* __restrict__ out) {
+    const int l = blockIdx.x * blockDim.x + threadIdx.x;
+    if (l <= layers) out[l] = cell_start[static_cast<size_t>(l) * cells_per_layer];
+}
+
 // Where the ghosts of a cell row sit: lo_end = one past the last x cell of the row's lower half that holds a ghost (0:
 // none), hi_begin = the first x cell of its upper half that holds one (nc[0]: none). One warp per (y, z) row.
 __global__ void k_ghost_row_extent(Grid g, const int* __restrict__ ghost_cell_start, int* __restrict__ lo_end,
@@ -685,8 +691,8 @@ template <bool COULOMB, bool ENERGY, bool MULTI, bool SWITCH, bool EXCL, bool QT
 __global__ void __launch_bounds__(kPairThreads)
 k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __restrict__ qf,
        const unsigned* __restrict__ nbr, int stride, const int* __restrict__ deg, const int* __restrict__ deg_int,
-       int phase, const int* __restrict__ atom_list, int n_threads, double* __restrict__ fx, double* __restrict__ fy,
-       double* __restrict__ fz, double* __restrict__ partials) {
+       int phase, const int* __restrict__ atom_list, int first, int n_threads, double* __restrict__ fx,
+       double* __restrict__ fy, double* __restrict__ fz, double* __restrict__ partials) {
     extern __shared__ float4 smem[];
     float2* s_c6c12 = reinterpret_cast<float2*>(smem);
     float4* s_ewald = smem + (MULTI ? (p.ntypes * p.ntypes + 1) / 2 : 0);
@@ -702,9 +708,10 @@ k_pair(PairParams p, int n_owned, const int4* __restrict__ pq, const float* __re
         for (int k = threadIdx.x; k < p.ntypes; k += blockDim.x) s_type_charge[k] = p.type_charge[k];
     if (MULTI || COULOMB) __syncthreads();
 
-    // atom_list (boundary pass): the atoms that have a ghost partner, a small part of a brick; null: every owned atom
+    // atom_list (boundary pass): the atoms that have a ghost partner, a small part of a brick; null: the owned atoms
+    // first .. first + n_threads
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    const int i = t < n_threads ? (atom_list ? atom_list[t] : t) : n_owned;
+    const int i = t < n_threads ? (atom_list ? atom_list[t] : first + t) : n_owned;
     PairAccumulator<COULOMB, ENERGY, MULTI, SWITCH> acc;
     if (i < n_owned) {
         const int4 pi = pq[i];
@@ -904,6 +911,13 @@ struct dsmd_ctx {
     unsigned* key[2] = {};
     int* val[2] = {};
     int* ghost_slot = nullptr;
+    // the host-buffer force call as a pipeline (dsmd_forces_host): first slot of every z layer of cells as of the last
+    // build, two copy streams, one event pair per piece
+    int* d_layer_start = nullptr;
+    int* h_layer_start = nullptr;     // pinned, [nc_z + 1]
+    int layer_capacity = 0;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t piece_up[16] = {}, piece_done[16] = {}, pipe_begin = nullptr, pipe_end = nullptr;
     int* boundary_list = nullptr;     // [capacity] owned atoms with a ghost partner, as the last list build found them
     int64_t n_boundary = 0;
     float* type_charge = nullptr;     // [ntypes] charges by type (dsmd_set_type_charges), or null: per-atom charges
@@ -1192,10 +1206,8 @@ int read_status(dsmd_ctx* c, cudaStream_t s) {
 }
 
 template <bool COULOMB, bool ENERGY, bool MULTI>
-void launch_pair(dsmd_ctx* c, const PairParams& p, int phase, bool sw, cudaStream_t s) {
-    const bool listed = phase == DSMD_PHASE_BOUNDARY;
-    const int n_threads = static_cast<int>(listed ? c->n_boundary : c->n_owned);
-    const int* atom_list = listed ? c->boundary_list : nullptr;
+void launch_pair(dsmd_ctx* c, const PairParams& p, int phase, bool sw, cudaStream_t s, int first, int n_threads) {
+    const int* atom_list = phase == DSMD_PHASE_BOUNDARY ? c->boundary_list : nullptr;
     const unsigned blocks = blocks_for(n_threads, kPairThreads);
     size_t smem = 0;
     if (MULTI) smem += sizeof(float4) * ((p.ntypes * p.ntypes + 1) / 2);
@@ -1207,7 +1219,7 @@ void launch_pair(dsmd_ctx* c, const PairParams& p, int phase, bool sw, cudaStrea
     const bool ex = c->excl_off != nullptr;
 #define DSMD_PAIR_LAUNCH(SW, EX, QT)                                                                                  \
     k_pair<COULOMB, ENERGY, MULTI, SW, EX, QT><<<blocks, kPairThreads, smem, s>>>(                                      \
-        p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, atom_list,         \
+        p, static_cast<int>(c->n_owned), c->pq, c->qf, c->nbr, c->stride, c->deg, c->deg_int, phase, atom_list, first,  \
         n_threads, fx, fy, fz, c->partials)
     if (COULOMB && p.type_charge) {   // charges by type: only the kernels with Coulomb have this form
         if (sw) { if (ex) DSMD_PAIR_LAUNCH(true, true, COULOMB); else DSMD_PAIR_LAUNCH(true, false, COULOMB); }
@@ -1285,6 +1297,16 @@ void dsmd_destroy(dsmd_ctx* c) {
     cudaFree(c->partials); cudaFree(c->scalars); cudaFree(c->status); cudaFree(c->flag); cudaFree(c->offsets64);
     cudaFree(c->cl_gid); cudaFree(c->cl_a); cudaFree(c->cl_b); cudaFree(c->cl_d2); cudaFree(c->slot_of_gid);
     free_bonded(c);
+    cudaFree(c->d_layer_start);
+    if (c->h_layer_start) cudaFreeHost(c->h_layer_start);
+    if (c->copy_in) cudaStreamDestroy(c->copy_in);
+    if (c->copy_out) cudaStreamDestroy(c->copy_out);
+    for (int k = 0; k < 16; ++k) {
+        if (c->piece_up[k]) cudaEventDestroy(c->piece_up[k]);
+        if (c->piece_done[k]) cudaEventDestroy(c->piece_done[k]);
+    }
+    if (c->pipe_begin) cudaEventDestroy(c->pipe_begin);
+    if (c->pipe_end) cudaEventDestroy(c->pipe_end);
     for (int a = 0; a < 3; ++a) cudaFree(c->pre[a]);
     cudaFreeHost(c->h_status); cudaFreeHost(c->h_scalars);
     for (int k = 0; k < 2; ++k) {
@@ -1553,6 +1575,21 @@ int dsmd_build_neighbor_list(dsmd_ctx* c, void* stream) {
         DSMD_CUDA(c, cudaMalloc(&c->ghost_rows, sizeof(int) * 4 * rows));
         c->ghost_rows_capacity = 4 * rows;
     }
+    {   // slab boundaries for the pipelined host-buffer call; they arrive with the status read-back below
+        const int layers = c->grid.nc[2];
+        if (layers + 1 > c->layer_capacity) {
+            cudaFree(c->d_layer_start);
+            if (c->h_layer_start) cudaFreeHost(c->h_layer_start);
+            c->d_layer_start = c->h_layer_start = nullptr;
+            DSMD_CUDA(c, cudaMalloc(&c->d_layer_start, sizeof(int) * (layers + 1)));
+            DSMD_CUDA(c, cudaMallocHost(&c->h_layer_start, sizeof(int) * (layers + 1)));
+            c->layer_capacity = layers + 1;
+        }
+        k_layer_starts<<<blocks_for(layers + 1, kThreads), kThreads, 0, s>>>(c->cell_start, c->grid.nc[0] * c->grid.nc[1], layers,
+                                                                           c->d_layer_start);
+        DSMD_LAUNCHED(c);
+        DSMD_CUDA(c, cudaMemcpyAsync(c->h_layer_start, c->d_layer_start, sizeof(int) * (layers + 1), cudaMemcpyDeviceToHost, s));
+    }
     if (c->n_total > c->n_owned) {
         k_ghost_row_extent<<<blocks_for(rows * 32, kThreads), kThreads, 0, s>>>(c->grid, c->cell_start + c->grid.ncells,
                                                                                c->ghost_rows, c->ghost_rows + rows);
@@ -1700,9 +1737,14 @@ int dsmd_max_displacement_sq_lagged(dsmd_ctx* c, double* out, void* stream) {
     return DSMD_OK;
 }
 
-int dsmd_compute_forces(dsmd_ctx* c, int phase, int want_energy, void* stream) {
+// The pair kernel over the owned atoms first .. first + count of a FULL or INTERIOR pass without energy (count < 0: all
+// of them, any phase), or over the atoms with a ghost partner (BOUNDARY).
+static int compute_forces_impl(dsmd_ctx* c, int phase, int want_energy, int64_t first, int64_t count, void* stream) {
     if (!c || phase < DSMD_PHASE_FULL || phase > DSMD_PHASE_BOUNDARY) return DSMD_ERR_INVALID;
     if (!c->list_valid) return fail(c, DSMD_ERR_STATE, "build the neighbour list before computing forces");
+    const bool ranged = count >= 0;
+    if (ranged && (phase == DSMD_PHASE_BOUNDARY || want_energy || first < 0 || first + count > c->n_owned))
+        return fail(c, DSMD_ERR_INVALID, "a range of atoms is for FULL or INTERIOR passes without energy, inside the owned atoms");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     PairParams p{};
     for (int a = 0; a < 3; ++a) p.scale[a] = c->grid.scale[a];
@@ -1725,18 +1767,19 @@ int dsmd_compute_forces(dsmd_ctx* c, int phase, int want_energy, void* stream) {
     p.type_charge = c->coulomb ? c->type_charge : nullptr;
     const bool multi = c->ntypes > 1;
     // the boundary pass runs over the atoms the list build found a ghost partner for (none: nothing to launch)
-    const int64_t pair_threads = phase == DSMD_PHASE_BOUNDARY ? c->n_boundary : c->n_owned;
+    const int64_t pair_threads = phase == DSMD_PHASE_BOUNDARY ? c->n_boundary : (ranged ? count : c->n_owned);
+    const int f0 = static_cast<int>(ranged ? first : 0), nt = static_cast<int>(pair_threads);
     const int64_t blocks = blocks_for(pair_threads, kPairThreads);
     if (want_energy) { const int rc = ensure_partials(c, std::max<int64_t>(blocks, 1)); if (rc) return rc; }
     const bool e = want_energy != 0;
     if (pair_threads == 0) {
         // nothing to add to the forces; the energy sums of a boundary pass stay as the interior pass left them
     } else if (c->coulomb) {
-        if (e) { if (multi) launch_pair<true, true, true>(c, p, phase, sw, s); else launch_pair<true, true, false>(c, p, phase, sw, s); }
-        else   { if (multi) launch_pair<true, false, true>(c, p, phase, sw, s); else launch_pair<true, false, false>(c, p, phase, sw, s); }
+        if (e) { if (multi) launch_pair<true, true, true>(c, p, phase, sw, s, f0, nt); else launch_pair<true, true, false>(c, p, phase, sw, s, f0, nt); }
+        else   { if (multi) launch_pair<true, false, true>(c, p, phase, sw, s, f0, nt); else launch_pair<true, false, false>(c, p, phase, sw, s, f0, nt); }
     } else {
-        if (e) { if (multi) launch_pair<false, true, true>(c, p, phase, sw, s); else launch_pair<false, true, false>(c, p, phase, sw, s); }
-        else   { if (multi) launch_pair<false, false, true>(c, p, phase, sw, s); else launch_pair<false, false, false>(c, p, phase, sw, s); }
+        if (e) { if (multi) launch_pair<false, true, true>(c, p, phase, sw, s, f0, nt); else launch_pair<false, true, false>(c, p, phase, sw, s, f0, nt); }
+        else   { if (multi) launch_pair<false, false, true>(c, p, phase, sw, s, f0, nt); else launch_pair<false, false, false>(c, p, phase, sw, s, f0, nt); }
     }
     if (pair_threads > 0) DSMD_LAUNCHED(c);
     if (e && (pair_threads > 0 || phase != DSMD_PHASE_BOUNDARY)) {
@@ -1745,6 +1788,10 @@ int dsmd_compute_forces(dsmd_ctx* c, int phase, int want_energy, void* stream) {
         DSMD_LAUNCHED(c);
     }
     return DSMD_OK;
+}
+
+int dsmd_compute_forces(dsmd_ctx* c, int phase, int want_energy, void* stream) {
+    return compute_forces_impl(c, phase, want_energy, 0, -1, stream);
 }
 
 int dsmd_read_scalars(dsmd_ctx* c, double out[6], void* stream) {
@@ -2206,10 +2253,75 @@ int dsmd_run_nve(dsmd_ctx* c, int64_t n_steps, double dt, double f2a, double hi_
     return DSMD_OK;
 }
 
+// The pipelined form of the host-buffer call, for a step without rebuild and without energy on a single-rank system:
+// the sorted atoms are cut into slabs of z layers of cells; positions go up slab by slab on one copy stream (each slab is
+// packed as it lands), the pair kernel of a slab starts once the slab and its two neighbours are on the device (a slab is
+// at least twice the stencil thick, so a slab's partners lie in itself and the slabs next to it, the first and the last
+// being neighbours through the periodic boundary), and its forces go down on a second copy stream while the later
+// slabs are still coming up or being worked on: the two directions of the host link and the kernel run side by side.
+// Returns DSMD_ERR_STATE when the system does not cut into at least four slabs (the caller falls back).
+static int forces_host_pipelined(dsmd_ctx* c, const double* x, const double* y, const double* z, double* fx, double* fy,
+                                 double* fz, cudaStream_t s) {
+    const int layers = c->grid.nc[2];
+    const int thick = 2 * c->grid.stencil;
+    int pieces = std::min(8, layers / thick);
+    if (pieces < 4 || !c->h_layer_start || c->n_total != c->n_owned) return DSMD_ERR_STATE;
+    if (!c->copy_in) {
+        DSMD_CUDA(c, cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking));
+        DSMD_CUDA(c, cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking));
+        for (int k = 0; k < 16; ++k) {
+            DSMD_CUDA(c, cudaEventCreateWithFlags(&c->piece_up[k], cudaEventDisableTiming));
+            DSMD_CUDA(c, cudaEventCreateWithFlags(&c->piece_done[k], cudaEventDisableTiming));
+        }
+        DSMD_CUDA(c, cudaEventCreateWithFlags(&c->pipe_begin, cudaEventDisableTiming));
+        DSMD_CUDA(c, cudaEventCreateWithFlags(&c->pipe_end, cudaEventDisableTiming));
+    }
+    int64_t begin[17];
+    for (int k = 0; k <= pieces; ++k) begin[k] = c->h_layer_start[static_cast<int64_t>(layers) * k / pieces];
+    begin[0] = 0;
+    begin[pieces] = c->n_owned;
+    // everything queued on the caller's stream so far comes first
+    DSMD_CUDA(c, cudaEventRecord(c->pipe_begin, s));
+    DSMD_CUDA(c, cudaStreamWaitEvent(c->copy_in, c->pipe_begin, 0));
+    DSMD_CUDA(c, cudaStreamWaitEvent(c->copy_out, c->pipe_begin, 0));
+    const double* src[3] = {x, y, z};
+    double* dst[3] = {fx, fy, fz};
+    for (int k = 0; k < pieces; ++k) {
+        const int64_t first = begin[k], count = begin[k + 1] - begin[k];
+        for (int a = 0; a < 3 && count > 0; ++a)
+            DSMD_CUDA(c, cudaMemcpyAsync(c->real[c->cur][a] + first, src[a] + first, sizeof(double) * count,
+                                         cudaMemcpyHostToDevice, c->copy_in));
+        { const int rc = pack_impl(c, first, count, false, 0.0, 0.0, c->copy_in); if (rc) return rc; }
+        DSMD_CUDA(c, cudaEventRecord(c->piece_up[k], c->copy_in));
+    }
+    // slabs 1 .. pieces - 2 need only slabs that come up early; the last and the first (neighbours through the boundary)
+    // close the round
+    for (int turn = 0; turn < pieces; ++turn) {
+        const int k = turn < pieces - 1 ? turn + 1 : 0;
+        const int64_t first = begin[k], count = begin[k + 1] - begin[k];
+        const int needs[3] = {(k + pieces - 1) % pieces, k, (k + 1) % pieces};
+        for (int q = 0; q < 3; ++q) DSMD_CUDA(c, cudaStreamWaitEvent(s, c->piece_up[needs[q]], 0));
+        if (count > 0) { const int rc = compute_forces_impl(c, DSMD_PHASE_FULL, 0, first, count, s); if (rc) return rc; }
+        DSMD_CUDA(c, cudaEventRecord(c->piece_done[k], s));
+        DSMD_CUDA(c, cudaStreamWaitEvent(c->copy_out, c->piece_done[k], 0));
+        for (int a = 0; a < 3 && count > 0; ++a)
+            DSMD_CUDA(c, cudaMemcpyAsync(dst[a] + first, c->real[c->cur][DSMD_FX + a] + first, sizeof(double) * count,
+                                         cudaMemcpyDeviceToHost, c->copy_out));
+    }
+    DSMD_CUDA(c, cudaEventRecord(c->pipe_end, c->copy_out));
+    DSMD_CUDA(c, cudaStreamWaitEvent(s, c->pipe_end, 0));
+    DSMD_CUDA(c, cudaStreamSynchronize(s));
+    return DSMD_OK;
+}
+
 int dsmd_forces_host(dsmd_ctx* c, const double* x, const double* y, const double* z, int rebuild, double* fx,
                      double* fy, double* fz, double* out6, void* stream) {
     if (!c || !x || !y || !z || !fx || !fy || !fz) return DSMD_ERR_INVALID;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (!rebuild && c->list_valid && !out6) {
+        const int rc = forces_host_pipelined(c, x, y, z, fx, fy, fz, s);
+        if (rc != DSMD_ERR_STATE) return rc;   // DSMD_ERR_STATE: too small to cut into slabs, the plain way below
+    }
     { const int rc = dsmd_upload_positions(c, x, y, z, s); if (rc) return rc; }
     if (rebuild || !c->list_valid) {
         const int rc = dsmd_build_neighbor_list(c, s);

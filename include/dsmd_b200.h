@@ -247,6 +247,9 @@ int dsmd_run_nve(dsmd_ctx* ctx, int64_t n_steps, double dt, double force_to_acce
 
 /* One force evaluation with host buffers, as a force-provider plugin is called: uploads positions (context order),
  * packs, evaluates, downloads forces (and the six scalars of dsmd_read_scalars when out6 != NULL). Rebuilds the list first when rebuild != 0.
+ * Without rebuild and without out6, on a single-rank system tall enough to cut into at least four slabs of cell layers,
+ * the call runs as a pipeline over two internal copy streams: slabs of the sorted atoms are uploaded, evaluated and
+ * downloaded side by side (the same forces, bit for bit); pinned host buffers are what makes the copies overlap.
  * Synchronises. */
 int dsmd_forces_host(dsmd_ctx* ctx, const double* x, const double* y, const double* z, int rebuild, double* fx,
                      double* fy, double* fz, double* out6, void* stream);

@@ -432,6 +432,43 @@ def test_host_buffer_force_call(cuda_device):
     ctx.close()
 
 
+def test_host_buffer_force_call_in_slabs_gives_the_same_bits(cuda_device):
+    """A system tall enough to be cut into slabs of cell layers: the host-buffer call without rebuild and without energy
+    uploads, evaluates and downloads slab by slab; its forces are bit for bit those of the device-resident evaluation,
+    also after the atoms have moved (positions handed over in the context's order), and a call with energy (which takes
+    the plain way) agrees with it."""
+    import torch
+    s = syn.fcc_lj(20, seed=3)                     # 32,000 atoms, 24 layers of cells along z: six slabs
+    ctx = make_context(s)
+    ctx.build_neighbor_list()
+    order = ctx.download("global_id")
+    rng = np.random.default_rng(8)
+    moved = s.pos[order] + rng.uniform(-0.04, 0.04, (s.n, 3))        # well inside half the skin
+    host = [torch.from_numpy(np.ascontiguousarray(moved[:, k])).pin_memory() for k in range(3)]
+    out = [torch.zeros(s.n, dtype=torch.float64).pin_memory() for _ in range(3)]
+    args = [t.numpy() for t in host] + [t.numpy() for t in out]
+    ctx.forces_host(*args, rebuild=False)
+    f_slabs = np.stack([t.numpy().copy() for t in out], axis=1)
+    # the same positions are on the device now: the plain evaluation
+    ctx.compute_forces(capi.PHASE_FULL)
+    f_plain = np.stack([ctx.download(k, s.n) for k in ("fx", "fy", "fz")], axis=1)
+    assert np.array_equal(f_slabs, f_plain) and np.abs(f_plain).max() > 1.0
+    sc = np.zeros(6)
+    ctx.forces_host(*args, rebuild=False, scalars=sc)
+    f_energy = np.stack([t.numpy().copy() for t in out], axis=1)
+    assert rms(f_energy - f_slabs) <= 1e-6 * rms(f_slabs) and sc[0] < 0.0
+    # against the oracle on the moved positions
+    f = np.empty((s.n, 3))
+    f[order] = f_slabs
+    pos = np.empty_like(moved)
+    pos[order] = moved
+    x, y, z = (np.ascontiguousarray(pos[:, k]) for k in range(3))
+    c6, c12 = co.lj_tables(s.eps, s.sig)
+    f_o, _ = co.forces(x, y, z, s.n, s.box, co.pairs(x, y, z, s.n, s.box, search=s.cutoff), c6, c12, s.cutoff)
+    assert rms(f - f_o) <= FORCE_RTOL * rms(f_o)
+    ctx.close()
+
+
 def test_error_statuses(cuda_device):
     s = syn.fcc_lj(3, seed=1)          # box 5.04 sigma < 3 cells of 2.8
     ctx = make_context(s)
