@@ -34,7 +34,7 @@ SYMBOLS = [
     "dsmd_edges_result_compact", "dsmd_images_build", "dsmd_images_result", "dsmd_images_fold_forces",
     "dsmd_virial_from_forces", "dsmd_mark_receivers",
     "dsmd_kinetic_energy_noalloc", "dsmd_nccl_unique_id", "dsmd_domain_create",
-    "dsmd_domain_destroy", "dsmd_domain_last_error", "dsmd_domain_rebuild", "dsmd_domain_refresh", "dsmd_domain_run",
+    "dsmd_domain_destroy", "dsmd_domain_last_error", "dsmd_domain_rebuild", "dsmd_domain_refresh", "dsmd_domain_forces_host", "dsmd_domain_run",
     "dsmd_domain_stats", "dsmd_domain_profile", "dsmd_domain_set_wait_limit", "dsmd_domain_abort",
     "dsmd_domain_reverse_forces", "dsmd_domain_exchange_field", "dsmd_domain_peers", "dsmd_domain_reduce",
 ]
@@ -451,6 +451,14 @@ class Domain:
 
     def refresh(self, stream=None):
         self._check(self.lib.dsmd_domain_refresh(self.h, _stream_handle(stream)))
+
+    def forces_host(self, x, y, z, fx, fy, fz, buffer_atoms, rebuild=False, stream=None):
+        """Host-buffer force call on several ranks: raw host addresses (ints) or numpy arrays of this rank's owned atoms,
+        each buffer with room for buffer_atoms atoms."""
+        def addr(a):
+            return c_void_p(a) if isinstance(a, int) else _p(a)
+        self._check(self.lib.dsmd_domain_forces_host(self.h, addr(x), addr(y), addr(z), c_int(int(rebuild)), addr(fx), addr(fy),
+                                                     addr(fz), c_int64(int(buffer_atoms)), _stream_handle(stream)))
 
     def run(self, n_steps, dt, force_to_accel=1.0, hi_frac=0.5, stream=None):
         self._check(self.lib.dsmd_domain_run(self.h, c_int64(n_steps), c_double(dt), c_double(force_to_accel),

@@ -854,6 +854,51 @@ int dsmd_domain_refresh(dsmd_domain* d, void* stream) {
     return DSMD_OK;
 }
 
+int dsmd_domain_forces_host(dsmd_domain* d, const double* x, const double* y, const double* z, int with_rebuild, double* fx,
+                            double* fy, double* fz, int64_t buffer_atoms, void* stream) {
+    if (!d || !x || !y || !z || !fx || !fy || !fz || buffer_atoms < 0) return DSMD_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    {   // the owned atoms, in the context's order
+        int64_t n_owned = 0, n_total = 0;
+        dsmd_counts(d->ctx, &n_owned, &n_total);
+        if (n_owned > buffer_atoms) return dfail(d, DSMD_ERR_CAPACITY, "the host buffers are shorter than the owned atoms");
+        const double* src[3] = {x, y, z};
+        const int ids[3] = {DSMD_X, DSMD_Y, DSMD_Z};
+        for (int a = 0; a < 3; ++a) {
+            void* dst = nullptr;
+            DOM_CTX(d, dsmd_device_pointer(d->ctx, ids[a], &dst));
+            DOM_CUDA(d, cudaMemcpyAsync(dst, src[a], sizeof(double) * n_owned, cudaMemcpyHostToDevice, s));
+        }
+    }
+    if (with_rebuild) {
+        { const int rc = rebuild(d, s); if (rc) return rc; }
+        DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_FULL, 0, s));
+    } else {
+        int64_t n_owned = 0, n_total = 0;
+        dsmd_counts(d->ctx, &n_owned, &n_total);
+        DOM_CTX(d, dsmd_pack_positions(d->ctx, 0, n_owned, s));
+        if (d->world > 1) {
+            // the ghost refresh on the side stream beside the interior pass, then the boundary pass
+            { const int rc = refresh(d, s); if (rc) return rc; }
+            DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_INTERIOR, 0, s));
+            DOM_CUDA(d, cudaStreamWaitEvent(s, d->ev_side, 0));
+            DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_BOUNDARY, 0, s));
+        } else {
+            DOM_CTX(d, dsmd_compute_forces(d->ctx, DSMD_PHASE_FULL, 0, s));
+        }
+    }
+    int64_t n_owned = 0, n_total = 0;
+    dsmd_counts(d->ctx, &n_owned, &n_total);
+    if (n_owned > buffer_atoms)   // a rebuild brought more atoms in than the buffers hold
+        return dfail(d, DSMD_ERR_CAPACITY, "the host buffers are shorter than the owned atoms after the rebuild");
+    const MutableForces f = forces_of(d->ctx);
+    const double* src[3] = {f.fx, f.fy, f.fz};
+    double* dst[3] = {fx, fy, fz};
+    for (int a = 0; a < 3; ++a)
+        DOM_CUDA(d, cudaMemcpyAsync(dst[a], src[a], sizeof(double) * n_owned, cudaMemcpyDeviceToHost, s));
+    return wait_stream(d, s, "host-buffer force call");
+}
+
 int dsmd_domain_reverse_forces(dsmd_domain* d, void* stream) {
     if (!d) return DSMD_ERR_INVALID;
     if (d->world == 1 || d->plan.n_peers == 0) return DSMD_OK;

@@ -116,27 +116,26 @@ def run(args):
     pair_flops = 8.0 * p_list_local + 19.0 * p_cut_local
 
     # end to end: host positions in, forces out, ghost refresh in between (every rank its own atoms)
-    host = [torch.from_numpy(ctx.download(k)).pin_memory() for k in ("x", "y", "z")]
-    hf = [torch.empty(n_owned, dtype=torch.float64).pin_memory() for _ in range(3)]
+    # The host keeps handing over the same positions. They are taken right after a rebuild, so that every atom lies in
+    # its owner's brick: the rebuilds inside the loop then move no atom and the owned set and its order stay as they are
+    # (a rebuild after a drift would hand atoms to other ranks, and positions indexed by the old order would be wrong).
+    dom.rebuild(stream)
+    n_owned, n_total = ctx.counts()
+    room = n_owned + 4096
+    host = [torch.zeros(room, dtype=torch.float64).pin_memory() for _ in range(3)]
+    for k, name in enumerate(("x", "y", "z")):
+        host[k][:n_owned] = torch.from_numpy(ctx.download(name, n_owned))
+    hf = [torch.empty(room, dtype=torch.float64).pin_memory() for _ in range(3)]
 
     cadence = max(1, round(args.steps / max(rebuilds, 1)))
     calls = {"k": 0}
 
     def e2e_call():
-        # what the single-GPU end-to-end call does, per rank: positions in, rebuild (migration, ghost plan, list) at the
-        # MD run's cadence or else pack + ghost refresh, forces, forces out
-        ctx.upload_positions_ptr(host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), stream)
-        if calls["k"] % cadence == 0:
-            dom.rebuild(stream)
-        else:
-            ctx.pack_positions(0, n_owned, stream)
-            dom.refresh(stream)
+        # what the single-GPU end-to-end call does, per rank, in one native call: positions in, rebuild (migration, ghost
+        # plan, list) at the MD run's cadence or else pack + ghost refresh beside the interior pass, forces out
+        dom.forces_host(host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), hf[0].data_ptr(), hf[1].data_ptr(),
+                        hf[2].data_ptr(), room, rebuild=(calls["k"] % cadence == 0), stream=stream)
         calls["k"] += 1
-        ctx.compute_forces(capi.PHASE_FULL, False, stream)
-        for k in range(3):
-            view = capi._tensor_from_ptr(ctx.device_pointer(("fx", "fy", "fz")[k]), (n_owned,), torch.float64, device)
-            hf[k].copy_(view, non_blocking=True)
-        torch.cuda.synchronize()
 
     for _ in range(3):
         e2e_call()
@@ -189,10 +188,11 @@ def run(args):
             },
             "cpu_baseline": None,
             "e2e": {"value": s.n * e2e_steps / float(e2e_t.item()), "unit": "atom-steps/s",
-                    "h2d_bytes_per_step": 24 * n_total, "d2h_bytes_per_step": 24 * n_owned, "steps": e2e_steps,
+                    "h2d_bytes_per_step": 24 * s.n, "d2h_bytes_per_step": 24 * s.n, "steps": e2e_steps,
                     "rebuild_every": cadence,
-                    "call": "per rank: pinned host positions in, rebuild (migration, ghost plan, list) at the MD run's cadence "
-                            "or pack + ghost refresh, forces, forces out"},
+                    "call": "dsmd_domain_forces_host on every rank: pinned host positions of the owned atoms in, rebuild "
+                            "(migration, ghost plan, list) at the MD run's cadence or pack + ghost refresh beside the interior "
+                            "pass, forces out; bytes are the sum over the ranks"},
             "gpu_launches": int(launches),
         }
         print(json.dumps(line))

@@ -329,6 +329,14 @@ int dsmd_domain_abort(dsmd_domain* dom);
  * ncclSend / ncclRecv with the neighbour directions, unpack, on the domain's side stream; `stream` then waits for it. */
 int dsmd_domain_refresh(dsmd_domain* dom, void* stream);
 
+/* dsmd_forces_host on several ranks: this rank's owned atoms' positions in (host buffers, the context's order), then
+ * either the rebuild step (with_rebuild != 0: migration, ghosts, list; the owned set and its order may change, ask
+ * dsmd_counts / DSMD_GLOBAL_ID afterwards) and a full pass, or pack, ghost refresh beside the interior pass and the
+ * boundary pass; the owned atoms' forces out. buffer_atoms = how many atoms each host buffer holds (a rebuild may bring
+ * atoms in: DSMD_ERR_CAPACITY when they do not fit). Collective; waits with the domain's deadline. */
+int dsmd_domain_forces_host(dsmd_domain* dom, const double* x, const double* y, const double* z, int with_rebuild,
+                            double* fx, double* fy, double* fz, int64_t buffer_atoms, void* stream);
+
 /* n_steps MD steps (MDSimulation::single_step, src/md_simulation.cpp:899-941, restricted to this path): first
  * velocity-Verlet half + pack, rebuild vote (8-byte MAX all-reduce on a communicator and stream of its own, read one step
  * late and extrapolated), then either a rebuild + full force pass, or the ghost refresh on the side stream overlapped

@@ -118,10 +118,23 @@ def worker_native(rank, world, port, steps, dt, out_path):
     torch.cuda.synchronize()
     n_owned, n_total_now = ctx.counts()
     st = dom.stats()
+    # the host-buffer call: the owned atoms' positions in, forces out; equal to the device-resident evaluation
+    ctx.compute_forces(capi.PHASE_FULL)
+    f_device = np.stack([ctx.download(k, n_owned) for k in ("fx", "fy", "fz")], axis=1)
+    host_in = [torch.from_numpy(ctx.download(k, n_owned)).pin_memory() for k in "xyz"]
+    host_out = [torch.zeros(n_owned, dtype=torch.float64).pin_memory() for _ in range(3)]
+    dom.forces_host(*[t.data_ptr() for t in host_in], *[t.data_ptr() for t in host_out], n_owned, rebuild=False)
+    f_host = np.stack([t.numpy().copy() for t in host_out], axis=1)
+    host_call_ok = bool(np.abs(f_host - f_device).max() <= 1e-5 * np.abs(f_device).max())   # two passes against one: fp32 partial sums differ in the last bits
+    too_short = False
+    try:
+        dom.forces_host(*[t.data_ptr() for t in host_in], *[t.data_ptr() for t in host_out], n_owned - 1, rebuild=False)
+    except capi.DsmdError as err:
+        too_short = err.code == capi.ERR_CAPACITY
     result = dict(gid_first=gid_first, f_first=f_first, first=dict(pe=float(first[0]), virial=float(first[1])),
                   ghosts=n_total - n_owned, gid=ctx.download("global_id", n_owned),
                   pos=np.stack([ctx.download(k, n_owned) for k in "xyz"], axis=1), rebuilds=st["rebuilds"],
-                  worst=st["worst_disp_sq"], peers=dom.peers())
+                  worst=st["worst_disp_sq"], peers=dom.peers(), host_call_ok=host_call_ok, too_short=too_short)
     # -- the exchanges of the MLIP path along the same ghost plan ---------------------------------------------------------
     device = torch.device("cuda", rank)
     gid_all = torch.tensor(ctx.download("global_id", n_total_now), device=device, dtype=torch.float64)
@@ -310,6 +323,7 @@ def test_two_gpus_equal_the_undivided_system(tmp_path, which):
         # two bricks are each other's only neighbour rank: one message each way per exchange
         assert all(p["peers"]["ranks"] == [1 - r] and p["peers"]["messages_per_exchange"] == 2 for r, p in enumerate(parts))
         assert all(p["forward_ok_4"] and p["forward_ok_8"] for p in parts)
+        assert all(p["host_call_ok"] and p["too_short"] for p in parts)
         copies = np.zeros(s.n)
         for p in parts:
             np.add.at(copies, p["ghost_gid"], 1.0)             # how often each atom is a ghost somewhere
